@@ -1,0 +1,271 @@
+"""The cache manager: block tables per request and group, and per-request state slots.
+
+It holds metadata only (the bytes live in ``cache.pools``).  Layers whose mixers
+have equal needs form a *group*; each group has pages of its own (its own page
+ids) and each request has one block table per group.  A group with a window
+gives a page back as soon as every position in it is older than the window
+(the table keeps ``-1`` there).  Beside the pages, each live request holds one
+*state slot*, an index into per-layer tensors of fixed-size state.
+
+Calls mirror src/dli/kv/block_manager.py (allocate :238, append_slots :286,
+mark_computed :322, free :360, slot_mapping :204, check_invariants :384): a call
+that cannot get its pages raises ``OutOfPages`` before it changes anything.
+Prefix reuse (hash-chained full pages) works when every group keeps all keys;
+with a windowed group, or with mixers that hold state, a prefix's pages alone
+do not restore a request, so reuse is off.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, Sequence
+
+from .page_pool import ROOT, OutOfPages, PagePool, chain_hashes, page_hash
+
+
+class UnknownRequest(KeyError):
+    pass
+
+
+@dataclass(frozen=True)
+class GroupSpec:
+    """One cache group: how many pages it has and whether it keeps a window only."""
+
+    num_pages: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class Allocation:
+    num_cached_tokens: int  # leading tokens whose keys and values are already in pages
+    state_slot: int
+
+
+@dataclass
+class CacheStats:
+    prompt_tokens_queried: int = 0
+    prompt_tokens_hit: int = 0
+
+    @property
+    def hit_rate(self) -> float:
+        return self.prompt_tokens_hit / self.prompt_tokens_queried if self.prompt_tokens_queried else 0.0
+
+
+@dataclass
+class _Request:
+    tables: list[list[int]]  # per group: page of block j, or -1 once the window passed it
+    num_tokens: int
+    num_computed: int
+    namespace: bytes
+    slot: int
+    hashes: list[bytes] = field(default_factory=list)  # chain over the leading full pages known so far
+    tail: list[int] = field(default_factory=list)  # tokens after the hashed ones
+    registered: int = 0  # leading pages already indexed or taken from the index
+
+
+class CacheManager:
+    def __init__(
+        self,
+        groups: Sequence[GroupSpec],
+        page_size: int,
+        max_requests: int,
+        *,
+        enable_prefix_caching: bool = True,
+        has_state: bool = False,
+        watermark: float = 0.01,
+    ) -> None:
+        if not 0.0 <= watermark < 1.0:
+            raise ValueError("watermark must be in [0, 1)")
+        if max_requests < 1:
+            raise ValueError("max_requests must be positive")
+        self.page_size = page_size
+        self.groups = list(groups)
+        self.prefix_caching = bool(enable_prefix_caching and groups and not has_state and all(g.window is None for g in groups))
+        self.pools = [PagePool(g.num_pages, page_size, self.prefix_caching) for g in groups]
+        self._reserve = [int(watermark * g.num_pages) for g in groups]
+        self.max_requests = max_requests
+        self._free_slots = list(range(max_requests - 1, -1, -1))
+        self._requests: dict[Hashable, _Request] = {}
+        self.stats = CacheStats()
+
+    # ------------------------------------------------------------ queries
+
+    def has_request(self, rid: Hashable) -> bool:
+        return rid in self._requests
+
+    def _get(self, rid: Hashable) -> _Request:
+        try:
+            return self._requests[rid]
+        except KeyError:
+            raise UnknownRequest(f"unknown request {rid!r}") from None
+
+    def num_tokens(self, rid: Hashable) -> int:
+        return self._get(rid).num_tokens
+
+    def num_computed_tokens(self, rid: Hashable) -> int:
+        return self._get(rid).num_computed
+
+    def state_slot(self, rid: Hashable) -> int:
+        return self._get(rid).slot
+
+    def block_table(self, rid: Hashable, group: int = 0) -> list[int]:
+        return list(self._get(rid).tables[group])
+
+    def slot_mapping(self, rid: Hashable, group: int, start: int, end: int) -> list[int]:
+        """Flat slot (page * page_size + offset) of positions [start, end)
+        (src/dli/kv/block_manager.py:204-210)."""
+        req = self._get(rid)
+        if not 0 <= start <= end <= req.num_tokens:
+            raise ValueError(f"positions [{start}, {end}) outside reserved [0, {req.num_tokens})")
+        ps, table = self.page_size, req.tables[group]
+        out = []
+        for p in range(start, end):
+            page = table[p // ps]
+            if page < 0:
+                raise ValueError(f"position {p} lies in a page the window has given back")
+            out.append(page * ps + p % ps)
+        return out
+
+    def min_available_pages(self) -> int:
+        return min((p.available for p in self.pools), default=0)
+
+    def pages_for(self, num_tokens: int) -> int:
+        return -(-num_tokens // self.page_size)
+
+    def fits_at_all(self, num_tokens: int) -> bool:
+        """Whether a request of this many tokens could ever hold its pages, running alone."""
+        return all(self.pages_for(num_tokens) <= g.num_pages for g in self.groups)
+
+    # ------------------------------------------------------------ life of a request
+
+    def _hits(self, token_ids: Sequence[int], namespace: bytes) -> tuple[list[list[int]], list[bytes]]:
+        """Per group the pages of the longest indexed prefix, never covering the last token:
+        a step must run at least one token to give logits (src/dli/kv/block_manager.py:451-465)."""
+        if not self.prefix_caching:
+            return [[] for _ in self.pools], []
+        eligible = (len(token_ids) - 1) // self.page_size * self.page_size
+        hashes = chain_hashes(namespace, token_ids[:eligible], self.page_size)
+        per_group = [pool.lookup(hashes) for pool in self.pools]
+        n = min(len(h) for h in per_group)
+        return [h[:n] for h in per_group], hashes
+
+    def _admissible(self, num_tokens: int, hits: list[list[int]], respect_watermark: bool) -> bool:
+        if not self._free_slots:
+            return False
+        need = self.pages_for(num_tokens)
+        for pool, h, reserve in zip(self.pools, hits, self._reserve):
+            revived = sum(1 for page in h if pool.ref[page] == 0)  # idle hits stop being evictable
+            if pool.available - revived - (need - len(h)) < (reserve if respect_watermark else 0):
+                return False
+        return True
+
+    def can_allocate(self, token_ids: Sequence[int], namespace: bytes = b"") -> bool:
+        hits, _ = self._hits(token_ids, namespace)
+        return self._admissible(len(token_ids), hits, True)
+
+    def allocate(self, rid: Hashable, token_ids: Sequence[int], *, namespace: bytes = b"", respect_watermark: bool = True) -> Allocation:
+        """Admit a request: pages for all its tokens in every group (indexed prefix pages are
+        shared, the rest are taken), and a state slot."""
+        if rid in self._requests:
+            raise ValueError(f"request {rid!r} already holds pages")
+        if not token_ids:
+            raise ValueError("cannot allocate an empty prompt")
+        hits, hashes = self._hits(token_ids, namespace)
+        if not self._admissible(len(token_ids), hits, respect_watermark):
+            raise OutOfPages(f"{self.pages_for(len(token_ids))} pages needed, {self.min_available_pages()} available, "
+                             f"{len(self._free_slots)} state slots free")
+        tables = []
+        for pool, h in zip(self.pools, hits):
+            for page in h:  # revive hits before taking pages, so eviction cannot pick them
+                pool.share(page)
+            tables.append(list(h) + [pool.take() for _ in range(self.pages_for(len(token_ids)) - len(h))])
+        n_hit = len(hits[0]) if hits else 0
+        cached = n_hit * self.page_size
+        self.stats.prompt_tokens_queried += len(token_ids)
+        self.stats.prompt_tokens_hit += cached
+        req = _Request(tables, len(token_ids), cached, namespace, self._free_slots.pop())
+        if self.prefix_caching:
+            req.hashes = hashes
+            req.tail = list(token_ids[len(hashes) * self.page_size :])
+            req.registered = n_hit
+        self._requests[rid] = req
+        return Allocation(cached, req.slot)
+
+    def append_slots(self, rid: Hashable, token_ids: Sequence[int]) -> None:
+        """Room for tokens appended to the request (a sampled token); ignores the watermark."""
+        req = self._get(rid)
+        ps = self.page_size
+        need = sum(1 for p in range(req.num_tokens, req.num_tokens + len(token_ids)) if p % ps == 0)
+        if any(need > pool.available for pool in self.pools):
+            raise OutOfPages(f"append needs {need} pages")
+        for pool, table in zip(self.pools, req.tables):
+            table.extend(pool.take() for _ in range(need))
+        req.num_tokens += len(token_ids)
+        if self.prefix_caching:
+            req.tail.extend(token_ids)
+
+    def mark_computed(self, rid: Hashable, num_computed: int) -> None:
+        """Keys and values of the first ``num_computed`` tokens are written: full pages become
+        shareable, and windowed groups give back the pages no later token can read."""
+        req = self._get(rid)
+        if not req.num_computed <= num_computed <= req.num_tokens:
+            raise ValueError(f"computed must be in [{req.num_computed}, {req.num_tokens}], got {num_computed}")
+        req.num_computed = num_computed
+        ps = self.page_size
+        if self.prefix_caching:
+            full = num_computed // ps
+            while req.registered < full:
+                i = req.registered
+                while len(req.hashes) <= i:
+                    req.hashes.append(page_hash(req.namespace, req.hashes[-1] if req.hashes else ROOT, req.tail[:ps]))
+                    del req.tail[:ps]
+                for pool, table in zip(self.pools, req.tables):
+                    pool.register(table[i], req.hashes[i], req.hashes[i - 1] if i else None, table[i - 1] if i else None)
+                req.registered += 1
+        for group, pool, table in zip(self.groups, self.pools, req.tables):
+            if group.window is None:
+                continue
+            # the next query sits at position >= num_computed and reads keys > position - window
+            dead_pages = max(0, (num_computed - group.window + 1) // ps)
+            for j in range(min(dead_pages, len(table))):
+                if table[j] >= 0:
+                    pool.release(table[j])
+                    table[j] = -1
+
+    def free(self, rid: Hashable) -> None:
+        """Give back everything a finished, aborted or preempted request holds."""
+        req = self._requests.pop(rid, None)
+        if req is None:
+            raise UnknownRequest(f"unknown request {rid!r}")
+        for pool, table in zip(self.pools, req.tables):
+            for page in reversed(table):  # deepest first: children become evictable before parents
+                if page >= 0:
+                    pool.release(page)
+        self._free_slots.append(req.slot)
+
+    def reset_prefix_cache(self) -> int:
+        return sum(pool.drop_index() for pool in self.pools)
+
+    # ------------------------------------------------------------ verification
+
+    def check_invariants(self) -> None:
+        """No page lost, held twice without a count, or freed twice; slots likewise."""
+        slots = [r.slot for r in self._requests.values()]
+        assert len(set(slots)) == len(slots), "a state slot is held twice"
+        assert not set(slots) & set(self._free_slots), "a state slot is both held and free"
+        assert len(slots) + len(self._free_slots) == self.max_requests, "a state slot is lost"
+        assert len(set(self._free_slots)) == len(self._free_slots), "a state slot is free twice"
+        for g, pool in enumerate(self.pools):
+            expected: dict[int, int] = {}
+            for req in self._requests.values():
+                table = req.tables[g]
+                assert len(table) == self.pages_for(req.num_tokens), "table size != ceil(tokens / page_size)"
+                assert 0 <= req.num_computed <= req.num_tokens
+                for j, page in enumerate(table):
+                    if page >= 0:
+                        expected[page] = expected.get(page, 0) + 1
+                    else:
+                        w = self.groups[g].window
+                        assert w is not None and (j + 1) * self.page_size - 1 <= req.num_computed - w, \
+                            "a page still inside the window was given back"
+            pool.check(expected)

@@ -1,0 +1,101 @@
+"""Device memory of the cache: key and value pools per group, and state-slot tensors.
+
+Pools of one group: ``k, v [layers_in_group, pages, kv_heads, page_size, head_dim]`` —
+head-major inside a page, so the keys of one (page, kv head) are one contiguous tile.
+A run step's ``LayerCache`` is the view its mixer works on.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .needs import PagedKVNeed, StateNeed
+
+
+@dataclass
+class LayerCache:
+    """What one run step's mixer sees."""
+
+    group: int | None = None  # cache group of the pools (index into the batch's group views)
+    k: torch.Tensor | None = None  # [pages, kv_heads, page_size, head_dim]
+    v: torch.Tensor | None = None
+    page_size: int = 0
+    writes: bool = True  # False: reads another run step's cache and writes nothing
+    state: torch.Tensor | None = None  # [max_requests, *shape] for a mixer with fixed-size state
+
+
+def plan_groups(needs: list, run_order) -> tuple[list[PagedKVNeed], list[int | None]]:
+    """Group run steps by equal paged needs.  Returns the groups' needs and, for each run step,
+    its group (None for steps without pages); a step that reads another step's cache gets that
+    step's group."""
+    groups: list[PagedKVNeed] = []
+    of_step: list[int | None] = []
+    for i, need in enumerate(needs):
+        src = run_order[i].cache_of
+        if src is not None:
+            of_step.append(of_step[src])
+        elif isinstance(need, PagedKVNeed):
+            if need not in groups:
+                groups.append(need)
+            of_step.append(groups.index(need))
+        else:
+            of_step.append(None)
+    return groups, of_step
+
+
+class CachePools:
+    def __init__(self, needs: list, run_order, pages_per_group: list[int], page_size: int, max_requests: int,
+                 dtype: torch.dtype, device: torch.device | str) -> None:
+        self.page_size = page_size
+        self.group_needs, self.group_of_step = plan_groups(needs, run_order)
+        if len(pages_per_group) != len(self.group_needs):
+            raise ValueError(f"{len(self.group_needs)} cache groups, {len(pages_per_group)} page counts")
+        owners: list[list[int]] = [[] for _ in self.group_needs]
+        for i, need in enumerate(needs):
+            if isinstance(need, PagedKVNeed) and run_order[i].cache_of is None:
+                owners[self.group_of_step[i]].append(i)
+        self.k: list[torch.Tensor] = []
+        self.v: list[torch.Tensor] = []
+        for need, pages, own in zip(self.group_needs, pages_per_group, owners):
+            shape = (len(own), pages, need.num_kv_heads, page_size, need.head_dim)
+            self.k.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+        self.layer_caches: list[LayerCache] = []
+        for i, need in enumerate(needs):
+            src = run_order[i].cache_of
+            if src is not None:
+                base = self.layer_caches[src]
+                self.layer_caches.append(LayerCache(base.group, base.k, base.v, page_size, writes=False, state=base.state))
+            elif isinstance(need, PagedKVNeed):
+                g = self.group_of_step[i]
+                j = owners[g].index(i)
+                self.layer_caches.append(LayerCache(g, self.k[g][j], self.v[g][j], page_size))
+            elif isinstance(need, StateNeed):
+                state = torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=device)
+                self.layer_caches.append(LayerCache(state=state))
+            else:
+                self.layer_caches.append(LayerCache())
+
+    @property
+    def has_state(self) -> bool:
+        return any(c.state is not None for c in self.layer_caches)
+
+    def reset_state(self, slot: int) -> None:
+        """Zero a slot's state in every layer: a request starts (or starts over) from nothing."""
+        seen = set()
+        for c in self.layer_caches:
+            if c.state is not None and c.state.data_ptr() not in seen:
+                seen.add(c.state.data_ptr())
+                c.state[slot].zero_()
+
+    @staticmethod
+    def bytes_per_page(needs: list, run_order, page_size: int, dtype: torch.dtype) -> list[int]:
+        """Bytes one page costs in each group (keys and values, all the group's layers)."""
+        group_needs, group_of_step = plan_groups(needs, run_order)
+        out = [0] * len(group_needs)
+        for i, need in enumerate(needs):
+            if isinstance(need, PagedKVNeed) and run_order[i].cache_of is None:
+                out[group_of_step[i]] += 2 * need.num_kv_heads * page_size * need.head_dim * dtype.itemsize
+        return out

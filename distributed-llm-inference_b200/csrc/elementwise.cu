@@ -1,0 +1,181 @@
+// Embedding gather, fused residual-add + RMSNorm, rotary embedding fused with
+// the write of keys and values into cache pages, and SiLU(gate) * up.
+// Each kernel has a float32 and a bfloat16 instantiation; all arithmetic is float32.
+#include "common.cuh"
+
+using namespace dli;
+
+// ---------------------------------------------------------------- embedding
+// h[t, :] = float(table[ids[t], :]); h is the float32 residual stream.
+template <typename T>
+__global__ void embedding_kernel(float* __restrict__ h, const T* __restrict__ table, const int* __restrict__ ids, int H) {
+  const int t = blockIdx.x;
+  const T* src = table + (size_t)ids[t] * H;
+  float* dst = h + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]);
+}
+
+DLI_EXPORT int dli_embedding(float* h, const void* table, const int* ids, int n, int H, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (dtype == DLI_F32)
+    embedding_kernel<float><<<n, threads, 0, stream>>>(h, (const float*)table, ids, H);
+  else
+    embedding_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(h, (const __nv_bfloat16*)table, ids, H);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- add + rmsnorm
+// For output row r (source row s = rows ? rows[r] : r):
+//   v = h[s] + delta[s]            (float32; written back to h[s] when rows == nullptr)
+//   y[r] = v * rsqrt(mean(v^2) + eps) * w
+// One block per row; the row is kept in registers between the two passes when it fits.
+template <typename T, int THREADS, int PER_THREAD>
+__global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ h, const T* __restrict__ delta,
+                                   const float* __restrict__ w, const int* __restrict__ rows, int H, float eps) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int s = rows ? rows[r] : r;
+  float* hrow = h + (size_t)s * H;
+  const T* drow = delta ? delta + (size_t)s * H : nullptr;
+  float v[PER_THREAD];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < PER_THREAD; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    float x = 0.f;
+    if (i < H) {
+      x = hrow[i];
+      if (drow) x += to_float(drow[i]);
+      if (!rows && drow) hrow[i] = x;
+    }
+    v[k] = x;
+    ss += x * x;
+  }
+  // columns beyond THREADS * PER_THREAD (very wide models): streamed, re-read in pass two
+  for (int i = threadIdx.x + PER_THREAD * THREADS; i < H; i += THREADS) {
+    float x = hrow[i];
+    if (drow) x += to_float(drow[i]);
+    if (!rows && drow) hrow[i] = x;
+    ss += x * x;
+  }
+  const float total = block_sum(ss, red);
+  const float inv = rsqrtf(total / (float)H + eps);
+  T* yrow = y + (size_t)r * H;
+#pragma unroll
+  for (int k = 0; k < PER_THREAD; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    if (i < H) yrow[i] = from_float<T>(v[k] * inv * w[i]);
+  }
+  for (int i = threadIdx.x + PER_THREAD * THREADS; i < H; i += THREADS) {
+    float x = hrow[i];
+    if (rows && drow) x += to_float(drow[i]);
+    yrow[i] = from_float<T>(x * inv * w[i]);
+  }
+}
+
+DLI_EXPORT int dli_add_rmsnorm(void* y, float* h, const void* delta, const float* w, const int* rows, int n_rows, int H,
+                               float eps, int dtype, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  constexpr int THREADS = 256, PER = 16;  // 4096 columns in registers, more are streamed
+  if (dtype == DLI_F32)
+    add_rmsnorm_kernel<float, THREADS, PER><<<n_rows, THREADS, 0, stream>>>((float*)y, h, (const float*)delta, w, rows, H, eps);
+  else
+    add_rmsnorm_kernel<__nv_bfloat16, THREADS, PER>
+        <<<n_rows, THREADS, 0, stream>>>((__nv_bfloat16*)y, h, (const __nv_bfloat16*)delta, w, rows, H, eps);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- rotary + cache write
+// qkv: [n, (nh + 2 nkv) * d], rows = tokens.  Query heads are rotated in place; key heads are
+// rotated and written to the key pool, value heads are copied to the value pool, at the token's
+// slot (page * page_size + offset; a negative slot writes nothing).  Pool layout of one layer:
+// [page][kv_head][page_size][d].  Rotation pairs element i with i + rot/2 for i < rot/2
+// (rotate-half); elements >= rot pass through.  Angle = float(position) * inv_freq[i], float32.
+template <typename T>
+__global__ void rotary_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                    const int* __restrict__ slots, T* __restrict__ k_pool, T* __restrict__ v_pool, int nh,
+                                    int nkv, int d, int rot, int page_size, int write_kv) {
+  const int t = blockIdx.x;
+  const int half = rot >> 1;
+  const int row = (nh + 2 * nkv) * d;
+  T* base = qkv + (size_t)t * row;
+  const float pos = (float)positions[t];
+  const int slot = slots ? slots[t] : -1;
+  const bool store = write_kv && slot >= 0;
+  const int page = store ? slot / page_size : 0, off = store ? slot % page_size : 0;
+
+  // rotated halves of q and k heads: one thread per (head, i < half)
+  const int rot_items = (nh + nkv) * half;
+  for (int idx = threadIdx.x; idx < rot_items; idx += blockDim.x) {
+    const int head = idx / half, i = idx - head * half;
+    float sn, cs;
+    sincosf(pos * inv_freq[i], &sn, &cs);
+    T* x = base + (size_t)head * d;
+    const float a = to_float(x[i]), b = to_float(x[i + half]);
+    const T ra = from_float<T>(a * cs - b * sn);
+    const T rb = from_float<T>(b * cs + a * sn);
+    if (head < nh) {
+      x[i] = ra;
+      x[i + half] = rb;
+    } else if (store) {
+      T* dst = k_pool + (((size_t)page * nkv + (head - nh)) * page_size + off) * d;
+      dst[i] = ra;
+      dst[i + half] = rb;
+    }
+  }
+  if (!store) return;
+  // pass-through part of keys (elements >= rot) and all of the values
+  const int tail = d - rot;
+  for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
+    const int head = idx / tail, i = rot + idx - head * tail;
+    k_pool[(((size_t)page * nkv + head) * page_size + off) * d + i] = base[(size_t)(nh + head) * d + i];
+  }
+  for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
+    const int head = idx / d, i = idx - head * d;
+    v_pool[(((size_t)page * nkv + head) * page_size + off) * d + i] = base[(size_t)(nh + nkv + head) * d + i];
+  }
+}
+
+DLI_EXPORT int dli_rotary_store(void* qkv, const int* positions, const float* inv_freq, const int* slots, void* k_pool,
+                                void* v_pool, int n, int nh, int nkv, int d, int rot, int page_size, int write_kv,
+                                int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (rot < 0 || rot > d || (rot & 1)) return DLI_ERR_UNSUPPORTED;
+  if (rot > 0 && inv_freq == nullptr) return DLI_ERR_UNSUPPORTED;
+  const int threads = 256;
+  if (dtype == DLI_F32)
+    rotary_store_kernel<float><<<n, threads, 0, stream>>>((float*)qkv, positions, inv_freq, slots, (float*)k_pool,
+                                                          (float*)v_pool, nh, nkv, d, rot, page_size, write_kv);
+  else
+    rotary_store_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, inv_freq, slots,
+                                                                  (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh, nkv, d,
+                                                                  rot, page_size, write_kv);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- silu(gate) * up
+// gu: [n, 2 I] with gate in columns [0, I) and up in [I, 2 I); out: [n, I].
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int n, int I) {
+  const size_t total = (size_t)n * I;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = to_float(gu[t * 2 * I + i]);
+    const float u = to_float(gu[t * 2 * I + I + i]);
+    out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const size_t total = (size_t)n * I;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == DLI_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gu, n, I);
+  else
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,106 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner.step`` runs only the tokens it is given, as one batch, against the
+cache that earlier steps left, and returns the logits at the wanted places.
+Portions of prompts and single decoded tokens, cut anywhere, take the same path
+(the reference has three: src/dli/engine/runner.py:57-61).
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Any, Sequence
+
+import torch
+
+from ..cache import CacheManager, CachePools, GroupSpec
+from ..cache.needs import PagedKVNeed, StateNeed
+from ..config.registry import load_config, resolve_architecture
+from ..parts import DecoderModel
+from ..weights import load_tensors, random_tensors
+from .batch import StepEntry, build_batch
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def resolve_dtype(dtype: str | torch.dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        return dtype
+    if dtype == "auto":
+        return torch.bfloat16
+    try:
+        return DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype {dtype!r} is not supported (bfloat16, float32)") from None
+
+
+def _require_cuda(device: torch.device) -> None:
+    if device.type != "cuda":
+        raise RuntimeError(f"device {device} is not a CUDA device: the engine's kernels run on the GPU only")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available: the engine has no CPU path")
+
+
+def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16", device: str | torch.device = "cuda:0") -> DecoderModel:
+    """Build the model config.json names and load its tensors strictly by name
+    (src/dli/model/loader.py:43-93)."""
+    device = torch.device(device)
+    _require_cuda(device)
+    arch, cfg = load_config(model_dir)
+    model = DecoderModel(arch.model_spec(cfg), resolve_dtype(dtype), device)
+    model.load(load_tensors(model_dir, model.declared_tensors(), model.dtype, device))
+    model.config = cfg
+    return model
+
+
+def random_model(config_json: dict[str, Any], seed: int, dtype: str | torch.dtype = "bfloat16",
+                 device: str | torch.device = "cuda:0") -> DecoderModel:
+    """A model with seeded random weights drawn on the device (no folder is written)."""
+    device = torch.device(device)
+    _require_cuda(device)
+    arch = resolve_architecture(config_json)
+    cfg = arch.parse_config(config_json)
+    model = DecoderModel(arch.model_spec(cfg), resolve_dtype(dtype), device)
+    model.load(random_tensors(model.declared_tensors(), seed, dtype=model.dtype, device=device))
+    model.config = cfg
+    return model
+
+
+class ModelRunner:
+    """A model with its cache pools and cache manager."""
+
+    def __init__(self, model: DecoderModel, *, num_pages: int | Sequence[int], page_size: int = 16, max_requests: int = 64,
+                 enable_prefix_caching: bool = True, watermark: float = 0.01) -> None:
+        self.model = model
+        needs = model.cache_needs()
+        order = model.spec.run_order
+        n_groups = len({n for n in needs if isinstance(n, PagedKVNeed)})
+        pages = [num_pages] * n_groups if isinstance(num_pages, int) else list(num_pages)
+        self.pools = CachePools(needs, order, pages, page_size, max_requests, model.dtype, model.device)
+        self.manager = CacheManager(
+            [GroupSpec(p, need.window) for p, need in zip(pages, self.pools.group_needs)],
+            page_size, max_requests, enable_prefix_caching=enable_prefix_caching,
+            has_state=any(isinstance(n, StateNeed) for n in needs), watermark=watermark,
+        )
+        self.page_size = page_size
+
+    @staticmethod
+    def pages_for_budget(model: DecoderModel, budget_bytes: float, page_size: int) -> int:
+        """Pages per group that ``budget_bytes`` buys, every group getting the same count
+        (src/dli/kv/paged_store.py:78-89)."""
+        per_page = sum(CachePools.bytes_per_page(model.cache_needs(), model.spec.run_order, page_size, model.dtype))
+        return max(1, int(budget_bytes // max(1, per_page)))
+
+    def start_request(self, request_id, slot: int) -> None:
+        if self.pools.has_state:
+            self.pools.reset_state(slot)
+
+    @torch.inference_mode()
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Logits [wanted, vocab] float32 on the device, in the order of ``entries`` and of
+        each entry's ``want``.  Afterwards every entry's tokens count as computed."""
+        batch, _ = build_batch(entries, self.manager, self.model.device, self.model.spec.vocab_size)
+        logits = self.model.forward(batch, self.pools.layer_caches)
+        for e, start in zip(entries, [self.manager.num_computed_tokens(e.request_id) for e in entries]):
+            self.manager.mark_computed(e.request_id, start + len(e.token_ids))
+        return logits

@@ -1,0 +1,252 @@
+"""Python wrappers of the hand-written CUDA kernels.
+
+Every wrapper checks device, dtype, shape and contiguity, then launches on the
+current CUDA stream through the compiled library's C entry point.  There is no
+CPU or library fallback: a tensor that is not on a CUDA device, or a library
+that cannot be built, raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..csrc.build import ExtensionError, load_library
+
+DT_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+# number of this package's kernels launched since import (a graph replay adds its node count)
+launch_count = 0
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_ERRORS = {1001: "size or option not supported by this kernel"}
+
+
+def _check(code: int, what: str) -> None:
+    global launch_count
+    if code != 0:
+        detail = _ERRORS.get(code)
+        if detail is None:
+            try:
+                detail = torch.cuda.cudart().cudaGetErrorString(code)  # type: ignore[attr-defined]
+            except Exception:
+                detail = f"CUDA error {code}"
+        raise KernelError(f"{what}: {detail} (code {code})")
+    launch_count += 1
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor: the engine has no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+
+
+_fns: dict[str, ctypes._CFuncPtr] = {}
+
+
+def _fn(source: str, name: str, argtypes: list, defines: dict | None = None):
+    key = f"{source}:{name}:{sorted((defines or {}).items())}"
+    f = _fns.get(key)
+    if f is None:
+        lib = load_library(source, defines)
+        try:
+            f = getattr(lib, name)
+        except AttributeError as exc:
+            raise ExtensionError(f"{name} missing from {source}") from exc
+        f.argtypes = argtypes
+        f.restype = c_int
+        _fns[key] = f
+    return f
+
+
+# ------------------------------------------------------------------ elementwise
+
+
+def embedding(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """h[t] = float32(table[ids[t]]); h is the float32 residual stream [n, H]."""
+    _need(h, "h", torch.float32), _need(table, "table"), _need(ids, "ids", torch.int32)
+    n, H = h.shape
+    if table.shape[1] != H or ids.numel() != n or table.dtype not in DT_CODE:
+        raise KernelError("embedding: shapes or dtype do not agree")
+    f = _fn("elementwise.cu", "dli_embedding", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), _ptr(table), _ptr(ids), n, H, DT_CODE[table.dtype], _stream()), "embedding")
+
+
+def add_rmsnorm(
+    y: torch.Tensor,
+    h: torch.Tensor,
+    delta: torch.Tensor | None,
+    weight: torch.Tensor,
+    eps: float,
+    rows: torch.Tensor | None = None,
+) -> None:
+    """y[r] = rmsnorm(h[s] + delta[s]) * weight with s = rows[r] (or r).
+
+    Without ``rows`` the sum is written back to ``h`` (the residual stream moves on);
+    with ``rows`` only the selected rows are read and ``h`` is left alone.
+    """
+    _need(y, "y"), _need(h, "h", torch.float32), _need(weight, "weight", torch.float32)
+    H = h.shape[1]
+    n_rows = y.shape[0]
+    if y.dtype not in DT_CODE or y.shape[1] != H or weight.numel() != H:
+        raise KernelError("add_rmsnorm: shapes or dtype do not agree")
+    if delta is not None:
+        _need(delta, "delta", y.dtype)
+        if delta.shape != h.shape:
+            raise KernelError("add_rmsnorm: delta and h differ in shape")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() != n_rows:
+            raise KernelError("add_rmsnorm: one output row per entry of rows")
+    elif n_rows != h.shape[0]:
+        raise KernelError("add_rmsnorm: y and h differ in rows")
+    f = _fn(
+        "elementwise.cu", "dli_add_rmsnorm",
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    )
+    _check(f(_ptr(y), _ptr(h), _ptr(delta), _ptr(weight), _ptr(rows), n_rows, H, eps, DT_CODE[y.dtype], _stream()), "add_rmsnorm")
+
+
+def rotary_store(
+    qkv: torch.Tensor,
+    positions: torch.Tensor,
+    inv_freq: torch.Tensor | None,
+    slots: torch.Tensor | None,
+    k_pool: torch.Tensor | None,
+    v_pool: torch.Tensor | None,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    rotary_dim: int,
+    page_size: int,
+    write_kv: bool = True,
+) -> None:
+    """Rotate q and k heads of qkv [n, (nh + 2 nkv) d] by position; q in place, k and v into
+    one layer's pools [pages, nkv, page_size, d] at ``slots`` (page * page_size + offset)."""
+    _need(qkv, "qkv"), _need(positions, "positions", torch.int32)
+    n = qkv.shape[0]
+    if qkv.dtype not in DT_CODE or qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or positions.numel() != n:
+        raise KernelError("rotary_store: shapes or dtype do not agree")
+    if rotary_dim:
+        if inv_freq is None:
+            raise KernelError("rotary_store: inv_freq is needed when rotary_dim > 0")
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("rotary_store: inv_freq must have rotary_dim / 2 entries")
+    if write_kv:
+        if slots is None or k_pool is None or v_pool is None:
+            raise KernelError("rotary_store: slots and pools are needed to write keys and values")
+        _need(slots, "slots", torch.int32), _need(k_pool, "k_pool", qkv.dtype), _need(v_pool, "v_pool", qkv.dtype)
+        if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, head_dim) or k_pool.shape != v_pool.shape or slots.numel() != n:
+            raise KernelError("rotary_store: pool layout must be [pages, kv_heads, page_size, head_dim]")
+    f = _fn(
+        "elementwise.cu", "dli_rotary_store",
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 8 + [c_void_p],
+    )
+    _check(
+        f(_ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(k_pool), _ptr(v_pool), n, num_heads, num_kv_heads,
+          head_dim, rotary_dim, page_size, int(write_kv), DT_CODE[qkv.dtype], _stream()),
+        "rotary_store",
+    )
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
+    """out[n, I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _need(out, "out"), _need(gate_up, "gate_up", out.dtype)
+    n, I = out.shape
+    if out.dtype not in DT_CODE or tuple(gate_up.shape) != (n, 2 * I):
+        raise KernelError("silu_mul: shapes or dtype do not agree")
+    f = _fn("elementwise.cu", "dli_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(gate_up), n, I, DT_CODE[out.dtype], _stream()), "silu_mul")
+
+
+# ------------------------------------------------------------------ attention
+
+
+def paged_attention_simt(
+    out: torch.Tensor,
+    qkv: torch.Tensor,
+    k_pool: torch.Tensor,
+    v_pool: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    positions: torch.Tensor,
+    num_heads: int,
+    scale: float,
+    window: int | None = None,
+) -> None:
+    """Causal attention of every token over its sequence's pages, on CUDA cores.
+
+    out [n, nh * d]; queries are the first nh * d columns of qkv; pools [pages, nkv, page_size, d];
+    block_tables [seqs, max_blocks]; a token at position p reads keys max(0, p - window + 1) .. p.
+    """
+    _need(out, "out"), _need(qkv, "qkv", out.dtype), _need(k_pool, "k_pool", out.dtype), _need(v_pool, "v_pool", out.dtype)
+    _need(block_tables, "block_tables", torch.int32), _need(seq_of_token, "seq_of_token", torch.int32)
+    _need(positions, "positions", torch.int32)
+    n = out.shape[0]
+    _, nkv, page_size, d = k_pool.shape
+    if out.dtype not in DT_CODE or out.shape[1] != num_heads * d or qkv.shape[0] != n or qkv.shape[1] < num_heads * d:
+        raise KernelError("paged_attention_simt: shapes or dtype do not agree")
+    if d > 256 or num_heads % nkv:
+        raise KernelError(f"paged_attention_simt: head_dim {d} (<= 256) / heads {num_heads} per kv head {nkv} not supported")
+    f = _fn(
+        "attention_simt.cu", "dli_paged_attention_simt",
+        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 6 + [c_float, c_int, c_void_p],
+    )
+    _check(
+        f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1],
+          _ptr(seq_of_token), _ptr(positions), n, num_heads, nkv, d, page_size, int(window or 0), scale, DT_CODE[out.dtype], _stream()),
+        "paged_attention_simt",
+    )
+
+
+# ------------------------------------------------------------------ sampling
+
+
+def sample(
+    out: torch.Tensor,
+    logits: torch.Tensor,
+    temperature: torch.Tensor | None = None,
+    top_k: torch.Tensor | None = None,
+    top_p: torch.Tensor | None = None,
+    seed: torch.Tensor | None = None,
+    draw: torch.Tensor | None = None,
+) -> None:
+    """out[r] = token of row r of float32 logits [rows, V]; all-greedy when temperature is None.
+    seed and draw are int64 tensors read as unsigned 64-bit."""
+    _need(out, "out", torch.int32), _need(logits, "logits", torch.float32)
+    rows, V = logits.shape
+    if out.numel() != rows:
+        raise KernelError("sample: one output per row")
+    if temperature is not None:
+        if top_k is None or top_p is None or seed is None or draw is None:
+            raise KernelError("sample: stochastic rows need top_k, top_p, seed and draw")
+        _need(temperature, "temperature", torch.float32), _need(top_k, "top_k", torch.int32), _need(top_p, "top_p", torch.float32)
+        _need(seed, "seed", torch.int64), _need(draw, "draw", torch.int64)
+        if not (temperature.numel() == top_k.numel() == top_p.numel() == seed.numel() == draw.numel() == rows):
+            raise KernelError("sample: one parameter per row")
+    f = _fn(
+        "sampling.cu", "dli_sample",
+        [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    )
+    _check(
+        f(_ptr(out), _ptr(logits), logits.stride(0), rows, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(draw), _stream()),
+        "sample",
+    )

@@ -1,0 +1,99 @@
+"""Interfaces of the parts a model is put together from, and their registry.
+
+A part is built from a ``PartSpec`` (its sizes and constants) and a
+``BuildEnv`` (dtype, device).  It declares the tensors it reads from the
+checkpoint by full name, takes them in ``load``, and runs on the tokens of a
+step.  No part knows which model it is in.
+
+Interfaces by category (what a new part of that category must provide):
+
+``norm``          ``add_norm(h, delta, rows=None) -> y``: h is the float32 residual stream
+                  [n, H]; delta (activation dtype, or None) is added to h first, and the sum is
+                  written back to h when ``rows`` is None; y (activation dtype) is the normed sum of
+                  the rows asked for.
+``position``      ``rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv)``:
+                  encodes position into the q and k heads of qkv in place and writes k, v into the
+                  cache's pages at ``batch.group(cache.group).slots``.
+``mixer``         ``cache_need() -> PagedKVNeed | StateNeed | None`` and
+                  ``forward(x, batch, cache) -> [n, H]``; x is the normed input (activation dtype).
+                  ``cache`` is the ``LayerCache`` of its run step (pools or state slots; ``writes``
+                  is False when the step reads another step's cache).
+``feed_forward``  ``forward(x) -> [n, H]``.
+``arrangement``   built from a ``LayerSpec``; ``forward(stream, batch, cache)`` wires norms, mixer
+                  and feed-forward around the residual ``stream`` (h plus a pending delta).
+``embedding``     ``forward(token_ids) -> h`` float32 [n, H].
+``head``          ``forward(y) -> logits`` float32 [k, V].
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable
+
+import torch
+
+from ..config.spec import PartSpec
+from ..weights.loader import TensorDecl
+
+
+@dataclass(frozen=True)
+class BuildEnv:
+    dtype: torch.dtype  # activation and matrix dtype: torch.bfloat16 or torch.float32
+    device: torch.device
+
+
+class Part:
+    """Base of every part: declares tensors by full name and receives them."""
+
+    def __init__(self, spec: PartSpec, env: BuildEnv) -> None:
+        self.spec = spec
+        self.env = env
+
+    def declare(self) -> dict[str, TensorDecl]:
+        return {}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        pass
+
+    def children(self) -> list["Part"]:
+        return []
+
+
+@dataclass
+class ResidualStream:
+    """The float32 residual h [n, H] and a delta (activation dtype) not yet added to it.
+    Keeping the delta pending lets the next norm do the addition in the same kernel."""
+
+    h: torch.Tensor
+    pending: torch.Tensor | None = None
+
+
+_REGISTRY: dict[tuple[str, str], Callable[..., Any]] = {}
+
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head")
+
+
+def register_part(category: str, kind: str):
+    """Class decorator: ``@register_part("mixer", "my_mixer")``."""
+    if category not in CATEGORIES:
+        raise ValueError(f"unknown part category {category!r} (known: {CATEGORIES})")
+
+    def deco(cls):
+        _REGISTRY[(category, kind)] = cls
+        return cls
+
+    return deco
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _REGISTRY.pop((category, kind), None)
+
+
+def build_part(category: str, spec, env: BuildEnv):
+    try:
+        cls = _REGISTRY[(category, spec.kind if category != "arrangement" else spec.arrangement)]
+    except KeyError:
+        kind = spec.kind if category != "arrangement" else spec.arrangement
+        known = sorted(k for c, k in _REGISTRY if c == category)
+        raise ValueError(f"no {category} part of kind {kind!r} is registered (known: {known})") from None
+    return cls(spec, env)

@@ -1,0 +1,28 @@
+"""Arrangements: how a layer's norms, mixer and feed-forward sit around the residual."""
+
+from __future__ import annotations
+
+from .base import BuildEnv, Part, ResidualStream, build_part, register_part
+
+
+@register_part("arrangement", "prenorm")
+class PreNormBlock(Part):
+    """x = x + mixer(norm(x)); x = x + ffn(norm(x)) (src/dli/model/llama.py:211-212).
+    Roles: mixer_norm, mixer, ffn_norm, ffn.  The feed-forward's output stays pending on the
+    stream; the next norm adds it."""
+
+    def __init__(self, spec, env: BuildEnv) -> None:
+        self.spec, self.env = spec, env
+        self.mixer_norm = build_part("norm", spec.parts["mixer_norm"], env)
+        self.mixer = build_part("mixer", spec.parts["mixer"], env)
+        self.ffn_norm = build_part("norm", spec.parts["ffn_norm"], env)
+        self.ffn = build_part("feed_forward", spec.parts["ffn"], env)
+
+    def children(self):
+        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def forward(self, stream: ResidualStream, batch, cache) -> None:
+        y = self.mixer_norm.add_norm(stream.h, stream.pending)
+        a = self.mixer.forward(y, batch, cache)
+        y = self.ffn_norm.add_norm(stream.h, a)
+        stream.pending = self.ffn.forward(y)

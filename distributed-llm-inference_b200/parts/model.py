@@ -1,0 +1,126 @@
+"""The decoder: embedding, layers in run order, final norm, head — built from a ModelSpec."""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.spec import ModelSpec
+from ..kernels import ops
+from ..kernels.gemm import linear
+from ..weights.loader import TensorDecl
+from .base import BuildEnv, Part, ResidualStream, build_part, register_part
+
+
+@register_part("embedding", "token_embedding")
+class TokenEmbedding(Part):
+    """h = table[token_ids], no scale (src/dli/model/llama.py:291).  params: vocab_size, hidden_size."""
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
+        self.weight: torch.Tensor | None = None
+
+    def declare(self):
+        return {self.spec.prefix + "weight": TensorDecl((self.vocab, self.hidden))}
+
+    def load(self, tensors):
+        self.weight = tensors[self.spec.prefix + "weight"]
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        h = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
+        ops.embedding(h, self.weight, token_ids)
+        return h
+
+
+@register_part("head", "lm_head")
+class LMHead(Part):
+    """logits = y W^T in float32, W the embedding matrix when ``tied_to`` names it
+    (src/dli/model/llama.py:304-305).  A tied checkpoint that stores the head anyway is
+    accepted if both are equal (src/dli/model/loader.py:75-80).
+    params: vocab_size, hidden_size, tied_to."""
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
+        self.tied_to = spec.params.get("tied_to")
+        self.weight: torch.Tensor | None = None
+
+    def declare(self):
+        return {self.spec.prefix + "weight": TensorDecl((self.vocab, self.hidden), optional_alias_of=self.tied_to)}
+
+    def load(self, tensors):
+        self.weight = tensors[self.tied_to or self.spec.prefix + "weight"]
+
+    def forward(self, y: torch.Tensor) -> torch.Tensor:
+        return linear(y, self.weight).float()
+
+
+def _walk(part) -> list[Part]:
+    out = [part]
+    for c in part.children():
+        out.extend(_walk(c))
+    return out
+
+
+class DecoderModel:
+    """Runs the tokens of one step through the layers, in the order ``spec.run_order`` gives."""
+
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device: torch.device | str) -> None:
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {dtype} is not supported (bfloat16, float32)")
+        self.spec = spec
+        self.env = BuildEnv(dtype, torch.device(device))
+        self.embedding = build_part("embedding", spec.embedding, self.env)
+        self.layers = [build_part("arrangement", layer, self.env) for layer in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, self.env)
+        self.head = build_part("head", spec.head, self.env)
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.env.dtype
+
+    @property
+    def device(self) -> torch.device:
+        return self.env.device
+
+    def parts(self) -> list[Part]:
+        out: list[Part] = []
+        for top in (self.embedding, *self.layers, self.final_norm, self.head):
+            out.extend(_walk(top))
+        return out
+
+    def declared_tensors(self) -> dict[str, TensorDecl]:
+        out: dict[str, TensorDecl] = {}
+        for part in self.parts():
+            for name, decl in part.declare().items():
+                if name in out and out[name] != decl:
+                    raise ValueError(f"tensor {name!r} is declared twice with different shapes")
+                out[name] = decl
+        return out
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        for part in self.parts():
+            part.load(tensors)
+
+    def cache_needs(self) -> list:
+        """The need of each run step's mixer (None for a step that reads another step's cache)."""
+        needs = []
+        for step in self.spec.run_order:
+            mixer = getattr(self.layers[step.layer], "mixer", None)
+            needs.append(mixer.cache_need() if mixer is not None and step.cache_of is None else None)
+        return needs
+
+    def forward(self, batch, caches) -> torch.Tensor:
+        """Logits [k, vocab] (float32) at ``batch.logit_rows``; every token's cache entries are written."""
+        stream = ResidualStream(self.embedding.forward(batch.token_ids))
+        for i, step in enumerate(self.spec.run_order):
+            self.layers[step.layer].forward(stream, batch, caches[i])
+        if batch.logit_rows.numel() == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        y = self.final_norm.add_norm(stream.h, stream.pending, rows=batch.logit_rows)
+        return self.head.forward(y)
+
+
+def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
+    """Names, shapes and kinds of a spec's tensors, without touching a device."""
+    return DecoderModel(spec, torch.float32, "meta").declared_tensors()

@@ -1,0 +1,72 @@
+"""Rotary position encoding (rotate-half pairing), default and llama3 frequency scaling."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..kernels import ops
+from .base import Part, register_part
+
+
+def inverse_frequencies(params) -> torch.Tensor:
+    """[rotary_dim / 2] float32 on the CPU, every step in float32 as the reference does it
+    (src/dli/model/rope.py:21-47): exponents 2j/d, 1 / theta**e; for ``llama3`` wavelengths
+    beyond original_max / low_freq_factor are divided by ``factor``, those under
+    original_max / high_freq_factor kept, and the band between interpolated."""
+    d = int(params["rotary_dim"])
+    exponents = torch.arange(0, d, 2, dtype=torch.int64).to(torch.float32) / d
+    inv = 1.0 / (float(params["theta"]) ** exponents)
+    scaling = params.get("scaling", "default")
+    if scaling == "default":
+        return inv
+    if scaling != "llama3":
+        raise ValueError(f"rotary scaling {scaling!r} is not supported (default, llama3)")
+    old = params["original_max_position_embeddings"]
+    factor, low, high = float(params["factor"]), float(params["low_freq_factor"]), float(params["high_freq_factor"])
+    wavelen = 2 * math.pi / inv
+    scaled = torch.where(wavelen > old / low, inv / factor, inv)
+    smooth = (old / wavelen - low) / (high - low)
+    smoothed = (1 - smooth) * scaled / factor + smooth * scaled
+    medium = ~(wavelen < old / high) & ~(wavelen > old / low)
+    return torch.where(medium, smoothed, scaled)
+
+
+@register_part("position", "rotary")
+class Rotary(Part):
+    """params: head_dim, rotary_dim (<= head_dim; elements beyond it pass through), theta,
+    scaling and its constants.  The angle float32(position) * inv_freq and its sine and cosine
+    are computed in float32 inside the kernel that also writes k and v to the cache."""
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        self.head_dim = int(spec.params["head_dim"])
+        self.rotary_dim = int(spec.params.get("rotary_dim", self.head_dim))
+        if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
+            raise ValueError(f"rotary_dim={self.rotary_dim} must be even and at most head_dim={self.head_dim}")
+        self.inv_freq = inverse_frequencies(spec.params).to(env.device) if self.rotary_dim else None
+
+    def rotate_and_store(self, qkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool) -> None:
+        group = batch.group(cache.group)
+        ops.rotary_store(
+            qkv, batch.positions, self.inv_freq, group.slots if write_kv else None,
+            cache.k if write_kv else None, cache.v if write_kv else None,
+            num_heads, num_kv_heads, self.head_dim, self.rotary_dim, cache.page_size, write_kv,
+        )
+
+
+@register_part("position", "none")
+class NoPosition(Part):
+    """No position encoding: q passes through, k and v are written to the cache as they are."""
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        self.head_dim = int(spec.params["head_dim"])
+
+    def rotate_and_store(self, qkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool) -> None:
+        if not write_kv:
+            return
+        group = batch.group(cache.group)
+        ops.rotary_store(qkv, batch.positions, None, group.slots, cache.k, cache.v, num_heads, num_kv_heads,
+                         self.head_dim, 0, cache.page_size, True)
