@@ -1,4 +1,11 @@
 from .batch import StepBatch, StepEntry, build_batch
+from .llm_engine import LLMEngine, RequestOutput, StepStats
+from .request import FinishReason, Request, RequestStatus
 from .runner import ModelRunner, load_model, random_model, resolve_dtype
+from .scheduler import ScheduledChunk, Scheduler, SchedulerConfig, SchedulerOutput
 
-__all__ = ["ModelRunner", "StepBatch", "StepEntry", "build_batch", "load_model", "random_model", "resolve_dtype"]
+__all__ = [
+    "FinishReason", "LLMEngine", "ModelRunner", "Request", "RequestOutput", "RequestStatus", "ScheduledChunk",
+    "Scheduler", "SchedulerConfig", "SchedulerOutput", "StepBatch", "StepEntry", "StepStats", "build_batch",
+    "load_model", "random_model", "resolve_dtype",
+]

@@ -101,6 +101,15 @@ class ModelRunner:
         each entry's ``want``.  Afterwards every entry's tokens count as computed."""
         batch, _ = build_batch(entries, self.manager, self.model.device, self.model.spec.vocab_size)
         logits = self.model.forward(batch, self.pools.layer_caches)
-        for e, start in zip(entries, [self.manager.num_computed_tokens(e.request_id) for e in entries]):
-            self.manager.mark_computed(e.request_id, start + len(e.token_ids))
+        for e in entries:
+            self.manager.mark_computed(e.request_id, self.manager.num_computed_tokens(e.request_id) + len(e.token_ids))
         return logits
+
+    def execute(self, chunks) -> torch.Tensor:
+        """The engine's view of ``step``: one entry per scheduled chunk, logits at the last
+        token of the chunks that sample (src/dli/engine/runner.py:53-80)."""
+        entries = []
+        for ch in chunks:
+            tokens = ch.request.all_token_ids[ch.start : ch.start + ch.num_tokens]
+            entries.append(StepEntry(ch.request.request_id, tokens, [ch.num_tokens - 1] if ch.needs_logits else []))
+        return self.step(entries)

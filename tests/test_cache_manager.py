@@ -1,0 +1,210 @@
+"""The cache manager: no page lost, held twice or freed twice, under random orders (no GPU)."""
+
+import random
+
+import pytest
+
+from dli_b200.cache import CacheManager, GroupSpec, OutOfPages, UnknownRequest, chain_hashes, page_hash
+
+
+def make(pages=8, page=4, **kw):
+    kw.setdefault("watermark", 0.0)
+    return CacheManager([GroupSpec(pages)], page, kw.pop("max_requests", 8), **kw)
+
+
+def test_allocate_tables_slots_and_free():
+    m = make()
+    a = m.allocate("a", list(range(10)))
+    assert a.num_cached_tokens == 0 and len(m.block_table("a")) == 3
+    t = m.block_table("a")
+    assert m.slot_mapping("a", 0, 3, 10) == [t[0] * 4 + 3, *[t[1] * 4 + i for i in range(4)], t[2] * 4, t[2] * 4 + 1]
+    m.append_slots("a", [1, 2])  # fills the third page
+    assert len(m.block_table("a")) == 3
+    m.append_slots("a", [3])
+    assert len(m.block_table("a")) == 4 and m.num_tokens("a") == 13
+    m.check_invariants()
+    m.free("a")
+    assert m.min_available_pages() == 8
+    with pytest.raises(UnknownRequest):
+        m.free("a")
+    m.check_invariants()
+
+
+def test_out_of_pages_changes_nothing():
+    m = make(pages=4)
+    m.allocate("a", list(range(12)))
+    with pytest.raises(OutOfPages):
+        m.allocate("b", list(range(8)))
+    assert not m.has_request("b")
+    m.append_slots("a", [0, 0, 0, 0])
+    with pytest.raises(OutOfPages):
+        m.append_slots("a", [0])
+    assert m.num_tokens("a") == 16
+    m.check_invariants()
+
+
+def test_watermark_holds_pages_back_for_running_requests():
+    m = CacheManager([GroupSpec(100)], 4, 8, watermark=0.1)
+    assert not m.can_allocate(list(range(4 * 91)))
+    assert m.can_allocate(list(range(4 * 90)))
+    m.allocate("a", list(range(4 * 90)))
+    m.append_slots("a", list(range(4 * 10)))  # growth ignores the watermark
+    m.check_invariants()
+
+
+def test_state_slots_are_unique_and_reused():
+    m = make(pages=32, max_requests=3)
+    slots = [m.allocate(i, [1, 2]).state_slot for i in range(3)]
+    assert sorted(slots) == [0, 1, 2]
+    assert not m.can_allocate([1])
+    with pytest.raises(OutOfPages):
+        m.allocate(9, [1])
+    m.free(1)
+    assert m.allocate(9, [1]).state_slot == slots[1]
+    m.check_invariants()
+
+
+def test_prefix_pages_are_shared_only_after_they_were_computed():
+    m = make(pages=16)
+    prompt = list(range(100, 110))  # 2 full pages + 2 tokens
+    m.allocate("a", prompt)
+    assert m.allocate("b", prompt).num_cached_tokens == 0  # nothing computed yet
+    m.mark_computed("a", 10)
+    m.mark_computed("b", 10)  # same contents in other pages: stays private
+    assert m.pools[0].duplicate_registrations == 2
+    c = m.allocate("c", prompt + [7, 8, 9])
+    assert c.num_cached_tokens == 8 and m.block_table("c")[:2] == m.block_table("a")[:2]
+    assert m.num_computed_tokens("c") == 8
+    m.check_invariants()
+    for r in "abc":
+        m.free(r)
+    m.check_invariants()
+    assert m.pools[0].num_idle == 2  # the two indexed pages stay, revivable
+    d = m.allocate("d", prompt[:8])  # the page of the last token is always recomputed
+    assert d.num_cached_tokens == 4
+    m.check_invariants()
+
+
+def test_namespace_separates_prefixes():
+    assert chain_hashes(b"x", [1, 2, 3, 4], 4) != chain_hashes(b"y", [1, 2, 3, 4], 4)
+    assert page_hash(b"ab", b"\0" * 32, [1]) != page_hash(b"a", b"\0" * 32, [1])
+    m = make(pages=16)
+    m.allocate("a", list(range(9)), namespace=b"m1")
+    m.mark_computed("a", 9)
+    assert m.allocate("b", list(range(9)), namespace=b"m2").num_cached_tokens == 0
+    assert m.allocate("c", list(range(9)), namespace=b"m1").num_cached_tokens == 8
+
+
+def test_idle_pages_are_evicted_leaf_first_oldest_first():
+    m = make(pages=4)
+    m.allocate("a", list(range(9)))  # 3 pages, 2 full
+    m.mark_computed("a", 9)
+    m.free("a")
+    assert m.pools[0].num_idle == 2 and m.min_available_pages() == 4
+    m.allocate("b", [50] * 13)  # needs all 4: evicts the leaf, then its parent
+    assert m.pools[0].evictions == 2
+    m.check_invariants()
+    m.free("b")
+    assert m.allocate("c", list(range(9))).num_cached_tokens == 0
+
+
+def test_prefix_caching_off():
+    m = make(enable_prefix_caching=False)
+    m.allocate("a", list(range(9)))
+    m.mark_computed("a", 9)
+    m.free("a")
+    assert m.pools[0].num_idle == 0 and m.allocate("b", list(range(9))).num_cached_tokens == 0
+
+
+def test_window_group_gives_pages_back_as_the_window_passes():
+    m = CacheManager([GroupSpec(8), GroupSpec(8, window=6)], 4, 4, watermark=0.0)
+    assert not m.prefix_caching  # a prefix's pages alone would not restore a windowed group
+    m.allocate("a", list(range(14)))
+    assert len(m.block_table("a", 0)) == 4 and len(m.block_table("a", 1)) == 4
+    m.mark_computed("a", 9)  # next query at >= 9 reads keys > 3: page 0 (keys 0..3) is dead
+    assert m.block_table("a", 1)[0] == -1 and m.block_table("a", 1)[1] >= 0
+    assert m.pools[1].available == 5 and m.pools[0].available == 4
+    m.check_invariants()
+    with pytest.raises(ValueError, match="given back"):
+        m.slot_mapping("a", 1, 0, 4)
+    m.mark_computed("a", 14)  # keys > 8 stay: pages 0 and 1 dead
+    assert m.block_table("a", 1)[:2] == [-1, -1]
+    m.append_slots("a", [1, 2, 3])
+    m.check_invariants()
+    m.free("a")
+    assert m.pools[1].available == 8 and m.pools[0].available == 8
+    m.check_invariants()
+
+
+def test_mark_computed_is_monotone():
+    m = make()
+    m.allocate("a", list(range(6)))
+    m.mark_computed("a", 4)
+    with pytest.raises(ValueError):
+        m.mark_computed("a", 3)
+    with pytest.raises(ValueError):
+        m.mark_computed("a", 7)
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("prefix_caching, window", [(True, None), (False, None), (False, 7)])
+def test_random_orders_keep_every_invariant(seed, prefix_caching, window):
+    """Requests arrive, grow, are computed in portions, finish and are preempted in random
+    order.  A shadow store maps every slot to the token prefix written there, so a page held
+    twice, freed while in use, or shared with other contents shows as a wrong read."""
+    rng = random.Random(seed)
+    page = rng.choice([1, 3, 4])
+    groups = [GroupSpec(24)] + ([GroupSpec(20, window=window)] if window else [])
+    m = CacheManager(groups, page, 5, enable_prefix_caching=prefix_caching, watermark=0.0)
+    shadow = [dict() for _ in groups]  # per group: slot -> prefix tuple
+    tokens: dict[int, list[int]] = {}
+    stems = [[rng.randrange(5) for _ in range(12)] for _ in range(3)]
+    next_id = 0
+    for _ in range(600):
+        op = rng.random()
+        live = list(tokens)
+        if op < 0.25 or not live:
+            toks = (rng.choice(stems)[: rng.randrange(1, 13)] if rng.random() < 0.7 else []) + [rng.randrange(5) for _ in range(rng.randrange(1, 9))]
+            ok = m.can_allocate(toks)
+            try:
+                alloc = m.allocate(next_id, toks)
+                assert ok
+                tokens[next_id] = toks
+                # cached tokens must already hold this very prefix
+                for g in range(len(groups)):
+                    for pos, slot in enumerate(m.slot_mapping(next_id, g, 0, alloc.num_cached_tokens)):
+                        assert shadow[g][slot] == tuple(toks[: pos + 1])
+                next_id += 1
+            except OutOfPages:
+                assert not ok
+        elif op < 0.45:
+            rid = rng.choice(live)
+            new = [rng.randrange(5) for _ in range(rng.randrange(1, 4))]
+            try:
+                m.append_slots(rid, new)
+                tokens[rid] += new
+            except OutOfPages:
+                pass
+        elif op < 0.8:
+            rid = rng.choice(live)
+            done, total = m.num_computed_tokens(rid), m.num_tokens(rid)
+            if done < total:
+                upto = rng.randrange(done + 1, total + 1)
+                for g, grp in enumerate(groups):
+                    # reads: every key the window still needs holds this request's prefix
+                    lo = 0 if grp.window is None else max(0, done - grp.window + 1)
+                    for pos, slot in zip(range(lo, done), m.slot_mapping(rid, g, lo, done)):
+                        assert shadow[g][slot] == tuple(tokens[rid][: pos + 1]), "a live slot was overwritten"
+                    for pos, slot in zip(range(done, upto), m.slot_mapping(rid, g, done, upto)):
+                        shadow[g][slot] = tuple(tokens[rid][: pos + 1])
+                m.mark_computed(rid, upto)
+        else:
+            rid = rng.choice(live)
+            m.free(rid)
+            del tokens[rid]
+        m.check_invariants()
+    for rid in list(tokens):
+        m.free(rid)
+    m.check_invariants()
+    for pool in m.pools:
+        assert pool.available == pool.num_pages

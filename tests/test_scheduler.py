@@ -1,0 +1,166 @@
+"""The scheduler's decisions, with a model that has no tensors (no GPU)."""
+
+import random
+
+import pytest
+
+from dli_b200 import SamplingParams
+from dli_b200.engine import FinishReason
+from tests.fake_runner import fake_engine, sequential
+
+
+def prompts(rng, n, lo=1, hi=30):
+    return [[rng.randrange(50) for _ in range(rng.randrange(lo, hi))] for _ in range(n)]
+
+
+def test_batched_equals_sequential():
+    rng = random.Random(0)
+    ps = prompts(rng, 12)
+    eng, runner = fake_engine()
+    outs = eng.generate(ps, SamplingParams(max_tokens=20))
+    assert outs == [sequential(p, 20) for p in ps]
+    assert eng.manager.min_available_pages() == 64 and not eng.has_unfinished()
+    eng.manager.check_invariants()
+
+
+def test_budget_and_request_cap_hold_every_step():
+    rng = random.Random(1)
+    eng, runner = fake_engine(budget=16, max_num_seqs=3)
+    eng.generate(prompts(rng, 9, 10, 40), SamplingParams(max_tokens=6))
+    for step in runner.steps:
+        assert sum(n for _, _, n, _ in step) <= 16 and len(step) <= 3
+    assert any(n > 1 and not logits for step in runner.steps for _, _, n, logits in step), "no prompt was cut"
+
+
+def test_long_prompt_is_cut_and_decodes_go_on_beside_it():
+    eng, runner = fake_engine(budget=8)
+    eng.add_request("short", [1, 2, 3], SamplingParams(max_tokens=12))
+    eng.step()
+    eng.add_request("long", list(range(40)), SamplingParams(max_tokens=2))
+    for _ in range(5):
+        eng.step()
+    for step in runner.steps[1:6]:
+        kinds = {rid: n for rid, _, n, _ in step}
+        assert kinds["short"] == 1 and kinds["long"] == 7  # the running request first, the prompt takes the rest
+    while eng.has_unfinished():
+        eng.step()
+
+
+def test_pages_run_out_newest_is_preempted_and_recomputed():
+    rng = random.Random(2)
+    ps = prompts(rng, 6, 8, 16)
+    eng, runner = fake_engine(num_pages=14, page_size=4, budget=64, watermark=0.0)
+    reqs = [eng.add_request(f"r{i}", p, SamplingParams(max_tokens=24)) for i, p in enumerate(ps)]
+    seen_preempt_step_admits = False
+    while eng.has_unfinished():
+        before = {r.request_id for r in eng.scheduler.running}
+        eng.step()
+        st = eng.stats.steps[-1]
+        if st.num_preempted:
+            after = {r.request_id for r in eng.scheduler.running}
+            assert after <= before, "a step that preempted also admitted"
+            seen_preempt_step_admits = True
+    assert seen_preempt_step_admits and sum(r.num_preemptions for r in reqs) > 0
+    assert reqs[0].num_preemptions == 0, "the oldest request was preempted"
+    assert [r.output_ids for r in reqs] == [sequential(p, 24) for p in ps]
+    assert eng.manager.min_available_pages() == 14
+    eng.manager.check_invariants()
+
+
+def test_request_that_can_never_fit_is_refused():
+    eng, _ = fake_engine(num_pages=4, page_size=4)
+    r = eng.add_request("big", list(range(10)), SamplingParams(max_tokens=7))
+    assert r.is_finished and r.finish_reason is FinishReason.CAPACITY and not eng.has_unfinished()
+    ok = eng.add_request("fits", list(range(10)), SamplingParams(max_tokens=6))
+    assert not ok.is_finished
+    with pytest.raises(ValueError, match="duplicate"):
+        eng.add_request("fits", [1])
+    with pytest.raises(ValueError, match="non-empty"):
+        eng.add_request("empty", [])
+
+
+def test_stop_tokens_eos_and_length():
+    p = [3, 1, 4]
+    full = sequential(p, 10)
+    eng, _ = fake_engine()
+    eng.eos = frozenset({full[4]})
+    a = eng.add_request("a", p, SamplingParams(max_tokens=10))
+    b = eng.add_request("b", p, SamplingParams(max_tokens=10, ignore_eos=True))
+    c = eng.add_request("c", p, SamplingParams(max_tokens=10, ignore_eos=True, stop_token_ids=(full[2],)))
+    while eng.has_unfinished():
+        eng.step()
+    first = full.index(full[4])
+    assert a.output_ids == full[: first + 1] and a.finish_reason is FinishReason.STOP
+    assert b.output_ids == full and b.finish_reason is FinishReason.LENGTH
+    assert c.output_ids == full[: full.index(full[2]) + 1] and c.finish_reason is FinishReason.STOP
+
+
+def test_abort_frees_everything_and_is_idempotent():
+    eng, _ = fake_engine(budget=8)
+    eng.add_request("a", list(range(30)), SamplingParams(max_tokens=5))
+    eng.add_request("b", list(range(5)), SamplingParams(max_tokens=5))
+    eng.step()
+    assert eng.abort("a") and not eng.abort("a") and eng.abort("b") and not eng.abort("nobody")
+    assert not eng.has_unfinished() and eng.manager.min_available_pages() == 64
+    eng.manager.check_invariants()
+
+
+def test_shared_prefix_starts_after_the_cached_pages():
+    eng, runner = fake_engine(page_size=4, budget=64)
+    stem = list(range(30))
+    eng.generate([stem + [40]], SamplingParams(max_tokens=2))
+    eng.generate([stem + [41, 42]], SamplingParams(max_tokens=2))
+    first_chunk_of_second = runner.steps[2][0]
+    assert first_chunk_of_second[1] == 28  # 7 full pages of the stem are reused
+    assert eng.manager.stats.prompt_tokens_hit == 28
+
+
+def test_head_of_queue_is_not_overtaken():
+    eng, runner = fake_engine(num_pages=8, page_size=4, budget=64, watermark=0.0)
+    eng.add_request("run", list(range(20)), SamplingParams(max_tokens=4))  # 6 pages at the end
+    eng.step()
+    eng.add_request("big", list(range(100, 116)), SamplingParams(max_tokens=4))  # does not fit beside it
+    eng.add_request("small", [1], SamplingParams(max_tokens=1))  # would fit, but must wait its turn
+    eng.step()
+    assert {rid for rid, *_ in runner.steps[-1]} == {"run"}
+    while eng.has_unfinished():
+        eng.step()
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_scenarios(seed):
+    """Random pools, budgets, arrivals and aborts: outputs equal the sequential ones, every step
+    keeps the invariants (checked inside the fake runner), nothing leaks."""
+    rng = random.Random(seed)
+    page = rng.choice([1, 2, 4, 8])
+    pages = rng.randrange(12, 40)
+    eng, runner = fake_engine(num_pages=pages, page_size=page, max_num_seqs=rng.randrange(1, 6),
+                              budget=rng.randrange(1, 24), watermark=rng.choice([0.0, 0.1]),
+                              prefix_caching=rng.random() < 0.7)
+    pending = []
+    for i in range(14):
+        stem = [7] * rng.randrange(0, 10)
+        pending.append((f"r{i}", stem + [rng.randrange(50) for _ in range(rng.randrange(1, 12))], rng.randrange(1, 10)))
+    live, aborted = {}, set()
+    steps = 0
+    while pending or eng.has_unfinished():
+        if pending and rng.random() < 0.5:
+            rid, p, mt = pending.pop()
+            req = eng.add_request(rid, p, SamplingParams(max_tokens=mt))
+            live[rid] = (req, p, mt)
+        if live and rng.random() < 0.05:
+            rid = rng.choice(sorted(live))
+            if eng.abort(rid):
+                aborted.add(rid)
+        eng.step()
+        steps += 1
+        assert steps < 5000, "the engine does not make progress"
+    for rid, (req, p, mt) in live.items():
+        if rid in aborted:
+            assert req.finish_reason is FinishReason.ABORTED
+        elif req.finish_reason is FinishReason.CAPACITY:
+            assert -(-(len(p) + mt) // page) > pages
+        else:
+            assert req.output_ids == sequential(p, mt)
+    eng.manager.check_invariants()
+    assert eng.manager.min_available_pages() == pages
