@@ -1,9 +1,9 @@
 """Chooses the attention kernels of a step.
 
-float32: the CUDA-core kernel for every token (true 32-bit).  bfloat16: tensor-core
-kernels where the head size has one — the split-key decode kernel for sequences that
-bring one token, the tiled prefill kernel for longer portions — and the CUDA-core
-kernel otherwise (windowed attention, head sizes that are no multiple of 16).
+float32: the CUDA-core kernel for every token (true 32-bit).  bfloat16: the tensor-core
+kernel where the head size is a multiple of 16 — launched once for the sequences that bring
+one token (keys split across CTAs when there are few sequences and long contexts) and once
+for the longer portions — and the CUDA-core kernel otherwise.
 """
 
 from __future__ import annotations
@@ -12,8 +12,36 @@ import torch
 
 from . import ops
 
+TARGET_CTAS = 148 * 4  # enough CTAs to fill the SMs a few times over
+MIN_TILES_PER_SPLIT = 4  # key tiles (of 64) a split should at least cover
+
+
+def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int) -> int:
+    """Key splits for single-token sequences: as many as fill the GPU, none shorter than
+    MIN_TILES_PER_SPLIT key tiles (the role of src/dli/model/paged_attention.py:63-74)."""
+    tiles = -(-max_kv_len // 64)
+    want = -(-TARGET_CTAS // max(1, num_seqs * ctas_per_seq))
+    return max(1, min(want, tiles // MIN_TILES_PER_SPLIT))
+
 
 def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_heads: int, scale: float, window: int | None) -> None:
     group = batch.group(cache.group)
-    ops.paged_attention_simt(out, qkv, cache.k, cache.v, group.block_tables, batch.seq_of_token, batch.positions,
-                             num_heads, scale, window)
+    _, nkv, _, d = cache.k.shape
+    if out.dtype != torch.bfloat16 or not ops.mma_head_dim_supported(d):
+        ops.paged_attention_simt(out, qkv, cache.k, cache.v, group.block_tables, batch.seq_of_token, batch.positions,
+                                 num_heads, scale, window)
+        return
+    singles, total = batch.num_single, batch.num_seqs
+    if singles:
+        per_kv_head = -(-(num_heads // nkv) // 64)
+        splits = batch.forced_splits or choose_splits(singles, nkv * per_kv_head, batch.max_kv_len_single)
+        scratch = None
+        if splits > 1:
+            rows = singles * num_heads
+            scratch = (torch.empty(rows * splits * d, dtype=torch.float32, device=out.device),
+                       torch.empty(rows * splits * 2, dtype=torch.float32, device=out.device))
+        ops.paged_attention_mma(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, 0, singles, 1, 0,
+                                num_heads, scale, window, splits, scratch)
+    if total > singles:
+        ops.paged_attention_mma(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, singles,
+                                total - singles, batch.max_q_len, singles, num_heads, scale, window)

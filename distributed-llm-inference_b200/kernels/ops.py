@@ -250,3 +250,69 @@ def sample(
         f(_ptr(out), _ptr(logits), logits.stride(0), rows, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(draw), _stream()),
         "sample",
     )
+
+
+def mma_head_dim_supported(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def paged_attention_mma(
+    out: torch.Tensor,
+    qkv: torch.Tensor,
+    k_pool: torch.Tensor,
+    v_pool: torch.Tensor,
+    block_tables: torch.Tensor,
+    q_start: torch.Tensor,
+    kv_len: torch.Tensor,
+    seq0: int,
+    num_seqs: int,
+    max_q_len: int,
+    first_row: int,
+    num_heads: int,
+    scale: float,
+    window: int | None = None,
+    splits: int = 1,
+    scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
+) -> None:
+    """bfloat16 tensor-core attention for the sequences [seq0, seq0 + num_seqs) of a batch.
+
+    Queries are the first nh * d columns of qkv; a sequence's tokens sit in rows
+    q_start[s] .. q_start[s + 1] at positions kv_len[s] - q_len .. kv_len[s] - 1.  With
+    ``splits`` > 1 (single-token sequences only) the keys are cut into that many runs;
+    ``scratch`` = (float32 [rows * splits * d], float32 [rows * splits * 2]) with
+    rows = (first_row + num_seqs) * nh holds the partial results.
+    """
+    for t, name in ((out, "out"), (qkv, "qkv"), (k_pool, "k_pool"), (v_pool, "v_pool")):
+        _need(t, name, torch.bfloat16)
+    _need(block_tables, "block_tables", torch.int32), _need(q_start, "q_start", torch.int32), _need(kv_len, "kv_len", torch.int32)
+    _, nkv, page_size, d = k_pool.shape
+    if not mma_head_dim_supported(d):
+        raise KernelError(f"paged_attention_mma: head_dim {d} is not a multiple of 16 in [16, 256]")
+    if out.shape[1] != num_heads * d or qkv.shape[0] != out.shape[0] or qkv.shape[1] < num_heads * d or num_heads % nkv:
+        raise KernelError("paged_attention_mma: shapes do not agree")
+    if seq0 + num_seqs > kv_len.numel() or q_start.numel() != kv_len.numel() + 1:
+        raise KernelError("paged_attention_mma: sequence range outside the batch")
+    acc = ml = None
+    if splits > 1:
+        if max_q_len != 1 or scratch is None:
+            raise KernelError("paged_attention_mma: split keys need single-token sequences and scratch")
+        acc, ml = scratch
+        _need(acc, "scratch[0]", torch.float32), _need(ml, "scratch[1]", torch.float32)
+        rows = (first_row + num_seqs) * num_heads
+        if acc.numel() < rows * splits * d or ml.numel() < rows * splits * 2:
+            raise KernelError("paged_attention_mma: scratch too small")
+    f = _fn(
+        "attention_mma.cu", "dli_paged_attention_mma",
+        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+        + [c_int] * 8 + [c_float, c_int, c_void_p, c_void_p, c_void_p],
+        {"HEAD_DIM": d},
+    )
+    _check(
+        f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1],
+          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, first_row, num_heads, nkv, page_size, int(window or 0),
+          scale, splits, _ptr(acc), _ptr(ml), _stream()),
+        "paged_attention_mma",
+    )
+    global launch_count
+    if splits > 1:
+        launch_count += 1  # the merge kernel

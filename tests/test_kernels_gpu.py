@@ -1,0 +1,330 @@
+"""Each CUDA kernel alone against a plain float64/float32 restatement, at sizes other than
+the engine's tiny and benchmark models; inputs are made so that a wrong key, a page edge or a
+window edge shows."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from dli_b200.kernels import ops
+from dli_b200.kernels.attention import choose_splits
+from tests.plain import llama_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ------------------------------------------------------------------ elementwise
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    table = rnd(300, 80, dtype=dtype)
+    ids = torch.tensor([0, 299, 7, 7, 150], dtype=torch.int32, device=DEV)
+    h = torch.empty(5, 80, dtype=torch.float32, device=DEV)
+    ops.embedding(h, table, ids)
+    assert torch.equal(h, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [80, 2064, 5000])
+def test_add_rmsnorm(dtype, H):
+    h = rnd(6, H, seed=1)
+    delta = rnd(6, H, dtype=dtype, seed=2)
+    w = 1 + 0.1 * rnd(H, seed=3)
+    eps = 3e-6
+    want_h = h.double() + delta.double()
+    want_y = plain.rms_norm(want_h.cpu().numpy(), w.double().cpu().numpy(), eps)
+    y = torch.empty(6, H, dtype=dtype, device=DEV)
+    h1 = h.clone()
+    ops.add_rmsnorm(y, h1, delta, w, eps)
+    np.testing.assert_allclose(h1.cpu().numpy(), want_h.float().cpu().numpy(), rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(y.float().cpu().numpy(), want_y, atol=tol(dtype, 4))
+    # without delta the stream is left alone
+    h2 = h.clone()
+    ops.add_rmsnorm(y, h2, None, w, eps)
+    assert torch.equal(h2, h)
+    np.testing.assert_allclose(y.float().cpu().numpy(), plain.rms_norm(h.double().cpu().numpy(), w.double().cpu().numpy(), eps), atol=tol(dtype, 4))
+    # selected rows: only those are read, nothing is written back
+    rows = torch.tensor([4, 0, 4], dtype=torch.int32, device=DEV)
+    y3 = torch.empty(3, H, dtype=dtype, device=DEV)
+    h3 = h.clone()
+    ops.add_rmsnorm(y3, h3, delta, w, eps, rows)
+    assert torch.equal(h3, h)
+    np.testing.assert_allclose(y3.float().cpu().numpy(), want_y[[4, 0, 4]], atol=tol(dtype, 4))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rot", [48, 32, 0])
+def test_rotary_store(dtype, rot):
+    nh, nkv, d, page, pages, n = 5, 1, 48, 8, 6, 7
+    qkv = rnd(n, (nh + 2 * nkv) * d, dtype=dtype, seed=4)
+    positions = torch.tensor([0, 1, 63, 64, 4095, 100000, 17], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([5, 8, 47, 0, 16, -1, 23], dtype=torch.int32, device=DEV)
+    kp = torch.full((pages, nkv, page, d), 9.0, dtype=dtype, device=DEV)
+    vp = torch.full((pages, nkv, page, d), 9.0, dtype=dtype, device=DEV)
+    inv = None
+    x = qkv.double().cpu().numpy().reshape(n, nh + 2 * nkv, d)
+    want = x.copy()
+    if rot:
+        c = {"head_dim": rot, "theta": 500000.0, "rope_type": "llama3", "factor": 8.0, "low": 1.0, "high": 4.0, "old_ctx": 64}
+        inv_np = plain.inverse_frequencies(c)
+        inv = torch.from_numpy(inv_np).to(DEV)
+        cos, sin = plain.rope_cos_sin(inv_np, positions.cpu().numpy())
+        heads = x[:, : nh + nkv, :rot].transpose(1, 0, 2)
+        want[:, : nh + nkv, :rot] = plain.apply_rope(heads, cos.astype(np.float64), sin.astype(np.float64)).transpose(1, 0, 2)
+    got = qkv.clone()
+    ops.rotary_store(got, positions, inv, slots, kp, vp, nh, nkv, d, rot, page)
+    g = got.double().cpu().numpy().reshape(n, nh + 2 * nkv, d)
+    np.testing.assert_allclose(g[:, :nh], want[:, :nh], atol=tol(dtype, 4))
+    np.testing.assert_array_equal(g[:, nh:], x[:, nh:])  # k and v columns of qkv are not touched
+    kflat = kp.double().cpu().numpy().transpose(0, 2, 1, 3).reshape(pages * page, nkv, d)
+    vflat = vp.double().cpu().numpy().transpose(0, 2, 1, 3).reshape(pages * page, nkv, d)
+    written = set()
+    for t, s in enumerate(slots.tolist()):
+        if s < 0:
+            continue
+        written.add(s)
+        np.testing.assert_allclose(kflat[s], want[t, nh : nh + nkv], atol=tol(dtype, 4))
+        np.testing.assert_array_equal(vflat[s], x[t, nh + nkv :])
+    untouched = [s for s in range(pages * page) if s not in written]
+    assert (kflat[untouched] == 9.0).all() and (vflat[untouched] == 9.0).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    gu = rnd(7, 400, dtype=dtype, seed=5, scale=3.0)
+    out = torch.empty(7, 200, dtype=dtype, device=DEV)
+    ops.silu_mul(out, gu)
+    g = gu.double().cpu().numpy()
+    np.testing.assert_allclose(out.float().cpu().numpy(), plain.silu(g[:, :200]) * g[:, 200:], atol=tol(dtype, 10))
+
+
+# ------------------------------------------------------------------ attention
+
+
+def attention_case(nh, nkv, d, page, seqs, dtype, seed=0, sharp=None):
+    """seqs: [(start, q_len)].  Builds pools with shuffled pages, tables whose unused entries
+    point at a poisoned page (NaN: a stray read shows without faulting), qkv rows, and the plain
+    result.  sharp = (seq, token, key): that query and key are scaled so the score stands out."""
+    rng = np.random.default_rng(seed)
+    kv_lens = [s + q for s, q in seqs]
+    blocks = [-(-k // page) for k in kv_lens]
+    pages = sum(blocks) + 1
+    poison = pages - 1
+    perm = rng.permutation(pages - 1)
+    tables = np.full((len(seqs), max(blocks) + 2), poison, dtype=np.int32)
+    at = 0
+    for i, b in enumerate(blocks):
+        tables[i, :b] = perm[at : at + b]
+        at += b
+    K = [rng.standard_normal((k, nkv, d)) for k in kv_lens]
+    V = [rng.standard_normal((k, nkv, d)) for k in kv_lens]
+    Q = [rng.standard_normal((q, nh, d)) for _, q in seqs]
+    if sharp is not None:
+        si, ti, ki = sharp
+        direction = rng.standard_normal(d)
+        direction /= np.linalg.norm(direction)
+        Q[si][ti] = direction * 6.0 * math.sqrt(math.sqrt(d))
+        K[si][ki] = direction * 6.0 * math.sqrt(math.sqrt(d))
+    tt = torch.float32 if dtype == torch.float32 else torch.bfloat16
+    cast = lambda a: torch.from_numpy(a).to(tt)
+    K, V, Q = [[cast(a) for a in L] for L in (K, V, Q)]
+    kp = torch.full((pages, nkv, page, d), float("nan"), dtype=tt)
+    vp = torch.full((pages, nkv, page, d), float("nan"), dtype=tt)
+    for i, klen in enumerate(kv_lens):
+        for pos in range(klen):
+            pg = tables[i, pos // page]
+            kp[pg, :, pos % page] = K[i][pos]
+            vp[pg, :, pos % page] = V[i][pos]
+    # rows of a half-used page beyond the sequence hold finite junk, as a reused page would
+    for i, klen in enumerate(kv_lens):
+        if klen % page:
+            pg = tables[i, klen // page]
+            kp[pg, :, klen % page :] = 1e4
+            vp[pg, :, klen % page :] = 1e4
+    n = sum(q for _, q in seqs)
+    qkv = torch.zeros(n, (nh + 2 * nkv) * d, dtype=tt)
+    qkv[:, : nh * d] = torch.cat([q.reshape(q.shape[0], nh * d) for q in Q])
+    q_start = np.cumsum([0] + [q for _, q in seqs]).astype(np.int32)
+    seq_of_token = np.concatenate([np.full(q, i, dtype=np.int32) for i, (_, q) in enumerate(seqs)])
+    positions = np.concatenate([np.arange(s, s + q, dtype=np.int32) for s, q in seqs])
+    dev = lambda a: (a if isinstance(a, torch.Tensor) else torch.from_numpy(a)).to(DEV).contiguous()
+    t = dict(qkv=dev(qkv), kp=dev(kp), vp=dev(vp), tables=dev(tables), q_start=dev(q_start), kv_len=dev(np.array(kv_lens, dtype=np.int32)),
+             seq_of_token=dev(seq_of_token), positions=dev(positions), n=n, Q=Q, K=K, V=V)
+    return t
+
+
+def plain_attention(t, seqs, nh, window):
+    outs = []
+    for i, (start, qlen) in enumerate(seqs):
+        klen = start + qlen
+        # run the whole sequence through the plain causal attention, keep the last q_len rows
+        qfull = np.zeros((nh, klen, t["Q"][i].shape[-1]))
+        qfull[:, start:] = t["Q"][i].double().numpy().transpose(1, 0, 2)
+        o = plain.causal_attention(qfull, t["K"][i].double().numpy().transpose(1, 0, 2), t["V"][i].double().numpy().transpose(1, 0, 2), window)
+        outs.append(o[:, start:].transpose(1, 0, 2).reshape(qlen, -1))
+    return np.concatenate(outs)
+
+
+SHAPES = [(4, 2, 16, 4), (3, 1, 32, 16), (5, 5, 48, 8), (8, 2, 64, 16), (6, 1, 128, 32), (2, 2, 256, 16), (7, 7, 80, 5)]
+MIX = [(0, 1), (199, 1), (63, 1), (0, 37), (40, 2), (64, 64), (3, 130), (255, 1), (16, 17)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,page", SHAPES)
+@pytest.mark.parametrize("window", [None, 70, 5])
+def test_paged_attention_simt(dtype, nh, nkv, d, page, window):
+    t = attention_case(nh, nkv, d, page, MIX, dtype, seed=nh)
+    out = torch.empty(t["n"], nh * d, dtype=dtype, device=DEV)
+    ops.paged_attention_simt(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["seq_of_token"], t["positions"], nh, d**-0.5, window)
+    want = plain_attention(t, MIX, nh, window)
+    np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(dtype, 2))
+
+
+def run_mma(t, seqs, nh, d, window, splits=1):
+    """Single-token sequences first (the engine's order is the caller's duty here)."""
+    singles = sum(1 for _, q in seqs if q == 1)
+    assert all(q == 1 for _, q in seqs[:singles]) and all(q > 1 for _, q in seqs[singles:])
+    out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    if singles:
+        scratch = None
+        if splits > 1:
+            scratch = (torch.full((singles * nh * splits * d,), float("nan"), device=DEV), torch.full((singles * nh * splits * 2,), float("nan"), device=DEV))
+        ops.paged_attention_mma(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, singles, 1, 0, nh, d**-0.5, window, splits, scratch)
+    if len(seqs) > singles:
+        ops.paged_attention_mma(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], singles, len(seqs) - singles,
+                                max(q for _, q in seqs), singles, nh, d**-0.5, window)
+    return out
+
+
+ORDERED = sorted(MIX, key=lambda sq: sq[1] != 1)
+
+
+@pytest.mark.parametrize("nh,nkv,d,page", [s for s in SHAPES if s[2] % 16 == 0] + [(128, 1, 32, 16), (70, 1, 16, 16)])
+@pytest.mark.parametrize("window", [None, 70, 5])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_paged_attention_mma(nh, nkv, d, page, window, splits):
+    t = attention_case(nh, nkv, d, page, ORDERED, torch.bfloat16, seed=nh + d)
+    out = run_mma(t, ORDERED, nh, d, window, splits)
+    want = plain_attention(t, ORDERED, nh, window)
+    np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2))
+
+
+def test_mma_rejects_other_head_sizes():
+    t = attention_case(2, 1, 24, 8, [(0, 4)], torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="multiple of 16"):
+        run_mma(t, [(0, 4)], 2, 24, None)
+
+
+@pytest.mark.parametrize("kernel", ["simt-f32", "simt-bf16", "mma"])
+@pytest.mark.parametrize("where", ["far_key", "page_first", "page_last", "tile_edge_63", "tile_edge_64", "window_inside", "window_outside", "self"])
+def test_one_key_stands_out(kernel, where):
+    """The query of one token matches one key so strongly that the output is that key's value.
+    The key sits where an indexing fault would hide among random data: far back among hundreds,
+    on both sides of a page edge and of a 64-key tile edge, and on both sides of a window edge."""
+    nh, nkv, d, page = 4, 2, 64, 16
+    start, qlen = 600, 40
+    token = 25
+    pos = start + token
+    window = None
+    key = {"far_key": 3, "page_first": 16 * 20, "page_last": 16 * 20 - 1, "tile_edge_63": 64 * 5 - 1, "tile_edge_64": 64 * 5, "self": pos}.get(where)
+    if where.startswith("window"):
+        window = 100
+        key = pos - window + 1 if where == "window_inside" else pos - window
+    dtype = torch.float32 if kernel == "simt-f32" else torch.bfloat16
+    seqs = [(12, 1), (start, qlen)]
+    t = attention_case(nh, nkv, d, page, seqs, dtype, seed=11, sharp=(1, token, key))
+    if kernel == "mma":
+        out = run_mma(t, seqs, nh, d, window)
+    else:
+        out = torch.empty(t["n"], nh * d, dtype=dtype, device=DEV)
+        ops.paged_attention_simt(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["seq_of_token"], t["positions"], nh, d**-0.5, window)
+    want = plain_attention(t, seqs, nh, window)
+    got = out.float().cpu().numpy()
+    np.testing.assert_allclose(got, want, atol=tol(dtype, 4))
+    row = got[1 + token].reshape(nh, d)
+    v = t["V"][1][key].float().numpy()  # [nkv, d]
+    if where == "window_outside":
+        assert np.abs(row[0] - v[0]).max() > 0.5  # the strong key is just outside: it must not be seen
+    else:
+        np.testing.assert_allclose(row[0], v[0], atol=0.05)  # every head points at it
+        np.testing.assert_allclose(row[3], v[1], atol=0.05)
+
+
+def test_choose_splits():
+    assert choose_splits(64, 8, 4096) == 2
+    assert choose_splits(1, 8, 4096) == 16
+    assert choose_splits(1, 8, 100) == 1
+    assert choose_splits(1000, 8, 100000) == 1
+
+
+# ------------------------------------------------------------------ sampling
+
+
+def test_greedy_takes_the_lowest_id_on_ties():
+    logits = torch.zeros(3, 1000, device=DEV)
+    logits[0, [17, 400, 999]] = 5.0
+    logits[1, 999] = 1.0
+    logits[2] = -float("inf")
+    logits[2, 3] = -1e30
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.sample(out, logits)
+    assert out.tolist() == [17, 999, 3]
+
+
+def sample_rows(logits, temps, ks, ps, seeds, draws):
+    n = logits.shape[0]
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    mk = lambda v, dt: torch.tensor(v, dtype=dt, device=DEV)
+    ops.sample(out, logits, mk(temps, torch.float32), mk(ks, torch.int32), mk(ps, torch.float32), mk(seeds, torch.int64), mk(draws, torch.int64))
+    return out.tolist()
+
+
+@pytest.mark.parametrize("V", [517, 5000])
+def test_sampling_equals_the_plain_sampler(V):
+    g = torch.Generator().manual_seed(V)
+    logits = (torch.randn(24, V, generator=g) * 2.5).to(DEV)
+    temps = [0.8, 1.0, 0.3, 2.0, 0.0, 1.3] * 4
+    ks = [-1, 50, -1, 7, -1, 1] * 4
+    ps = [1.0, 1.0, 0.9, 0.5, 1.0, 0.8] * 4
+    seeds = [1234 + 77 * i for i in range(24)]
+    draws = [i * 3 for i in range(24)]
+    got = sample_rows(logits, temps, ks, ps, seeds, draws)
+    host = logits.cpu().numpy()
+    want = [plain.sample_token(host[i], temps[i], ks[i], ps[i], seeds[i], draws[i]) for i in range(24)]
+    assert got == want
+
+
+def test_a_rows_draw_does_not_depend_on_its_neighbours():
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(8, 700, generator=g).to(DEV)
+    alone = sample_rows(logits[2:3].contiguous(), [0.9], [-1], [0.95], [42], [5])
+    busy = sample_rows(logits, [0.9] * 8, [-1] * 8, [0.95] * 8, [1, 2, 42, 4, 5, 6, 7, 8], [5] * 8)
+    assert busy[2] == alone[0]
+
+
+def test_sampled_frequencies_follow_the_distribution():
+    probs = np.array([0.5, 0.25, 0.125, 0.125])
+    logits = torch.tensor(np.log(probs), dtype=torch.float32, device=DEV).repeat(4000, 1)
+    toks = sample_rows(logits, [1.0] * 4000, [-1] * 4000, [1.0] * 4000, [9] * 4000, list(range(4000)))
+    freq = np.bincount(toks, minlength=4) / 4000
+    assert np.abs(freq - probs).max() < 0.03
+    # top_k = 2 renormalises over the two best; a tiny top_p leaves only the best
+    toks = sample_rows(logits, [1.0] * 4000, [2] * 4000, [1.0] * 4000, [9] * 4000, list(range(4000)))
+    freq = np.bincount(toks, minlength=4) / 4000
+    assert freq[2:].sum() == 0 and abs(freq[0] - 2 / 3) < 0.03
+    toks = sample_rows(logits[:50].contiguous(), [1.0] * 50, [-1] * 50, [0.01] * 50, [9] * 50, list(range(50)))
+    assert set(toks) == {0}
