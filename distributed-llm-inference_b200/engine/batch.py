@@ -44,6 +44,7 @@ class StepBatch:
     # host copies, for launch decisions only
     q_lens: list[int] = field(default_factory=list)
     starts: list[int] = field(default_factory=list)
+    state_slots: list[int] = field(default_factory=list)
     max_q_len: int = 0
     max_kv_len: int = 0
     max_kv_len_single: int = 0  # longest context among the single-token sequences
@@ -138,7 +139,7 @@ def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int) 
     batch = StepBatch(
         n=n, num_seqs=S, num_single=sum(1 for q in q_lens if q == 1), token_ids=b_tokens, positions=b_pos,
         seq_of_token=b_seq, q_start=b_qstart, kv_len=b_kvlen, state_slot=b_slot, logit_rows=b_rows, groups=views,
-        q_lens=q_lens, starts=starts, max_q_len=max(q_lens), max_kv_len=max(kv_len),
+        q_lens=q_lens, starts=starts, state_slots=state_slot, max_q_len=max(q_lens), max_kv_len=max(kv_len),
         max_kv_len_single=max((k for k, q in zip(kv_len, q_lens) if q == 1), default=0),
     )
     return batch, place
