@@ -132,7 +132,7 @@ def make_engine(model, batch, steps_total):
                                enable_prefix_caching=False, watermark=0.0)
 
 
-def decode_device_timed(model, batch, steps, warmup, sampler_clock=None):
+def decode_device_timed(model, batch, steps, warmup, sampler_clock=None, graphs=True):
     """K decode steps timed on the device: step function plus greedy sampling, token ids fed
     back from the host copy of the previous step's result."""
     import torch
@@ -142,7 +142,7 @@ def decode_device_timed(model, batch, steps, warmup, sampler_clock=None):
     from dli_b200.sampling import Sampler, SamplingParams
 
     runner = ModelRunner(model, num_pages=batch * (CONTEXT // PAGE) + 8, page_size=PAGE, max_requests=batch,
-                         enable_prefix_caching=False, watermark=0.0)
+                         enable_prefix_caching=False, watermark=0.0, cuda_graphs=graphs)
     sampler = Sampler(model.device)
     g = torch.Generator().manual_seed(1)
     vocab = model.spec.vocab_size
@@ -159,7 +159,7 @@ def decode_device_timed(model, batch, steps, warmup, sampler_clock=None):
         for b in range(batch):
             runner.manager.append_slots(b, [tokens[b]])
             entries.append(StepEntry(b, [tokens[b]], [0]))
-        return sampler.sample(runner.step(entries), params, [0] * batch, [0] * batch)
+        return sampler.sample(runner.step(entries, borrow=True), params, [0] * batch, [0] * batch)
 
     for _ in range(warmup):
         tokens = one_step(tokens)
@@ -252,6 +252,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=LLAMA_3_2_1B["num_hidden_layers"], help="fewer layers than the model has, if memory or time needs it")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the main batch size (for profiling runs)")
+    ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
+                    help="profiling runs: only the device-timed decode steps, or only the prefill step (prints a short line)")
+    ap.add_argument("--no-graphs", action="store_true", help="profiling runs: launch the decode step's kernels one by one")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -271,6 +274,13 @@ def main() -> int:
     pk = peaks()
     model = dli_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     clocks = ClockSampler()
+    if args.phase == "decode":
+        run = decode_device_timed(model, args.batch, args.steps, args.warmup, graphs=not args.no_graphs)
+        print(json.dumps({"phase": "decode", "batch": args.batch, "layers": args.layers, **run}))
+        return 0
+    if args.phase == "prefill":
+        print(json.dumps({"phase": "prefill", "layers": args.layers, **prefill_timed(model, cfg, args.layers, pk["bf16_tflops"], reps=args.steps)}))
+        return 0
     main_run = decode_device_timed(model, args.batch, args.steps, args.warmup, clocks)
     e2e = decode_end_to_end(model, args.batch, args.steps, args.warmup)
     prefill = prefill_timed(model, cfg, args.layers, pk["bf16_tflops"])

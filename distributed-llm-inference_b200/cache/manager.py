@@ -20,6 +20,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Hashable, Sequence
 
+import numpy as np
+
 from .page_pool import ROOT, OutOfPages, PagePool, chain_hashes, page_hash
 
 
@@ -87,6 +89,9 @@ class CacheManager:
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._requests: dict[Hashable, _Request] = {}
         self.stats = CacheStats()
+        # per group, a copy of every live request's block table as rows of one array (row =
+        # state slot), so a step's tables and slots are gathered with array operations
+        self._mirror = [np.full((max_requests, 16), -1, dtype=np.int32) for _ in groups]
 
     # ------------------------------------------------------------ queries
 
@@ -125,6 +130,20 @@ class CacheManager:
                 raise ValueError(f"position {p} lies in a page the window has given back")
             out.append(page * ps + p % ps)
         return out
+
+    def table_array(self, group: int) -> np.ndarray:
+        """[max_requests, width] int32: row ``state_slot`` holds that request's block table
+        (valid up to its number of blocks; -1 where a page was given back)."""
+        return self._mirror[group]
+
+    def _mirror_write(self, group: int, slot: int, first: int, pages: Sequence[int]) -> None:
+        m = self._mirror[group]
+        need = first + len(pages)
+        if need > m.shape[1]:
+            wider = np.full((m.shape[0], max(need, 2 * m.shape[1])), -1, dtype=np.int32)
+            wider[:, : m.shape[1]] = m
+            self._mirror[group] = m = wider
+        m[slot, first:need] = pages
 
     def min_available_pages(self) -> int:
         return min((p.available for p in self.pools), default=0)
@@ -189,6 +208,8 @@ class CacheManager:
             req.tail = list(token_ids[len(hashes) * self.page_size :])
             req.registered = n_hit
         self._requests[rid] = req
+        for g, table in enumerate(tables):
+            self._mirror_write(g, req.slot, 0, table)
         return Allocation(cached, req.slot)
 
     def append_slots(self, rid: Hashable, token_ids: Sequence[int]) -> None:
@@ -198,8 +219,11 @@ class CacheManager:
         need = sum(1 for p in range(req.num_tokens, req.num_tokens + len(token_ids)) if p % ps == 0)
         if any(need > pool.available for pool in self.pools):
             raise OutOfPages(f"append needs {need} pages")
-        for pool, table in zip(self.pools, req.tables):
-            table.extend(pool.take() for _ in range(need))
+        if need:
+            for g, (pool, table) in enumerate(zip(self.pools, req.tables)):
+                new = [pool.take() for _ in range(need)]
+                self._mirror_write(g, req.slot, len(table), new)
+                table.extend(new)
         req.num_tokens += len(token_ids)
         if self.prefix_caching:
             req.tail.extend(token_ids)
@@ -222,7 +246,7 @@ class CacheManager:
                 for pool, table in zip(self.pools, req.tables):
                     pool.register(table[i], req.hashes[i], req.hashes[i - 1] if i else None, table[i - 1] if i else None)
                 req.registered += 1
-        for group, pool, table in zip(self.groups, self.pools, req.tables):
+        for g, (group, pool, table) in enumerate(zip(self.groups, self.pools, req.tables)):
             if group.window is None:
                 continue
             # the next query sits at position >= num_computed and reads keys > position - window
@@ -231,6 +255,7 @@ class CacheManager:
                 if table[j] >= 0:
                     pool.release(table[j])
                     table[j] = -1
+                    self._mirror[g][req.slot, j] = -1
 
     def free(self, rid: Hashable) -> None:
         """Give back everything a finished, aborted or preempted request holds."""
@@ -268,4 +293,5 @@ class CacheManager:
                         w = self.groups[g].window
                         assert w is not None and (j + 1) * self.page_size - 1 <= req.num_computed - w, \
                             "a page still inside the window was given back"
+                assert self._mirror[g][req.slot, : len(table)].tolist() == table, "the table array differs from the table"
             pool.check(expected)

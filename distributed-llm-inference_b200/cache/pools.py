@@ -58,8 +58,10 @@ class CachePools:
                 owners[self.group_of_step[i]].append(i)
         self.k: list[torch.Tensor] = []
         self.v: list[torch.Tensor] = []
+        # one page more than the manager hands out: padding rows of a replayed graph live there
+        self.scratch_pages = list(pages_per_group)
         for need, pages, own in zip(self.group_needs, pages_per_group, owners):
-            shape = (len(own), pages, need.num_kv_heads, page_size, need.head_dim)
+            shape = (len(own), pages + 1, need.num_kv_heads, page_size, need.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
             self.v.append(torch.zeros(shape, dtype=dtype, device=device))
         self.layer_caches: list[LayerCache] = []

@@ -4,7 +4,8 @@ A step is a list of entries (request, its next tokens, the places whose logits
 are wanted).  All entries are flattened into one token vector; entries of a
 single token come first, longer portions after them (attention kernels launch
 once per kind), and ``logit_rows`` restores the caller's order.  Every integer
-array of a step travels to the device in one pinned copy.
+array of a step is laid out in one host array and travels to the device in one
+copy from pinned memory.
 """
 
 from __future__ import annotations
@@ -12,6 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Hashable, Sequence
 
+import numpy as np
 import torch
 
 
@@ -54,73 +56,127 @@ class StepBatch:
         return self.groups[index]
 
 
-def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int) -> tuple[StepBatch, list[int]]:
+class Uploader:
+    """Host-to-device copies of a step's integers through pinned memory.
+
+    Two pinned buffers alternate; before one is written again, the copy that last read it
+    has finished (an event is recorded after each copy)."""
+
+    def __init__(self, device: torch.device | str) -> None:
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self._bufs: list[torch.Tensor | None] = [None, None]
+        self._events: list[torch.cuda.Event | None] = [None, None]
+        self._turn = 0
+        self.bytes_last = 0
+
+    def stage(self, flat: np.ndarray) -> torch.Tensor:
+        """A pinned int32 tensor holding ``flat`` (a plain tensor without a CUDA device)."""
+        if not self.cuda:
+            return torch.from_numpy(flat)
+        i = self._turn
+        self._turn ^= 1
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        buf = self._bufs[i]
+        if buf is None or buf.numel() < flat.size:
+            buf = self._bufs[i] = torch.empty(max(4096, 2 * flat.size), dtype=torch.int32).pin_memory()
+        view = buf[: flat.size]
+        view.numpy()[:] = flat
+        self._pending = i
+        return view
+
+    def upload(self, flat: np.ndarray, out: torch.Tensor | None = None) -> torch.Tensor:
+        src = self.stage(flat)
+        self.bytes_last = flat.size * 4
+        if out is None:
+            out = torch.empty(flat.size, dtype=torch.int32, device=self.device)
+        out[: flat.size].copy_(src, non_blocking=True)
+        if self.cuda:
+            ev = self._events[self._pending] or torch.cuda.Event()
+            ev.record()
+            self._events[self._pending] = ev
+        return out
+
+
+def _check_entries(entries: Sequence[StepEntry], vocab_size: int) -> list[np.ndarray]:
+    if not entries:
+        raise ValueError("a step needs at least one entry")
+    seen = set()
+    arrays = []
+    for e in entries:
+        if e.request_id in seen:
+            raise ValueError(f"request {e.request_id!r} appears twice in one step")
+        seen.add(e.request_id)
+        a = np.asarray(e.token_ids, dtype=np.int64)
+        if a.ndim != 1 or a.size == 0:
+            raise ValueError(f"request {e.request_id!r} brings no tokens")
+        if a.min() < 0 or a.max() >= vocab_size:
+            bad = int(a[(a < 0) | (a >= vocab_size)][0])
+            raise ValueError(f"token id {bad} of request {e.request_id!r} is outside the vocabulary [0, {vocab_size})")
+        for w in e.want:
+            if not 0 <= w < a.size:
+                raise ValueError(f"want index {w} of request {e.request_id!r} is outside its {a.size} tokens")
+        arrays.append(a)
+    return arrays
+
+
+def gather_host(entries: Sequence[StepEntry], manager, vocab_size: int):
+    """The step's integer arrays on the host.  Returns a dict of int32 arrays and lists."""
+    arrays = _check_entries(entries, vocab_size)
+    order = sorted(range(len(entries)), key=lambda i: (arrays[i].size != 1, i))
+    place = [0] * len(entries)
+    for new, old in enumerate(order):
+        place[old] = new
+    S = len(order)
+    q_lens = np.empty(S, dtype=np.int64)
+    starts = np.empty(S, dtype=np.int64)
+    rows = np.empty(S, dtype=np.int64)
+    for s, old in enumerate(order):
+        rid = entries[old].request_id
+        q_lens[s] = arrays[old].size
+        starts[s] = manager.num_computed_tokens(rid)
+        rows[s] = manager.state_slot(rid)
+        if starts[s] + q_lens[s] > manager.num_tokens(rid):
+            raise ValueError(f"request {rid!r}: tokens up to {starts[s] + q_lens[s]} have no slots reserved")
+    q_start = np.zeros(S + 1, dtype=np.int64)
+    np.cumsum(q_lens, out=q_start[1:])
+    n = int(q_start[-1])
+    seq_of_token = np.repeat(np.arange(S), q_lens)
+    positions = np.arange(n) - q_start[seq_of_token] + starts[seq_of_token]
+    kv_len = starts + q_lens
+    ps = manager.page_size
+    width = int(-(-kv_len.max() // ps))
+    slots, tables = [], []
+    for g in range(len(manager.pools)):
+        table = manager.table_array(g)
+        pages = table[rows[seq_of_token], positions // ps].astype(np.int64)
+        if (pages < 0).any():
+            raise ValueError("a token's position lies in a page the window has given back")
+        slots.append(pages * ps + positions % ps)
+        tables.append(table[rows, :width])
+    logit_rows = [int(q_start[place[i]]) + w for i, e in enumerate(entries) for w in e.want]
+    return dict(
+        token_ids=np.concatenate([arrays[old] for old in order]), positions=positions, seq_of_token=seq_of_token,
+        q_start=q_start, kv_len=kv_len, state_slot=rows, logit_rows=np.asarray(logit_rows, dtype=np.int64),
+        slots=slots, tables=tables, q_lens=q_lens, starts=starts, n=n, S=S, width=width, place=place,
+    )
+
+
+def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int, uploader: Uploader | None = None) -> tuple[StepBatch, list[int]]:
     """Flatten ``entries`` against the cache manager's tables.
 
     Each request's tokens must already have slots (allocate / append_slots); its first token
     sits at the position the manager has computed up to.  Returns the batch and, for each
     entry in the caller's order, its index in the batch's sequence order.
     """
-    if not entries:
-        raise ValueError("a step needs at least one entry")
-    seen = set()
-    for e in entries:
-        if e.request_id in seen:
-            raise ValueError(f"request {e.request_id!r} appears twice in one step")
-        seen.add(e.request_id)
-        if len(e.token_ids) == 0:
-            raise ValueError(f"request {e.request_id!r} brings no tokens")
-        for t in e.token_ids:
-            if not 0 <= t < vocab_size:
-                raise ValueError(f"token id {t} of request {e.request_id!r} is outside the vocabulary [0, {vocab_size})")
-        for w in e.want:
-            if not 0 <= w < len(e.token_ids):
-                raise ValueError(f"want index {w} of request {e.request_id!r} is outside its {len(e.token_ids)} tokens")
-    order = sorted(range(len(entries)), key=lambda i: (len(entries[i].token_ids) != 1, i))
-    place = [0] * len(entries)
-    for new, old in enumerate(order):
-        place[old] = new
-
-    token_ids: list[int] = []
-    positions: list[int] = []
-    seq_of_token: list[int] = []
-    q_start = [0]
-    kv_len: list[int] = []
-    state_slot: list[int] = []
-    starts: list[int] = []
-    num_groups = len(manager.pools)
-    slots: list[list[int]] = [[] for _ in range(num_groups)]
-    tables: list[list[list[int]]] = [[] for _ in range(num_groups)]
-    for s, old in enumerate(order):
-        e = entries[old]
-        start = manager.num_computed_tokens(e.request_id)
-        end = start + len(e.token_ids)
-        if end > manager.num_tokens(e.request_id):
-            raise ValueError(f"request {e.request_id!r}: tokens up to {end} have no slots reserved")
-        token_ids.extend(e.token_ids)
-        positions.extend(range(start, end))
-        seq_of_token.extend([s] * len(e.token_ids))
-        q_start.append(len(token_ids))
-        kv_len.append(end)
-        starts.append(start)
-        state_slot.append(manager.state_slot(e.request_id))
-        for g in range(num_groups):
-            slots[g].extend(manager.slot_mapping(e.request_id, g, start, end))
-            tables[g].append(manager.block_table(e.request_id, g))
-    logit_rows = [q_start[place[i]] + w for i, e in enumerate(entries) for w in e.want]
-
-    n, S = len(token_ids), len(order)
-    widths = [max(1, max(len(t) for t in tables[g])) for g in range(num_groups)]
-    flat: list[int] = []
-    flat += token_ids + positions + seq_of_token + q_start + kv_len + state_slot + logit_rows
-    for g in range(num_groups):
-        flat += slots[g]
-        for t in tables[g]:
-            flat += t + [-1] * (widths[g] - len(t))
-    host = torch.tensor(flat, dtype=torch.int32)
-    if torch.device(device).type == "cuda":
-        host = host.pin_memory()
-    dev = host.to(device, non_blocking=True)
+    h = gather_host(entries, manager, vocab_size)
+    n, S, width = h["n"], h["S"], h["width"]
+    pieces = [h["token_ids"], h["positions"], h["seq_of_token"], h["q_start"], h["kv_len"], h["state_slot"], h["logit_rows"]]
+    for g in range(len(manager.pools)):
+        pieces += [h["slots"][g], h["tables"][g].reshape(-1)]
+    flat = np.concatenate([np.asarray(p).reshape(-1) for p in pieces]).astype(np.int32)
+    dev = (uploader or Uploader(device)).upload(flat)
     cut = 0
 
     def take(count: int) -> torch.Tensor:
@@ -130,16 +186,17 @@ def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int) 
         return out
 
     b_tokens, b_pos, b_seq = take(n), take(n), take(n)
-    b_qstart, b_kvlen, b_slot, b_rows = take(S + 1), take(S), take(S), take(len(logit_rows))
+    b_qstart, b_kvlen, b_slot, b_rows = take(S + 1), take(S), take(S), take(h["logit_rows"].size)
     views = []
-    for g in range(num_groups):
+    for g in range(len(manager.pools)):
         gs = take(n)
-        views.append(GroupView(take(S * widths[g]).view(S, widths[g]), gs))
-    q_lens = [q_start[i + 1] - q_start[i] for i in range(S)]
+        views.append(GroupView(take(S * width).view(S, width), gs))
+    q_lens = h["q_lens"].tolist()
+    kv = h["kv_len"].tolist()
     batch = StepBatch(
         n=n, num_seqs=S, num_single=sum(1 for q in q_lens if q == 1), token_ids=b_tokens, positions=b_pos,
         seq_of_token=b_seq, q_start=b_qstart, kv_len=b_kvlen, state_slot=b_slot, logit_rows=b_rows, groups=views,
-        q_lens=q_lens, starts=starts, state_slots=state_slot, max_q_len=max(q_lens), max_kv_len=max(kv_len),
-        max_kv_len_single=max((k for k, q in zip(kv_len, q_lens) if q == 1), default=0),
+        q_lens=q_lens, starts=h["starts"].tolist(), state_slots=h["state_slot"].tolist(), max_q_len=max(q_lens), max_kv_len=max(kv),
+        max_kv_len_single=max((k for k, q in zip(kv, q_lens) if q == 1), default=0),
     )
-    return batch, place
+    return batch, h["place"]

@@ -11,6 +11,7 @@ from __future__ import annotations
 from pathlib import Path
 from typing import Any, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, CachePools, GroupSpec
@@ -18,7 +19,8 @@ from ..cache.needs import PagedKVNeed, StateNeed
 from ..config.registry import load_config, resolve_architecture
 from ..parts import DecoderModel
 from ..weights import load_tensors, random_tensors
-from .batch import StepEntry, build_batch
+from .batch import StepEntry, Uploader, build_batch, gather_host
+from .graphs import DecodeGraphs
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -70,7 +72,7 @@ class ModelRunner:
     """A model with its cache pools and cache manager."""
 
     def __init__(self, model: DecoderModel, *, num_pages: int | Sequence[int], page_size: int = 16, max_requests: int = 64,
-                 enable_prefix_caching: bool = True, watermark: float = 0.01) -> None:
+                 enable_prefix_caching: bool = True, watermark: float = 0.01, cuda_graphs: bool = True) -> None:
         self.model = model
         needs = model.cache_needs()
         order = model.spec.run_order
@@ -83,6 +85,10 @@ class ModelRunner:
             has_state=any(isinstance(n, StateNeed) for n in needs), watermark=watermark,
         )
         self.page_size = page_size
+        self.uploader = Uploader(model.device)
+        # graphs replay padding rows through every mixer: not with per-request state, which they would touch
+        self.graphs = DecodeGraphs(model, self.pools, page_size) if cuda_graphs and not self.pools.has_state else None
+        self.graph_steps = 0
 
     @staticmethod
     def pages_for_budget(model: DecoderModel, budget_bytes: float, page_size: int) -> int:
@@ -96,14 +102,35 @@ class ModelRunner:
             self.pools.reset_state(slot)
 
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
         """Logits [wanted, vocab] float32 on the device, in the order of ``entries`` and of
-        each entry's ``want``.  Afterwards every entry's tokens count as computed."""
-        batch, _ = build_batch(entries, self.manager, self.model.device, self.model.spec.vocab_size)
-        logits = self.model.forward(batch, self.pools.layer_caches)
+        each entry's ``want``.  Afterwards every entry's tokens count as computed.
+        With ``borrow`` the result may be a view of a buffer the next step overwrites."""
+        logits = None
+        if self.graphs is not None and all(len(e.token_ids) == 1 for e in entries):
+            logits = self._replay_decode(entries)
+            if logits is not None and not borrow:
+                logits = logits.clone()
+        if logits is None:
+            batch, _ = build_batch(entries, self.manager, self.model.device, self.model.spec.vocab_size, self.uploader)
+            logits = self.model.forward(batch, self.pools.layer_caches)
         for e in entries:
             self.manager.mark_computed(e.request_id, self.manager.num_computed_tokens(e.request_id) + len(e.token_ids))
         return logits
+
+    def _replay_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+        """A step of single tokens through a captured graph; None if no graph takes its shape."""
+        h = gather_host(entries, self.manager, self.model.spec.vocab_size)
+        graph = self.graphs.lookup(h["S"], h["width"], int(h["kv_len"].max()))
+        if graph is None:
+            return None
+        self.uploader.upload(graph.fill(h), out=graph.ints)
+        logits = graph.replay()
+        self.graph_steps += 1
+        rows = h["logit_rows"]
+        if rows.size == h["S"] and (rows == np.arange(h["S"])).all():
+            return logits[: h["S"]]
+        return logits[torch.from_numpy(rows).to(logits.device)]
 
     def execute(self, chunks) -> torch.Tensor:
         """The engine's view of ``step``: one entry per scheduled chunk, logits at the last
@@ -112,4 +139,4 @@ class ModelRunner:
         for ch in chunks:
             tokens = ch.request.all_token_ids[ch.start : ch.start + ch.num_tokens]
             entries.append(StepEntry(ch.request.request_id, tokens, [ch.num_tokens - 1] if ch.needs_logits else []))
-        return self.step(entries)
+        return self.step(entries, borrow=True)
