@@ -15,8 +15,27 @@ __global__ void embedding_kernel(float* __restrict__ h, const T* __restrict__ ta
   for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]);
 }
 
+// bfloat16 rows of H % 8 == 0: 16-byte loads, two float4 stores per thread
+__global__ void embedding_bf16_vec_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ table,
+                                          const int* __restrict__ ids, int H) {
+  const int t = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)ids[t] * H);
+  float4* dst = reinterpret_cast<float4*>(h + (size_t)t * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    const uint4 v = src[i];
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+    const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]), c = __bfloat1622float2(p[2]), d = __bfloat1622float2(p[3]);
+    dst[2 * i] = make_float4(a.x, a.y, b.x, b.y);
+    dst[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+  }
+}
+
 DLI_EXPORT int dli_embedding(float* h, const void* table, const int* ids, int n, int H, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
+  if (dtype == DLI_BF16 && H % 8 == 0) {
+    embedding_bf16_vec_kernel<<<n, H >= 2048 ? 256 : 64, 0, stream>>>(h, (const __nv_bfloat16*)table, ids, H);
+    return (int)cudaGetLastError();
+  }
   const int threads = H >= 1024 ? 256 : 128;
   if (dtype == DLI_F32)
     embedding_kernel<float><<<n, threads, 0, stream>>>(h, (const float*)table, ids, H);
@@ -74,9 +93,94 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ h, con
   }
 }
 
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* q = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(q[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) q[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// The same for H % 8 == 0 and H <= 8 * THREADS * CHUNKS: each thread owns CHUNKS runs of 8
+// columns, read and written 16 or 32 bytes at a time, and keeps them in registers between the
+// sum of squares and the scaling.  The order of the additions is fixed by H and THREADS.
+template <typename T, int THREADS, int CHUNKS>
+__global__ void __launch_bounds__(THREADS) add_rmsnorm_vec_kernel(T* __restrict__ y, float* __restrict__ h,
+                                                                  const T* __restrict__ delta, const float* __restrict__ w,
+                                                                  const int* __restrict__ rows, int H, float eps) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int s = rows ? rows[r] : r;
+  float* hrow = h + (size_t)s * H;
+  const T* drow = delta ? delta + (size_t)s * H : nullptr;
+  float v[CHUNKS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (threadIdx.x + c * THREADS) * 8;
+    if (col < H) {
+      load8(hrow + col, v[c]);
+      if (drow) {
+        float d[8];
+        load8(drow + col, d);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[c][k] += d[k];
+        if (!rows) store8(hrow + col, v[c]);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += v[c][k] * v[c][k];
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  T* yrow = y + (size_t)r * H;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (threadIdx.x + c * THREADS) * 8;
+    if (col < H) {
+      float wv[8], o[8];
+      load8(w + col, wv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = v[c][k] * inv * wv[k];
+      store8(yrow + col, o);
+    }
+  }
+}
+
+template <typename T>
+static int launch_add_rmsnorm_vec(void* y, float* h, const void* delta, const float* w, const int* rows, int n_rows, int H,
+                                  float eps, cudaStream_t stream) {
+  if (H <= 8 * 128 * 1)
+    add_rmsnorm_vec_kernel<T, 128, 1><<<n_rows, 128, 0, stream>>>((T*)y, h, (const T*)delta, w, rows, H, eps);
+  else if (H <= 8 * 256 * 1)
+    add_rmsnorm_vec_kernel<T, 256, 1><<<n_rows, 256, 0, stream>>>((T*)y, h, (const T*)delta, w, rows, H, eps);
+  else if (H <= 8 * 256 * 2)
+    add_rmsnorm_vec_kernel<T, 256, 2><<<n_rows, 256, 0, stream>>>((T*)y, h, (const T*)delta, w, rows, H, eps);
+  else
+    add_rmsnorm_vec_kernel<T, 512, 4><<<n_rows, 512, 0, stream>>>((T*)y, h, (const T*)delta, w, rows, H, eps);
+  return (int)cudaGetLastError();
+}
+
 DLI_EXPORT int dli_add_rmsnorm(void* y, float* h, const void* delta, const float* w, const int* rows, int n_rows, int H,
                                float eps, int dtype, cudaStream_t stream) {
   if (n_rows == 0) return 0;
+  if (H % 8 == 0 && H <= 8 * 512 * 4) {
+    return dtype == DLI_F32 ? launch_add_rmsnorm_vec<float>(y, h, delta, w, rows, n_rows, H, eps, stream)
+                            : launch_add_rmsnorm_vec<__nv_bfloat16>(y, h, delta, w, rows, n_rows, H, eps, stream);
+  }
   constexpr int THREADS = 256, PER = 16;  // 4096 columns in registers, more are streamed
   if (dtype == DLI_F32)
     add_rmsnorm_kernel<float, THREADS, PER><<<n_rows, THREADS, 0, stream>>>((float*)y, h, (const float*)delta, w, rows, H, eps);
@@ -96,11 +200,14 @@ template <typename T>
 __global__ void rotary_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                     const int* __restrict__ slots, T* __restrict__ k_pool, T* __restrict__ v_pool, int nh,
                                     int nkv, int d, int rot, int page_size, int write_kv) {
+  extern __shared__ float trig[];  // cos[half], sin[half] of this token's angles
   const int t = blockIdx.x;
   const int half = rot >> 1;
   const int row = (nh + 2 * nkv) * d;
   T* base = qkv + (size_t)t * row;
   const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &trig[half + i], &trig[i]);
+  __syncthreads();
   const int slot = slots ? slots[t] : -1;
   const bool store = write_kv && slot >= 0;
   const int page = store ? slot / page_size : 0, off = store ? slot % page_size : 0;
@@ -109,8 +216,7 @@ __global__ void rotary_store_kernel(T* __restrict__ qkv, const int* __restrict__
   const int rot_items = (nh + nkv) * half;
   for (int idx = threadIdx.x; idx < rot_items; idx += blockDim.x) {
     const int head = idx / half, i = idx - head * half;
-    float sn, cs;
-    sincosf(pos * inv_freq[i], &sn, &cs);
+    const float cs = trig[i], sn = trig[half + i];
     T* x = base + (size_t)head * d;
     const float a = to_float(x[i]), b = to_float(x[i + half]);
     const T ra = from_float<T>(a * cs - b * sn);
@@ -144,11 +250,12 @@ DLI_EXPORT int dli_rotary_store(void* qkv, const int* positions, const float* in
   if (rot < 0 || rot > d || (rot & 1)) return DLI_ERR_UNSUPPORTED;
   if (rot > 0 && inv_freq == nullptr) return DLI_ERR_UNSUPPORTED;
   const int threads = 256;
+  const size_t smem = (size_t)rot * sizeof(float);
   if (dtype == DLI_F32)
-    rotary_store_kernel<float><<<n, threads, 0, stream>>>((float*)qkv, positions, inv_freq, slots, (float*)k_pool,
+    rotary_store_kernel<float><<<n, threads, smem, stream>>>((float*)qkv, positions, inv_freq, slots, (float*)k_pool,
                                                           (float*)v_pool, nh, nkv, d, rot, page_size, write_kv);
   else
-    rotary_store_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, inv_freq, slots,
+    rotary_store_kernel<__nv_bfloat16><<<n, threads, smem, stream>>>((__nv_bfloat16*)qkv, positions, inv_freq, slots,
                                                                   (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh, nkv, d,
                                                                   rot, page_size, write_kv);
   return (int)cudaGetLastError();
@@ -168,8 +275,32 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
   }
 }
 
+// bfloat16, I % 8 == 0: one 16-byte load of gate and of up, one 16-byte store, per thread
+__global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I) {
+  const int t = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= I / 8) return;
+  const uint4 g = reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * I)[i];
+  const uint4 u = reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * I + I)[i];
+  const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+  const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+  uint4 r;
+  __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 a = __bfloat1622float2(gp[k]), b = __bfloat1622float2(up[k]);
+    rp[k] = __floats2bfloat162_rn(a.x / (1.f + expf(-a.x)) * b.x, a.y / (1.f + expf(-a.y)) * b.y);
+  }
+  reinterpret_cast<uint4*>(out + (size_t)t * I)[i] = r;
+}
+
 DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
+  if (dtype == DLI_BF16 && I % 8 == 0 && n <= 65535) {
+    dim3 grid((I / 8 + 255) / 256, n);
+    silu_mul_bf16_vec_kernel<<<grid, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I);
+    return (int)cudaGetLastError();
+  }
   const size_t total = (size_t)n * I;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
