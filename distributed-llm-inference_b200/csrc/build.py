@@ -104,7 +104,7 @@ def compile_library(source: str, defines: dict[str, object] | None = None, extra
 
 
 def load_library(source: str, defines: dict[str, object] | None = None, extra: list[str] | None = None) -> ctypes.CDLL:
-    key = str(library_path(source, defines))
+    key = f"{source}|{sorted((defines or {}).items())}"  # sources are hashed once per process, not per call
     with _lock:
         lib = _loaded.get(key)
     if lib is not None:

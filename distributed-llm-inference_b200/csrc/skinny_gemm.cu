@@ -1,0 +1,286 @@
+// out[s, t, f] = sum over the s-th slice of K of x[t, k] * W[f, k]      (bfloat16 in, float32 out)
+//
+// The matrix product of the decode step: a few tokens (t < 256) against a large weight matrix
+// that is read once from HBM.  Weights take the 128-row side of the tensor-core instruction
+// (features are the MMA's M, tokens its N), so a tile of 128 features x 64 k is one
+// tcgen05.mma group whatever the number of tokens:
+//
+//   * TMA (cp.async.bulk.tensor, 128-byte swizzle) brings a [128 x 64] weight tile and the
+//     [tokens x 64] activation tile of the same k range into shared memory, several stages ahead;
+//     rows or columns beyond the matrices are filled with zeros by the copy itself;
+//   * one thread issues tcgen05.mma (M = 128, N = tokens rounded up to 16, K = 16, four per
+//     stage) into an accumulator in tensor memory; tcgen05.commit frees the stage and, at the
+//     end, signals the epilogue;
+//   * four warps read the accumulator with tcgen05.ld (lane = feature, column = token) and
+//     store float32, coalesced along features.
+//
+// The grid is (feature tiles, K slices).  Slices exist to fill the GPU when a matrix has few
+// feature tiles; each writes its own slab out[s], and the consumer (norm, rotary, activation
+// kernels) adds the slabs in a fixed order, so the result does not depend on timing.
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel records an error
+// code in *error_flag, stops issuing work, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+using namespace dli;
+
+namespace {
+
+constexpr int BM = 128;       // features per CTA
+constexpr int BK = 64;        // k per stage: 128 bytes of bfloat16, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr unsigned WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// true when the phase with this parity has completed; false after WAIT_LIMIT polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
+// 128-byte mode: start address, 1024 bytes between groups of eight rows, layout code 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // bits 0-13: start address / 16
+  d |= (uint64_t)0 << 16;                           // bits 16-29: leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                 // bits 32-45: stride byte offset / 16
+  d |= (uint64_t)1 << 46;                           // bits 46-47: descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                           // bits 61-63: 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor of kind::f16: float32 accumulator, bfloat16 A and B, both K-major.
+__device__ __forceinline__ uint32_t instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                          const __grid_constant__ CUtensorMap map_x, float* __restrict__ out,
+                                                          int tokens, int features, int k_tiles, int tiles_per_slice, int npad,
+                                                          int stages, int tmem_cols, int* error_flag) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int b_bytes = npad * BK * 2;
+  const int stage_bytes = A_BYTES + b_bytes;
+  uint64_t* bars = (uint64_t*)(smem + (size_t)stages * stage_bytes);  // full[stages], empty[stages], accum
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * stages + 1);
+  volatile int* failed = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + stages), accum = smem_u32(bars + 2 * stages);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(accum, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  const int tile = blockIdx.x, slice = blockIdx.y;
+  const int kt0 = slice * tiles_per_slice;
+  const int nkt = max(0, min(k_tiles, kt0 + tiles_per_slice) - kt0);
+
+  // The other lanes of the two role warps park at __syncwarp: if they polled the accumulator
+  // barrier meanwhile, their warp would alternate between the poll and the role loop.
+  if (warp == 0) {
+    // ---- producer: TMA loads, `stages` ahead of the MMAs
+    if (lane == 0)
+    for (int i = 0; i < nkt; ++i) {
+      const int s = i % stages;
+      if (i >= stages && !mbar_wait(empty0 + 8 * s, ((i / stages) - 1) & 1)) {
+        *failed = 1;
+        atomicExch(error_flag, 1);
+        break;
+      }
+      if (*failed) break;
+      const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
+      mbar_expect_tx(full0 + 8 * s, (uint32_t)stage_bytes);
+      tma_load_2d(a, &map_w, (kt0 + i) * BK, tile * BM, full0 + 8 * s);
+      tma_load_2d(a + A_BYTES, &map_x, (kt0 + i) * BK, 0, full0 + 8 * s);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    const uint32_t idesc = instr_desc(BM, npad);
+    if (lane == 0) {
+    for (int i = 0; i < nkt; ++i) {
+      const int s = i % stages;
+      if (!mbar_wait(full0 + 8 * s, (i / stages) & 1)) {
+        *failed = 2;
+        atomicExch(error_flag, 2);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k)
+        umma(tmem, smem_desc_sw128(a + k * UMMA_K * 2), smem_desc_sw128(a + A_BYTES + k * UMMA_K * 2), idesc, (i | k) != 0);
+      umma_commit(empty0 + 8 * s);  // arrives once these MMAs have read the stage
+    }
+    umma_commit(accum);  // arrives once every MMA issued so far has finished
+    }
+    __syncwarp();
+  }
+
+  // ---- epilogue: all four warps; lane = feature row of the tile, column = token
+  bool ok = true;
+  if (nkt > 0) {
+    ok = mbar_wait(accum, 0);
+    if (!ok) atomicExch(error_flag, 3);
+  }
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  ok = ok && !*failed;
+  const int f = tile * BM + warp * 32 + lane;
+  float* dst = out + (size_t)slice * tokens * features + f;
+  for (int c = 0; c < npad && c < ((tokens + 7) & ~7); c += 8) {
+    uint32_t r[8];
+    if (nkt > 0 && ok) {
+      const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c;
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                   : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) r[j] = 0u;
+    }
+    if (f < features) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (c + j < tokens) dst[(size_t)(c + j) * features] = __uint_as_float(r[j]);
+    }
+  }
+
+  // ---- teardown: nobody touches tensor memory after this barrier; warp 0 frees it
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)p;
+  }
+  return fn;
+}
+
+// [rows, K] bfloat16 row-major, boxes of [box_rows x 64 k], 128-byte swizzle, zeros outside
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+  EncodeTiled fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int* error_flag_device = nullptr;  // mapped pinned host memory: the host reads it without a copy
+int* error_flag_host = nullptr;
+
+}  // namespace
+
+// Number of K slices this launch uses for the given sizes: enough CTAs to fill the GPU, no
+// slice shorter than four k-tiles.  The caller sizes `out` as [slices, tokens, features].
+DLI_EXPORT int dli_skinny_gemm_slices(int features, int K) {
+  const int tiles = (features + BM - 1) / BM;
+  const int k_tiles = (K + BK - 1) / BK;
+  int want = (148 * 2 + tiles - 1) / tiles;
+  int most = k_tiles / 4;
+  if (most < 1) most = 1;
+  int slices = want < most ? want : most;
+  if (slices < 1) slices = 1;
+  const int per = (k_tiles + slices - 1) / slices;
+  return (k_tiles + per - 1) / per;  // no empty slice
+}
+
+DLI_EXPORT int dli_skinny_gemm(float* out, const void* x, const void* w, int tokens, int features, int K, int slices,
+                               cudaStream_t stream) {
+  if (tokens < 1 || tokens > 256 || features < 1 || K < 8 || K % 8 || slices < 1) return DLI_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return DLI_ERR_UNSUPPORTED;
+  if (!error_flag_host) {
+    if (cudaHostAlloc((void**)&error_flag_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return (int)cudaGetLastError();
+    *error_flag_host = 0;
+    if (cudaHostGetDevicePointer((void**)&error_flag_device, error_flag_host, 0) != cudaSuccess) return (int)cudaGetLastError();
+  }
+  const int npad = (tokens + 15) & ~15;
+  CUtensorMap map_w, map_x;
+  if (!make_map(&map_w, w, features, K, BM) || !make_map(&map_x, x, tokens, K, npad)) return DLI_ERR_UNSUPPORTED;
+  const int k_tiles = (K + BK - 1) / BK;
+  const int per = (k_tiles + slices - 1) / slices;
+  const int stage_bytes = A_BYTES + npad * BK * 2;
+  int stages = per < 6 ? per : 6;
+  while (stages > 2 && stages * stage_bytes > 72 * 1024) --stages;  // leave room for three CTAs per SM
+  if (stages < 1) stages = 1;
+  const int smem = stages * stage_bytes + (2 * stages + 1) * 8 + 16 + 1024;
+  int tmem_cols = 32;
+  while (tmem_cols < npad) tmem_cols <<= 1;
+  static int configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  dim3 grid((features + BM - 1) / BM, slices);
+  skinny_gemm_kernel<<<grid, 128, smem, stream>>>(map_w, map_x, out, tokens, features, k_tiles, per, npad, stages, tmem_cols, error_flag_device);
+  return (int)cudaGetLastError();
+}
+
+// 0, or the code of the first wait that ran out (1 producer, 2 MMA issuer, 3 epilogue)
+DLI_EXPORT int dli_skinny_gemm_error() { return error_flag_host ? *error_flag_host : 0; }

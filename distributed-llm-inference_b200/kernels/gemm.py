@@ -16,6 +16,22 @@ torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 
 
+# Up to this many tokens a bfloat16 product is bound by reading the weights once and goes to the
+# engine's own tcgen05 kernel; beyond it the library's large-tile kernels are the better choice.
+SKINNY_MAX_TOKENS = 64
+
+
+def project(x: torch.Tensor, weight: torch.Tensor, slices: int | None = None) -> torch.Tensor:
+    """y = x W^T for a step's tokens.  Returns either y [n, out] in x's dtype, or — for few
+    bfloat16 tokens — float32 slabs [slices, n, out] whose sum is y, which the engine's norm,
+    rotary and activation kernels add up as they read."""
+    from . import ops
+
+    if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_TOKENS and ops.skinny_gemm_supported(x.shape[0], x.shape[1]):
+        return ops.skinny_gemm(x, weight, slices)
+    return linear(x, weight)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """x [n, in] times weight [out, in] transposed; float32 accumulation in both dtypes."""
     if not x.is_cuda:

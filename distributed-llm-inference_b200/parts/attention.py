@@ -6,7 +6,7 @@ import torch
 
 from ..cache.needs import PagedKVNeed
 from ..kernels import attention as attn_kernels
-from ..kernels.gemm import linear
+from ..kernels.gemm import project
 from ..weights.loader import TensorDecl
 from .base import Part, build_part, register_part
 
@@ -56,8 +56,8 @@ class GQAttention(Part):
         return PagedKVNeed(self.nkv, self.d, self.window)
 
     def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
-        qkv = linear(x, self.wqkv)
-        self.position.rotate_and_store(qkv, batch, cache, self.nh, self.nkv, cache.writes)
+        qkv = project(x, self.wqkv)
+        q = self.position.rotate_and_store(qkv, batch, cache, self.nh, self.nkv, cache.writes)
         out = torch.empty((x.shape[0], self.nh * self.d), dtype=x.dtype, device=x.device)
-        attn_kernels.paged_attention(out, qkv, cache, batch, self.nh, self.scale, self.window)
-        return linear(out, self.wo)
+        attn_kernels.paged_attention(out, q, cache, batch, self.nh, self.scale, self.window)
+        return project(out, self.wo)

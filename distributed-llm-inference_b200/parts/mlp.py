@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from ..kernels.gemm import linear
+from ..kernels.gemm import project
 from ..weights.loader import TensorDecl
 from .base import Part, register_part
 
@@ -37,7 +37,7 @@ class SwiGLU(Part):
         self.w_down = tensors[px + "down_proj.weight"]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gate_up = linear(x, self.w_gate_up)
+        gate_up = project(x, self.w_gate_up)
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         ops.silu_mul(act, gate_up)
-        return linear(act, self.w_down)
+        return project(act, self.w_down)

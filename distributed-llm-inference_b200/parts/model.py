@@ -6,7 +6,7 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..kernels.gemm import linear
+from ..kernels.gemm import linear, project
 from ..weights.loader import TensorDecl
 from .base import BuildEnv, Part, ResidualStream, build_part, register_part
 
@@ -52,7 +52,8 @@ class LMHead(Part):
         self.weight = tensors[self.tied_to or self.spec.prefix + "weight"]
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
-        return linear(y, self.weight).float()
+        logits = project(y, self.weight, slices=1)
+        return logits[0] if logits.dim() == 3 else logits.float()
 
 
 def _walk(part) -> list[Part]:

@@ -33,6 +33,22 @@ def inverse_frequencies(params) -> torch.Tensor:
     return torch.where(medium, smoothed, scaled)
 
 
+def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq):
+    """Runs the fused kernel and returns the tensor whose leading num_heads * head_dim columns
+    are the encoded queries: qkv itself (rotated in place), or a new tensor when qkv came as
+    float32 slabs."""
+    group = batch.group(cache.group)
+    args = (batch.positions, inv_freq, group.slots if write_kv else None, cache.k if write_kv else None,
+            cache.v if write_kv else None, num_heads, num_kv_heads, head_dim, rotary_dim, cache.page_size, write_kv)
+    if qkv.dim() == 3:
+        q = torch.empty((qkv.shape[1], num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+        ops.rotary_store_slabs(q, qkv, *args)
+        return q
+    if rotary_dim or write_kv:
+        ops.rotary_store(qkv, *args)
+    return qkv
+
+
 @register_part("position", "rotary")
 class Rotary(Part):
     """params: head_dim, rotary_dim (<= head_dim; elements beyond it pass through), theta,
@@ -47,13 +63,8 @@ class Rotary(Part):
             raise ValueError(f"rotary_dim={self.rotary_dim} must be even and at most head_dim={self.head_dim}")
         self.inv_freq = inverse_frequencies(spec.params).to(env.device) if self.rotary_dim else None
 
-    def rotate_and_store(self, qkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool) -> None:
-        group = batch.group(cache.group)
-        ops.rotary_store(
-            qkv, batch.positions, self.inv_freq, group.slots if write_kv else None,
-            cache.k if write_kv else None, cache.v if write_kv else None,
-            num_heads, num_kv_heads, self.head_dim, self.rotary_dim, cache.page_size, write_kv,
-        )
+    def rotate_and_store(self, qkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
+        return _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, self.rotary_dim, self.inv_freq)
 
 
 @register_part("position", "none")
@@ -64,9 +75,5 @@ class NoPosition(Part):
         super().__init__(spec, env)
         self.head_dim = int(spec.params["head_dim"])
 
-    def rotate_and_store(self, qkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool) -> None:
-        if not write_kv:
-            return
-        group = batch.group(cache.group)
-        ops.rotary_store(qkv, batch.positions, None, group.slots, cache.k, cache.v, num_heads, num_kv_heads,
-                         self.head_dim, 0, cache.page_size, True)
+    def rotate_and_store(self, qkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
+        return _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, 0, None)
