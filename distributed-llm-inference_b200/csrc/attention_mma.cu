@@ -83,6 +83,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Params p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sQ = smem;
   unsigned char* sK = smem + BLOCK_M * ROW_BYTES;
@@ -299,6 +301,8 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Para
 // out[row] = sum_i acc_i 2^(m_i - max m) / sum_i l_i 2^(m_i - max m); one block per (token, head) row.
 __global__ void merge_splits_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc,
                                     const float* __restrict__ part_ml, int row0, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = (size_t)row0 + blockIdx.x;
   const float* ml = part_ml + row * splits * 2;
   float mmax = -CUDART_INF_F;
@@ -351,11 +355,11 @@ DLI_EXPORT int dli_paged_attention_mma(void* out, const void* q, long long q_str
   p.splits = splits; p.part_acc = part_acc; p.part_ml = part_ml;
   const int tiles = (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
   dim3 grid(tiles * splits, num_seqs, nkv * p.head_chunks);
-  paged_attention_mma_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p);
+  launch_pdl((paged_attention_mma_kernel), dim3(grid), dim3(THREADS), SMEM_BYTES, stream, 1, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (splits > 1) {
-    merge_splits_kernel<<<num_seqs * nh, D < 128 ? 64 : 128, 0, stream>>>((bf16*)out, part_acc, part_ml, first_row * nh, splits);
+    launch_pdl((merge_splits_kernel), dim3(num_seqs * nh), dim3(D < 128 ? 64 : 128), 0, stream, 1, (bf16*)out, part_acc, part_ml, first_row * nh, splits);
     e = cudaGetLastError();
   }
   return (int)e;

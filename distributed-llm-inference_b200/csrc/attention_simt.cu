@@ -14,6 +14,8 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
                                             const int* __restrict__ block_tables, int max_blocks,
                                             const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n,
                                             int nh, int nkv, int d, int page_size, int window, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31;
   const int warp_in_block = threadIdx.x >> 5;
@@ -85,11 +87,11 @@ DLI_EXPORT int dli_paged_attention_simt(void* out, const void* q, int q_stride, 
   const int blocks = (int)((total + warps - 1) / warps);
   const size_t smem = (size_t)warps * d * sizeof(float);
   if (dtype == DLI_F32)
-    paged_attention_simt_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+    launch_pdl((paged_attention_simt_kernel<float>), dim3(blocks), dim3(warps * 32), smem, stream, 1, 
         (float*)out, (const float*)q, q_stride, (const float*)k_pool, (const float*)v_pool, block_tables, max_blocks,
         seq_of_token, positions, n, nh, nkv, d, page_size, window, scale);
   else
-    paged_attention_simt_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+    launch_pdl((paged_attention_simt_kernel<__nv_bfloat16>), dim3(blocks), dim3(warps * 32), smem, stream, 1, 
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
         block_tables, max_blocks, seq_of_token, positions, n, nh, nkv, d, page_size, window, scale);
   return (int)cudaGetLastError();

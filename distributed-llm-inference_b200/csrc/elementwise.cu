@@ -9,6 +9,8 @@ using namespace dli;
 // h[t, :] = float(table[ids[t], :]); h is the float32 residual stream.
 template <typename T>
 __global__ void embedding_kernel(float* __restrict__ h, const T* __restrict__ table, const int* __restrict__ ids, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const T* src = table + (size_t)ids[t] * H;
   float* dst = h + (size_t)t * H;
@@ -18,6 +20,8 @@ __global__ void embedding_kernel(float* __restrict__ h, const T* __restrict__ ta
 // bfloat16 rows of H % 8 == 0: 16-byte loads, two float4 stores per thread
 __global__ void embedding_bf16_vec_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ table,
                                           const int* __restrict__ ids, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)ids[t] * H);
   float4* dst = reinterpret_cast<float4*>(h + (size_t)t * H);
@@ -33,14 +37,14 @@ __global__ void embedding_bf16_vec_kernel(float* __restrict__ h, const __nv_bflo
 DLI_EXPORT int dli_embedding(float* h, const void* table, const int* ids, int n, int H, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
   if (dtype == DLI_BF16 && H % 8 == 0) {
-    embedding_bf16_vec_kernel<<<n, H >= 2048 ? 256 : 64, 0, stream>>>(h, (const __nv_bfloat16*)table, ids, H);
+    launch_pdl((embedding_bf16_vec_kernel), dim3(n), dim3(H >= 2048 ? 256 : 64), 0, stream, 1, h, (const __nv_bfloat16*)table, ids, H);
     return (int)cudaGetLastError();
   }
   const int threads = H >= 1024 ? 256 : 128;
   if (dtype == DLI_F32)
-    embedding_kernel<float><<<n, threads, 0, stream>>>(h, (const float*)table, ids, H);
+    launch_pdl((embedding_kernel<float>), dim3(n), dim3(threads), 0, stream, 1, h, (const float*)table, ids, H);
   else
-    embedding_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(h, (const __nv_bfloat16*)table, ids, H);
+    launch_pdl((embedding_kernel<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, 1, h, (const __nv_bfloat16*)table, ids, H);
   return (int)cudaGetLastError();
 }
 
@@ -52,6 +56,8 @@ DLI_EXPORT int dli_embedding(float* h, const void* table, const int* ids, int n,
 template <typename T, int THREADS, int PER_THREAD>
 __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ h, const T* __restrict__ delta,
                                    const float* __restrict__ w, const int* __restrict__ rows, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[33];
   const int r = blockIdx.x;
   const int s = rows ? rows[r] : r;
@@ -122,6 +128,8 @@ template <typename T, int THREADS, int CHUNKS>
 __global__ void __launch_bounds__(THREADS) add_rmsnorm_vec_kernel(T* __restrict__ y, float* __restrict__ h,
                                                                   const T* __restrict__ delta, const float* __restrict__ w,
                                                                   const int* __restrict__ rows, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[33];
   const int r = blockIdx.x;
   const int s = rows ? rows[r] : r;
@@ -164,13 +172,13 @@ template <typename T>
 static int launch_add_rmsnorm_vec(void* y, float* h, const void* delta, const float* w, const int* rows, int n_rows, int H,
                                   float eps, cudaStream_t stream) {
   if (H <= 8 * 128 * 1)
-    add_rmsnorm_vec_kernel<T, 128, 1><<<n_rows, 128, 0, stream>>>((T*)y, h, (const T*)delta, w, rows, H, eps);
+    launch_pdl((add_rmsnorm_vec_kernel<T, 128, 1>), dim3(n_rows), dim3(128), 0, stream, 1, (T*)y, h, (const T*)delta, w, rows, H, eps);
   else if (H <= 8 * 256 * 1)
-    add_rmsnorm_vec_kernel<T, 256, 1><<<n_rows, 256, 0, stream>>>((T*)y, h, (const T*)delta, w, rows, H, eps);
+    launch_pdl((add_rmsnorm_vec_kernel<T, 256, 1>), dim3(n_rows), dim3(256), 0, stream, 1, (T*)y, h, (const T*)delta, w, rows, H, eps);
   else if (H <= 8 * 256 * 2)
-    add_rmsnorm_vec_kernel<T, 256, 2><<<n_rows, 256, 0, stream>>>((T*)y, h, (const T*)delta, w, rows, H, eps);
+    launch_pdl((add_rmsnorm_vec_kernel<T, 256, 2>), dim3(n_rows), dim3(256), 0, stream, 1, (T*)y, h, (const T*)delta, w, rows, H, eps);
   else
-    add_rmsnorm_vec_kernel<T, 512, 4><<<n_rows, 512, 0, stream>>>((T*)y, h, (const T*)delta, w, rows, H, eps);
+    launch_pdl((add_rmsnorm_vec_kernel<T, 512, 4>), dim3(n_rows), dim3(512), 0, stream, 1, (T*)y, h, (const T*)delta, w, rows, H, eps);
   return (int)cudaGetLastError();
 }
 
@@ -183,10 +191,9 @@ DLI_EXPORT int dli_add_rmsnorm(void* y, float* h, const void* delta, const float
   }
   constexpr int THREADS = 256, PER = 16;  // 4096 columns in registers, more are streamed
   if (dtype == DLI_F32)
-    add_rmsnorm_kernel<float, THREADS, PER><<<n_rows, THREADS, 0, stream>>>((float*)y, h, (const float*)delta, w, rows, H, eps);
+    launch_pdl((add_rmsnorm_kernel<float, THREADS, PER>), dim3(n_rows), dim3(THREADS), 0, stream, 1, (float*)y, h, (const float*)delta, w, rows, H, eps);
   else
-    add_rmsnorm_kernel<__nv_bfloat16, THREADS, PER>
-        <<<n_rows, THREADS, 0, stream>>>((__nv_bfloat16*)y, h, (const __nv_bfloat16*)delta, w, rows, H, eps);
+    launch_pdl((add_rmsnorm_kernel<__nv_bfloat16, THREADS, PER>), dim3(n_rows), dim3(THREADS), 0, stream, 1, (__nv_bfloat16*)y, h, (const __nv_bfloat16*)delta, w, rows, H, eps);
   return (int)cudaGetLastError();
 }
 
@@ -200,6 +207,8 @@ template <typename T>
 __global__ void rotary_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                     const int* __restrict__ slots, T* __restrict__ k_pool, T* __restrict__ v_pool, int nh,
                                     int nkv, int d, int rot, int page_size, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float trig[];  // cos[half], sin[half] of this token's angles
   const int t = blockIdx.x;
   const int half = rot >> 1;
@@ -252,10 +261,10 @@ DLI_EXPORT int dli_rotary_store(void* qkv, const int* positions, const float* in
   const int threads = 256;
   const size_t smem = (size_t)rot * sizeof(float);
   if (dtype == DLI_F32)
-    rotary_store_kernel<float><<<n, threads, smem, stream>>>((float*)qkv, positions, inv_freq, slots, (float*)k_pool,
+    launch_pdl((rotary_store_kernel<float>), dim3(n), dim3(threads), smem, stream, 1, (float*)qkv, positions, inv_freq, slots, (float*)k_pool,
                                                           (float*)v_pool, nh, nkv, d, rot, page_size, write_kv);
   else
-    rotary_store_kernel<__nv_bfloat16><<<n, threads, smem, stream>>>((__nv_bfloat16*)qkv, positions, inv_freq, slots,
+    launch_pdl((rotary_store_kernel<__nv_bfloat16>), dim3(n), dim3(threads), smem, stream, 1, (__nv_bfloat16*)qkv, positions, inv_freq, slots,
                                                                   (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh, nkv, d,
                                                                   rot, page_size, write_kv);
   return (int)cudaGetLastError();
@@ -265,6 +274,8 @@ DLI_EXPORT int dli_rotary_store(void* qkv, const int* positions, const float* in
 // gu: [n, 2 I] with gate in columns [0, I) and up in [I, 2 I); out: [n, I].
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int n, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t total = (size_t)n * I;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
@@ -277,6 +288,8 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
 
 // bfloat16, I % 8 == 0: one 16-byte load of gate and of up, one 16-byte store, per thread
 __global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= I / 8) return;
@@ -298,147 +311,15 @@ DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int dtype, 
   if (n == 0) return 0;
   if (dtype == DLI_BF16 && I % 8 == 0 && n <= 65535) {
     dim3 grid((I / 8 + 255) / 256, n);
-    silu_mul_bf16_vec_kernel<<<grid, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I);
+    launch_pdl((silu_mul_bf16_vec_kernel), dim3(grid), dim3(256), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I);
     return (int)cudaGetLastError();
   }
   const size_t total = (size_t)n * I;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == DLI_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gu, n, I);
+    launch_pdl((silu_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, 1, (float*)out, (const float*)gu, n, I);
   else
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I);
-  return (int)cudaGetLastError();
-}
-
-// ================================================================ consumers of K-slice slabs
-// The decode matrix product writes float32 slabs [slices, n, cols] whose sum over the slices
-// is the product.  The three kernels below take such slabs in place of a bfloat16 input and
-// add them, slice 0 first, while they read: the order is fixed, so results do not depend on
-// timing, and the sum never travels through memory in bfloat16.
-
-__device__ __forceinline__ float slab_sum(const float* __restrict__ slabs, size_t idx, int slices, size_t slab_stride) {
-  float v = slabs[idx];
-  for (int s = 1; s < slices; ++s) v += slabs[(size_t)s * slab_stride + idx];
-  return v;
-}
-
-// y[r] = rmsnorm(h[s] + sum of slabs[., s]) * w  (s = rows ? rows[r] : r; h updated when rows == nullptr)
-__global__ void add_rmsnorm_slabs_kernel(__nv_bfloat16* __restrict__ y, float* __restrict__ h, const float* __restrict__ slabs,
-                                         int slices, size_t slab_stride, const float* __restrict__ w,
-                                         const int* __restrict__ rows, int H, float eps) {
-  extern __shared__ float rowbuf[];  // H floats
-  __shared__ float red[33];
-  const int r = blockIdx.x;
-  const int s = rows ? rows[r] : r;
-  float* hrow = h + (size_t)s * H;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = hrow[i] + slab_sum(slabs, (size_t)s * H + i, slices, slab_stride);
-    rowbuf[i] = v;
-    if (!rows) hrow[i] = v;
-    ss += v * v;
-  }
-  const float inv = rsqrtf(block_sum(ss, red) / (float)H + eps);
-  __nv_bfloat16* yrow = y + (size_t)r * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) yrow[i] = __float2bfloat16_rn(rowbuf[i] * inv * w[i]);
-}
-
-DLI_EXPORT int dli_add_rmsnorm_slabs(void* y, float* h, const float* slabs, int slices, long long slab_stride, const float* w,
-                                     const int* rows, int n_rows, int H, float eps, cudaStream_t stream) {
-  if (n_rows == 0) return 0;
-  if (slices < 1 || (size_t)H * sizeof(float) > 160 * 1024) return DLI_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)H * sizeof(float);
-  static size_t configured = 48 * 1024;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_slabs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
-  const int threads = H >= 4096 ? 512 : 256;
-  add_rmsnorm_slabs_kernel<<<n_rows, threads, smem, stream>>>((__nv_bfloat16*)y, h, slabs, slices, (size_t)slab_stride, w, rows, H, eps);
-  return (int)cudaGetLastError();
-}
-
-// Rotary embedding and cache write from slabs of q | k | v columns; rotated queries go to
-// q_out [n, nh * d] (bfloat16), keys and values to the pools as in rotary_store_kernel.
-__global__ void rotary_store_slabs_kernel(__nv_bfloat16* __restrict__ q_out, const float* __restrict__ slabs, int slices,
-                                          size_t slab_stride, const int* __restrict__ positions,
-                                          const float* __restrict__ inv_freq, const int* __restrict__ slots,
-                                          __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int nh, int nkv,
-                                          int d, int rot, int page_size, int write_kv) {
-  extern __shared__ float trig[];
-  const int t = blockIdx.x;
-  const int half = rot >> 1;
-  const int row = (nh + 2 * nkv) * d;
-  const size_t base = (size_t)t * row;
-  const float pos = (float)positions[t];
-  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &trig[half + i], &trig[i]);
-  __syncthreads();
-  const int slot = slots ? slots[t] : -1;
-  const bool store = write_kv && slot >= 0;
-  const int page = store ? slot / page_size : 0, off = store ? slot % page_size : 0;
-  __nv_bfloat16* qrow = q_out + (size_t)t * nh * d;
-
-  const int rot_items = (nh + nkv) * half;
-  for (int idx = threadIdx.x; idx < rot_items; idx += blockDim.x) {
-    const int head = idx / half, i = idx - head * half;
-    const float cs = trig[i], sn = trig[half + i];
-    const float a = slab_sum(slabs, base + (size_t)head * d + i, slices, slab_stride);
-    const float b = slab_sum(slabs, base + (size_t)head * d + i + half, slices, slab_stride);
-    const __nv_bfloat16 ra = __float2bfloat16_rn(a * cs - b * sn), rb = __float2bfloat16_rn(b * cs + a * sn);
-    if (head < nh) {
-      qrow[head * d + i] = ra;
-      qrow[head * d + i + half] = rb;
-    } else if (store) {
-      __nv_bfloat16* dst = k_pool + (((size_t)page * nkv + (head - nh)) * page_size + off) * d;
-      dst[i] = ra;
-      dst[i + half] = rb;
-    }
-  }
-  const int tail = d - rot;  // elements that are not rotated
-  for (int idx = threadIdx.x; idx < (nh + nkv) * tail; idx += blockDim.x) {
-    const int head = idx / tail, i = rot + idx - head * tail;
-    const __nv_bfloat16 v = __float2bfloat16_rn(slab_sum(slabs, base + (size_t)head * d + i, slices, slab_stride));
-    if (head < nh) qrow[head * d + i] = v;
-    else if (store) k_pool[(((size_t)page * nkv + (head - nh)) * page_size + off) * d + i] = v;
-  }
-  if (!store) return;
-  for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
-    const int head = idx / d, i = idx - head * d;
-    v_pool[(((size_t)page * nkv + head) * page_size + off) * d + i] =
-        __float2bfloat16_rn(slab_sum(slabs, base + (size_t)(nh + nkv + head) * d + i, slices, slab_stride));
-  }
-}
-
-DLI_EXPORT int dli_rotary_store_slabs(void* q_out, const float* slabs, int slices, long long slab_stride, const int* positions,
-                                      const float* inv_freq, const int* slots, void* k_pool, void* v_pool, int n, int nh, int nkv,
-                                      int d, int rot, int page_size, int write_kv, cudaStream_t stream) {
-  if (n == 0) return 0;
-  if (rot < 0 || rot > d || (rot & 1) || slices < 1) return DLI_ERR_UNSUPPORTED;
-  if (rot > 0 && inv_freq == nullptr) return DLI_ERR_UNSUPPORTED;
-  rotary_store_slabs_kernel<<<n, 256, (size_t)rot * sizeof(float), stream>>>(
-      (__nv_bfloat16*)q_out, slabs, slices, (size_t)slab_stride, positions, inv_freq, slots, (__nv_bfloat16*)k_pool,
-      (__nv_bfloat16*)v_pool, nh, nkv, d, rot, page_size, write_kv);
-  return (int)cudaGetLastError();
-}
-
-// out[n, I] = silu(gate) * up from slabs [slices, n, 2 I]
-__global__ void silu_mul_slabs_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ slabs, int slices,
-                                      size_t slab_stride, int I) {
-  const int t = blockIdx.y;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= I) return;
-  const float g = slab_sum(slabs, (size_t)t * 2 * I + i, slices, slab_stride);
-  const float u = slab_sum(slabs, (size_t)t * 2 * I + I + i, slices, slab_stride);
-  out[(size_t)t * I + i] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
-}
-
-DLI_EXPORT int dli_silu_mul_slabs(void* out, const float* slabs, int slices, long long slab_stride, int n, int I,
-                                  cudaStream_t stream) {
-  if (n == 0) return 0;
-  if (slices < 1 || n > 65535) return DLI_ERR_UNSUPPORTED;
-  dim3 grid((I + 255) / 256, n);
-  silu_mul_slabs_kernel<<<grid, 256, 0, stream>>>((__nv_bfloat16*)out, slabs, slices, (size_t)slab_stride, I);
+    launch_pdl((silu_mul_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I);
   return (int)cudaGetLastError();
 }

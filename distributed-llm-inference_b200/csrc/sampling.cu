@@ -56,6 +56,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, 
                                                          const int* __restrict__ top_k, const float* __restrict__ top_p,
                                                          const unsigned long long* __restrict__ seed,
                                                          const unsigned long long* __restrict__ draw) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float redf[33];
   __shared__ unsigned redu[33];
   __shared__ float wmax[32];
@@ -203,6 +205,6 @@ DLI_EXPORT int dli_sample(int* out, const float* logits, long long row_stride, i
                           const unsigned long long* draw, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (V < 1) return DLI_ERR_UNSUPPORTED;
-  sample_kernel<<<rows, THREADS, 0, stream>>>(out, logits, row_stride, V, temperature, top_k, top_p, seed, draw);
+  launch_pdl((sample_kernel), dim3(rows), dim3(THREADS), 0, stream, 1, out, logits, row_stride, V, temperature, top_k, top_p, seed, draw);
   return (int)cudaGetLastError();
 }

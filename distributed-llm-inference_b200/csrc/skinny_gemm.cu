@@ -1,4 +1,4 @@
-// out[s, t, f] = sum over the s-th slice of K of x[t, k] * W[f, k]      (bfloat16 in, float32 out)
+// out[t, f] = sum over k of x[t, k] * W[f, k]      (bfloat16 in; bfloat16 or float32 out)
 //
 // The matrix product of the decode step: a few tokens (t < 256) against a large weight matrix
 // that is read once from HBM.  Weights take the 128-row side of the tensor-core instruction
@@ -12,11 +12,14 @@
 //     stage) into an accumulator in tensor memory; tcgen05.commit frees the stage and, at the
 //     end, signals the epilogue;
 //   * four warps read the accumulator with tcgen05.ld (lane = feature, column = token) and
-//     store float32, coalesced along features.
+//     store, coalesced along features.
 //
 // The grid is (feature tiles, K slices).  Slices exist to fill the GPU when a matrix has few
-// feature tiles; each writes its own slab out[s], and the consumer (norm, rotary, activation
-// kernels) adds the slabs in a fixed order, so the result does not depend on timing.
+// feature tiles.  The CTAs of one tile's slices form a thread-block cluster (up to 8): each
+// parks its partial sums in its own shared memory, and after a cluster barrier CTA r adds, for
+// its share of the tokens, the partial sums of all slices — read through distributed shared
+// memory, slice 0 first, so the order is fixed — and writes the output.  No partial sum ever
+// leaves the chip, and no scratch memory is needed.
 //
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel records an error
 // code in *error_flag, stops issuing work, frees its tensor memory and returns.
@@ -88,10 +91,27 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void store_out(void* out, int out_f32, size_t idx, float v) {
+  if (out_f32) ((float*)out)[idx] = v;
+  else ((__nv_bfloat16*)out)[idx] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_shared(uint32_t local_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
-                                                          const __grid_constant__ CUtensorMap map_x, float* __restrict__ out,
-                                                          int tokens, int features, int k_tiles, int tiles_per_slice, int npad,
-                                                          int stages, int tmem_cols, int* error_flag) {
+                                                          const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
+                                                          int out_f32, int tokens, int features, int k_tiles, int tiles_per_slice,
+                                                          int npad, int stages, int tmem_cols, int* error_flag) {
+  pdl_launch_dependents();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int b_bytes = npad * BK * 2;
@@ -129,11 +149,21 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   // The other lanes of the two role warps park at __syncwarp: if they polled the accumulator
   // barrier meanwhile, their warp would alternate between the poll and the role loop.
   if (warp == 0) {
-    // ---- producer: TMA loads, `stages` ahead of the MMAs
-    if (lane == 0)
-    for (int i = 0; i < nkt; ++i) {
+    // ---- producer: TMA loads, `stages` ahead of the MMAs.  Weights do not depend on the
+    // kernel that runs before this one, so the first stages' weight tiles are requested before
+    // the wait on that kernel; the activations only after it.
+    if (lane == 0) {
+    const int pre = min(nkt, stages);
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(full0 + 8 * i, (uint32_t)stage_bytes);
+      tma_load_2d(smem_u32(smem + (size_t)i * stage_bytes), &map_w, (kt0 + i) * BK, tile * BM, full0 + 8 * i);
+    }
+    pdl_wait();
+    for (int i = 0; i < pre; ++i)
+      tma_load_2d(smem_u32(smem + (size_t)i * stage_bytes) + A_BYTES, &map_x, (kt0 + i) * BK, 0, full0 + 8 * i);
+    for (int i = pre; i < nkt; ++i) {
       const int s = i % stages;
-      if (i >= stages && !mbar_wait(empty0 + 8 * s, ((i / stages) - 1) & 1)) {
+      if (!mbar_wait(empty0 + 8 * s, ((i / stages) - 1) & 1)) {
         *failed = 1;
         atomicExch(error_flag, 1);
         break;
@@ -143,6 +173,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
       mbar_expect_tx(full0 + 8 * s, (uint32_t)stage_bytes);
       tma_load_2d(a, &map_w, (kt0 + i) * BK, tile * BM, full0 + 8 * s);
       tma_load_2d(a + A_BYTES, &map_x, (kt0 + i) * BK, 0, full0 + 8 * s);
+    }
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -175,10 +206,15 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
     if (!ok) atomicExch(error_flag, 3);
   }
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  pdl_wait();  // the output may alias memory the kernel before this one still reads
   ok = ok && !*failed;
-  const int f = tile * BM + warp * 32 + lane;
-  float* dst = out + (size_t)slice * tokens * features + f;
-  for (int c = 0; c < npad && c < ((tokens + 7) & ~7); c += 8) {
+  const int fl = warp * 32 + lane, f = tile * BM + fl;
+  const int slices = gridDim.y;  // the cluster spans the grid's y dimension: slice = rank in the cluster
+  // with several slices the partial sums go to shared memory, [token][feature of the tile];
+  // the pipeline stages are free by now (every MMA that read them has finished)
+  float* red = reinterpret_cast<float*>(smem);
+  const int tok8 = (tokens + 7) & ~7;
+  for (int c = 0; c < npad && c < tok8; c += 8) {
     uint32_t r[8];
     if (nkt > 0 && ok) {
       const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c;
@@ -190,11 +226,28 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
 #pragma unroll
       for (int j = 0; j < 8; ++j) r[j] = 0u;
     }
-    if (f < features) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (c + j < tokens) dst[(size_t)(c + j) * features] = __uint_as_float(r[j]);
+    for (int j = 0; j < 8; ++j) {
+      if (c + j >= tokens) continue;
+      if (slices > 1) red[(c + j) * BM + fl] = __uint_as_float(r[j]);
+      else if (f < features) store_out(out, out_f32, (size_t)(c + j) * features + f, __uint_as_float(r[j]));
     }
+  }
+  if (slices > 1) {
+    cluster_sync();  // every slice's partial sums are in its shared memory
+    const uint32_t red_addr = smem_u32(red);
+    for (int t = slice; t < tokens; t += slices) {
+      const uint32_t a = red_addr + (uint32_t)(t * BM + fl) * 4u;
+      float acc = 0.f;
+      int s2 = 0;
+      for (; s2 + 4 <= slices; s2 += 4) {
+        const float v0 = ld_peer_shared(a, s2), v1 = ld_peer_shared(a, s2 + 1), v2 = ld_peer_shared(a, s2 + 2), v3 = ld_peer_shared(a, s2 + 3);
+        acc = (((acc + v0) + v1) + v2) + v3;
+      }
+      for (; s2 < slices; ++s2) acc += ld_peer_shared(a, s2);
+      if (f < features) store_out(out, out_f32, (size_t)t * features + f, acc);
+    }
+    cluster_sync();  // nobody leaves while a peer may still read its shared memory
   }
 
   // ---- teardown: nobody touches tensor memory after this barrier; warp 0 frees it
@@ -236,23 +289,24 @@ int* error_flag_host = nullptr;
 
 }  // namespace
 
-// Number of K slices this launch uses for the given sizes: enough CTAs to fill the GPU, no
-// slice shorter than four k-tiles.  The caller sizes `out` as [slices, tokens, features].
-DLI_EXPORT int dli_skinny_gemm_slices(int features, int K) {
+// Number of K slices recommended for the given sizes: enough CTAs to fill the GPU, no slice
+// shorter than four k-tiles, at most 8 (the portable cluster size).
+DLI_EXPORT int dli_skinny_gemm_slices(int tokens, int features, int K) {
   const int tiles = (features + BM - 1) / BM;
   const int k_tiles = (K + BK - 1) / BK;
   int want = (148 * 2 + tiles - 1) / tiles;
   int most = k_tiles / 4;
   if (most < 1) most = 1;
+  if (most > 8) most = 8;
   int slices = want < most ? want : most;
   if (slices < 1) slices = 1;
   const int per = (k_tiles + slices - 1) / slices;
   return (k_tiles + per - 1) / per;  // no empty slice
 }
 
-DLI_EXPORT int dli_skinny_gemm(float* out, const void* x, const void* w, int tokens, int features, int K, int slices,
-                               cudaStream_t stream) {
-  if (tokens < 1 || tokens > 256 || features < 1 || K < 8 || K % 8 || slices < 1) return DLI_ERR_UNSUPPORTED;
+DLI_EXPORT int dli_skinny_gemm(void* out, int out_f32, const void* x, const void* w, int tokens, int features, int K,
+                               int slices, cudaStream_t stream) {
+  if (tokens < 1 || tokens > 256 || features < 1 || K < 8 || K % 8 || slices < 1 || slices > 8) return DLI_ERR_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return DLI_ERR_UNSUPPORTED;
   if (!error_flag_host) {
     if (cudaHostAlloc((void**)&error_flag_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return (int)cudaGetLastError();
@@ -268,6 +322,7 @@ DLI_EXPORT int dli_skinny_gemm(float* out, const void* x, const void* w, int tok
   int stages = per < 6 ? per : 6;
   while (stages > 2 && stages * stage_bytes > 72 * 1024) --stages;  // leave room for three CTAs per SM
   if (stages < 1) stages = 1;
+  while (slices > 1 && stages * stage_bytes < npad * BM * 4) ++stages;  // room for the partial sums [npad][128] float32
   const int smem = stages * stage_bytes + (2 * stages + 1) * 8 + 16 + 1024;
   int tmem_cols = 32;
   while (tmem_cols < npad) tmem_cols <<= 1;
@@ -277,9 +332,9 @@ DLI_EXPORT int dli_skinny_gemm(float* out, const void* x, const void* w, int tok
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  dim3 grid((features + BM - 1) / BM, slices);
-  skinny_gemm_kernel<<<grid, 128, smem, stream>>>(map_w, map_x, out, tokens, features, k_tiles, per, npad, stages, tmem_cols, error_flag_device);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch_pdl(skinny_gemm_kernel, dim3((features + BM - 1) / BM, slices), dim3(128), (size_t)smem, stream, slices, map_w,
+                             map_x, out, out_f32, tokens, features, k_tiles, per, npad, stages, tmem_cols, error_flag_device);
+  return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 // 0, or the code of the first wait that ran out (1 producer, 2 MMA issuer, 3 epilogue)

@@ -21,15 +21,14 @@ torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 SKINNY_MAX_TOKENS = 64
 
 
-def project(x: torch.Tensor, weight: torch.Tensor, slices: int | None = None) -> torch.Tensor:
-    """y = x W^T for a step's tokens.  Returns either y [n, out] in x's dtype, or — for few
-    bfloat16 tokens — float32 slabs [slices, n, out] whose sum is y, which the engine's norm,
-    rotary and activation kernels add up as they read."""
+def project(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """y = x W^T for a step's tokens, in x's dtype or in ``out_dtype`` (float32 for logits)."""
     from . import ops
 
     if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_TOKENS and ops.skinny_gemm_supported(x.shape[0], x.shape[1]):
-        return ops.skinny_gemm(x, weight, slices)
-    return linear(x, weight)
+        return ops.skinny_gemm(x, weight, out_dtype or x.dtype)
+    y = linear(x, weight)
+    return y if out_dtype in (None, y.dtype) else y.to(out_dtype)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -107,12 +107,7 @@ def add_rmsnorm(
     n_rows = y.shape[0]
     if y.dtype not in DT_CODE or y.shape[1] != H or weight.numel() != H:
         raise KernelError("add_rmsnorm: shapes or dtype do not agree")
-    slabs = delta is not None and delta.dim() == 3
-    if slabs:
-        _need(delta, "delta slabs", torch.float32)
-        if tuple(delta.shape[1:]) != tuple(h.shape) or y.dtype != torch.bfloat16:
-            raise KernelError("add_rmsnorm: slabs must be float32 [slices, n, H] and y bfloat16")
-    elif delta is not None:
+    if delta is not None:
         _need(delta, "delta", y.dtype)
         if delta.shape != h.shape:
             raise KernelError("add_rmsnorm: delta and h differ in shape")
@@ -122,13 +117,6 @@ def add_rmsnorm(
             raise KernelError("add_rmsnorm: one output row per entry of rows")
     elif n_rows != h.shape[0]:
         raise KernelError("add_rmsnorm: y and h differ in rows")
-    if slabs:
-        f = _fn(
-            "elementwise.cu", "dli_add_rmsnorm_slabs",
-            [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
-        )
-        _check(f(_ptr(y), _ptr(h), _ptr(delta), delta.shape[0], h.numel(), _ptr(weight), _ptr(rows), n_rows, H, eps, _stream()), "add_rmsnorm_slabs")
-        return
     f = _fn(
         "elementwise.cu", "dli_add_rmsnorm",
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
@@ -179,60 +167,10 @@ def rotary_store(
     )
 
 
-def rotary_store_slabs(
-    q_out: torch.Tensor,
-    slabs: torch.Tensor,
-    positions: torch.Tensor,
-    inv_freq: torch.Tensor | None,
-    slots: torch.Tensor | None,
-    k_pool: torch.Tensor | None,
-    v_pool: torch.Tensor | None,
-    num_heads: int,
-    num_kv_heads: int,
-    head_dim: int,
-    rotary_dim: int,
-    page_size: int,
-    write_kv: bool = True,
-) -> None:
-    """rotary_store for q | k | v given as float32 slabs [slices, n, (nh + 2 nkv) d] whose sum is
-    meant: rotated queries go to q_out [n, nh * d] (bfloat16), keys and values to the pools."""
-    _need(q_out, "q_out", torch.bfloat16), _need(slabs, "slabs", torch.float32), _need(positions, "positions", torch.int32)
-    n = q_out.shape[0]
-    if slabs.dim() != 3 or tuple(slabs.shape[1:]) != (n, (num_heads + 2 * num_kv_heads) * head_dim) or q_out.shape[1] != num_heads * head_dim:
-        raise KernelError("rotary_store_slabs: shapes do not agree")
-    if rotary_dim:
-        if inv_freq is None or inv_freq.numel() != rotary_dim // 2:
-            raise KernelError("rotary_store_slabs: inv_freq must have rotary_dim / 2 entries")
-        _need(inv_freq, "inv_freq", torch.float32)
-    if write_kv:
-        if slots is None or k_pool is None or v_pool is None:
-            raise KernelError("rotary_store_slabs: slots and pools are needed to write keys and values")
-        _need(slots, "slots", torch.int32), _need(k_pool, "k_pool", torch.bfloat16), _need(v_pool, "v_pool", torch.bfloat16)
-        if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, head_dim) or k_pool.shape != v_pool.shape or slots.numel() != n:
-            raise KernelError("rotary_store_slabs: pool layout must be [pages, kv_heads, page_size, head_dim]")
-    f = _fn(
-        "elementwise.cu", "dli_rotary_store_slabs",
-        [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p],
-    )
-    _check(
-        f(_ptr(q_out), _ptr(slabs), slabs.shape[0], slabs.shape[1] * slabs.shape[2], _ptr(positions), _ptr(inv_freq), _ptr(slots),
-          _ptr(k_pool), _ptr(v_pool), n, num_heads, num_kv_heads, head_dim, rotary_dim, page_size, int(write_kv), _stream()),
-        "rotary_store_slabs",
-    )
-
-
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
-    """out[n, I] = silu(gate_up[:, :I]) * gate_up[:, I:]; gate_up may be float32 slabs
-    [slices, n, 2 I] whose sum is meant (then out is bfloat16)."""
-    n, I = out.shape
-    if gate_up.dim() == 3:
-        _need(out, "out", torch.bfloat16), _need(gate_up, "gate_up slabs", torch.float32)
-        if tuple(gate_up.shape[1:]) != (n, 2 * I):
-            raise KernelError("silu_mul: slabs must be [slices, n, 2 I]")
-        f = _fn("elementwise.cu", "dli_silu_mul_slabs", [c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p])
-        _check(f(_ptr(out), _ptr(gate_up), gate_up.shape[0], n * 2 * I, n, I, _stream()), "silu_mul_slabs")
-        return
+    """out[n, I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
     _need(out, "out"), _need(gate_up, "gate_up", out.dtype)
+    n, I = out.shape
     if out.dtype not in DT_CODE or tuple(gate_up.shape) != (n, 2 * I):
         raise KernelError("silu_mul: shapes or dtype do not agree")
     f = _fn("elementwise.cu", "dli_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
@@ -387,41 +325,43 @@ def skinny_gemm_supported(tokens: int, in_features: int) -> bool:
     return 1 <= tokens <= 256 and in_features >= 8 and in_features % 8 == 0
 
 
-_slices_cache: dict[tuple[int, int], int] = {}
+_slices_cache: dict[tuple[int, int, int], int] = {}
 
 
-def skinny_gemm_slices(features: int, in_features: int) -> int:
-    """K slices the kernel's launcher recommends for a weight matrix of this shape."""
-    n = _slices_cache.get((features, in_features))
+def skinny_gemm_slices(tokens: int, features: int, in_features: int) -> int:
+    """K slices the kernel's launcher recommends for these sizes."""
+    key = (tokens, features, in_features)
+    n = _slices_cache.get(key)
     if n is None:
-        n = _slices_cache[(features, in_features)] = _fn("skinny_gemm.cu", "dli_skinny_gemm_slices", [c_int, c_int])(features, in_features)
+        n = _slices_cache[key] = _fn("skinny_gemm.cu", "dli_skinny_gemm_slices", [c_int, c_int, c_int])(*key)
     return n
 
 
-def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, slices: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, slices: int | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
     """x [tokens <= 256, K] times weight [features, K] transposed, bfloat16 in, on tcgen05 tensor
-    cores fed by TMA.  Returns float32 [slices, tokens, features]: the product is the sum of the
-    slabs (each covers a slice of K); with one slice it is the product itself."""
+    cores fed by TMA; returns [tokens, features] in bfloat16 or float32.  ``slices`` (1..8) cuts K
+    across the CTAs of a cluster, which add their partial sums through distributed shared memory."""
     _need(x, "x", torch.bfloat16), _need(weight, "weight", torch.bfloat16)
     tokens, K = x.shape
     features = weight.shape[0]
-    if weight.shape[1] != K or not skinny_gemm_supported(tokens, K):
-        raise KernelError(f"skinny_gemm: tokens {tokens} (1..256) or K {K} (a multiple of 8) not supported")
+    if weight.shape[1] != K or not skinny_gemm_supported(tokens, K) or out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"skinny_gemm: tokens {tokens} (1..256), K {K} (a multiple of 8) or output {out_dtype} not supported")
+    if slices is not None and not 1 <= slices <= 8:
+        raise KernelError("skinny_gemm: 1 to 8 K slices")
     if slices is None:
-        slices = skinny_gemm_slices(features, K)
+        slices = skinny_gemm_slices(tokens, features, K)
     if out is None:
-        out = torch.empty((slices, tokens, features), dtype=torch.float32, device=x.device)
+        out = torch.empty((tokens, features), dtype=out_dtype, device=x.device)
     else:
-        _need(out, "out", torch.float32)
-        if out.numel() < slices * tokens * features:
-            raise KernelError("skinny_gemm: out too small")
-    f = _fn("skinny_gemm.cu", "dli_skinny_gemm", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(out), _ptr(x), _ptr(weight), tokens, features, K, slices, _stream()), "skinny_gemm")
+        _need(out, "out", out_dtype)
+        if tuple(out.shape) != (tokens, features):
+            raise KernelError("skinny_gemm: out has the wrong shape")
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), int(out_dtype == torch.float32), _ptr(x), _ptr(weight), tokens, features, K, slices, _stream()), "skinny_gemm")
     return out
 
 
 def skinny_gemm_error() -> int:
     """0, or which bounded wait of the decode matrix product ran out since the library was loaded."""
-    lib = load_library("skinny_gemm.cu")
-    lib.dli_skinny_gemm_error.restype = c_int
-    return lib.dli_skinny_gemm_error()
+    return _fn("skinny_gemm.cu", "dli_skinny_gemm_error", [])()

@@ -8,19 +8,18 @@ step.  No part knows which model it is in.
 Interfaces by category (what a new part of that category must provide):
 
 ``norm``          ``add_norm(h, delta, rows=None) -> y``: h is the float32 residual stream
-                  [n, H]; delta (activation dtype [n, H]; or float32 [slices, n, H] slabs whose sum
-                  is meant, as the decode matrix product returns them; or None) is added to h first,
-                  and the sum is written back to h when ``rows`` is None; y (activation dtype) is the
-                  normed sum of the rows asked for.
+                  [n, H]; delta (activation dtype, or None) is added to h first, and the sum is
+                  written back to h when ``rows`` is None; y (activation dtype) is the normed sum of
+                  the rows asked for.
 ``position``      ``rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv) -> q``:
-                  encodes position into the q and k heads of qkv ([n, cols], or float32 slabs), writes
+                  encodes position into the q and k heads of qkv [n, cols], writes
                   k, v into the cache's pages at ``batch.group(cache.group).slots`` and returns the
                   tensor whose leading columns are the encoded queries.
 ``mixer``         ``cache_need() -> PagedKVNeed | StateNeed | None`` and
-                  ``forward(x, batch, cache) -> delta`` ([n, H], or slabs as above); x is the normed input (activation dtype).
+                  ``forward(x, batch, cache) -> [n, H]``; x is the normed input (activation dtype).
                   ``cache`` is the ``LayerCache`` of its run step (pools or state slots; ``writes``
                   is False when the step reads another step's cache).
-``feed_forward``  ``forward(x) -> delta`` ([n, H], or slabs as above).
+``feed_forward``  ``forward(x) -> [n, H]``.
 ``arrangement``   built from a ``LayerSpec``; ``forward(stream, batch, cache)`` wires norms, mixer
                   and feed-forward around the residual ``stream`` (h plus a pending delta).
 ``embedding``     ``forward(token_ids) -> h`` float32 [n, H].

@@ -52,8 +52,7 @@ class LMHead(Part):
         self.weight = tensors[self.tied_to or self.spec.prefix + "weight"]
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
-        logits = project(y, self.weight, slices=1)
-        return logits[0] if logits.dim() == 3 else logits.float()
+        return project(y, self.weight, out_dtype=torch.float32)
 
 
 def _walk(part) -> list[Part]:

@@ -35,15 +35,10 @@ def inverse_frequencies(params) -> torch.Tensor:
 
 def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq):
     """Runs the fused kernel and returns the tensor whose leading num_heads * head_dim columns
-    are the encoded queries: qkv itself (rotated in place), or a new tensor when qkv came as
-    float32 slabs."""
+    are the encoded queries (qkv itself: queries are rotated in place)."""
     group = batch.group(cache.group)
     args = (batch.positions, inv_freq, group.slots if write_kv else None, cache.k if write_kv else None,
             cache.v if write_kv else None, num_heads, num_kv_heads, head_dim, rotary_dim, cache.page_size, write_kv)
-    if qkv.dim() == 3:
-        q = torch.empty((qkv.shape[1], num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
-        ops.rotary_store_slabs(q, qkv, *args)
-        return q
     if rotary_dim or write_kv:
         ops.rotary_store(qkv, *args)
     return qkv

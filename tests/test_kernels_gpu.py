@@ -328,3 +328,33 @@ def test_sampled_frequencies_follow_the_distribution():
     assert freq[2:].sum() == 0 and abs(freq[0] - 2 / 3) < 0.03
     toks = sample_rows(logits[:50].contiguous(), [1.0] * 50, [-1] * 50, [0.01] * 50, [9] * 50, list(range(50)))
     assert set(toks) == {0}
+
+
+# ------------------------------------------------------------------ decode matrix product
+
+
+@pytest.mark.parametrize("tokens,features,K", [(1, 200, 96), (5, 130, 40), (17, 1000, 104), (64, 384, 520), (100, 256, 64), (256, 77, 1032), (8, 4100, 2048)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_skinny_gemm(tokens, features, K, out_dtype):
+    """Sizes that are no multiples of the 128 x 64 tile, one K slice and several (a cluster),
+    against a float64 product."""
+    x = rnd(tokens, K, dtype=torch.bfloat16, seed=tokens)
+    w = rnd(features, K, dtype=torch.bfloat16, seed=features, scale=0.1)
+    want = (x.double() @ w.double().T).cpu().numpy()
+    scale = np.abs(want).max()
+    for slices in (None, 1, 2, 5, 8):
+        for _ in range(2):
+            got = ops.skinny_gemm(x, w, out_dtype, slices)
+            assert got.dtype == out_dtype and tuple(got.shape) == (tokens, features)
+            err = np.abs(got.double().cpu().numpy() - want).max()
+            assert err <= (1e-5 if out_dtype == torch.float32 else 8e-3) * max(1.0, scale), (slices, err)
+    assert ops.skinny_gemm_error() == 0
+
+
+def test_skinny_gemm_refuses_what_it_cannot_do():
+    x = rnd(4, 36, dtype=torch.bfloat16)
+    w = rnd(8, 36, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.skinny_gemm(x, w)
+    with pytest.raises(ops.KernelError):
+        ops.skinny_gemm(rnd(300, 64, dtype=torch.bfloat16), rnd(8, 64, dtype=torch.bfloat16))
