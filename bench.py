@@ -65,7 +65,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -282,7 +282,9 @@ def main() -> int:
         print(json.dumps({"phase": "prefill", "layers": args.layers, **prefill_timed(model, cfg, args.layers, pk["bf16_tflops"], reps=args.steps)}))
         return 0
     main_run = decode_device_timed(model, args.batch, args.steps, args.warmup, clocks)
+    clocks.start()  # the end-to-end steps are timed too: keep sampling
     e2e = decode_end_to_end(model, args.batch, args.steps, args.warmup)
+    clocks.stop()
     prefill = prefill_timed(model, cfg, args.layers, pk["bf16_tflops"])
     points = {}
     if not args.skip_points:

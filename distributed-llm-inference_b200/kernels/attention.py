@@ -12,8 +12,8 @@ import torch
 
 from . import ops
 
-TARGET_CTAS = 148 * 4  # enough CTAs to fill the SMs a few times over
-MIN_TILES_PER_SPLIT = 4  # key tiles (of 64) a split should at least cover
+TARGET_CTAS = 148 * 2  # the decode kernel keeps one CTA of four warps per SM busy; two rounds fill the tail
+MIN_TILES_PER_SPLIT = 8  # key tiles (of 64) a split should at least cover: two for each of its warps
 
 
 def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int) -> int:
