@@ -558,3 +558,44 @@ DLI_EXPORT int dli_paged_attention_mma(void* out, const void* q, long long q_str
 }
 
 DLI_EXPORT int dli_paged_attention_mma_head_dim() { return D; }
+
+// ---------------------------------------------------------------- entry point without allocation
+#include "no_alloc_entry.h"
+
+namespace {
+// Scratch of the no-allocation entry point: part of the library's device image, one copy per
+// GPU that loads the library.  In host code this name is only a handle for the runtime; the
+// address a kernel can use comes from cudaGetSymbolAddress.
+static __device__ __align__(256) float noalloc_scratch[DLI_NOALLOC_SCRATCH_FLOATS];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+}  // namespace
+
+DLI_EXPORT int dli_paged_decode_attention_noalloc(void* out, const void* q, long long q_stride, const void* k_pool,
+                                                  const void* v_pool, const int* block_tables, int max_blocks, const int* q_start,
+                                                  const int* kv_len, int seq0, int num_seqs, int first_row, int nh, int nkv,
+                                                  int page_size, int window, float scale, int splits, cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  if (splits < 1 || nh < 1 || first_row < 0) return DLI_ERR_UNSUPPORTED;
+  // rows are counted from token 0 of the batch, as the ordinary entry point indexes its scratch
+  const unsigned long long rows = (unsigned long long)(first_row + num_seqs) * (unsigned long long)nh;
+  const unsigned long long need = rows * (unsigned long long)splits * (unsigned long long)(D + 2);
+  if (need > DLI_NOALLOC_SCRATCH_FLOATS) return DLI_ERR_SCRATCH_TOO_SMALL;
+
+  // set-up, once per device: the device address of the array, looked up with that device current
+  static float* base[NOALLOC_MAX_DEVICES] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return DLI_ERR_UNSUPPORTED;
+  if (!base[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    base[dev] = p;
+  }
+  float* part_acc = base[dev];
+  float* part_ml = part_acc + rows * (unsigned long long)splits * (unsigned long long)D;
+  if (splits == 1) part_acc = part_ml = nullptr;  // no partial results: the kernel writes the output itself
+  return dli_paged_attention_mma(out, q, q_stride, k_pool, v_pool, block_tables, max_blocks, q_start, kv_len, seq0, num_seqs, 1,
+                                 first_row, nh, nkv, page_size, window, scale, splits, part_acc, part_ml, stream);
+}
