@@ -236,16 +236,26 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   if (slices > 1) {
     cluster_sync();  // every slice's partial sums are in its shared memory
     const uint32_t red_addr = smem_u32(red);
-    for (int t = slice; t < tokens; t += slices) {
-      const uint32_t a = red_addr + (uint32_t)(t * BM + fl) * 4u;
-      float acc = 0.f;
-      int s2 = 0;
-      for (; s2 + 4 <= slices; s2 += 4) {
-        const float v0 = ld_peer_shared(a, s2), v1 = ld_peer_shared(a, s2 + 1), v2 = ld_peer_shared(a, s2 + 2), v3 = ld_peer_shared(a, s2 + 3);
-        acc = (((acc + v0) + v1) + v2) + v3;
+    // CTA r adds tokens r, r + slices, ...; up to eight tokens' partial sums from all slices are
+    // requested at once (remote shared memory answers slowly: keep many loads in flight)
+    constexpr int TCH = 8;
+    for (int t0 = slice; t0 < tokens; t0 += slices * TCH) {
+      float v[TCH][8];
+#pragma unroll
+      for (int i = 0; i < TCH; ++i) {
+        const int t = t0 + i * slices;
+        const uint32_t a = red_addr + (uint32_t)(t * BM + fl) * 4u;
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2) v[i][s2] = (t < tokens && s2 < slices) ? ld_peer_shared(a, s2) : 0.f;
       }
-      for (; s2 < slices; ++s2) acc += ld_peer_shared(a, s2);
-      if (f < features) store_out(out, out_f32, (size_t)t * features + f, acc);
+#pragma unroll
+      for (int i = 0; i < TCH; ++i) {
+        const int t = t0 + i * slices;
+        float acc = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < 8; ++s2) acc += v[i][s2];  // slice 0 first; absent slices add exact zeros
+        if (t < tokens && f < features) store_out(out, out_f32, (size_t)t * features + f, acc);
+      }
     }
     cluster_sync();  // nobody leaves while a peer may still read its shared memory
   }
@@ -305,7 +315,7 @@ DLI_EXPORT int dli_skinny_gemm_slices(int tokens, int features, int K) {
 }
 
 DLI_EXPORT int dli_skinny_gemm(void* out, int out_f32, const void* x, const void* w, int tokens, int features, int K,
-                               int slices, cudaStream_t stream) {
+                               int slices, int max_stages, cudaStream_t stream) {
   if (tokens < 1 || tokens > 256 || features < 1 || K < 8 || K % 8 || slices < 1 || slices > 8) return DLI_ERR_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return DLI_ERR_UNSUPPORTED;
   if (!error_flag_host) {
@@ -319,8 +329,11 @@ DLI_EXPORT int dli_skinny_gemm(void* out, int out_f32, const void* x, const void
   const int k_tiles = (K + BK - 1) / BK;
   const int per = (k_tiles + slices - 1) / slices;
   const int stage_bytes = A_BYTES + npad * BK * 2;
-  int stages = per < 6 ? per : 6;
-  while (stages > 2 && stages * stage_bytes > 72 * 1024) --stages;  // leave room for three CTAs per SM
+  int stages = per < 8 ? per : 8;
+  // by default leave room for three CTAs per SM; a caller that launches one CTA per SM may ask for a deeper pipeline
+  const int budget = (max_stages > 0 ? 200 : 72) * 1024;
+  if (max_stages > 0 && stages > max_stages) stages = max_stages;
+  while (stages > 2 && stages * stage_bytes > budget) --stages;
   if (stages < 1) stages = 1;
   while (slices > 1 && stages * stage_bytes < npad * BM * 4) ++stages;  // room for the partial sums [npad][128] float32
   const int smem = stages * stage_bytes + (2 * stages + 1) * 8 + 16 + 1024;

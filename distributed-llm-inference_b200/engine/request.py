@@ -41,6 +41,15 @@ class Request:
     def all_token_ids(self) -> list[int]:
         return self.prompt_ids + self.output_ids
 
+    def token_slice(self, start: int, end: int) -> list[int]:
+        """Tokens at positions [start, end) of prompt + generated, without building the whole list."""
+        n = len(self.prompt_ids)
+        if start >= n:
+            return self.output_ids[start - n : end - n]
+        if end <= n:
+            return self.prompt_ids[start:end]
+        return self.prompt_ids[start:] + self.output_ids[: end - n]
+
     @property
     def num_tokens(self) -> int:
         return len(self.prompt_ids) + len(self.output_ids)

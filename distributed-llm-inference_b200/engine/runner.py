@@ -19,7 +19,7 @@ from ..cache.needs import PagedKVNeed, StateNeed
 from ..config.registry import load_config, resolve_architecture
 from ..parts import DecoderModel
 from ..weights import load_tensors, random_tensors
-from .batch import StepEntry, Uploader, build_batch, gather_host
+from .batch import StepEntry, Uploader, build_batch, gather_single_tokens
 from .graphs import DecodeGraphs
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -120,7 +120,7 @@ class ModelRunner:
 
     def _replay_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
         """A step of single tokens through a captured graph; None if no graph takes its shape."""
-        h = gather_host(entries, self.manager, self.model.spec.vocab_size)
+        h = gather_single_tokens(entries, self.manager, self.model.spec.vocab_size)
         graph = self.graphs.lookup(h["S"], h["width"], int(h["kv_len"].max()))
         if graph is None:
             return None
@@ -137,6 +137,6 @@ class ModelRunner:
         token of the chunks that sample (src/dli/engine/runner.py:53-80)."""
         entries = []
         for ch in chunks:
-            tokens = ch.request.all_token_ids[ch.start : ch.start + ch.num_tokens]
+            tokens = ch.request.token_slice(ch.start, ch.start + ch.num_tokens)
             entries.append(StepEntry(ch.request.request_id, tokens, [ch.num_tokens - 1] if ch.needs_logits else []))
         return self.step(entries, borrow=True)

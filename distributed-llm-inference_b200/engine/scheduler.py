@@ -160,7 +160,7 @@ class Scheduler:
         if missing <= 0:
             return True
         try:
-            self.manager.append_slots(req.request_id, req.all_token_ids[-missing:])
+            self.manager.append_slots(req.request_id, req.token_slice(req.num_tokens - missing, req.num_tokens))
             return True
         except OutOfPages:
             return False

@@ -41,7 +41,12 @@ def _check(code: int, what: str) -> None:
     launch_count += 1
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -338,7 +343,7 @@ def skinny_gemm_slices(tokens: int, features: int, in_features: int) -> int:
 
 
 def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, slices: int | None = None,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, max_stages: int = 0) -> torch.Tensor:
     """x [tokens <= 256, K] times weight [features, K] transposed, bfloat16 in, on tcgen05 tensor
     cores fed by TMA; returns [tokens, features] in bfloat16 or float32.  ``slices`` (1..8) cuts K
     across the CTAs of a cluster, which add their partial sums through distributed shared memory."""
@@ -357,8 +362,8 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
         _need(out, "out", out_dtype)
         if tuple(out.shape) != (tokens, features):
             raise KernelError("skinny_gemm: out has the wrong shape")
-    f = _fn("skinny_gemm.cu", "dli_skinny_gemm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(out), int(out_dtype == torch.float32), _ptr(x), _ptr(weight), tokens, features, K, slices, _stream()), "skinny_gemm")
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), int(out_dtype == torch.float32), _ptr(x), _ptr(weight), tokens, features, K, slices, max_stages, _stream()), "skinny_gemm")
     return out
 
 

@@ -20,6 +20,7 @@ from .params import SamplingParams
 class Sampler:
     def __init__(self, device: torch.device | str) -> None:
         self.device = torch.device(device)
+        self._out: torch.Tensor | None = None
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int], draws: Sequence[int]) -> list[int]:
         """logits [rows, vocab] float32 on the device; seeds[r] and draws[r] identify the
@@ -29,7 +30,9 @@ class Sampler:
             raise ValueError("logits, params, seeds and draws must have one entry per row")
         if rows == 0:
             return []
-        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if self._out is None or self._out.numel() < rows:
+            self._out = torch.empty(max(rows, 256), dtype=torch.int32, device=self.device)
+        out = self._out[:rows]
         if all(p.greedy for p in params):
             ops.sample(out, logits)
             return out.tolist()
