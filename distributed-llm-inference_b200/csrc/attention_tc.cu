@@ -1,0 +1,446 @@
+// Paged causal GQA attention for prompt portions on the fifth-generation tensor cores
+// (bfloat16, head size 64, page sizes 8..128 that divide 128).
+//
+// A CTA owns 128 rows — (token, query head) pairs that share one KV head — and walks the keys
+// of its sequence in tiles of 128:
+//
+//   * TMA brings the tile's pages of K and V, [page_size x 64] boxes with 128-byte swizzle, straight
+//     from the cache pools through the block table into two-stage shared-memory buffers;
+//   * S = Q K^T is one group of tcgen05.mma (M = 128 rows, N = 128 keys, K = 64) into tensor memory;
+//   * two threads share a row: each reads 64 of its 128 scores with tcgen05.ld, masks by absolute
+//     position, keeps running maximum and sum in float32 (the halves meet through shared memory
+//     once per tile), and writes its probabilities as bfloat16 into a swizzled shared-memory tile;
+//   * O_tile = P V is a second group of tcgen05.mma (V is the MN-major operand, exactly as it
+//     lies in the pages); the thread reads its row of O_tile and folds it into its float32
+//     accumulator with the usual rescaling.
+//
+// One thread issues all copies and matrix products and meets the softmax threads on mbarriers
+// only; loads run ahead (keys of the next tile as soon as S is done, values one tile ahead), and
+// two CTAs per SM overlap one's softmax with the other's matrix products.  Every mbarrier wait is bounded: after WAIT_LIMIT polls the kernel
+// sets *error_flag, stops using the tensor cores, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include <math_constants.h>
+
+using namespace dli;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int D = 64;
+constexpr int ROWS = 128;      // (token, head) rows per CTA
+constexpr int KEYS = 128;      // keys per tile
+constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 128 bytes (Q, K, V tiles and each half of P)
+constexpr int SOFTMAX_THREADS = 256;
+constexpr int THREADS = SOFTMAX_THREADS + 32;  // plus the warp whose first lane issues copies and matrix products
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 1 + 2 + 2) + 2 * ROWS * 4 + 256 + 1024;  // Q, K, V x2, P (two halves), row maxima, barriers, alignment
+constexpr int TMEM_COLS = 256;  // S: 128 columns, O_tile: 64 columns
+constexpr unsigned WAIT_LIMIT = 1u << 24;
+
+struct Params {
+  bf16* out;
+  const bf16* q;
+  long long q_stride;
+  const int* block_tables;
+  int max_blocks;
+  const int* q_start;
+  const int* kv_len;
+  int seq0, nh, nkv, page_size, window;
+  float scale_log2;
+  int tokens_per_tile, heads_per_chunk, head_chunks;
+  int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// 128-byte-swizzled tiles: 1024 bytes between groups of eight rows (both for K-major operands and,
+// along K, for the MN-major V operand); layout code 2; descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16, float32 accumulator, bfloat16 operands; A K-major; B K-major or MN-major
+__device__ __forceinline__ uint32_t instr_desc(int m, int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+      "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// bounded wait that also gives up as soon as another thread has recorded a failure
+__device__ __forceinline__ bool wait_or_fail(uint32_t bar, uint32_t parity, volatile int* failed, int code, int* error_flag) {
+  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if ((i & 1023) == 1023 && *failed) return false;
+  }
+  *failed = code;
+  atomicExch(error_flag, code);
+  return false;
+}
+
+// 288 threads.  Warps 0..7 do the softmax: thread t works on row (t & 127); its half (t >> 7)
+// owns 64 of the tile's 128 key columns and 32 of the 64 output columns (warps w and w + 4 read
+// the same 32 lanes of tensor memory: the lane group is the warp index modulo 4).  Warp 8 issues
+// every TMA copy (one page per lane) and, from its first lane, every tcgen05.mma, so the softmax
+// warps never wait for serial work; the two sides meet on mbarriers only:
+//   k_full, v_full[2]   TMA -> controller          s_done, o_done   MMA -> softmax threads
+//   p_ready (256)       probabilities written, S read      o_read (256)   O_tile read
+__global__ void __launch_bounds__(THREADS, 2) paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                      const __grid_constant__ CUtensorMap map_v, const Params p) {
+  pdl_launch_dependents();
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sQ = smem;
+  unsigned char* sK = sQ + TILE_BYTES;          // one stage: refilled as soon as S = Q K^T is done
+  unsigned char* sV = sK + TILE_BYTES;          // two stages
+  unsigned char* sP = sV + 2 * TILE_BYTES;      // keys 0..63 | keys 64..127
+  float* row_max = (float*)(sP + 2 * TILE_BYTES);   // [2][128]: each half's maximum of the tile, later its sum
+  uint64_t* bars = (uint64_t*)(row_max + 2 * ROWS);  // k_full, v_full[2], s_done, o_done, p_ready, o_read
+  uint32_t* tmem_slot = (uint32_t*)(bars + 7);
+  volatile int* failed = (volatile int*)(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = tid & (ROWS - 1), half = (tid >> 7) & 1;
+  const uint32_t k_full = smem_u32(bars), v_full = smem_u32(bars + 1), s_done = smem_u32(bars + 3), o_done = smem_u32(bars + 4),
+                 p_ready = smem_u32(bars + 5), o_read = smem_u32(bars + 6);
+
+  const int s = p.seq0 + blockIdx.y;
+  const int tile = blockIdx.x;
+  const int kvh = blockIdx.z / p.head_chunks, hc = blockIdx.z - kvh * p.head_chunks;
+  const int q0 = p.q_start[s];
+  const int qlen = p.q_start[s + 1] - q0;
+  const int tok0 = tile * p.tokens_per_tile;
+  if (tok0 >= qlen) return;  // the whole CTA: nothing was set up yet
+  const int kvlen = p.kv_len[s];
+  const int ntok = min(p.tokens_per_tile, qlen - tok0);
+  const int G = p.nh / p.nkv, Gc = p.heads_per_chunk;
+  const int head0 = kvh * G + hc * Gc;
+  const int nheads = min(Gc, G - hc * Gc);
+  const int pos0 = kvlen - qlen + tok0;
+  const int rows_used = ntok * Gc;
+  const int* table = p.block_tables + (size_t)s * p.max_blocks;
+  const int hi = pos0 + ntok;
+  const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+  const int t_begin = lo / KEYS, t_end = (hi + KEYS - 1) / KEYS;
+  const int num_tiles = t_end - t_begin;
+
+  if (tid == 0) {
+    mbar_init(k_full, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_full + 8, 1);
+    mbar_init(s_done, 1);
+    mbar_init(o_done, 1);
+    mbar_init(p_ready, SOFTMAX_THREADS);
+    mbar_init(o_read, SOFTMAX_THREADS);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pdl_wait();  // queries and the cache are the work of the kernels before this one
+
+  // ---- Q tile, swizzled by hand: 16-byte chunk c of row r lies at r * 128 + ((c ^ (r & 7)) * 16);
+  //      rows beyond the used ones are zero.  Both value stages start as zeros: pages beyond the
+  //      sequence are never fetched, and their (masked) columns must not multiply garbage.
+  for (int idx = tid; idx < ROWS * 8; idx += THREADS) {
+    const int rr = idx >> 3, c = idx & 7;
+    const int tok = rr / Gc, hd = rr - tok * Gc;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (rr < rows_used && hd < nheads)
+      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + tok0 + tok) * p.q_stride + (size_t)(head0 + hd) * D + c * 8);
+    *reinterpret_cast<uint4*>(sQ + rr * 128 + ((c ^ (rr & 7)) << 4)) = v;
+  }
+  for (int idx = tid; idx < 2 * TILE_BYTES / 16; idx += THREADS) reinterpret_cast<uint4*>(sV)[idx] = make_uint4(0, 0, 0, 0);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + KEYS;
+
+  if (warp == SOFTMAX_THREADS / 32) {
+    // ================================================================ controller warp
+    // Lane 0 waits and issues the matrix products.  The copies of a tile are issued by the whole
+    // warp, one page per lane (lanes 0..15 keys, lanes 16..31 values): a single thread would spend
+    // microseconds on sixteen table look-ups and address computations per tile.
+    const int pages = KEYS / p.page_size;
+    const int page_i = lane & 15;
+    auto page_row = [&](int t) -> int {  // first row of this lane's page in the pools, or -1 if it is not needed
+      const int first = t * KEYS + page_i * p.page_size;
+      const bool need = page_i < pages && first < hi && first + p.page_size > lo;
+      return need ? (table[first / p.page_size] * p.nkv + kvh) * p.page_size : -1;
+    };
+    auto issue = [&](bool keys, int stage, int row) {  // called by the sixteen lanes of one side
+      const uint32_t bar = keys ? k_full : v_full + 8 * stage;
+      unsigned char* dst = keys ? sK : sV + stage * TILE_BYTES;
+      const unsigned side = keys ? 0x0000ffffu : 0xffff0000u;
+      const int count = __popc(__ballot_sync(side, row >= 0));
+      if (page_i == 0) mbar_expect_tx(bar, (uint32_t)(count * p.page_size * 128));
+      __syncwarp(side);
+      if (row >= 0) tma_load_2d(smem_u32(dst + page_i * p.page_size * 128), keys ? &map_k : &map_v, 0, row, bar);
+    };
+    const uint32_t idesc_s = instr_desc(ROWS, KEYS, 0), idesc_o = instr_desc(ROWS, D, 1);
+    if (num_tiles > 0) {
+      const int row = page_row(t_begin);
+      if (lane < 16) issue(true, 0, row); else issue(false, 0, row);
+    }
+    for (int it = 0; it < num_tiles; ++it) {
+      const int stage = it & 1;
+      if (lane == 0 && wait_or_fail(k_full, it & 1, failed, 11, p.error_flag)) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = smem_u32(sQ), b = smem_u32(sK);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma(tmem_s, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), idesc_s, k != 0);
+        umma_commit(s_done);
+      }
+      const int next_row = it + 1 < num_tiles ? page_row(t_begin + it + 1) : -1;  // looked up while the product runs
+      if (lane == 0) wait_or_fail(s_done, it & 1, failed, 12, p.error_flag);  // the key buffer is free again
+      __syncwarp();
+      if (*failed) break;
+      if (it + 1 < num_tiles && lane < 16) issue(true, 0, next_row);
+      // the other value stage was read by P V of tile it - 1
+      if (lane == 0 && it > 0) wait_or_fail(o_done, (it - 1) & 1, failed, 13, p.error_flag);
+      __syncwarp();
+      if (*failed) break;
+      if (it + 1 < num_tiles && lane >= 16) issue(false, stage ^ 1, next_row);
+      if (lane == 0 && wait_or_fail(p_ready, it & 1, failed, 15, p.error_flag) &&
+          wait_or_fail(v_full + 8 * stage, (it >> 1) & 1, failed, 14, p.error_flag) &&
+          (it == 0 || wait_or_fail(o_read, (it - 1) & 1, failed, 16, p.error_flag))) {  // O_tile of the tile before was read
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = smem_u32(sP), b = smem_u32(sV + stage * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < KEYS / 16; ++k)
+          umma(tmem_o, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(b + k * 2048), idesc_o, k != 0);
+        umma_commit(o_done);
+      }
+      __syncwarp();
+      if (*failed) break;
+    }
+  } else {
+    // ================================================================ softmax threads
+    const int rtok = r / Gc;
+    const bool rvalid = r < rows_used && (r - rtok * Gc) < nheads;
+    const int rpos = pos0 + rtok;
+    const uint32_t lane_bits = (uint32_t)((warp & 3) * 32) << 16;
+    const int col0 = half * 64;
+    float m = -CUDART_INF_F, l = 0.f;  // m: running maximum of the raw scores; l: this half's share of the row sum
+    float o[32];                       // output columns 32 * half .. 32 * half + 31 of the row
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j] = 0.f;
+
+    for (int it = 0; it < num_tiles; ++it) {
+      const int base = (t_begin + it) * KEYS;
+      bool ok = wait_or_fail(s_done, it & 1, failed, 12, p.error_flag);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // a tile that lies wholly at or before the first row's position, inside every row's window, needs no mask
+      const bool full = base + KEYS - 1 <= pos0 && base >= lo && p.window <= 0;
+      auto masked = [&](uint32_t raw, int key) -> float {
+        const bool vis = key <= rpos && (p.window <= 0 || key > rpos - p.window);
+        return vis ? __uint_as_float(raw) : -CUDART_INF_F;
+      };
+      // ---- pass 1: the maximum of this thread's 64 raw scores
+      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+      if (ok) {  // every lane takes part in the aligned tensor-memory loads, also for rows that hold no query
+#pragma unroll
+        for (int c = 0; c < 64; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_s + lane_bits + col0 + c, v);
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(v[j]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], masked(v[j], base + col0 + c + j));
+          }
+        }
+      }
+      if (!rvalid) mx[0] = mx[1] = mx[2] = mx[3] = -CUDART_INF_F;
+      row_max[half * ROWS + r] = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
+      const float mnew = fmaxf(m, fmaxf(row_max[r], row_max[ROWS + r]));
+      const float msafe = (mnew == -CUDART_INF_F) ? 0.f : mnew;
+      const float corr = ex2((m - msafe) * p.scale_log2);
+      const float neg = -msafe * p.scale_log2;
+      m = mnew;
+      // ---- pass 2: probabilities, their sum, and the bfloat16 tile for the P V product
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      if (ok) {
+        unsigned char* prow = sP + half * TILE_BYTES + r * 128;
+#pragma unroll
+        for (int c = 0; c < 64; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_s + lane_bits + col0 + c, v);
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              float a0, a1;
+              if (full) {
+                a0 = __uint_as_float(v[j + e]);
+                a1 = __uint_as_float(v[j + e + 1]);
+              } else {
+                a0 = masked(v[j + e], base + col0 + c + j + e);
+                a1 = masked(v[j + e + 1], base + col0 + c + j + e + 1);
+              }
+              const float p0 = rvalid ? ex2(fmaf(a0, p.scale_log2, neg)) : 0.f;  // masked: ex2(-inf) = 0
+              const float p1 = rvalid ? ex2(fmaf(a1, p.scale_log2, neg)) : 0.f;
+              sum[(e >> 1) & 3] += p0 + p1;
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+              packed[e >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+            }
+            *reinterpret_cast<uint4*>(prow + ((((c + j) >> 3) ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        }
+      }
+      l = l * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor cores
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(p_ready);  // P is written and S has been read: the controller may issue P V, and later the next Q K^T
+
+      ok = wait_or_fail(o_done, it & 1, failed, 13, p.error_flag) && ok;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (ok) {
+        uint32_t v[32];
+        tmem_ld32(tmem_o + lane_bits + half * 32, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], corr, __uint_as_float(v[j]));
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(o_read);
+    }
+
+    // ---- the row sum is the two halves' sums; each half writes its 32 output columns
+    row_max[half * ROWS + r] = l;
+    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
+    if (!*failed && rvalid) {
+      const float inv = 1.f / (row_max[r] + row_max[ROWS + r]);
+      const size_t row = (size_t)(q0 + tok0 + rtok) * p.nh + head0 + (r - rtok * Gc);
+      uint4* dst = reinterpret_cast<uint4*>(p.out + row * D + half * 32);
+#pragma unroll
+      for (int c = 0; c < 32; c += 8) {
+        uint4 w;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(o[c + 2 * e] * inv, o[c + 2 * e + 1] * inv);
+        dst[c >> 3] = w;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)ptr;
+  }
+  return fn;
+}
+// a pool [pages, nkv, page_size, 64] seen as rows of 64 elements; boxes of one page of one head
+bool make_pool_map(CUtensorMap* map, const void* base, long long rows, int page_size) {
+  EncodeTiled fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  cuuint32_t box[2] = {(cuuint32_t)D, (cuuint32_t)page_size};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int* error_flag_device = nullptr;
+int* error_flag_host = nullptr;
+
+}  // namespace
+
+// Sequences [seq0, seq0 + num_seqs) of a batch, each bringing at most max_q_len tokens.
+// Head size 64 only; page_size must be 8, 16, 32, 64 or 128; num_pages is the pools' first extent.
+DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
+                                    long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
+                                    const int* kv_len, int seq0, int num_seqs, int max_q_len, int nh, int nkv, int page_size,
+                                    int window, float scale, cudaStream_t stream) {
+  if (num_seqs == 0) return 0;
+  if (nkv < 1 || nh % nkv || page_size < 8 || page_size > 128 || (KEYS % page_size) != 0) return DLI_ERR_UNSUPPORTED;
+  if (((uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)q) & 15) return DLI_ERR_UNSUPPORTED;
+  if (!error_flag_host) {
+    if (cudaHostAlloc((void**)&error_flag_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return (int)cudaGetLastError();
+    *error_flag_host = 0;
+    if (cudaHostGetDevicePointer((void**)&error_flag_device, error_flag_host, 0) != cudaSuccess) return (int)cudaGetLastError();
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap map_k, map_v;
+  const long long rows = num_pages * nkv * page_size;
+  if (!make_pool_map(&map_k, k_pool, rows, page_size) || !make_pool_map(&map_v, v_pool, rows, page_size)) return DLI_ERR_UNSUPPORTED;
+  Params p;
+  p.out = (bf16*)out; p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.q_start = q_start; p.kv_len = kv_len; p.seq0 = seq0;
+  p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int G = nh / nkv;
+  p.heads_per_chunk = G < ROWS ? G : ROWS;
+  p.head_chunks = (G + p.heads_per_chunk - 1) / p.heads_per_chunk;
+  p.tokens_per_tile = ROWS / p.heads_per_chunk;
+  p.error_flag = error_flag_device;
+  const int tiles = (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
+  cudaError_t e = launch_pdl(paged_prefill_tc_kernel, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(THREADS), (size_t)SMEM_BYTES, stream, 1,
+                             map_k, map_v, p);
+  return (int)e;
+}
+
+// 0, or the code of the first bounded wait that ran out (11 keys, 12 scores, 13 output tile, 14 values,
+// 15 probabilities, 16 output tile read)
+DLI_EXPORT int dli_paged_prefill_tc_error() { return error_flag_host ? *error_flag_host : 0; }

@@ -1,9 +1,10 @@
 """Chooses the attention kernels of a step.
 
-float32: the CUDA-core kernel for every token (true 32-bit).  bfloat16: the tensor-core
-kernel where the head size is a multiple of 16 — launched once for the sequences that bring
-one token (keys split across CTAs when there are few sequences and long contexts) and once
-for the longer portions — and the CUDA-core kernel otherwise.
+float32: the CUDA-core kernel for every token (true 32-bit).  bfloat16: tensor-core kernels
+where the head size is a multiple of 16 — one launch for the sequences that bring one token
+(keys split across CTAs when there are few sequences and long contexts) and one for the longer
+portions, which takes the tcgen05 + TMA kernel when head and page size allow it and the
+mma.sync kernel otherwise — and the CUDA-core kernel for any other head size.
 """
 
 from __future__ import annotations
@@ -42,6 +43,9 @@ def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_head
                        torch.empty(rows * splits * 2, dtype=torch.float32, device=out.device))
         ops.paged_attention_mma(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, 0, singles, 1, 0,
                                 num_heads, scale, window, splits, scratch)
-    if total > singles:
+    if total > singles and ops.prefill_tc_supported(d, cache.page_size):
+        ops.paged_prefill_tc(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, singles, total - singles,
+                             batch.max_q_len, num_heads, scale, window)
+    elif total > singles:
         ops.paged_attention_mma(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, singles,
                                 total - singles, batch.max_q_len, singles, num_heads, scale, window)

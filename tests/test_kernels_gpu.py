@@ -223,13 +223,39 @@ def test_paged_attention_mma(nh, nkv, d, page, window, splits):
     np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2))
 
 
+PREFILL_MIX = [(0, 37), (40, 2), (64, 64), (3, 130), (255, 300), (16, 17), (700, 129), (0, 128)]
+
+
+@pytest.mark.parametrize("nh,nkv,page", [(8, 2, 16), (3, 1, 8), (5, 5, 32), (4, 4, 128), (32, 8, 64), (130, 1, 16)])
+@pytest.mark.parametrize("window", [None, 70, 200])
+def test_paged_prefill_tc(nh, nkv, page, window):
+    """The tcgen05 + TMA prefill kernel: portions that start anywhere, cross tile and page edges,
+    with GQA groups from 1 to 130 heads per KV head."""
+    d = 64
+    t = attention_case(nh, nkv, d, page, PREFILL_MIX, torch.bfloat16, seed=nh + page)
+    out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_prefill_tc(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(PREFILL_MIX),
+                         max(q for _, q in PREFILL_MIX), nh, d**-0.5, window)
+    want = plain_attention(t, PREFILL_MIX, nh, window)
+    np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2))
+    assert ops.paged_prefill_tc_error() == 0
+
+
+def test_prefill_tc_refuses_other_sizes():
+    t = attention_case(2, 1, 32, 16, [(0, 4)], torch.bfloat16)
+    out = torch.empty((4, 64), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops.KernelError, match="head_dim"):
+        ops.paged_prefill_tc(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, 1, 4, 2, 1.0)
+    assert not ops.prefill_tc_supported(64, 4) and not ops.prefill_tc_supported(64, 48)
+
+
 def test_mma_rejects_other_head_sizes():
     t = attention_case(2, 1, 24, 8, [(0, 4)], torch.bfloat16)
     with pytest.raises(ops.KernelError, match="multiple of 16"):
         run_mma(t, [(0, 4)], 2, 24, None)
 
 
-@pytest.mark.parametrize("kernel", ["simt-f32", "simt-bf16", "mma"])
+@pytest.mark.parametrize("kernel", ["simt-f32", "simt-bf16", "mma", "tc"])
 @pytest.mark.parametrize("where", ["far_key", "page_first", "page_last", "tile_edge_63", "tile_edge_64", "window_inside", "window_outside", "self"])
 def test_one_key_stands_out(kernel, where):
     """The query of one token matches one key so strongly that the output is that key's value.
@@ -249,6 +275,9 @@ def test_one_key_stands_out(kernel, where):
     t = attention_case(nh, nkv, d, page, seqs, dtype, seed=11, sharp=(1, token, key))
     if kernel == "mma":
         out = run_mma(t, seqs, nh, d, window)
+    elif kernel == "tc":
+        out = run_mma(t, seqs[:1], nh, d, window)  # the single-token sequence
+        ops.paged_prefill_tc(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 1, 1, qlen, nh, d**-0.5, window)
     else:
         out = torch.empty(t["n"], nh * d, dtype=dtype, device=DEV)
         ops.paged_attention_simt(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["seq_of_token"], t["positions"], nh, d**-0.5, window)
