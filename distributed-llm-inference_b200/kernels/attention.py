@@ -13,16 +13,17 @@ import torch
 
 from . import ops
 
-TARGET_CTAS = 148 * 2  # the decode kernel keeps one CTA of four warps per SM busy; two rounds fill the tail
-MIN_TILES_PER_SPLIT = 8  # key tiles (of 64) a split should at least cover: two for each of its warps
+ONE_WAVE = 148 * 2  # CTAs of the decode kernel that are resident at once (two per SM in its few-sequences shape)
+MIN_TILES_PER_SPLIT = 2  # key tiles (of 64) a split should at least cover
 
 
 def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int) -> int:
-    """Key splits for single-token sequences: as many as fill the GPU, none shorter than
+    """Key splits for single-token sequences: as many as still fit the GPU in one wave (a second,
+    partly filled wave costs more than the extra parallelism brings), none shorter than
     MIN_TILES_PER_SPLIT key tiles (the role of src/dli/model/paged_attention.py:63-74)."""
+    pairs = max(1, num_seqs * ctas_per_seq)
     tiles = -(-max_kv_len // 64)
-    want = -(-TARGET_CTAS // max(1, num_seqs * ctas_per_seq))
-    return max(1, min(want, tiles // MIN_TILES_PER_SPLIT))
+    return max(1, min(ONE_WAVE // pairs, tiles // MIN_TILES_PER_SPLIT))
 
 
 def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_heads: int, scale: float, window: int | None) -> None:

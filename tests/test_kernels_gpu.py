@@ -295,8 +295,8 @@ def test_one_key_stands_out(kernel, where):
 
 def test_choose_splits():
     assert choose_splits(64, 8, 4096) == 1
-    assert choose_splits(8, 8, 4096) == 5
-    assert choose_splits(1, 8, 4096) == 8
+    assert choose_splits(8, 8, 4096) == 4
+    assert choose_splits(1, 8, 4096) == 32
     assert choose_splits(1, 8, 100) == 1
     assert choose_splits(1000, 8, 100000) == 1
 
