@@ -271,30 +271,46 @@ DLI_EXPORT int dli_rotary_store(void* qkv, const int* positions, const float* in
 }
 
 // ---------------------------------------------------------------- silu(gate) * up
-// gu: [n, 2 I] with gate in columns [0, I) and up in [I, 2 I); out: [n, I].
+// gu: [n, 2 I]; out: [n, I].  Plain layout: gate in columns [0, I), up in [I, 2 I).  Tiled layout
+// (the one the decode matrix product's fused epilogue wants of the weights): blocks of 128 columns,
+// gate features 64 j .. 64 j + 63 in columns 128 j .., their up features in columns 128 j + 64 ...
+__device__ __forceinline__ void gate_up_columns(int i, int I, int tiled, int& g, int& u) {
+  if (tiled) {
+    g = (i >> 6) * 128 + (i & 63);
+    u = g + 64;
+  } else {
+    g = i;
+    u = I + i;
+  }
+}
+
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int n, int I) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int n, int I, int tiled) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t total = (size_t)n * I;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
     const int i = (int)(idx - t * I);
-    const float g = to_float(gu[t * 2 * I + i]);
-    const float u = to_float(gu[t * 2 * I + I + i]);
+    int gc, uc;
+    gate_up_columns(i, I, tiled, gc, uc);
+    const float g = to_float(gu[t * 2 * I + gc]);
+    const float u = to_float(gu[t * 2 * I + uc]);
     out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
   }
 }
 
 // bfloat16, I % 8 == 0: one 16-byte load of gate and of up, one 16-byte store, per thread
-__global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I) {
+__global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I, int tiled) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= I / 8) return;
-  const uint4 g = reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * I)[i];
-  const uint4 u = reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * I + I)[i];
+  int gc, uc;
+  gate_up_columns(i * 8, I, tiled, gc, uc);  // eight columns never cross a block of 64
+  const uint4 g = *reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * I + gc);
+  const uint4 u = *reinterpret_cast<const uint4*>(gu + (size_t)t * 2 * I + uc);
   const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
   const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
   uint4 r;
@@ -307,19 +323,20 @@ __global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const 
   reinterpret_cast<uint4*>(out + (size_t)t * I)[i] = r;
 }
 
-DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int dtype, cudaStream_t stream) {
+DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int tiled, int dtype, cudaStream_t stream) {
+  if (tiled && (I % 64)) return DLI_ERR_UNSUPPORTED;
   if (n == 0) return 0;
   if (dtype == DLI_BF16 && I % 8 == 0 && n <= 65535) {
     dim3 grid((I / 8 + 255) / 256, n);
-    launch_pdl((silu_mul_bf16_vec_kernel), dim3(grid), dim3(256), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I);
+    launch_pdl((silu_mul_bf16_vec_kernel), dim3(grid), dim3(256), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, tiled);
     return (int)cudaGetLastError();
   }
   const size_t total = (size_t)n * I;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == DLI_F32)
-    launch_pdl((silu_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, 1, (float*)out, (const float*)gu, n, I);
+    launch_pdl((silu_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, 1, (float*)out, (const float*)gu, n, I, tiled);
   else
-    launch_pdl((silu_mul_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I);
+    launch_pdl((silu_mul_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I, tiled);
   return (int)cudaGetLastError();
 }

@@ -12,7 +12,8 @@
 //     stage) into an accumulator in tensor memory; tcgen05.commit frees the stage and, at the
 //     end, signals the epilogue;
 //   * four warps read the accumulator with tcgen05.ld (lane = feature, column = token) and
-//     store, coalesced along features.
+//     store, coalesced along features — or finish the layer's next elementwise step in place:
+//     SiLU(gate) * up, or the rotary embedding with the write of keys and values into the cache.
 //
 // The grid is (feature tiles, K slices).  Slices exist to fill the GPU when a matrix has few
 // feature tiles.  The CTAs of one tile's slices form a thread-block cluster (up to 8): each
@@ -96,6 +97,59 @@ __device__ __forceinline__ void store_out(void* out, int out_f32, size_t idx, fl
   else ((__nv_bfloat16*)out)[idx] = __float2bfloat16_rn(v);
 }
 
+// What happens to the finished sums of a tile.
+//   EP_STORE   out[t, f] = sum                                   (bfloat16 or float32)
+//   EP_SWIGLU  the weight rows were interleaved in blocks of 64 (64 gate rows, then the 64 up rows of the
+//              same features), so a tile holds both: out[t, 64 * tile + i] = silu(gate_i) * up_i
+//   EP_ROTARY  the features are q | k | v heads of size d (d divides 128, so a head never straddles tiles):
+//              q and k are rotated by the token's position (rotate-half pairing over the first `rot`
+//              elements), q goes to out[t, nh * d], k and v into the cache pages at the token's slot
+enum { EP_STORE = 0, EP_SWIGLU = 1, EP_ROTARY = 2 };
+struct Epilogue {
+  int mode;
+  const int* positions;
+  const float* inv_freq;
+  const int* slots;
+  __nv_bfloat16* k_pool;
+  __nv_bfloat16* v_pool;
+  int nh, nkv, d, rot, page_size, write_kv;
+};
+
+// fin: this token's 128 finished sums of the tile; fl: the feature of this thread
+__device__ __forceinline__ void fused_epilogue(const Epilogue& ep, void* out, const float* fin, int t, int tile, int fl, int features) {
+  if (ep.mode == EP_SWIGLU) {
+    const int I = features >> 1, col = tile * 64 + fl;
+    if (fl < 64 && col < I) {
+      const float g = fin[fl], u = fin[fl + 64];
+      ((__nv_bfloat16*)out)[(size_t)t * I + col] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+    }
+    return;
+  }
+  const int f = tile * BM + fl;
+  if (f >= features) return;
+  const int head = f / ep.d, i = f - head * ep.d;
+  float val = fin[fl];
+  if (head < ep.nh + ep.nkv && i < ep.rot) {
+    const int half = ep.rot >> 1;
+    const bool low = i < half;
+    const float other = fin[low ? fl + half : fl - half];
+    float sn, cs;
+    sincosf((float)ep.positions[t] * ep.inv_freq[low ? i : i - half], &sn, &cs);
+    val = low ? val * cs - other * sn : val * cs + other * sn;
+  }
+  const __nv_bfloat16 b = __float2bfloat16_rn(val);
+  if (head < ep.nh) {
+    ((__nv_bfloat16*)out)[((size_t)t * ep.nh + head) * ep.d + i] = b;
+    return;
+  }
+  const int slot = ep.write_kv ? ep.slots[t] : -1;
+  if (slot < 0) return;
+  const int page = slot / ep.page_size, off = slot - page * ep.page_size;
+  const int kvh = head - ep.nh;
+  if (kvh < ep.nkv) ep.k_pool[(((size_t)page * ep.nkv + kvh) * ep.page_size + off) * ep.d + i] = b;
+  else ep.v_pool[(((size_t)page * ep.nkv + (kvh - ep.nkv)) * ep.page_size + off) * ep.d + i] = b;
+}
+
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -110,7 +164,7 @@ __device__ __forceinline__ float ld_peer_shared(uint32_t local_addr, uint32_t ct
 __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
                                                           int out_f32, int tokens, int features, int k_tiles, int tiles_per_slice,
-                                                          int npad, int stages, int tmem_cols, int* error_flag) {
+                                                          int npad, int stages, int tmem_cols, int* error_flag, const Epilogue ep) {
   pdl_launch_dependents();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -213,6 +267,11 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   // with several slices the partial sums go to shared memory, [token][feature of the tile];
   // the pipeline stages are free by now (every MMA that read them has finished)
   float* red = reinterpret_cast<float*>(smem);
+  const bool fused = ep.mode != EP_STORE;
+  // finished sums of the tokens this CTA owns, [owned token][feature of the tile], for the fused
+  // epilogues (they combine features): behind the partial sums, or the partial sums themselves
+  // when there is one slice only
+  float* fin = slices > 1 ? red + npad * BM : red;
   const int tok8 = (tokens + 7) & ~7;
   for (int c = 0; c < npad && c < tok8; c += 8) {
     uint32_t r[8];
@@ -229,7 +288,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       if (c + j >= tokens) continue;
-      if (slices > 1) red[(c + j) * BM + fl] = __uint_as_float(r[j]);
+      if (slices > 1 || fused) red[(c + j) * BM + fl] = __uint_as_float(r[j]);
       else if (f < features) store_out(out, out_f32, (size_t)(c + j) * features + f, __uint_as_float(r[j]));
     }
   }
@@ -254,11 +313,17 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
         float acc = 0.f;
 #pragma unroll
         for (int s2 = 0; s2 < 8; ++s2) acc += v[i][s2];  // slice 0 first; absent slices add exact zeros
-        if (t < tokens && f < features) store_out(out, out_f32, (size_t)t * features + f, acc);
+        if (t >= tokens) continue;
+        if (fused) fin[((t - slice) / slices) * BM + fl] = acc;
+        else if (f < features) store_out(out, out_f32, (size_t)t * features + f, acc);
       }
     }
-    cluster_sync();  // nobody leaves while a peer may still read its shared memory
   }
+  if (fused) {
+    __syncthreads();  // the finished sums of every feature of the tile are in place
+    for (int t = slice, ti = 0; t < tokens; t += slices, ++ti) fused_epilogue(ep, out, fin + ti * BM, t, tile, fl, features);
+  }
+  if (slices > 1) cluster_sync();  // nobody leaves while a peer may still read its shared memory
 
   // ---- teardown: nobody touches tensor memory after this barrier; warp 0 frees it
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -314,8 +379,8 @@ DLI_EXPORT int dli_skinny_gemm_slices(int tokens, int features, int K) {
   return (k_tiles + per - 1) / per;  // no empty slice
 }
 
-DLI_EXPORT int dli_skinny_gemm(void* out, int out_f32, const void* x, const void* w, int tokens, int features, int K,
-                               int slices, int max_stages, cudaStream_t stream) {
+static int launch_skinny(void* out, int out_f32, const void* x, const void* w, int tokens, int features, int K, int slices,
+                         int max_stages, const Epilogue& ep, cudaStream_t stream) {
   if (tokens < 1 || tokens > 256 || features < 1 || K < 8 || K % 8 || slices < 1 || slices > 8) return DLI_ERR_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return DLI_ERR_UNSUPPORTED;
   if (!error_flag_host) {
@@ -335,7 +400,10 @@ DLI_EXPORT int dli_skinny_gemm(void* out, int out_f32, const void* x, const void
   if (max_stages > 0 && stages > max_stages) stages = max_stages;
   while (stages > 2 && stages * stage_bytes > budget) --stages;
   if (stages < 1) stages = 1;
-  while (slices > 1 && stages * stage_bytes < npad * BM * 4) ++stages;  // room for the partial sums [npad][128] float32
+  // room for the partial sums [npad][128] and, for a fused epilogue, the finished sums of the owned tokens
+  const int owned = (tokens + slices - 1) / slices;
+  const int scratch = (slices > 1 || ep.mode != EP_STORE ? npad * BM * 4 : 0) + (slices > 1 && ep.mode != EP_STORE ? owned * BM * 4 : 0);
+  while (stages * stage_bytes < scratch) ++stages;
   const int smem = stages * stage_bytes + (2 * stages + 1) * 8 + 16 + 1024;
   int tmem_cols = 32;
   while (tmem_cols < npad) tmem_cols <<= 1;
@@ -346,8 +414,40 @@ DLI_EXPORT int dli_skinny_gemm(void* out, int out_f32, const void* x, const void
     configured = smem;
   }
   cudaError_t e = launch_pdl(skinny_gemm_kernel, dim3((features + BM - 1) / BM, slices), dim3(128), (size_t)smem, stream, slices, map_w,
-                             map_x, out, out_f32, tokens, features, k_tiles, per, npad, stages, tmem_cols, error_flag_device);
+                             map_x, out, out_f32, tokens, features, k_tiles, per, npad, stages, tmem_cols, error_flag_device, ep);
   return (int)(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+DLI_EXPORT int dli_skinny_gemm(void* out, int out_f32, const void* x, const void* w, int tokens, int features, int K,
+                               int slices, int max_stages, cudaStream_t stream) {
+  Epilogue ep = {};
+  ep.mode = EP_STORE;
+  return launch_skinny(out, out_f32, x, w, tokens, features, K, slices, max_stages, ep, stream);
+}
+
+// act[tokens, features / 2] = silu(gate) * up, for weights whose rows are interleaved in blocks of 64
+// (rows 128 j .. 128 j + 63: gate features 64 j .., rows 128 j + 64 .. 128 j + 127: the same up features).
+DLI_EXPORT int dli_skinny_gemm_swiglu(void* act, const void* x, const void* w, int tokens, int features, int K, int slices,
+                                      cudaStream_t stream) {
+  if (features % 128) return DLI_ERR_UNSUPPORTED;
+  Epilogue ep = {};
+  ep.mode = EP_SWIGLU;
+  return launch_skinny(act, 0, x, w, tokens, features, K, slices, 0, ep, stream);
+}
+
+// q | k | v projection with the rotary embedding and the cache write in the epilogue: q_out [tokens, nh * d]
+// receives the rotated queries; keys (rotated) and values go to the pools [pages, nkv, page_size, d] at slots[t].
+DLI_EXPORT int dli_skinny_gemm_rotary(void* q_out, const void* x, const void* w, int tokens, int K, int slices, const int* positions,
+                                      const float* inv_freq, const int* slots, void* k_pool, void* v_pool, int nh, int nkv, int d,
+                                      int rot, int page_size, int write_kv, cudaStream_t stream) {
+  if (d < 2 || (BM % d) != 0 || rot < 0 || rot > d || (rot & 1) || (rot > 0 && !inv_freq)) return DLI_ERR_UNSUPPORTED;
+  if (write_kv && (!slots || !k_pool || !v_pool)) return DLI_ERR_UNSUPPORTED;
+  Epilogue ep = {};
+  ep.mode = EP_ROTARY;
+  ep.positions = positions; ep.inv_freq = inv_freq; ep.slots = slots;
+  ep.k_pool = (__nv_bfloat16*)k_pool; ep.v_pool = (__nv_bfloat16*)v_pool;
+  ep.nh = nh; ep.nkv = nkv; ep.d = d; ep.rot = rot; ep.page_size = page_size; ep.write_kv = write_kv;
+  return launch_skinny(q_out, 0, x, w, tokens, (nh + 2 * nkv) * d, K, slices, 0, ep, stream);
 }
 
 // 0, or the code of the first wait that ran out (1 producer, 2 MMA issuer, 3 epilogue)

@@ -21,11 +21,28 @@ torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 SKINNY_MAX_TOKENS = 64
 
 
+def decode_product(x: torch.Tensor) -> bool:
+    """Whether a product with these activations goes to the engine's own decode kernel."""
+    from . import ops
+
+    return x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_TOKENS and ops.skinny_gemm_supported(x.shape[0], x.shape[1])
+
+
+# Up to this many tokens the decode product also finishes the next elementwise step (rotary and
+# cache write, SiLU * up) in its epilogue; with more tokens per CTA the separate kernels, which
+# spread that work over the whole GPU, are faster.
+FUSED_EPILOGUE_MAX_TOKENS = 16
+
+
+def fused_epilogue(x: torch.Tensor) -> bool:
+    return decode_product(x) and x.shape[0] <= FUSED_EPILOGUE_MAX_TOKENS
+
+
 def project(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """y = x W^T for a step's tokens, in x's dtype or in ``out_dtype`` (float32 for logits)."""
     from . import ops
 
-    if x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_TOKENS and ops.skinny_gemm_supported(x.shape[0], x.shape[1]):
+    if decode_product(x):
         return ops.skinny_gemm(x, weight, out_dtype or x.dtype)
     y = linear(x, weight)
     return y if out_dtype in (None, y.dtype) else y.to(out_dtype)

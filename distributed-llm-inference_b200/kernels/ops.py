@@ -172,14 +172,15 @@ def rotary_store(
     )
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
-    """out[n, I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, tiled: bool = False) -> None:
+    """out[n, I] = silu(gate) * up.  gate_up [n, 2 I] holds gate | up side by side, or, ``tiled``
+    (I a multiple of 64), blocks of 128 columns: 64 gate features, then the same 64 up features."""
     _need(out, "out"), _need(gate_up, "gate_up", out.dtype)
     n, I = out.shape
-    if out.dtype not in DT_CODE or tuple(gate_up.shape) != (n, 2 * I):
+    if out.dtype not in DT_CODE or tuple(gate_up.shape) != (n, 2 * I) or (tiled and I % 64):
         raise KernelError("silu_mul: shapes or dtype do not agree")
-    f = _fn("elementwise.cu", "dli_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(out), _ptr(gate_up), n, I, DT_CODE[out.dtype], _stream()), "silu_mul")
+    f = _fn("elementwise.cu", "dli_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(gate_up), n, I, int(tiled), DT_CODE[out.dtype], _stream()), "silu_mul")
 
 
 # ------------------------------------------------------------------ attention
@@ -412,6 +413,52 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
     f = _fn("skinny_gemm.cu", "dli_skinny_gemm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(out), int(out_dtype == torch.float32), _ptr(x), _ptr(weight), tokens, features, K, slices, max_stages, _stream()), "skinny_gemm")
     return out
+
+
+def skinny_gemm_swiglu(x: torch.Tensor, weight_tiled: torch.Tensor) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) in one kernel: the decode matrix product with the activation in its
+    epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate rows, then the 64 up rows of
+    the same features.  Returns bfloat16 [tokens, I]."""
+    _need(x, "x", torch.bfloat16), _need(weight_tiled, "weight", torch.bfloat16)
+    tokens, K = x.shape
+    features = weight_tiled.shape[0]
+    if weight_tiled.shape[1] != K or features % 128 or not skinny_gemm_supported(tokens, K):
+        raise KernelError("skinny_gemm_swiglu: sizes not supported")
+    out = torch.empty((tokens, features // 2), dtype=torch.bfloat16, device=x.device)
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(weight_tiled), tokens, features, K, skinny_gemm_slices(tokens, features, K), _stream()), "skinny_gemm_swiglu")
+    return out
+
+
+def skinny_rotary_supported(head_dim: int) -> bool:
+    return head_dim >= 2 and 128 % head_dim == 0
+
+
+def skinny_gemm_rotary(x, wqkv, positions, inv_freq, slots, k_pool, v_pool, num_heads: int, num_kv_heads: int, head_dim: int,
+                       rotary_dim: int, page_size: int, write_kv: bool) -> torch.Tensor:
+    """q | k | v = x Wqkv^T with the rotary embedding and the write of keys and values into the
+    cache pages done in the product's epilogue; returns the rotated queries [tokens, nh * d]."""
+    _need(x, "x", torch.bfloat16), _need(wqkv, "wqkv", torch.bfloat16), _need(positions, "positions", torch.int32)
+    tokens, K = x.shape
+    features = (num_heads + 2 * num_kv_heads) * head_dim
+    if tuple(wqkv.shape) != (features, K) or not skinny_gemm_supported(tokens, K) or not skinny_rotary_supported(head_dim):
+        raise KernelError("skinny_gemm_rotary: sizes not supported")
+    if rotary_dim:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("skinny_gemm_rotary: inv_freq must have rotary_dim / 2 entries")
+    if write_kv:
+        _need(slots, "slots", torch.int32), _need(k_pool, "k_pool", torch.bfloat16), _need(v_pool, "v_pool", torch.bfloat16)
+        if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, head_dim) or k_pool.shape != v_pool.shape or slots.numel() != tokens:
+            raise KernelError("skinny_gemm_rotary: pool layout must be [pages, kv_heads, page_size, head_dim]")
+    q = torch.empty((tokens, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_rotary",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
+    _check(f(_ptr(q), _ptr(x), _ptr(wqkv), tokens, K, skinny_gemm_slices(tokens, features, K), _ptr(positions),
+             _ptr(inv_freq if rotary_dim else None), _ptr(slots if write_kv else None), _ptr(k_pool if write_kv else None),
+             _ptr(v_pool if write_kv else None), num_heads, num_kv_heads, head_dim, rotary_dim, page_size, int(write_kv), _stream()),
+           "skinny_gemm_rotary")
+    return q
 
 
 def skinny_gemm_error() -> int:

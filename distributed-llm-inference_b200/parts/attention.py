@@ -56,8 +56,11 @@ class GQAttention(Part):
         return PagedKVNeed(self.nkv, self.d, self.window)
 
     def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
-        qkv = project(x, self.wqkv)
-        q = self.position.rotate_and_store(qkv, batch, cache, self.nh, self.nkv, cache.writes)
+        encode = getattr(self.position, "project_and_encode", None)
+        if encode is not None:  # the position part may fuse the projection with its encoding
+            q = encode(x, self.wqkv, batch, cache, self.nh, self.nkv, cache.writes)
+        else:
+            q = self.position.rotate_and_store(project(x, self.wqkv), batch, cache, self.nh, self.nkv, cache.writes)
         out = torch.empty((x.shape[0], self.nh * self.d), dtype=x.dtype, device=x.device)
         attn_kernels.paged_attention(out, q, cache, batch, self.nh, self.scale, self.window)
         return project(out, self.wo)

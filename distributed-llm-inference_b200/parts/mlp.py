@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from ..kernels.gemm import project
+from ..kernels.gemm import fused_epilogue, project
 from ..weights.loader import TensorDecl
 from .base import Part, register_part
 
@@ -13,7 +13,9 @@ from .base import Part, register_part
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
     """down(silu(gate(x)) * up(x)) (src/dli/model/llama.py:189-191).  gate and up are read by
-    their own names and stacked at load, so one product yields gate | up.
+    their own names and laid together at load, so one product yields both: side by side, or —
+    when the intermediate size is a multiple of 64 — interleaved in blocks of 64 rows, the layout
+    in which the decode product applies SiLU(gate) * up in its own epilogue.
     params: hidden_size, intermediate_size."""
 
     def __init__(self, spec, env) -> None:
@@ -21,6 +23,7 @@ class SwiGLU(Part):
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
         self.w_gate_up: torch.Tensor | None = None
+        self.tiled = False
         self.w_down: torch.Tensor | None = None
 
     def declare(self):
@@ -33,11 +36,20 @@ class SwiGLU(Part):
 
     def load(self, tensors):
         px = self.spec.prefix
-        self.w_gate_up = torch.cat([tensors[px + "gate_proj.weight"], tensors[px + "up_proj.weight"]], 0).contiguous()
+        gate, up = tensors[px + "gate_proj.weight"], tensors[px + "up_proj.weight"]
+        self.tiled = self.inter % 64 == 0 and self.env.dtype == torch.bfloat16
+        if self.tiled:
+            blocks = self.inter // 64
+            self.w_gate_up = torch.stack([gate.view(blocks, 64, self.hidden), up.view(blocks, 64, self.hidden)], 1).reshape(2 * self.inter, self.hidden).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], 0).contiguous()
         self.w_down = tensors[px + "down_proj.weight"]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gate_up = project(x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        ops.silu_mul(act, gate_up)
+        if self.tiled and fused_epilogue(x):
+            act = ops.skinny_gemm_swiglu(x, self.w_gate_up)
+        else:
+            gate_up = project(x, self.w_gate_up)
+            act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+            ops.silu_mul(act, gate_up, self.tiled)
         return project(act, self.w_down)

@@ -7,6 +7,7 @@ import math
 import torch
 
 from ..kernels import ops
+from ..kernels.gemm import fused_epilogue, project
 from .base import Part, register_part
 
 
@@ -44,6 +45,16 @@ def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head
     return qkv
 
 
+def _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq):
+    """q | k | v projection followed by position encoding and cache write; for a decode step's few
+    tokens both happen in one kernel (the product's epilogue rotates and writes the cache)."""
+    if fused_epilogue(x) and ops.skinny_rotary_supported(head_dim):
+        group = batch.group(cache.group)
+        return ops.skinny_gemm_rotary(x, wqkv, batch.positions, inv_freq, group.slots, cache.k, cache.v, num_heads, num_kv_heads,
+                                      head_dim, rotary_dim, cache.page_size, write_kv)
+    return _rotate_and_store(project(x, wqkv), batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq)
+
+
 @register_part("position", "rotary")
 class Rotary(Part):
     """params: head_dim, rotary_dim (<= head_dim; elements beyond it pass through), theta,
@@ -61,6 +72,9 @@ class Rotary(Part):
     def rotate_and_store(self, qkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
         return _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, self.rotary_dim, self.inv_freq)
 
+    def project_and_encode(self, x, wqkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
+        return _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, self.rotary_dim, self.inv_freq)
+
 
 @register_part("position", "none")
 class NoPosition(Part):
@@ -72,3 +86,6 @@ class NoPosition(Part):
 
     def rotate_and_store(self, qkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
         return _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, 0, None)
+
+    def project_and_encode(self, x, wqkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
+        return _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, 0, None)

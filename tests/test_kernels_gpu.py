@@ -52,6 +52,10 @@ def test_add_rmsnorm(dtype, H):
     ops.add_rmsnorm(y, h1, delta, w, eps)
     np.testing.assert_allclose(h1.cpu().numpy(), want_h.float().cpu().numpy(), rtol=1e-6, atol=1e-6)
     np.testing.assert_allclose(y.float().cpu().numpy(), want_y, atol=tol(dtype, 4))
+    # rows so small that eps decides the scale
+    hs = h * 1e-3
+    ops.add_rmsnorm(y, hs.clone(), None, w, 1e-5)
+    np.testing.assert_allclose(y.float().cpu().numpy(), plain.rms_norm(hs.double().cpu().numpy(), w.double().cpu().numpy(), 1e-5), atol=tol(dtype, 4))
     # without delta the stream is left alone
     h2 = h.clone()
     ops.add_rmsnorm(y, h2, None, w, eps)
@@ -388,3 +392,44 @@ def test_skinny_gemm_refuses_what_it_cannot_do():
         ops.skinny_gemm(x, w)
     with pytest.raises(ops.KernelError):
         ops.skinny_gemm(rnd(300, 64, dtype=torch.bfloat16), rnd(8, 64, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("tokens,I,K,slices_hint", [(1, 64, 96, 1), (8, 192, 200, 2), (33, 1024, 2048, 3), (64, 128, 520, 8)])
+def test_skinny_gemm_with_swiglu_epilogue(tokens, I, K, slices_hint):
+    x = rnd(tokens, K, dtype=torch.bfloat16, seed=I)
+    gate = rnd(I, K, dtype=torch.bfloat16, seed=I + 1, scale=0.1)
+    up = rnd(I, K, dtype=torch.bfloat16, seed=I + 2, scale=0.1)
+    tiled = torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], 1).reshape(2 * I, K).contiguous()
+    got = ops.skinny_gemm_swiglu(x, tiled)
+    g = x.double() @ gate.double().T
+    u = x.double() @ up.double().T
+    want = (plain.silu(g.cpu().numpy()) * u.cpu().numpy())
+    np.testing.assert_allclose(got.double().cpu().numpy(), want, atol=8e-3 * max(1.0, np.abs(want).max()))
+    # and the stand-alone kernel reads the same tiled layout
+    gu = (x.float() @ tiled.float().T).to(torch.bfloat16)
+    out = torch.empty(tokens, I, dtype=torch.bfloat16, device=DEV)
+    ops.silu_mul(out, gu, tiled=True)
+    np.testing.assert_allclose(out.double().cpu().numpy(), want, atol=2e-2 * max(1.0, np.abs(want).max()))
+    assert ops.skinny_gemm_error() == 0
+
+
+@pytest.mark.parametrize("nh,nkv,d,rot,page", [(5, 1, 64, 64, 8), (4, 2, 16, 16, 4), (3, 3, 32, 16, 16), (2, 1, 128, 128, 16), (6, 2, 64, 0, 32)])
+def test_skinny_gemm_with_rotary_epilogue(nh, nkv, d, rot, page):
+    """The fused projection + rotary + cache write against the separate kernels."""
+    tokens, K, pages = 7, 264, 6
+    x = rnd(tokens, K, dtype=torch.bfloat16, seed=nh)
+    w = rnd((nh + 2 * nkv) * d, K, dtype=torch.bfloat16, seed=d, scale=0.1)
+    positions = torch.tensor([0, 1, 63, 64, 4095, 100000, 17], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([5, 8, pages * page - 1, 0, 16, -1, 22], dtype=torch.int32, device=DEV)
+    inv = torch.from_numpy(plain.inverse_frequencies({"head_dim": rot, "theta": 10000.0, "rope_type": "default"})).to(DEV) if rot else None
+    kp1, vp1 = (torch.full((pages, nkv, page, d), 9.0, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    kp2, vp2 = kp1.clone(), vp1.clone()
+    q = ops.skinny_gemm_rotary(x, w, positions, inv, slots, kp1, vp1, nh, nkv, d, rot, page, True)
+    qkv = (x.float() @ w.float().T)  # float32 product, then the stand-alone kernel on its bfloat16 rounding
+    ref = qkv.to(torch.bfloat16).contiguous()
+    ops.rotary_store(ref, positions, inv, slots, kp2, vp2, nh, nkv, d, rot, page, True)
+    t2 = 2e-2 * max(1.0, float(qkv.abs().max()))
+    np.testing.assert_allclose(q.float().cpu().numpy(), ref[:, : nh * d].float().cpu().numpy(), atol=t2)
+    np.testing.assert_allclose(kp1.float().cpu().numpy(), kp2.float().cpu().numpy(), atol=t2)
+    np.testing.assert_allclose(vp1.float().cpu().numpy(), vp2.float().cpu().numpy(), atol=t2)
+    assert ops.skinny_gemm_error() == 0
