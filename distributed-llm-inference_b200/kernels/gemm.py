@@ -16,33 +16,36 @@ torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
 
 
-# Up to this many tokens a bfloat16 product is bound by reading the weights once and goes to the
-# engine's own tcgen05 kernel; beyond it the library's large-tile kernels are the better choice.
-SKINNY_MAX_TOKENS = 64
+# Up to this many tokens a layer's bfloat16 products go to the engine's own tcgen05 kernel, which
+# there beats the library on three of the four shapes and fuses the next elementwise step;
+# measured on B200 at Llama-3.2-1B sizes, the library's kernels win from about 12 tokens on.
+# The head's product (float32 logits straight from the accumulator) stays with it up to 64.
+SKINNY_MAX_TOKENS = 8
+SKINNY_MAX_TOKENS_HEAD = 64
 
 
-def decode_product(x: torch.Tensor) -> bool:
+def decode_product(x: torch.Tensor, max_tokens: int = SKINNY_MAX_TOKENS) -> bool:
     """Whether a product with these activations goes to the engine's own decode kernel."""
     from . import ops
 
-    return x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_TOKENS and ops.skinny_gemm_supported(x.shape[0], x.shape[1])
+    return x.dtype == torch.bfloat16 and x.shape[0] <= max_tokens and ops.skinny_gemm_supported(x.shape[0], x.shape[1])
 
 
 # Up to this many tokens the decode product also finishes the next elementwise step (rotary and
 # cache write, SiLU * up) in its epilogue; with more tokens per CTA the separate kernels, which
 # spread that work over the whole GPU, are faster.
-FUSED_EPILOGUE_MAX_TOKENS = 16
+FUSED_EPILOGUE_MAX_TOKENS = 8
 
 
 def fused_epilogue(x: torch.Tensor) -> bool:
     return decode_product(x) and x.shape[0] <= FUSED_EPILOGUE_MAX_TOKENS
 
 
-def project(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def project(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None, max_tokens: int = SKINNY_MAX_TOKENS) -> torch.Tensor:
     """y = x W^T for a step's tokens, in x's dtype or in ``out_dtype`` (float32 for logits)."""
     from . import ops
 
-    if decode_product(x):
+    if decode_product(x, max_tokens):
         return ops.skinny_gemm(x, weight, out_dtype or x.dtype)
     y = linear(x, weight)
     return y if out_dtype in (None, y.dtype) else y.to(out_dtype)

@@ -6,7 +6,7 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..kernels.gemm import linear, project
+from ..kernels.gemm import SKINNY_MAX_TOKENS_HEAD, linear, project
 from ..weights.loader import TensorDecl
 from .base import BuildEnv, Part, ResidualStream, build_part, register_part
 
@@ -52,7 +52,7 @@ class LMHead(Part):
         self.weight = tensors[self.tied_to or self.spec.prefix + "weight"]
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
-        return project(y, self.weight, out_dtype=torch.float32)
+        return project(y, self.weight, out_dtype=torch.float32, max_tokens=SKINNY_MAX_TOKENS_HEAD)
 
 
 def _walk(part) -> list[Part]:
