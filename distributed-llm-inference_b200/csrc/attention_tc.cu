@@ -441,6 +441,339 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
   return (int)e;
 }
 
+
+// ================================================================ single-token sequences, TMA-fed
+namespace {
+
+constexpr int DN = 16;                 // keys per tile of one warp
+constexpr int DSTAGES = 3;
+constexpr int DWARPS = 4;
+constexpr int DTILE = DN * 128;        // one K or V tile: 16 rows of 128 bytes, swizzled
+constexpr int QROW = D * 2 + 16;       // padded query rows (read once)
+static_assert(DWARPS * 16 * (D + 2) * 4 <= DWARPS * DSTAGES * 2 * DTILE, "the merge buffer reuses the key/value stages");
+constexpr int DSMEM = 1024 + DWARPS * DSTAGES * 2 * DTILE + 16 * QROW + DWARPS * DSTAGES * 8 + 64;
+
+struct DecodeParams {
+  bf16* out;
+  const bf16* q;
+  long long q_stride;
+  const int* block_tables;
+  int max_blocks;
+  const int* q_start;
+  const int* kv_len;
+  int seq0, nh, nkv, page_size, window, splits;
+  float scale_log2;
+  float* part_acc;
+  float* part_ml;
+  int* error_flag;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// grid (splits, sequences, kv heads * chunks of 16 query heads).  The 16 rows of a warp's MMA tile
+// are the query heads of one KV head; each warp walks its own share of the 16-key tiles.  A tile's
+// keys and values arrive by TMA (one box per page piece, 128-byte swizzle), four tiles ahead, on the
+// warp's own mbarriers: no thread spends instructions on addresses of individual 16-byte copies.
+__global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                       const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sKV = smem;                                   // [warp][stage][K | V]
+  unsigned char* sQ = sKV + DWARPS * DSTAGES * 2 * DTILE;      // 16 padded rows
+  uint64_t* bars = (uint64_t*)(sQ + 16 * QROW);                // [warp][stage]
+  volatile int* failed = (volatile int*)(bars + DWARPS * DSTAGES);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int s = p.seq0 + blockIdx.y;
+  const int split = blockIdx.x;
+  const int G = p.nh / p.nkv;
+  const int chunks = (G + 15) / 16;
+  const int kvh = blockIdx.z / chunks, hc = blockIdx.z - kvh * chunks;
+  const int head0 = kvh * G + hc * 16;
+  const int nheads = min(16, G - hc * 16);
+  const int token = p.q_start[s];
+  const int kvlen = p.kv_len[s];
+  const int pos = kvlen - 1;
+  const int* table = p.block_tables + (size_t)s * p.max_blocks;
+  const int hi = kvlen;
+  const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  const int first_tile = lo / DN;
+  const int tiles_total = (hi + DN - 1) / DN - first_tile;
+  const int tiles_per_split = (tiles_total + p.splits - 1) / p.splits;
+  const int t_begin = first_tile + split * tiles_per_split;
+  const int t_end = min(first_tile + tiles_total, t_begin + tiles_per_split);
+
+  if (tid == 0) *failed = 0;
+  if (lane == 0) {
+    for (int st = 0; st < DSTAGES; ++st) mbar_init(smem_u32(bars + warp * DSTAGES + st), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  for (int idx = tid; idx < 16 * 8; idx += DWARPS * 32) {
+    const int r = idx >> 3, c = idx & 7;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < nheads) v = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)(head0 + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(sQ + r * QROW + c * 16) = v;
+  }
+  __syncthreads();
+
+  // the query fragments stay in registers
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) ldsm_x4(qf[kk], smem_u32(sQ + (lane & 15) * QROW + (kk * 16 + (lane >> 4) * 8) * 2));
+
+  unsigned char* wbuf = sKV + warp * DSTAGES * 2 * DTILE;
+  const uint32_t wbar = smem_u32(bars + warp * DSTAGES);
+  const int my_tiles = (t_end - t_begin - warp + DWARPS - 1) / DWARPS;
+  const int box_rows = p.page_size < DN ? p.page_size : DN;  // a tile is one piece of a page, or two whole pages of 8
+  const int boxes = DN / box_rows;
+
+  // Block-table entries are read 32 boxes at a time, one per lane, and handed to lane 0 by shuffle:
+  // lane 0 must never wait for a global load between two copies.
+  int cached_first = 0;
+  auto box_page = [&](int e) -> int {  // page of this warp's e-th box (box = tile piece of box_rows keys)
+    const int key = (t_begin + warp + (e / boxes) * DWARPS) * DN + (e % boxes) * box_rows;
+    if (key >= hi || key + box_rows <= lo) return -1;  // no key of the box is visible: it is filled with zeros
+    return table[key / p.page_size];
+  };
+  int cached = box_page(lane);
+  // every lane calls this (the shuffles need them all); lane 0 issues the copies of the warp's i-th tile
+  auto issue = [&](int i) {
+    const int st = i % DSTAGES;
+    const int key0 = (t_begin + warp + i * DWARPS) * DN;
+    const uint32_t bar = wbar + 8 * st;
+    if (lane == 0) mbar_expect_tx(bar, 2 * DTILE);
+    for (int b = 0; b < boxes; ++b) {
+      const int e = i * boxes + b;
+      if (e >= cached_first + 32) {
+        cached_first = e;
+        cached = box_page(e + lane);
+      }
+      const int page = __shfl_sync(0xffffffffu, cached, e - cached_first);
+      if (lane == 0) {
+        const int key = key0 + b * box_rows;
+        // a row coordinate beyond the pool makes the copy fill the box with zeros
+        const int row = page < 0 ? 0x3fffff00 : (page * p.nkv + kvh) * p.page_size + (key % p.page_size);
+        tma_load_2d(smem_u32(wbuf + st * 2 * DTILE + b * box_rows * 128), &map_k, 0, row, bar);
+        tma_load_2d(smem_u32(wbuf + st * 2 * DTILE + DTILE + b * box_rows * 128), &map_v, 0, row, bar);
+      }
+    }
+  };
+
+  const int r0 = lane >> 2, r1 = r0 + 8;
+  const bool rv0 = r0 < nheads, rv1 = r1 < nheads;
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F};
+  float l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+
+  for (int i = 0; i < DSTAGES - 1 && i < my_tiles; ++i) issue(i);
+  __syncwarp();
+
+  bool ok = true;
+  for (int i = 0; i < my_tiles; ++i) {
+    const int st = i % DSTAGES;
+    if (i + DSTAGES - 1 < my_tiles) issue(i + DSTAGES - 1);  // into the stage finished an iteration ago
+    if (ok && !wait_or_fail(wbar + 8 * st, (i / DSTAGES) & 1, failed, 21, p.error_flag)) ok = false;
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const uint32_t tK = smem_u32(wbuf + st * 2 * DTILE), tV = tK + DTILE;
+      const int base = (t_begin + warp + i * DWARPS) * DN;
+      // ---- S = Q K^T for 16 keys: two 8-key column tiles
+      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t b[4];
+        const int key = (lane & 7) + (lane >> 4) * 8;
+        const int chunk = kk * 2 + ((lane >> 3) & 1);
+        ldsm_x4(b, tK + key * 128 + ((chunk ^ (key & 7)) << 4));
+        mma16816(sc[0], qf[kk], b[0], b[1]);
+        mma16816(sc[1], qf[kk], b[2], b[3]);
+      }
+      // ---- mask and online softmax
+      float tmax[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = base + j * 8 + (lane & 3) * 2 + (e & 1);
+          const bool vis = ((e >> 1) ? rv1 : rv0) && key <= pos && key >= lo;
+          const float t = vis ? sc[j][e] * p.scale_log2 : -CUDART_INF_F;
+          sc[j][e] = t;
+          tmax[e >> 1] = fmaxf(tmax[e >> 1], t);
+        }
+      float corr[2], msafe[2];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
+        tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
+        const float mnew = fmaxf(m[rr], tmax[rr]);
+        msafe[rr] = (mnew == -CUDART_INF_F) ? 0.f : mnew;
+        corr[rr] = ex2(m[rr] - msafe[rr]);
+        m[rr] = mnew;
+        l[rr] *= corr[rr];
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = ex2(sc[j][e] - msafe[e >> 1]);
+          sc[j][e] = pv;
+          l[e >> 1] += pv;
+        }
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j) {
+        o[j][0] *= corr[0]; o[j][1] *= corr[0];
+        o[j][2] *= corr[1]; o[j][3] *= corr[1];
+      }
+      // ---- O += P V (16 keys = one k step)
+      uint32_t a[4] = {pack2(sc[0][0], sc[0][1]), pack2(sc[0][2], sc[0][3]), pack2(sc[1][0], sc[1][1]), pack2(sc[1][2], sc[1][3])};
+#pragma unroll
+      for (int jp = 0; jp < D / 16; ++jp) {
+        uint32_t b[4];
+        const int key = (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int chunk = jp * 2 + (lane >> 4);
+        ldsm_x4_trans(b, tV + key * 128 + ((chunk ^ (key & 7)) << 4));
+        mma16816(o[2 * jp], a, b[0], b[1]);
+        mma16816(o[2 * jp + 1], a, b[2], b[3]);
+      }
+    }
+    __syncwarp();  // every lane has read the stage before lane 0 refills it
+  }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+    l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+  }
+
+  // ---- merge the four warps' partial results in shared memory (the key/value stages are free)
+  __syncthreads();
+  float* mo = reinterpret_cast<float*>(sKV);   // [DWARPS][16][D]
+  float* mm = mo + DWARPS * 16 * D;            // [DWARPS][16]
+  float* ml = mm + DWARPS * 16;
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int row = rr ? r1 : r0;
+    float* dst = mo + (warp * 16 + row) * D;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) *reinterpret_cast<float2*>(dst + j * 8 + (lane & 3) * 2) = make_float2(o[j][2 * rr], o[j][2 * rr + 1]);
+    if ((lane & 3) == 0) {
+      mm[warp * 16 + row] = m[rr];
+      ml[warp * 16 + row] = l[rr];
+    }
+  }
+  __syncthreads();
+  if (*failed) return;
+  for (int idx = tid; idx < nheads * D; idx += DWARPS * 32) {
+    const int r = idx / D, dcol = idx - r * D;
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < DWARPS; ++w) mx = fmaxf(mx, mm[w * 16 + r]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < DWARPS; ++w) {
+      const float mw = mm[w * 16 + r];
+      const float f = (mw == -CUDART_INF_F) ? 0.f : ex2(mw - mx);
+      L += ml[w * 16 + r] * f;
+      acc += mo[(w * 16 + r) * D + dcol] * f;
+    }
+    const size_t row = (size_t)token * p.nh + head0 + r;
+    if (p.splits == 1) {
+      p.out[row * D + dcol] = __float2bfloat16_rn(acc / L);
+    } else {
+      p.part_acc[(row * p.splits + split) * D + dcol] = acc;
+      if (dcol == 0) {
+        p.part_ml[(row * p.splits + split) * 2] = mx;
+        p.part_ml[(row * p.splits + split) * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// out[row] = sum_i acc_i 2^(m_i - max m) / sum_i l_i 2^(m_i - max m); one block per (token, head) row.
+__global__ void merge_decode_splits_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                           int row0, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = (size_t)row0 + blockIdx.x;
+  const float* ml = part_ml + row * splits * 2;
+  float mmax = -CUDART_INF_F;
+  for (int i = 0; i < splits; ++i) mmax = fmaxf(mmax, ml[2 * i]);
+  float L = 0.f;
+  for (int i = 0; i < splits; ++i) {
+    const float mi = ml[2 * i];
+    if (mi != -CUDART_INF_F) L += ml[2 * i + 1] * exp2f(mi - mmax);
+  }
+  const float inv = 1.f / L;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < splits; ++i) {
+      const float mi = ml[2 * i];
+      if (mi != -CUDART_INF_F) acc += part_acc[(row * splits + i) * D + d] * exp2f(mi - mmax);
+    }
+    out[row * D + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+}  // namespace
+
+// Attention of num_seqs single-token sequences (head size 64; page size a multiple of 8, and of 16
+// if larger than 8).  part_acc / part_ml: scratch for splits > 1, as for dli_paged_attention_mma.
+DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
+                                    long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
+                                    const int* kv_len, int seq0, int num_seqs, int first_row, int nh, int nkv, int page_size,
+                                    int window, float scale, int splits, float* part_acc, float* part_ml, cudaStream_t stream) {
+  if (num_seqs == 0) return 0;
+  if (nkv < 1 || nh % nkv || splits < 1 || (splits > 1 && (!part_acc || !part_ml))) return DLI_ERR_UNSUPPORTED;
+  if (page_size < 8 || (page_size % 8) || (page_size > 8 && (page_size % 16)) || page_size > 256) return DLI_ERR_UNSUPPORTED;
+  if (((uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)q) & 15) return DLI_ERR_UNSUPPORTED;
+  if (!error_flag_host) {
+    if (cudaHostAlloc((void**)&error_flag_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return (int)cudaGetLastError();
+    *error_flag_host = 0;
+    if (cudaHostGetDevicePointer((void**)&error_flag_device, error_flag_host, 0) != cudaSuccess) return (int)cudaGetLastError();
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(paged_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DSMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap map_k, map_v;
+  const long long rows = num_pages * nkv * page_size;
+  const int box_rows = page_size < DN ? page_size : DN;
+  if (!make_pool_map(&map_k, k_pool, rows, box_rows) || !make_pool_map(&map_v, v_pool, rows, box_rows)) return DLI_ERR_UNSUPPORTED;
+  DecodeParams p;
+  p.out = (bf16*)out; p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.q_start = q_start; p.kv_len = kv_len; p.seq0 = seq0;
+  p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.window = window; p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.part_acc = part_acc; p.part_ml = part_ml; p.error_flag = error_flag_device;
+  const int G = nh / nkv;
+  cudaError_t e = launch_pdl(paged_decode_tma_kernel, dim3(splits, num_seqs, nkv * ((G + 15) / 16)), dim3(DWARPS * 32), (size_t)DSMEM, stream, 1,
+                             map_k, map_v, p);
+  if (e != cudaSuccess) return (int)e;
+  if (splits > 1)
+    e = launch_pdl(merge_decode_splits_kernel, dim3(num_seqs * nh), dim3(64), 0, stream, 1, (bf16*)out, (const float*)part_acc,
+                   (const float*)part_ml, first_row * nh, splits);
+  return (int)e;
+}
+
 // 0, or the code of the first bounded wait that ran out (11 keys, 12 scores, 13 output tile, 14 values,
-// 15 probabilities, 16 output tile read)
+// 15 probabilities, 16 output tile read; 21: a decode warp's keys and values)
 DLI_EXPORT int dli_paged_prefill_tc_error() { return error_flag_host ? *error_flag_host : 0; }

@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from ..kernels.attention import choose_splits
+from ..kernels.attention import decode_splits
 from .batch import GroupView, StepBatch
 
 SEQ_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
@@ -107,13 +107,18 @@ class DecodeGraphs:
         self.graphs: dict[tuple[int, int, int], DecodeGraph] = {}
         self.max_graphs = 32
 
+    def splits_for(self, seqs: int, max_kv_len: int) -> int:
+        """One split count per graph: the smallest any attention mixer of the model would choose."""
+        counts = [decode_splits(seqs, m.nh, m.nkv, m.d, self.page_size, max_kv_len)
+                  for layer in self.model.layers for m in [getattr(layer, "mixer", None)] if hasattr(m, "nkv")]
+        return min(counts, default=1)
+
     def lookup(self, num_seqs: int, width: int, max_kv_len: int) -> DecodeGraph | None:
         seqs = bucket_seqs(num_seqs)
         if seqs is None:
             return None
         width = -(-width // WIDTH_STEP) * WIDTH_STEP
-        heads = [(n.num_kv_heads) for n in self.pools.group_needs]
-        splits = choose_splits(seqs, min(heads) if heads else 1, width * self.page_size)
+        splits = self.splits_for(seqs, width * self.page_size)
         key = (seqs, width, splits)
         graph = self.graphs.get(key)
         if graph is None:

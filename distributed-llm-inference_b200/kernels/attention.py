@@ -13,17 +13,25 @@ import torch
 
 from . import ops
 
-ONE_WAVE = 148 * 2  # CTAs of the decode kernel that are resident at once (two per SM in its few-sequences shape)
+ONE_WAVE = 148 * 2  # CTAs of the mma.sync decode kernel resident at once (two per SM in its few-sequences shape)
+ONE_WAVE_TMA = 148 * 4  # ... of the TMA-fed decode kernel (four per SM)
 MIN_TILES_PER_SPLIT = 2  # key tiles (of 64) a split should at least cover
 
 
-def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int) -> int:
+def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int = ONE_WAVE) -> int:
     """Key splits for single-token sequences: as many as still fit the GPU in one wave (a second,
     partly filled wave costs more than the extra parallelism brings), none shorter than
     MIN_TILES_PER_SPLIT key tiles (the role of src/dli/model/paged_attention.py:63-74)."""
     pairs = max(1, num_seqs * ctas_per_seq)
     tiles = -(-max_kv_len // 64)
-    return max(1, min(ONE_WAVE // pairs, tiles // MIN_TILES_PER_SPLIT))
+    return max(1, min(wave // pairs, tiles // MIN_TILES_PER_SPLIT))
+
+
+def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_size: int, max_kv_len: int) -> int:
+    """Key splits of the decode kernel that will serve these sizes."""
+    ctas_per_seq = nkv * -(-(num_heads // nkv) // 16)
+    wave = ONE_WAVE_TMA if ops.decode_tma_supported(head_dim, page_size) else ONE_WAVE
+    return choose_splits(num_seqs, ctas_per_seq, max_kv_len, wave)
 
 
 def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_heads: int, scale: float, window: int | None) -> None:
@@ -35,15 +43,16 @@ def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_head
         return
     singles, total = batch.num_single, batch.num_seqs
     if singles:
-        per_kv_head = -(-(num_heads // nkv) // 64)
-        splits = batch.forced_splits or choose_splits(singles, nkv * per_kv_head, batch.max_kv_len_single)
+        tma = ops.decode_tma_supported(d, cache.page_size)
+        splits = batch.forced_splits or decode_splits(singles, num_heads, nkv, d, cache.page_size, batch.max_kv_len_single)
         scratch = None
         if splits > 1:
             rows = singles * num_heads
             scratch = (torch.empty(rows * splits * d, dtype=torch.float32, device=out.device),
                        torch.empty(rows * splits * 2, dtype=torch.float32, device=out.device))
-        ops.paged_attention_mma(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, 0, singles, 1, 0,
-                                num_heads, scale, window, splits, scratch)
+        kernel = ops.paged_decode_tma if tma else ops.paged_attention_mma
+        args = (out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, 0, singles) + (() if tma else (1,))
+        kernel(*args, 0, num_heads, scale, window, splits, scratch)
     if total > singles and ops.prefill_tc_supported(d, cache.page_size):
         ops.paged_prefill_tc(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, singles, total - singles,
                              batch.max_q_len, num_heads, scale, window)

@@ -245,6 +245,24 @@ def test_paged_prefill_tc(nh, nkv, page, window):
     assert ops.paged_prefill_tc_error() == 0
 
 
+@pytest.mark.parametrize("nh,nkv,page", [(8, 2, 16), (3, 1, 8), (5, 5, 32), (32, 8, 64), (40, 1, 16)])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_paged_decode_tma(nh, nkv, page, window, splits):
+    """The TMA-fed decode kernel: contexts from 1 to 1500 keys, ends on and off tile and page edges."""
+    d = 64
+    seqs = [(0, 1), (15, 1), (16, 1), (199, 1), (63, 1), (255, 1), (1499, 1), (700, 1)]
+    t = attention_case(nh, nkv, d, page, seqs, torch.bfloat16, seed=nh + page)
+    out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scratch = None
+    if splits > 1:
+        scratch = (torch.full((len(seqs) * nh * splits * d,), float("nan"), device=DEV), torch.full((len(seqs) * nh * splits * 2,), float("nan"), device=DEV))
+    ops.paged_decode_tma(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(seqs), 0, nh, d**-0.5, window, splits, scratch)
+    want = plain_attention(t, seqs, nh, window)
+    np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2))
+    assert ops.paged_prefill_tc_error() == 0
+
+
 def test_prefill_tc_refuses_other_sizes():
     t = attention_case(2, 1, 32, 16, [(0, 4)], torch.bfloat16)
     out = torch.empty((4, 64), dtype=torch.bfloat16, device=DEV)
