@@ -252,14 +252,106 @@ __global__ void rotary_store_kernel(T* __restrict__ qkv, const int* __restrict__
   }
 }
 
-DLI_EXPORT int dli_rotary_store(void* qkv, const int* positions, const float* inv_freq, const int* slots, void* k_pool,
-                                void* v_pool, int n, int nh, int nkv, int d, int rot, int page_size, int write_kv,
+// cos | sin of every token's angles, [n, rot] float32 (cos in the first rot / 2 columns): computed once
+// per step and read by every layer's rotary kernel, instead of once per layer.
+__global__ void rotary_table_kernel(float* __restrict__ table, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                    int n, int half) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * half) return;
+  const int t = idx / half, i = idx - t * half;
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+  table[(size_t)t * 2 * half + i] = cs;
+  table[(size_t)t * 2 * half + half + i] = sn;
+}
+
+DLI_EXPORT int dli_rotary_table(float* table, const int* positions, const float* inv_freq, int n, int rot, cudaStream_t stream) {
+  if (n == 0 || rot == 0) return 0;
+  if (rot & 1) return DLI_ERR_UNSUPPORTED;
+  const int total = n * (rot >> 1);
+  launch_pdl((rotary_table_kernel), dim3((total + 255) / 256), dim3(256), 0, stream, 1, table, positions, inv_freq, n, rot >> 1);
+  return (int)cudaGetLastError();
+}
+
+// bfloat16 with rot % 16 == 0 and d % 8 == 0: every access is 16 bytes.  Work items of a token:
+// (head of q or k, run of eight rotated pairs), (kv head, run of eight pass-through elements),
+// (kv head, run of eight value elements).
+__global__ void rotary_store_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                             const float* __restrict__ inv_freq, const float* __restrict__ table,
+                                             const int* __restrict__ slots,
+                                             __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int nh, int nkv,
+                                             int d, int rot, int page_size, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float trig[];
+  const int t = blockIdx.x;
+  const int half = rot >> 1;
+  __nv_bfloat16* base = qkv + (size_t)t * (nh + 2 * nkv) * d;
+  if (table) {
+    for (int i = threadIdx.x; i < rot; i += blockDim.x) trig[i] = table[(size_t)t * rot + i];
+  } else {
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &trig[half + i], &trig[i]);
+  }
+  __syncthreads();
+  const int slot = slots ? slots[t] : -1;
+  const bool store = write_kv && slot >= 0;
+  const int page = store ? slot / page_size : 0, off = store ? slot % page_size : 0;
+  const int hc = half >> 3;                 // runs of eight pairs per head
+  const int rot_items = (nh + nkv) * hc;
+  const int tail_items = store ? nkv * ((d - rot) >> 3) : 0;
+  const int v_items = store ? nkv * (d >> 3) : 0;
+  for (int idx = threadIdx.x; idx < rot_items + tail_items + v_items; idx += blockDim.x) {
+    if (idx < rot_items) {
+      const int head = idx / hc, i = (idx - head * hc) << 3;
+      __nv_bfloat16* x = base + (size_t)head * d;
+      float a[8], b[8];
+      load8(x + i, a);
+      load8(x + i + half, b);
+      float ra[8], rb[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float cs = trig[i + k], sn = trig[half + i + k];
+        ra[k] = a[k] * cs - b[k] * sn;
+        rb[k] = b[k] * cs + a[k] * sn;
+      }
+      if (head < nh) {
+        store8(x + i, ra);
+        store8(x + i + half, rb);
+      } else if (store) {
+        __nv_bfloat16* dst = k_pool + (((size_t)page * nkv + (head - nh)) * page_size + off) * d;
+        store8(dst + i, ra);
+        store8(dst + i + half, rb);
+      }
+    } else if (idx < rot_items + tail_items) {
+      const int per = (d - rot) >> 3;
+      const int j = idx - rot_items, head = j / per, i = rot + ((j - head * per) << 3);
+      *reinterpret_cast<uint4*>(k_pool + (((size_t)page * nkv + head) * page_size + off) * d + i) =
+          *reinterpret_cast<const uint4*>(base + (size_t)(nh + head) * d + i);
+    } else {
+      const int per = d >> 3;
+      const int j = idx - rot_items - tail_items, head = j / per, i = (j - head * per) << 3;
+      *reinterpret_cast<uint4*>(v_pool + (((size_t)page * nkv + head) * page_size + off) * d + i) =
+          *reinterpret_cast<const uint4*>(base + (size_t)(nh + nkv + head) * d + i);
+    }
+  }
+}
+
+DLI_EXPORT int dli_rotary_store(void* qkv, const int* positions, const float* inv_freq, const float* table, const int* slots,
+                                void* k_pool, void* v_pool, int n, int nh, int nkv, int d, int rot, int page_size, int write_kv,
                                 int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
   if (rot < 0 || rot > d || (rot & 1)) return DLI_ERR_UNSUPPORTED;
   if (rot > 0 && inv_freq == nullptr) return DLI_ERR_UNSUPPORTED;
   const int threads = 256;
   const size_t smem = (size_t)rot * sizeof(float);
+  if (dtype == DLI_BF16 && rot % 16 == 0 && d % 8 == 0) {
+    launch_pdl((rotary_store_bf16_vec_kernel), dim3(n), dim3(threads), smem, stream, 1, (__nv_bfloat16*)qkv, positions, inv_freq, table, slots,
+               (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh, nkv, d, rot, page_size, write_kv);
+    return (int)cudaGetLastError();
+  }
   if (dtype == DLI_F32)
     launch_pdl((rotary_store_kernel<float>), dim3(n), dim3(threads), smem, stream, 1, (float*)qkv, positions, inv_freq, slots, (float*)k_pool,
                                                           (float*)v_pool, nh, nkv, d, rot, page_size, write_kv);

@@ -51,6 +51,7 @@ class StepBatch:
     max_kv_len: int = 0
     max_kv_len_single: int = 0  # longest context among the single-token sequences
     forced_splits: int = 0  # key splits of decode attention fixed by the caller (0: chosen per step)
+    scratch: dict = field(default_factory=dict)  # per-step results that parts share across layers; cleared by each forward
 
     def group(self, index: int) -> GroupView:
         return self.groups[index]

@@ -142,9 +142,11 @@ def rotary_store(
     rotary_dim: int,
     page_size: int,
     write_kv: bool = True,
+    table: torch.Tensor | None = None,
 ) -> None:
     """Rotate q and k heads of qkv [n, (nh + 2 nkv) d] by position; q in place, k and v into
-    one layer's pools [pages, nkv, page_size, d] at ``slots`` (page * page_size + offset)."""
+    one layer's pools [pages, nkv, page_size, d] at ``slots`` (page * page_size + offset).
+    ``table`` [n, rotary_dim] (from rotary_table) spares the kernel the sines and cosines."""
     _need(qkv, "qkv"), _need(positions, "positions", torch.int32)
     n = qkv.shape[0]
     if qkv.dtype not in DT_CODE or qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or positions.numel() != n:
@@ -161,15 +163,29 @@ def rotary_store(
         _need(slots, "slots", torch.int32), _need(k_pool, "k_pool", qkv.dtype), _need(v_pool, "v_pool", qkv.dtype)
         if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, head_dim) or k_pool.shape != v_pool.shape or slots.numel() != n:
             raise KernelError("rotary_store: pool layout must be [pages, kv_heads, page_size, head_dim]")
+    if table is not None:
+        _need(table, "table", torch.float32)
+        if tuple(table.shape) != (n, rotary_dim):
+            raise KernelError("rotary_store: table must be [n, rotary_dim]")
     f = _fn(
         "elementwise.cu", "dli_rotary_store",
-        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 8 + [c_void_p],
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 8 + [c_void_p],
     )
     _check(
-        f(_ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(k_pool), _ptr(v_pool), n, num_heads, num_kv_heads,
+        f(_ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(table), _ptr(slots), _ptr(k_pool), _ptr(v_pool), n, num_heads, num_kv_heads,
           head_dim, rotary_dim, page_size, int(write_kv), DT_CODE[qkv.dtype], _stream()),
         "rotary_store",
     )
+
+
+def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """cos | sin of float32(position) * inv_freq for every token: float32 [n, 2 * len(inv_freq)]."""
+    _need(positions, "positions", torch.int32), _need(inv_freq, "inv_freq", torch.float32)
+    n, rot = positions.numel(), 2 * inv_freq.numel()
+    table = torch.empty((n, rot), dtype=torch.float32, device=positions.device)
+    f = _fn("elementwise.cu", "dli_rotary_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(table), _ptr(positions), _ptr(inv_freq), n, rot, _stream()), "rotary_table")
+    return table
 
 
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, tiled: bool = False) -> None:

@@ -112,6 +112,7 @@ class DecoderModel:
 
     def forward(self, batch, caches) -> torch.Tensor:
         """Logits [k, vocab] (float32) at ``batch.logit_rows``; every token's cache entries are written."""
+        batch.scratch.clear()
         stream = ResidualStream(self.embedding.forward(batch.token_ids))
         for i, step in enumerate(self.spec.run_order):
             self.layers[step.layer].forward(stream, batch, caches[i])

@@ -41,7 +41,14 @@ def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head
     args = (batch.positions, inv_freq, group.slots if write_kv else None, cache.k if write_kv else None,
             cache.v if write_kv else None, num_heads, num_kv_heads, head_dim, rotary_dim, cache.page_size, write_kv)
     if rotary_dim or write_kv:
-        ops.rotary_store(qkv, *args)
+        table = None
+        if rotary_dim and qkv.dtype == torch.bfloat16 and qkv.shape[0] > 64:
+            # many tokens: the sines and cosines of the step are computed once and shared by all layers
+            key = ("rotary_table", inv_freq.data_ptr())
+            table = batch.scratch.get(key)
+            if table is None:
+                table = batch.scratch[key] = ops.rotary_table(batch.positions, inv_freq)
+        ops.rotary_store(qkv, *args, table=table)
     return qkv
 
 
