@@ -86,6 +86,7 @@ class CacheManager:
         self.pools = [PagePool(g.num_pages, page_size, self.prefix_caching) for g in groups]
         self._reserve = [int(watermark * g.num_pages) for g in groups]
         self.max_requests = max_requests
+        self._has_window = any(g.window is not None for g in groups)
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._requests: dict[Hashable, _Request] = {}
         self.stats = CacheStats()
@@ -109,6 +110,11 @@ class CacheManager:
 
     def num_computed_tokens(self, rid: Hashable) -> int:
         return self._get(rid).num_computed
+
+    def progress(self, rid: Hashable) -> tuple[int, int, int]:
+        """(tokens computed, tokens with slots, state slot) of a request, in one look-up."""
+        req = self._get(rid)
+        return req.num_computed, req.num_tokens, req.slot
 
     def state_slot(self, rid: Hashable) -> int:
         return self._get(rid).slot
@@ -216,8 +222,9 @@ class CacheManager:
         """Room for tokens appended to the request (a sampled token); ignores the watermark."""
         req = self._get(rid)
         ps = self.page_size
-        need = sum(1 for p in range(req.num_tokens, req.num_tokens + len(token_ids)) if p % ps == 0)
-        if any(need > pool.available for pool in self.pools):
+        first, last = req.num_tokens, req.num_tokens + len(token_ids)
+        need = -(-last // ps) - -(-first // ps)  # positions in [first, last) that open a page
+        if need and any(need > pool.available for pool in self.pools):
             raise OutOfPages(f"append needs {need} pages")
         if need:
             for g, (pool, table) in enumerate(zip(self.pools, req.tables)):
@@ -236,7 +243,7 @@ class CacheManager:
             raise ValueError(f"computed must be in [{req.num_computed}, {req.num_tokens}], got {num_computed}")
         req.num_computed = num_computed
         ps = self.page_size
-        if self.prefix_caching:
+        if self.prefix_caching and req.registered < num_computed // ps:
             full = num_computed // ps
             while req.registered < full:
                 i = req.registered
@@ -246,6 +253,8 @@ class CacheManager:
                 for pool, table in zip(self.pools, req.tables):
                     pool.register(table[i], req.hashes[i], req.hashes[i - 1] if i else None, table[i - 1] if i else None)
                 req.registered += 1
+        if not self._has_window:
+            return
         for g, (group, pool, table) in enumerate(zip(self.groups, self.pools, req.tables)):
             if group.window is None:
                 continue

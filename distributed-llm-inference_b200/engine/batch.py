@@ -187,11 +187,12 @@ def gather_single_tokens(entries: Sequence[StepEntry], manager, vocab_size: int)
             if w != 0:
                 raise ValueError(f"want index {w} of request {rid!r} is outside its 1 tokens")
             logit_rows.append(s)
+        computed, reserved, slot = manager.progress(rid)
+        if computed + 1 > reserved:
+            raise ValueError(f"request {rid!r}: tokens up to {computed + 1} have no slots reserved")
         tokens[s] = tok
-        starts[s] = manager.num_computed_tokens(rid)
-        rows[s] = manager.state_slot(rid)
-        if starts[s] + 1 > manager.num_tokens(rid):
-            raise ValueError(f"request {rid!r}: tokens up to {starts[s] + 1} have no slots reserved")
+        starts[s] = computed
+        rows[s] = slot
     ps = manager.page_size
     kv_len = starts + 1
     width = int(starts.max()) // ps + 1

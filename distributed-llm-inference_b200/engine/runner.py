@@ -114,8 +114,9 @@ class ModelRunner:
         if logits is None:
             batch, _ = build_batch(entries, self.manager, self.model.device, self.model.spec.vocab_size, self.uploader)
             logits = self.model.forward(batch, self.pools.layer_caches)
+        manager = self.manager
         for e in entries:
-            self.manager.mark_computed(e.request_id, self.manager.num_computed_tokens(e.request_id) + len(e.token_ids))
+            manager.mark_computed(e.request_id, manager.progress(e.request_id)[0] + len(e.token_ids))
         return logits
 
     def _replay_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:

@@ -115,10 +115,11 @@ class Scheduler:
                 break
             if req.status is not RequestStatus.RUNNING:
                 continue  # taken as a victim earlier in this loop
-            n = min(req.num_tokens - req.num_computed_tokens, budget)
+            total = len(req.prompt_ids) + len(req.output_ids)
+            n = min(total - req.num_computed_tokens, budget)
             if n <= 0:
                 continue
-            while not self._reserve(req):
+            while not self._reserve(req, total):
                 victim = next((c for c in reversed(self.running) if c.request_id not in in_batch and c is not req), None)
                 if victim is None:
                     victim = req  # nobody else can yield
@@ -128,7 +129,8 @@ class Scheduler:
                     break
             if req.status is not RequestStatus.RUNNING:
                 continue
-            out.chunks.append(self._chunk(req, n))
+            start = req.num_computed_tokens
+            out.chunks.append(ScheduledChunk(req, start, n, start + n == total))
             in_batch.add(req.request_id)
             budget -= n
 
@@ -154,13 +156,13 @@ class Scheduler:
         start = req.num_computed_tokens
         return ScheduledChunk(req, start, n, needs_logits=start + n == req.num_tokens)
 
-    def _reserve(self, req: Request) -> bool:
+    def _reserve(self, req: Request, total: int) -> bool:
         """Slots for tokens the cache manager has not seen yet (the newly sampled one)."""
-        missing = req.num_tokens - self.manager.num_tokens(req.request_id)
+        missing = total - self.manager.num_tokens(req.request_id)
         if missing <= 0:
             return True
         try:
-            self.manager.append_slots(req.request_id, req.token_slice(req.num_tokens - missing, req.num_tokens))
+            self.manager.append_slots(req.request_id, req.token_slice(total - missing, total))
             return True
         except OutOfPages:
             return False
