@@ -208,9 +208,7 @@ def decode_end_to_end(model, batch, steps, warmup):
         assert len(out) == batch
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    # per step: token ids, positions, sequence index, starts, lengths, slots, logit rows, cache slots and tables
-    width = CONTEXT // PAGE
-    h2d = 4 * (3 * batch + (batch + 1) + 3 * batch + batch + batch * width)
+    h2d = eng.runner.uploader.bytes_last  # what the last step copied from pinned memory: token ids, positions, lengths, slots, block tables
     while eng.has_unfinished():
         for rid in [r.request_id for r in eng.scheduler.running]:
             eng.abort(rid)
