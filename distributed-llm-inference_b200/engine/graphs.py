@@ -106,6 +106,7 @@ class DecodeGraphs:
         self.model, self.pools, self.page_size = model, pools, page_size
         self.graphs: dict[tuple[int, int, int], DecodeGraph] = {}
         self.max_graphs = 32
+        self.failure: str | None = None
 
     def splits_for(self, seqs: int, max_kv_len: int) -> int:
         """One split count per graph: the smallest any attention mixer of the model would choose."""
@@ -124,6 +125,12 @@ class DecodeGraphs:
         if graph is None:
             if len(self.graphs) >= self.max_graphs:
                 return None
-            graph = self.graphs[key] = DecodeGraph(self.model, self.pools.layer_caches, len(self.pools.group_needs),
-                                                   self.pools.scratch_pages, self.page_size, seqs, width, splits)
+            try:
+                graph = self.graphs[key] = DecodeGraph(self.model, self.pools.layer_caches, len(self.pools.group_needs),
+                                                       self.pools.scratch_pages, self.page_size, seqs, width, splits)
+            except RuntimeError as exc:  # a part turned out not to be capturable after all: run step by step from now on
+                self.max_graphs = 0
+                self.failure = str(exc)
+                torch.cuda.synchronize(self.model.device)
+                return None
         return graph

@@ -87,7 +87,8 @@ class ModelRunner:
         self.page_size = page_size
         self.uploader = Uploader(model.device)
         # graphs replay padding rows through every mixer: not with per-request state, which they would touch
-        self.graphs = DecodeGraphs(model, self.pools, page_size) if cuda_graphs and not self.pools.has_state else None
+        capturable = all(getattr(part, "graph_capturable", False) for part in model.parts())
+        self.graphs = DecodeGraphs(model, self.pools, page_size) if cuda_graphs and capturable and not self.pools.has_state else None
         self.graph_steps = 0
 
     @staticmethod

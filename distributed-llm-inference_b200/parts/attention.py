@@ -22,6 +22,8 @@ class GQAttention(Part):
     params: hidden_size, num_heads, num_kv_heads, head_dim, scale, window, position (PartSpec).
     """
 
+    graph_capturable = True
+
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
         p = spec.params

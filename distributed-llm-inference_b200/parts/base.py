@@ -44,7 +44,14 @@ class BuildEnv:
 
 
 class Part:
-    """Base of every part: declares tensors by full name and receives them."""
+    """Base of every part: declares tensors by full name and receives them.
+
+    ``graph_capturable``: whether the part's work on a step can be recorded in a CUDA graph (only
+    launches on the current stream, no host synchronisation, no shapes that depend on the data).
+    The engine replays decode steps from graphs only if every part of the model says so; a part
+    that does not set it is taken to be not capturable, and the model then runs step by step."""
+
+    graph_capturable = False
 
     def __init__(self, spec: PartSpec, env: BuildEnv) -> None:
         self.spec = spec

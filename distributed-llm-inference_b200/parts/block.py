@@ -11,6 +11,8 @@ class PreNormBlock(Part):
     Roles: mixer_norm, mixer, ffn_norm, ffn.  The feed-forward's output stays pending on the
     stream; the next norm adds it."""
 
+    graph_capturable = True
+
     def __init__(self, spec, env: BuildEnv) -> None:
         self.spec, self.env = spec, env
         self.mixer_norm = build_part("norm", spec.parts["mixer_norm"], env)

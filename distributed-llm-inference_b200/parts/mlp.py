@@ -18,6 +18,8 @@ class SwiGLU(Part):
     in which the decode product applies SiLU(gate) * up in its own epilogue.
     params: hidden_size, intermediate_size."""
 
+    graph_capturable = True
+
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
         self.hidden = int(spec.params["hidden_size"])

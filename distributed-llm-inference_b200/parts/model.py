@@ -15,6 +15,8 @@ from .base import BuildEnv, Part, ResidualStream, build_part, register_part
 class TokenEmbedding(Part):
     """h = table[token_ids], no scale (src/dli/model/llama.py:291).  params: vocab_size, hidden_size."""
 
+    graph_capturable = True
+
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
@@ -38,6 +40,8 @@ class LMHead(Part):
     (src/dli/model/llama.py:304-305).  A tied checkpoint that stores the head anyway is
     accepted if both are equal (src/dli/model/loader.py:75-80).
     params: vocab_size, hidden_size, tied_to."""
+
+    graph_capturable = True
 
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)

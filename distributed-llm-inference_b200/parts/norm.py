@@ -15,6 +15,8 @@ class RMSNorm(Part):
     once (src/dli/model/llama.py:41-44 rounds before the weight product; one rounding is closer
     to the float32 result).  params: size, eps."""
 
+    graph_capturable = True
+
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
         self.size = int(spec.params["size"])

@@ -68,6 +68,8 @@ class Rotary(Part):
     scaling and its constants.  The angle float32(position) * inv_freq and its sine and cosine
     are computed in float32 inside the kernel that also writes k and v to the cache."""
 
+    graph_capturable = True
+
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
         self.head_dim = int(spec.params["head_dim"])
@@ -86,6 +88,8 @@ class Rotary(Part):
 @register_part("position", "none")
 class NoPosition(Part):
     """No position encoding: q passes through, k and v are written to the cache as they are."""
+
+    graph_capturable = True
 
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)

@@ -360,3 +360,85 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(toy_architecture):
 def test_unknown_part_kind_is_named():
     with pytest.raises(ValueError, match="no mixer part of kind 'nonesuch'"):
         build_part("mixer", PartSpec("nonesuch"), env(torch.float32))
+
+
+# ------------------------------------------------------------------ a toy feed-forward with routing
+
+
+class RoutedFFN(Part):
+    """Three small SwiGLU experts, top-1 routing by float32 router logits; defined here only."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden, self.inter, self.experts = spec.params["hidden_size"], spec.params["intermediate_size"], spec.params["experts"]
+
+    def declare(self):
+        px = self.spec.prefix
+        out = {px + "router.weight": TensorDecl((self.experts, self.hidden))}
+        for e in range(self.experts):
+            out[px + f"experts.{e}.gate_up.weight"] = TensorDecl((2 * self.inter, self.hidden))
+            out[px + f"experts.{e}.down.weight"] = TensorDecl((self.hidden, self.inter))
+        return out
+
+    def load(self, tensors):
+        px = self.spec.prefix
+        self.router = tensors[px + "router.weight"]
+        self.gate_up = [tensors[px + f"experts.{e}.gate_up.weight"] for e in range(self.experts)]
+        self.down = [tensors[px + f"experts.{e}.down.weight"] for e in range(self.experts)]
+
+    def forward(self, x):
+        choice = (x.float() @ self.router.float().t()).argmax(-1)  # router logits in float32
+        out = torch.zeros_like(x)
+        for e in range(self.experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                gu = x[rows] @ self.gate_up[e].t()
+                act = torch.nn.functional.silu(gu[:, : self.inter].float()) * gu[:, self.inter :].float()
+                out[rows] = (act.to(x.dtype) @ self.down[e].t())
+        return out
+
+
+def test_toy_routed_feed_forward_is_registered_and_stepped():
+    """One model, different feed-forwards in different layers: layer 0 keeps SwiGLU, layer 1
+    routes among experts.  Float32, cut into portions, against a numpy restatement."""
+    register_part("feed_forward", "toy_routed")(RoutedFFN)
+    try:
+        base = llama_model_spec(LlamaConfig.from_hf_dict(TINY_A))
+        layers = list(base.layers)
+        routed = PartSpec("toy_routed", {"hidden_size": 64, "intermediate_size": 24, "experts": 3}, "model.layers.1.moe.")
+        layers[1] = LayerSpec("prenorm", {**layers[1].parts, "ffn": routed})
+        spec = dataclasses.replace(base, layers=tuple(layers))
+        model, w = build(spec, torch.float32, seed=12)
+        for k in list(w):  # make routing decisive: no near ties between experts
+            if k.endswith("router.weight"):
+                w[k] = w[k] * 50
+        model.load({k: torch.from_numpy(v).to(DEV) for k, v in w.items()})
+        tokens = np.random.default_rng(6).integers(0, 256, 40).tolist()
+
+        c = plain.read_config(TINY_A)
+        x = w["model.embed_tokens.weight"][np.asarray(tokens)]
+        cos, sin = plain.rope_cos_sin(plain.inverse_frequencies(c), np.arange(len(tokens)))
+        x, _ = plain_layer(x, w, 0, c, cos, sin)
+        p = "model.layers.1."
+        y = plain.rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
+        n, d = len(tokens), c["head_dim"]
+        q = (y @ w[p + "self_attn.q_proj.weight"].T).reshape(n, c["heads"], d).transpose(1, 0, 2)
+        k = (y @ w[p + "self_attn.k_proj.weight"].T).reshape(n, c["kv_heads"], d).transpose(1, 0, 2)
+        v = (y @ w[p + "self_attn.v_proj.weight"].T).reshape(n, c["kv_heads"], d).transpose(1, 0, 2)
+        o = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v).transpose(1, 0, 2).reshape(n, -1)
+        x = x + o @ w[p + "self_attn.o_proj.weight"].T
+        y = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
+        choice = (y @ w[p + "moe.router.weight"].T).argmax(-1)
+        delta = np.zeros_like(y)
+        for t, e in enumerate(choice):
+            gu = y[t] @ w[p + f"moe.experts.{e}.gate_up.weight"].T
+            delta[t] = (plain.silu(gu[:24]) * gu[24:]) @ w[p + f"moe.experts.{e}.down.weight"].T
+        x = plain.rms_norm(x + delta, w["model.norm.weight"], c["eps"])
+        want = x @ w["model.embed_tokens.weight"].T
+        assert len(set(choice.tolist())) > 1, "the router sent every token to one expert"
+
+        whole, cut = run_whole_and_cut(model, tokens, 4, [9, 1, 1, 27, 2])
+        np.testing.assert_allclose(whole, want, atol=1e-4)
+        np.testing.assert_allclose(cut, want, atol=1e-4)
+    finally:
+        unregister_part("feed_forward", "toy_routed")
