@@ -17,10 +17,10 @@
 //
 // The grid is (feature tiles, K slices).  Slices exist to fill the GPU when a matrix has few
 // feature tiles.  The CTAs of one tile's slices form a thread-block cluster (up to 8): each
-// parks its partial sums in its own shared memory, and after a cluster barrier CTA r adds, for
-// its share of the tokens, the partial sums of all slices — read through distributed shared
-// memory, slice 0 first, so the order is fixed — and writes the output.  No partial sum ever
-// leaves the chip, and no scratch memory is needed.
+// pushes its partial sums of a token into the shared memory of the CTA that owns the token
+// (distributed shared memory), and after one cluster barrier the owner adds them, slice 0
+// first, so the order is fixed, and writes the output.  No partial sum ever leaves the chip,
+// and no scratch memory is needed.
 //
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel records an error
 // code in *error_flag, stops issuing work, frees its tensor memory and returns.
@@ -36,6 +36,7 @@ constexpr int BM = 128;       // features per CTA
 constexpr int BK = 64;        // k per stage: 128 bytes of bfloat16, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
+constexpr int BARRIER_BYTES = 256;  // mbarriers (at most 17), the TMEM address and the failure flag, behind the stages
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -150,15 +151,16 @@ __device__ __forceinline__ void fused_epilogue(const Epilogue& ep, void* out, co
   else ep.v_pool[(((size_t)page * ep.nkv + (kvh - ep.nkv)) * ep.page_size + off) * ep.d + i] = b;
 }
 
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_peer_shared(uint32_t local_addr, uint32_t cta_rank) {
+// store into the same shared-memory offset of another CTA of the cluster
+__device__ __forceinline__ void st_peer_shared(uint32_t local_addr, uint32_t cta_rank, float v) {
   uint32_t remote;
-  float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
 __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -195,6 +197,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  if (gridDim.y > 1) cluster_arrive();  // waited for just before the first store into a peer's memory
 
   const int tile = blockIdx.x, slice = blockIdx.y;
   const int kt0 = slice * tiles_per_slice;
@@ -264,15 +267,18 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   ok = ok && !*failed;
   const int fl = warp * 32 + lane, f = tile * BM + fl;
   const int slices = gridDim.y;  // the cluster spans the grid's y dimension: slice = rank in the cluster
-  // with several slices the partial sums go to shared memory, [token][feature of the tile];
-  // the pipeline stages are free by now (every MMA that read them has finished)
-  float* red = reinterpret_cast<float*>(smem);
   const bool fused = ep.mode != EP_STORE;
-  // finished sums of the tokens this CTA owns, [owned token][feature of the tile], for the fused
-  // epilogues (they combine features): behind the partial sums, or the partial sums themselves
-  // when there is one slice only
-  float* fin = slices > 1 ? red + npad * BM : red;
+  // With several slices, token t belongs to CTA (t mod slices) of the cluster.  Every CTA pushes its
+  // partial sums of a token straight into the owner's shared memory (remote stores need no answer),
+  // one cluster barrier makes them visible, and the owner adds them from its own memory, slice 0
+  // first.  Nobody reads a peer's memory after the barrier, so CTAs may leave as they finish.
+  //   recv[slice][owned token][feature of the tile], a region of its own behind the barriers: a peer
+  // may push while this CTA's pipeline stages are still in use
+  float* recv = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes + BARRIER_BYTES);
+  const int owned_max = (tokens + slices - 1) / slices;
+  const uint32_t recv_addr = smem_u32(recv);
   const int tok8 = (tokens + 7) & ~7;
+  if (slices > 1) cluster_wait();  // every CTA of the cluster runs (they arrived during setup): its memory may be written
   for (int c = 0; c < npad && c < tok8; c += 8) {
     uint32_t r[8];
     if (nkt > 0 && ok) {
@@ -287,43 +293,34 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      if (c + j >= tokens) continue;
-      if (slices > 1 || fused) red[(c + j) * BM + fl] = __uint_as_float(r[j]);
-      else if (f < features) store_out(out, out_f32, (size_t)(c + j) * features + f, __uint_as_float(r[j]));
+      const int t = c + j;
+      if (t >= tokens) continue;
+      if (slices > 1) {
+        const int owner = t % slices, ti = t / slices;
+        st_peer_shared(recv_addr + (uint32_t)(((slice * owned_max + ti) * BM + fl) * 4), owner, __uint_as_float(r[j]));
+      } else if (fused) {
+        recv[t * BM + fl] = __uint_as_float(r[j]);
+      } else if (f < features) {
+        store_out(out, out_f32, (size_t)t * features + f, __uint_as_float(r[j]));
+      }
     }
   }
+  // finished sums of the owned tokens for the fused epilogues (they combine features of a tile)
+  float* fin = slices > 1 ? recv + slices * owned_max * BM : recv;
   if (slices > 1) {
-    cluster_sync();  // every slice's partial sums are in its shared memory
-    const uint32_t red_addr = smem_u32(red);
-    // CTA r adds tokens r, r + slices, ...; up to eight tokens' partial sums from all slices are
-    // requested at once (remote shared memory answers slowly: keep many loads in flight)
-    constexpr int TCH = 8;
-    for (int t0 = slice; t0 < tokens; t0 += slices * TCH) {
-      float v[TCH][8];
-#pragma unroll
-      for (int i = 0; i < TCH; ++i) {
-        const int t = t0 + i * slices;
-        const uint32_t a = red_addr + (uint32_t)(t * BM + fl) * 4u;
-#pragma unroll
-        for (int s2 = 0; s2 < 8; ++s2) v[i][s2] = (t < tokens && s2 < slices) ? ld_peer_shared(a, s2) : 0.f;
-      }
-#pragma unroll
-      for (int i = 0; i < TCH; ++i) {
-        const int t = t0 + i * slices;
-        float acc = 0.f;
-#pragma unroll
-        for (int s2 = 0; s2 < 8; ++s2) acc += v[i][s2];  // slice 0 first; absent slices add exact zeros
-        if (t >= tokens) continue;
-        if (fused) fin[((t - slice) / slices) * BM + fl] = acc;
-        else if (f < features) store_out(out, out_f32, (size_t)t * features + f, acc);
-      }
+    cluster_sync();  // every slice's partial sums of my tokens have arrived
+    for (int t = slice, ti = 0; t < tokens; t += slices, ++ti) {
+      float acc = 0.f;
+#pragma unroll 8
+      for (int s2 = 0; s2 < slices; ++s2) acc += recv[(s2 * owned_max + ti) * BM + fl];  // slice 0 first
+      if (fused) fin[ti * BM + fl] = acc;
+      else if (f < features) store_out(out, out_f32, (size_t)t * features + f, acc);
     }
   }
   if (fused) {
     __syncthreads();  // the finished sums of every feature of the tile are in place
     for (int t = slice, ti = 0; t < tokens; t += slices, ++ti) fused_epilogue(ep, out, fin + ti * BM, t, tile, fl, features);
   }
-  if (slices > 1) cluster_sync();  // nobody leaves while a peer may still read its shared memory
 
   // ---- teardown: nobody touches tensor memory after this barrier; warp 0 frees it
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -395,16 +392,21 @@ static int launch_skinny(void* out, int out_f32, const void* x, const void* w, i
   const int per = (k_tiles + slices - 1) / slices;
   const int stage_bytes = A_BYTES + npad * BK * 2;
   int stages = per < 8 ? per : 8;
-  // by default leave room for three CTAs per SM; a caller that launches one CTA per SM may ask for a deeper pipeline
-  const int budget = (max_stages > 0 ? 200 : 72) * 1024;
-  if (max_stages > 0 && stages > max_stages) stages = max_stages;
-  while (stages > 2 && stages * stage_bytes > budget) --stages;
-  if (stages < 1) stages = 1;
-  // room for the partial sums [npad][128] and, for a fused epilogue, the finished sums of the owned tokens
+  // room for the partial sums pushed by every slice [slices][owned][128] and, for a fused epilogue, the
+  // finished sums of the owned tokens (one slice: the tile's sums [tokens][128])
   const int owned = (tokens + slices - 1) / slices;
-  const int scratch = (slices > 1 || ep.mode != EP_STORE ? npad * BM * 4 : 0) + (slices > 1 && ep.mode != EP_STORE ? owned * BM * 4 : 0);
-  while (stages * stage_bytes < scratch) ++stages;
-  const int smem = stages * stage_bytes + (2 * stages + 1) * 8 + 16 + 1024;
+  const int scratch = slices > 1 ? (slices + (ep.mode != EP_STORE ? 1 : 0)) * owned * BM * 4 : (ep.mode != EP_STORE ? tokens * BM * 4 : 0);
+  // A grid of more than one CTA per SM fits three per SM, all told; a smaller one takes 72 KB of stages
+  // beside its scratch (two per SM, this kernel's and the next one's; measured: deeper pipelines were
+  // slower in a chain of such kernels).  A caller that launches one CTA per SM and nothing behind it may ask for more.
+  const int ctas = ((features + BM - 1) / BM) * slices;
+  const int budget = max_stages > 0 ? 200 * 1024 : ctas > 148 ? 73 * 1024 - scratch : 72 * 1024;
+  if (max_stages > 0 && stages > max_stages) stages = max_stages;
+  const int fixed = BARRIER_BYTES + scratch + 1024;
+  while (stages > 1 && (stages * stage_bytes > budget || stages * stage_bytes + fixed > 227 * 1024)) --stages;
+  if (stages < 1) stages = 1;
+  const int smem = stages * stage_bytes + fixed;
+  if (smem > 227 * 1024) return DLI_ERR_UNSUPPORTED;
   int tmem_cols = 32;
   while (tmem_cols < npad) tmem_cols <<= 1;
   static int configured = 0;
