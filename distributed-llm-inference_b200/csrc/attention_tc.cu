@@ -451,7 +451,16 @@ constexpr int DWARPS = 4;
 constexpr int DTILE = DN * 128;        // one K or V tile: 16 rows of 128 bytes, swizzled
 constexpr int QROW = D * 2 + 16;       // padded query rows (read once)
 static_assert(DWARPS * 16 * (D + 2) * 4 <= DWARPS * DSTAGES * 2 * DTILE, "the merge buffer reuses the key/value stages");
-constexpr int DSMEM = 1024 + DWARPS * DSTAGES * 2 * DTILE + 16 * QROW + DWARPS * DSTAGES * 8 + 64;
+// Splits merged inside a cluster: row r of the 16 belongs to CTA (r mod splits); every CTA pushes its
+// partial (sums[D], maximum, denominator) of a row into the owner's memory.  At most 16 + 7 rows arrive
+// at one CTA (splits * ceil(16 / splits)).  The region starts where the query rows lay: they are in
+// registers by then.  With it the kernel still fits four CTAs per SM.
+constexpr int CLUSTER_SPLITS_MAX = 8;
+constexpr int RECV_ROW = D + 2;
+constexpr int RECV_BYTES = (16 + CLUSTER_SPLITS_MAX - 1) * RECV_ROW * 4;
+static_assert(RECV_BYTES >= 16 * QROW, "the received partial results lie over the query rows");
+constexpr int DSMEM = 1024 + DWARPS * DSTAGES * 2 * DTILE + RECV_BYTES + DWARPS * DSTAGES * 8 + 64;
+static_assert(4 * (DSMEM + 1024) <= 227 * 1024, "four CTAs per SM");
 
 struct DecodeParams {
   bf16* out;
@@ -462,11 +471,21 @@ struct DecodeParams {
   const int* q_start;
   const int* kv_len;
   int seq0, nh, nkv, page_size, window, splits;
+  int cluster_merge;  // the splits of a (sequence, head group) are one cluster and merge through shared memory
   float scale_log2;
   float* part_acc;
   float* part_ml;
   int* error_flag;
 };
+
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// store into the same shared-memory offset of another CTA of the cluster
+__device__ __forceinline__ void st_peer_shared(uint32_t local_addr, uint32_t cta_rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -483,24 +502,23 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// grid (splits, sequences, kv heads * chunks of 16 query heads).  The 16 rows of a warp's MMA tile
+// grid (sequences, splits, kv heads * chunks of 16 query heads).  The 16 rows of a warp's MMA tile
 // are the query heads of one KV head; each warp walks its own share of the 16-key tiles.  A tile's
 // keys and values arrive by TMA (one box per page piece, 128-byte swizzle), four tiles ahead, on the
 // warp's own mbarriers: no thread spends instructions on addresses of individual 16-byte copies.
 __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
   pdl_launch_dependents();
-  pdl_wait();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sKV = smem;                                   // [warp][stage][K | V]
   unsigned char* sQ = sKV + DWARPS * DSTAGES * 2 * DTILE;      // 16 padded rows
-  uint64_t* bars = (uint64_t*)(sQ + 16 * QROW);                // [warp][stage]
+  uint64_t* bars = (uint64_t*)(sQ + RECV_BYTES);               // [warp][stage]
   volatile int* failed = (volatile int*)(bars + DWARPS * DSTAGES);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int s = p.seq0 + blockIdx.y;
-  const int split = blockIdx.x;
+  const int s = p.seq0 + blockIdx.x;
+  const int split = blockIdx.y;
   const int G = p.nh / p.nkv;
   const int chunks = (G + 15) / 16;
   const int kvh = blockIdx.z / chunks, hc = blockIdx.z - kvh * chunks;
@@ -524,18 +542,7 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  for (int idx = tid; idx < 16 * 8; idx += DWARPS * 32) {
-    const int r = idx >> 3, c = idx & 7;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < nheads) v = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)(head0 + r) * D + c * 8);
-    *reinterpret_cast<uint4*>(sQ + r * QROW + c * 16) = v;
-  }
-  __syncthreads();
-
-  // the query fragments stay in registers
-  uint32_t qf[D / 16][4];
-#pragma unroll
-  for (int kk = 0; kk < D / 16; ++kk) ldsm_x4(qf[kk], smem_u32(sQ + (lane & 15) * QROW + (kk * 16 + (lane >> 4) * 8) * 2));
+  __syncwarp();  // this warp's barriers are set up
 
   unsigned char* wbuf = sKV + warp * DSTAGES * 2 * DTILE;
   const uint32_t wbar = smem_u32(bars + warp * DSTAGES);
@@ -583,8 +590,31 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
 #pragma unroll
   for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
 
-  for (int i = 0; i < DSTAGES - 1 && i < my_tiles; ++i) issue(i);
-  __syncwarp();
+  // Keys and values of earlier steps do not depend on the kernel before this one (it wrote this
+  // step's token only), nor do the tables and lengths: the first tiles are requested before the wait
+  // on that kernel, all but the tile that holds the new token.
+  const int newest_tile = pos / DN;
+  int deferred = -1;
+  for (int i = 0; i < DSTAGES - 1 && i < my_tiles; ++i) {
+    if (t_begin + warp + i * DWARPS == newest_tile) deferred = i;  // the last of this warp's tiles, if any
+    else issue(i);
+  }
+  pdl_wait();
+  if (deferred >= 0) issue(deferred);
+
+  for (int idx = tid; idx < 16 * 8; idx += DWARPS * 32) {
+    const int r = idx >> 3, c = idx & 7;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < nheads) v = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)(head0 + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(sQ + r * QROW + c * 16) = v;
+  }
+  __syncthreads();
+
+  // the query fragments stay in registers
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) ldsm_x4(qf[kk], smem_u32(sQ + (lane & 15) * QROW + (kk * 16 + (lane >> 4) * 8) * 2));
+  if (p.cluster_merge) cluster_arrive();  // this thread is done with the query rows; waited for before the first push
 
   bool ok = true;
   for (int i = 0; i < my_tiles; ++i) {
@@ -679,7 +709,11 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
     }
   }
   __syncthreads();
-  if (*failed) return;
+  const bool bad = *failed != 0;
+  if (bad && !p.cluster_merge) return;
+  float* recv = reinterpret_cast<float*>(sQ);  // [split][owned row][sums | maximum | denominator]
+  const int owned_max = (16 + p.splits - 1) / p.splits;
+  if (p.cluster_merge) cluster_wait();  // every CTA of the cluster has its query in registers: the region may be written
   for (int idx = tid; idx < nheads * D; idx += DWARPS * 32) {
     const int r = idx / D, dcol = idx - r * D;
     float mx = -CUDART_INF_F;
@@ -696,6 +730,14 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
     const size_t row = (size_t)token * p.nh + head0 + r;
     if (p.splits == 1) {
       p.out[row * D + dcol] = __float2bfloat16_rn(acc / L);
+    } else if (p.cluster_merge) {
+      const uint32_t dst = smem_u32(recv + (split * owned_max + r / p.splits) * RECV_ROW);
+      const int owner = r % p.splits;
+      st_peer_shared(dst + dcol * 4, owner, acc);
+      if (dcol == 0) {
+        st_peer_shared(dst + D * 4, owner, mx);
+        st_peer_shared(dst + (D + 1) * 4, owner, L);
+      }
     } else {
       p.part_acc[(row * p.splits + split) * D + dcol] = acc;
       if (dcol == 0) {
@@ -703,6 +745,29 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
         p.part_ml[(row * p.splits + split) * 2 + 1] = L;
       }
     }
+  }
+  if (!p.cluster_merge) return;
+  __syncwarp();
+  cluster_arrive();
+  cluster_wait();  // every split's partial result of my rows has arrived; nobody touches a peer's memory from here on
+  if (bad) return;
+  const int mine = split < nheads ? (nheads - split + p.splits - 1) / p.splits : 0;
+  for (int idx = tid; idx < mine * D; idx += DWARPS * 32) {
+    const int ri = idx / D, dcol = idx - ri * D;
+    const int r = split + ri * p.splits;
+    float mx = -CUDART_INF_F;
+    for (int i = 0; i < p.splits; ++i) mx = fmaxf(mx, recv[(i * owned_max + ri) * RECV_ROW + D]);
+    float L = 0.f, acc = 0.f;
+    for (int i = 0; i < p.splits; ++i) {  // split 0 first: a fixed order
+      const float* part = recv + (i * owned_max + ri) * RECV_ROW;
+      const float mi = part[D];
+      if (mi != -CUDART_INF_F) {
+        const float f = ex2(mi - mx);
+        L += part[D + 1] * f;
+        acc += part[dcol] * f;
+      }
+    }
+    p.out[((size_t)token * p.nh + head0 + r) * D + dcol] = __float2bfloat16_rn(acc / L);
   }
 }
 
@@ -734,7 +799,8 @@ __global__ void merge_decode_splits_kernel(bf16* __restrict__ out, const float* 
 }  // namespace
 
 // Attention of num_seqs single-token sequences (head size 64; page size a multiple of 8, and of 16
-// if larger than 8).  part_acc / part_ml: scratch for splits > 1, as for dli_paged_attention_mma.
+// if larger than 8).  Up to 8 splits are one cluster and merge on the chip; more go through
+// part_acc / part_ml (scratch, as for dli_paged_attention_mma) and a second kernel.
 DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                     long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
                                     const int* kv_len, int seq0, int num_seqs, int first_row, int nh, int nkv, int page_size,
@@ -764,11 +830,12 @@ DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride
   p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.window = window; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.part_acc = part_acc; p.part_ml = part_ml; p.error_flag = error_flag_device;
+  p.cluster_merge = splits > 1 && splits <= CLUSTER_SPLITS_MAX;
   const int G = nh / nkv;
-  cudaError_t e = launch_pdl(paged_decode_tma_kernel, dim3(splits, num_seqs, nkv * ((G + 15) / 16)), dim3(DWARPS * 32), (size_t)DSMEM, stream, 1,
-                             map_k, map_v, p);
+  cudaError_t e = launch_pdl(paged_decode_tma_kernel, dim3(num_seqs, splits, nkv * ((G + 15) / 16)), dim3(DWARPS * 32), (size_t)DSMEM, stream,
+                             p.cluster_merge ? splits : 1, map_k, map_v, p);
   if (e != cudaSuccess) return (int)e;
-  if (splits > 1)
+  if (splits > 1 && !p.cluster_merge)
     e = launch_pdl(merge_decode_splits_kernel, dim3(num_seqs * nh), dim3(64), 0, stream, 1, (bf16*)out, (const float*)part_acc,
                    (const float*)part_ml, first_row * nh, splits);
   return (int)e;

@@ -18,6 +18,10 @@ ONE_WAVE_TMA = 148 * 4  # ... of the TMA-fed decode kernel (four per SM)
 MIN_TILES_PER_SPLIT = 2  # key tiles (of 64) a split should at least cover
 
 
+CLUSTER_SPLITS_MAX = ops.DECODE_TMA_CLUSTER_SPLITS  # splits that the TMA decode kernel merges inside one thread-block cluster
+CLUSTER_SPLITS_KV_LIMIT = 16384
+
+
 def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int = ONE_WAVE) -> int:
     """Key splits for single-token sequences: as many as still fit the GPU in one wave (a second,
     partly filled wave costs more than the extra parallelism brings), none shorter than
@@ -30,8 +34,11 @@ def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int =
 def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_size: int, max_kv_len: int) -> int:
     """Key splits of the decode kernel that will serve these sizes."""
     ctas_per_seq = nkv * -(-(num_heads // nkv) // 16)
-    wave = ONE_WAVE_TMA if ops.decode_tma_supported(head_dim, page_size) else ONE_WAVE
-    return choose_splits(num_seqs, ctas_per_seq, max_kv_len, wave)
+    tma = ops.decode_tma_supported(head_dim, page_size)
+    splits = choose_splits(num_seqs, ctas_per_seq, max_kv_len, ONE_WAVE_TMA if tma else ONE_WAVE)
+    if tma and splits > CLUSTER_SPLITS_MAX and max_kv_len <= CLUSTER_SPLITS_KV_LIMIT:
+        splits = CLUSTER_SPLITS_MAX  # merged on the chip by one cluster: measured faster than more splits and a merge kernel
+    return splits
 
 
 def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_heads: int, scale: float, window: int | None) -> None:

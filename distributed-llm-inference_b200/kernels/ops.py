@@ -19,6 +19,7 @@ DT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 # number of this package's kernels launched since import (a graph replay adds its node count)
 launch_count = 0
+DECODE_TMA_CLUSTER_SPLITS = 8  # CLUSTER_SPLITS_MAX of csrc/attention_tc.cu
 
 
 class KernelError(RuntimeError):
@@ -335,8 +336,8 @@ def paged_decode_tma(
         "paged_decode_tma",
     )
     global launch_count
-    if splits > 1:
-        launch_count += 1  # the merge kernel
+    if splits > DECODE_TMA_CLUSTER_SPLITS:
+        launch_count += 1  # the merge kernel; up to that many splits merge inside the kernel, as one cluster
 
 
 def paged_prefill_tc_error() -> int:
