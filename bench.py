@@ -133,10 +133,12 @@ def make_engine(model, batch, steps_total):
 
 
 def decode_device_timed(model, batch, steps, warmup, sampler_clock=None, graphs=True):
-    """K decode steps timed on the device: step function plus greedy sampling, token ids fed
-    back from the host copy of the previous step's result."""
+    """K decode steps timed on the device: step function plus greedy sampling.  Each step runs on
+    the ids the step before sampled, taken on the device; the host reads every step's ids, one
+    step late (the engine's own way of stepping)."""
     import torch
 
+    from dli_b200.cache import UNKNOWN_TOKEN
     from dli_b200.engine import ModelRunner, StepEntry
     from dli_b200.kernels import ops
     from dli_b200.sampling import Sampler, SamplingParams
@@ -154,15 +156,31 @@ def decode_device_timed(model, batch, steps, warmup, sampler_clock=None, graphs=
         logits = runner.step([StepEntry(b, prompt, [PROMPT_LEN - 1])])
         tokens.append(sampler.sample(logits, params[:1], [0], [0])[0])
 
-    def one_step(tokens):
+    def launch(prev):
+        """One decode step of every request, launched on the ids the step before left on the device
+        (``prev``: PendingTokens), as LLMEngine.step does; the host reads those ids afterwards."""
         entries = []
         for b in range(batch):
-            runner.manager.append_slots(b, [tokens[b]])
-            entries.append(StepEntry(b, [tokens[b]], [0]))
-        return sampler.sample(runner.step(entries, borrow=True), params, [0] * batch, [0] * batch)
+            runner.manager.append_slots(b, [UNKNOWN_TOKEN])  # no prefix index in this run: the id is never needed
+            entries.append(StepEntry(b, [0], [0], token_src=b))
+        logits = runner.step(entries, borrow=True, token_source=prev.device_ids)
+        return sampler.sample_async(logits, params, [0] * batch, [0] * batch)
+
+    # the first step runs on ids the host knows
+    for b in range(batch):
+        runner.manager.append_slots(b, [tokens[b]])
+    flight = sampler.sample_async(runner.step([StepEntry(b, [tokens[b]], [0]) for b in range(batch)], borrow=True),
+                                  params, [0] * batch, [0] * batch)
+
+    def one_step(flight):
+        ahead = launch(flight)
+        ids = flight.result()  # this step's tokens reach the host while the next step runs
+        assert len(ids) == batch
+        return ahead
 
     for _ in range(warmup):
-        tokens = one_step(tokens)
+        flight = one_step(flight)
+    flight.result()
     ctx_start = runner.manager.num_tokens(0)
     torch.cuda.synchronize()
     if sampler_clock:
@@ -171,9 +189,10 @@ def decode_device_timed(model, batch, steps, warmup, sampler_clock=None, graphs=
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(steps):
-        tokens = one_step(tokens)
+        flight = one_step(flight)
     end.record()
     torch.cuda.synchronize()
+    flight.result()
     if sampler_clock:
         sampler_clock.stop()
     ms = start.elapsed_time(end) / steps

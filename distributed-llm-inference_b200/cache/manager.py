@@ -24,6 +24,8 @@ import numpy as np
 
 from .page_pool import ROOT, OutOfPages, PagePool, chain_hashes, page_hash
 
+UNKNOWN_TOKEN = -1  # stands for a token id that is still on the device (append_slots, set_token)
+
 
 class UnknownRequest(KeyError):
     pass
@@ -219,7 +221,9 @@ class CacheManager:
         return Allocation(cached, req.slot)
 
     def append_slots(self, rid: Hashable, token_ids: Sequence[int]) -> None:
-        """Room for tokens appended to the request (a sampled token); ignores the watermark."""
+        """Room for tokens appended to the request (a sampled token); ignores the watermark.
+        A token whose id is not known yet (sampled on the device, not read) is UNKNOWN_TOKEN;
+        ``set_token`` names it later, and no page that holds one is indexed until then."""
         req = self._get(rid)
         ps = self.page_size
         first, last = req.num_tokens, req.num_tokens + len(token_ids)
@@ -243,16 +247,7 @@ class CacheManager:
             raise ValueError(f"computed must be in [{req.num_computed}, {req.num_tokens}], got {num_computed}")
         req.num_computed = num_computed
         ps = self.page_size
-        if self.prefix_caching and req.registered < num_computed // ps:
-            full = num_computed // ps
-            while req.registered < full:
-                i = req.registered
-                while len(req.hashes) <= i:
-                    req.hashes.append(page_hash(req.namespace, req.hashes[-1] if req.hashes else ROOT, req.tail[:ps]))
-                    del req.tail[:ps]
-                for pool, table in zip(self.pools, req.tables):
-                    pool.register(table[i], req.hashes[i], req.hashes[i - 1] if i else None, table[i - 1] if i else None)
-                req.registered += 1
+        self._index_full_pages(req)
         if not self._has_window:
             return
         for g, (group, pool, table) in enumerate(zip(self.groups, self.pools, req.tables)):
@@ -265,6 +260,34 @@ class CacheManager:
                     pool.release(table[j])
                     table[j] = -1
                     self._mirror[g][req.slot, j] = -1
+
+    def _index_full_pages(self, req: _Request) -> None:
+        """Full pages whose keys and values are written and whose tokens are all known become shareable."""
+        ps = self.page_size
+        if not self.prefix_caching or req.registered >= req.num_computed // ps:
+            return
+        full = req.num_computed // ps
+        while req.registered < full:
+            i = req.registered
+            if len(req.hashes) <= i:
+                if UNKNOWN_TOKEN in req.tail[:ps]:
+                    return  # waits for set_token
+                req.hashes.append(page_hash(req.namespace, req.hashes[-1] if req.hashes else ROOT, req.tail[:ps]))
+                del req.tail[:ps]
+            for pool, table in zip(self.pools, req.tables):
+                pool.register(table[i], req.hashes[i], req.hashes[i - 1] if i else None, table[i - 1] if i else None)
+            req.registered += 1
+
+    def set_token(self, rid: Hashable, position: int, token_id: int) -> None:
+        """Name the token at ``position`` that was appended as UNKNOWN_TOKEN."""
+        req = self._get(rid)
+        if not self.prefix_caching:
+            return
+        i = position - len(req.hashes) * self.page_size
+        if not 0 <= i < len(req.tail) or req.tail[i] != UNKNOWN_TOKEN:
+            raise ValueError(f"request {rid!r} has no unknown token at position {position}")
+        req.tail[i] = int(token_id)
+        self._index_full_pages(req)
 
     def free(self, rid: Hashable) -> None:
         """Give back everything a finished, aborted or preempted request holds."""

@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(THREADS, 2) paged_prefill_tc_kernel(const __gr
                  p_ready = smem_u32(bars + 5), o_read = smem_u32(bars + 6);
 
   const int s = p.seq0 + blockIdx.y;
-  const int tile = blockIdx.x;
+  const int tile = gridDim.x - 1 - blockIdx.x;  // the last tokens see the most keys: their CTAs start first
   const int kvh = blockIdx.z / p.head_chunks, hc = blockIdx.z - kvh * p.head_chunks;
   const int q0 = p.q_start[s];
   const int qlen = p.q_start[s + 1] - q0;

@@ -48,6 +48,21 @@ DLI_EXPORT int dli_embedding(float* h, const void* table, const int* ids, int n,
   return (int)cudaGetLastError();
 }
 
+// Token ids that were sampled on the device one step earlier and never travelled to the host:
+// ids[i] = source[src[i]] wherever src[i] >= 0.
+__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ source, const int* __restrict__ src, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && src[i] >= 0) ids[i] = source[src[i]];
+}
+
+DLI_EXPORT int dli_patch_tokens(int* ids, const int* source, const int* src, int n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  launch_pdl(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 1, ids, source, src, n);
+  return (int)cudaGetLastError();
+}
+
 // ---------------------------------------------------------------- add + rmsnorm
 // For output row r (source row s = rows ? rows[r] : r):
 //   v = h[s] + delta[s]            (float32; written back to h[s] when rows == nullptr)

@@ -13,7 +13,8 @@
 //     end, signals the epilogue;
 //   * four warps read the accumulator with tcgen05.ld (lane = feature, column = token) and
 //     store, coalesced along features — or finish the layer's next elementwise step in place:
-//     SiLU(gate) * up, or the rotary embedding with the write of keys and values into the cache.
+//     SiLU(gate) * up, the rotary embedding with the write of keys and values into the cache, or
+//     the residual addition with the first half of the next RMS norm (see Epilogue).
 //
 // The grid is (feature tiles, K slices).  Slices exist to fill the GPU when a matrix has few
 // feature tiles.  The CTAs of one tile's slices form a thread-block cluster (up to 8): each
@@ -36,7 +37,10 @@ constexpr int BM = 128;       // features per CTA
 constexpr int BK = 64;        // k per stage: 128 bytes of bfloat16, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int BARRIER_BYTES = 256;  // mbarriers (at most 17), the TMEM address and the failure flag, behind the stages
+constexpr int BARRIER_BYTES = 512;  // behind the stages: mbarriers (at most 17), the TMEM address, the failure flag,
+constexpr int WSUM_OFFSET = 192;    // four warp sums,
+constexpr int RSTD_OFFSET = 256;    // and the row factors of up to RSTD_MAX_TOKENS tokens
+constexpr int RSTD_MAX_TOKENS = 64;
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -99,13 +103,20 @@ __device__ __forceinline__ void store_out(void* out, int out_f32, size_t idx, fl
 }
 
 // What happens to the finished sums of a tile.
-//   EP_STORE   out[t, f] = sum                                   (bfloat16 or float32)
-//   EP_SWIGLU  the weight rows were interleaved in blocks of 64 (64 gate rows, then the 64 up rows of the
-//              same features), so a tile holds both: out[t, 64 * tile + i] = silu(gate_i) * up_i
-//   EP_ROTARY  the features are q | k | v heads of size d (d divides 128, so a head never straddles tiles):
-//              q and k are rotated by the token's position (rotate-half pairing over the first `rot`
-//              elements), q goes to out[t, nh * d], k and v into the cache pages at the token's slot
-enum { EP_STORE = 0, EP_SWIGLU = 1, EP_ROTARY = 2 };
+//   EP_STORE     out[t, f] = sum                                   (bfloat16 or float32)
+//   EP_SWIGLU    the weight rows were interleaved in blocks of 64 (64 gate rows, then the 64 up rows of the
+//                same features), so a tile holds both: out[t, 64 * tile + i] = silu(gate_i) * up_i
+//   EP_ROTARY    the features are q | k | v heads of size d (d divides 128, so a head never straddles tiles):
+//                q and k are rotated by the token's position (rotate-half pairing over the first `rot`
+//                elements), q goes to out[t, nh * d], k and v into the cache pages at the token's slot
+//   EP_RESIDUAL  the product is the delta of a residual stream: h[t, f] += sum (float32, in place),
+//                out[t, f] = bfloat16(h[t, f] * gain[f]), the input of the next RMS norm's consumer, and
+//                out_ssq[t, tile] = the tile's sum of h[t, f]^2.  The division by the row's RMS is left to
+//                the product that reads `out` (row scaling, below): it is a factor per token, so it
+//                commutes with the product and is applied to the float32 sums.
+// Row scaling of the input (in_ssq != null): the activations are h * gain of EP_RESIDUAL; every sum of
+// token t is multiplied by rsqrt(sum over in_tiles of in_ssq[t, .] * in_inv_size + in_eps).
+enum { EP_STORE = 0, EP_SWIGLU = 1, EP_ROTARY = 2, EP_RESIDUAL = 3 };
 struct Epilogue {
   int mode;
   const int* positions;
@@ -114,10 +125,34 @@ struct Epilogue {
   __nv_bfloat16* k_pool;
   __nv_bfloat16* v_pool;
   int nh, nkv, d, rot, page_size, write_kv;
+  float* h;
+  const float* gain;
+  float* out_ssq;
+  const float* in_ssq;
+  int in_tiles;
+  float in_eps, in_inv_size;
 };
 
-// fin: this token's 128 finished sums of the tile; fl: the feature of this thread
-__device__ __forceinline__ void fused_epilogue(const Epilogue& ep, void* out, const float* fin, int t, int tile, int fl, int features) {
+// fin: this token's 128 finished sums of the tile; fl: the feature of this thread; h_pre: h[t, f] if the
+// caller loaded it ahead (have_h); gain: the next norm's weight of this feature (EP_RESIDUAL).  Called by all threads of the CTA together.
+__device__ __forceinline__ void fused_epilogue(const Epilogue& ep, void* out, const float* fin, int t, int tile, int fl, int features,
+                                               float* wsum, float h_pre, bool have_h, float gain) {
+  if (ep.mode == EP_RESIDUAL) {
+    const int f = tile * BM + fl;
+    float hn = 0.f;
+    if (f < features) {
+      const size_t idx = (size_t)t * features + f;
+      hn = (have_h ? h_pre : ep.h[idx]) + fin[fl];
+      ep.h[idx] = hn;
+      ((__nv_bfloat16*)out)[idx] = __float2bfloat16_rn(hn * gain);
+    }
+    const float sq = warp_sum(hn * hn);
+    if ((fl & 31) == 0) wsum[fl >> 5] = sq;
+    __syncthreads();
+    if (fl == 0) ep.out_ssq[(size_t)t * gridDim.x + tile] = (wsum[0] + wsum[1]) + (wsum[2] + wsum[3]);
+    __syncthreads();  // the warp sums are free for the next token
+    return;
+  }
   if (ep.mode == EP_SWIGLU) {
     const int I = features >> 1, col = tile * 64 + fl;
     if (fl < 64 && col < I) {
@@ -175,6 +210,8 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   uint64_t* bars = (uint64_t*)(smem + (size_t)stages * stage_bytes);  // full[stages], empty[stages], accum
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * stages + 1);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
+  float* wsum = (float*)((unsigned char*)bars + WSUM_OFFSET);
+  float* rstd = (float*)((unsigned char*)bars + RSTD_OFFSET);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + stages), accum = smem_u32(bars + 2 * stages);
@@ -254,9 +291,24 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
     umma_commit(accum);  // arrives once every MMA issued so far has finished
     }
     __syncwarp();
+  } else if (ep.in_ssq) {
+    // ---- the other two warps: the factor of every token's row, while the products run
+    // (a warp per token, a lane per tile's sum of squares: the loads of a token are in flight together, and
+    // the order of the additions depends on the number of tiles alone)
+    pdl_wait();
+#pragma unroll 4
+    for (int t = warp - 2; t < tokens; t += 2) {
+      float sum = 0.f;
+      for (int i = lane; i < ep.in_tiles; i += 32) sum += ep.in_ssq[(size_t)t * ep.in_tiles + i];
+      sum = warp_sum(sum);
+      if (lane == 0) rstd[t] = rsqrtf(sum * ep.in_inv_size + ep.in_eps);
+    }
   }
 
   // ---- epilogue: all four warps; lane = feature row of the tile, column = token
+  // (the norm's gain is a weight: asked for before anything is waited for)
+  const int f_own = blockIdx.x * BM + (int)threadIdx.x;
+  const float gain_pre = (ep.mode == EP_RESIDUAL && f_own < features) ? ep.gain[f_own] : 0.f;
   bool ok = true;
   if (nkt > 0) {
     ok = mbar_wait(accum, 0);
@@ -267,6 +319,11 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   ok = ok && !*failed;
   const int fl = warp * 32 + lane, f = tile * BM + fl;
   const int slices = gridDim.y;  // the cluster spans the grid's y dimension: slice = rank in the cluster
+  const bool scaled = ep.in_ssq != nullptr;
+  if (scaled) __syncthreads();  // the row factors are in place
+  // the residual of this CTA's first token is asked for now and used after the reduction
+  const bool have_h = ep.mode == EP_RESIDUAL && slice < tokens && f < features;
+  const float h_pre = have_h ? ep.h[(size_t)slice * features + f] : 0.f;
   const bool fused = ep.mode != EP_STORE;
   // With several slices, token t belongs to CTA (t mod slices) of the cluster.  Every CTA pushes its
   // partial sums of a token straight into the owner's shared memory (remote stores need no answer),
@@ -299,9 +356,9 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
         const int owner = t % slices, ti = t / slices;
         st_peer_shared(recv_addr + (uint32_t)(((slice * owned_max + ti) * BM + fl) * 4), owner, __uint_as_float(r[j]));
       } else if (fused) {
-        recv[t * BM + fl] = __uint_as_float(r[j]);
+        recv[t * BM + fl] = __uint_as_float(r[j]) * (scaled ? rstd[t] : 1.f);
       } else if (f < features) {
-        store_out(out, out_f32, (size_t)t * features + f, __uint_as_float(r[j]));
+        store_out(out, out_f32, (size_t)t * features + f, __uint_as_float(r[j]) * (scaled ? rstd[t] : 1.f));
       }
     }
   }
@@ -313,13 +370,15 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
       float acc = 0.f;
 #pragma unroll 8
       for (int s2 = 0; s2 < slices; ++s2) acc += recv[(s2 * owned_max + ti) * BM + fl];  // slice 0 first
+      if (scaled) acc *= rstd[t];
       if (fused) fin[ti * BM + fl] = acc;
       else if (f < features) store_out(out, out_f32, (size_t)t * features + f, acc);
     }
   }
   if (fused) {
     __syncthreads();  // the finished sums of every feature of the tile are in place
-    for (int t = slice, ti = 0; t < tokens; t += slices, ++ti) fused_epilogue(ep, out, fin + ti * BM, t, tile, fl, features);
+    for (int t = slice, ti = 0; t < tokens; t += slices, ++ti)
+      fused_epilogue(ep, out, fin + ti * BM, t, tile, fl, features, wsum, h_pre, have_h && ti == 0, gain_pre);
   }
 
   // ---- teardown: nobody touches tensor memory after this barrier; warp 0 frees it
@@ -420,20 +479,32 @@ static int launch_skinny(void* out, int out_f32, const void* x, const void* w, i
   return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
+// Row scaling of the input (see Epilogue): in_ssq [tokens, in_tiles] or null.
+static bool set_row_scale(Epilogue& ep, int tokens, const float* in_ssq, int in_tiles, float in_eps, int in_size) {
+  ep.in_ssq = in_ssq;
+  if (!in_ssq) return true;
+  if (tokens > RSTD_MAX_TOKENS || in_tiles < 1 || in_size < 1) return false;
+  ep.in_tiles = in_tiles; ep.in_eps = in_eps; ep.in_inv_size = 1.f / (float)in_size;
+  return true;
+}
+
 DLI_EXPORT int dli_skinny_gemm(void* out, int out_f32, const void* x, const void* w, int tokens, int features, int K,
-                               int slices, int max_stages, cudaStream_t stream) {
+                               int slices, int max_stages, const float* in_ssq, int in_tiles, float in_eps, int in_size,
+                               cudaStream_t stream) {
   Epilogue ep = {};
   ep.mode = EP_STORE;
+  if (!set_row_scale(ep, tokens, in_ssq, in_tiles, in_eps, in_size)) return DLI_ERR_UNSUPPORTED;
   return launch_skinny(out, out_f32, x, w, tokens, features, K, slices, max_stages, ep, stream);
 }
 
 // act[tokens, features / 2] = silu(gate) * up, for weights whose rows are interleaved in blocks of 64
 // (rows 128 j .. 128 j + 63: gate features 64 j .., rows 128 j + 64 .. 128 j + 127: the same up features).
 DLI_EXPORT int dli_skinny_gemm_swiglu(void* act, const void* x, const void* w, int tokens, int features, int K, int slices,
-                                      cudaStream_t stream) {
+                                      const float* in_ssq, int in_tiles, float in_eps, int in_size, cudaStream_t stream) {
   if (features % 128) return DLI_ERR_UNSUPPORTED;
   Epilogue ep = {};
   ep.mode = EP_SWIGLU;
+  if (!set_row_scale(ep, tokens, in_ssq, in_tiles, in_eps, in_size)) return DLI_ERR_UNSUPPORTED;
   return launch_skinny(act, 0, x, w, tokens, features, K, slices, 0, ep, stream);
 }
 
@@ -441,15 +512,31 @@ DLI_EXPORT int dli_skinny_gemm_swiglu(void* act, const void* x, const void* w, i
 // receives the rotated queries; keys (rotated) and values go to the pools [pages, nkv, page_size, d] at slots[t].
 DLI_EXPORT int dli_skinny_gemm_rotary(void* q_out, const void* x, const void* w, int tokens, int K, int slices, const int* positions,
                                       const float* inv_freq, const int* slots, void* k_pool, void* v_pool, int nh, int nkv, int d,
-                                      int rot, int page_size, int write_kv, cudaStream_t stream) {
+                                      int rot, int page_size, int write_kv, const float* in_ssq, int in_tiles, float in_eps,
+                                      int in_size, cudaStream_t stream) {
   if (d < 2 || (BM % d) != 0 || rot < 0 || rot > d || (rot & 1) || (rot > 0 && !inv_freq)) return DLI_ERR_UNSUPPORTED;
   if (write_kv && (!slots || !k_pool || !v_pool)) return DLI_ERR_UNSUPPORTED;
   Epilogue ep = {};
   ep.mode = EP_ROTARY;
+  if (!set_row_scale(ep, tokens, in_ssq, in_tiles, in_eps, in_size)) return DLI_ERR_UNSUPPORTED;
   ep.positions = positions; ep.inv_freq = inv_freq; ep.slots = slots;
   ep.k_pool = (__nv_bfloat16*)k_pool; ep.v_pool = (__nv_bfloat16*)v_pool;
   ep.nh = nh; ep.nkv = nkv; ep.d = d; ep.rot = rot; ep.page_size = page_size; ep.write_kv = write_kv;
   return launch_skinny(q_out, 0, x, w, tokens, (nh + 2 * nkv) * d, K, slices, 0, ep, stream);
+}
+
+// The delta of a residual stream with the first half of the next RMS norm (EP_RESIDUAL): h [tokens, features]
+// float32 is updated in place, x_out [tokens, features] receives bfloat16(h * gain), out_ssq
+// [tokens, ceil(features / 128)] the sums of squares per tile of 128 features.
+DLI_EXPORT int dli_skinny_gemm_residual(void* x_out, float* h, const float* gain, float* out_ssq, const void* x, const void* w,
+                                        int tokens, int features, int K, int slices, const float* in_ssq, int in_tiles, float in_eps,
+                                        int in_size, cudaStream_t stream) {
+  if (!h || !gain || !out_ssq) return DLI_ERR_UNSUPPORTED;
+  Epilogue ep = {};
+  ep.mode = EP_RESIDUAL;
+  ep.h = h; ep.gain = gain; ep.out_ssq = out_ssq;
+  if (!set_row_scale(ep, tokens, in_ssq, in_tiles, in_eps, in_size)) return DLI_ERR_UNSUPPORTED;
+  return launch_skinny(x_out, 0, x, w, tokens, features, K, slices, 0, ep, stream);
 }
 
 // 0, or the code of the first wait that ran out (1 producer, 2 MMA issuer, 3 epilogue)

@@ -22,6 +22,9 @@ class StepEntry:
     request_id: Hashable
     token_ids: Sequence[int]  # the request's next tokens, at positions start .. start + len - 1
     want: Sequence[int] = ()  # indices into token_ids whose logits are returned
+    # >= 0: the entry brings one token whose id the host does not know yet; it is this row of the
+    # step's token source (ids sampled on the device by the step before), and token_ids[0] is ignored
+    token_src: int = -1
 
 
 @dataclass
@@ -51,6 +54,8 @@ class StepBatch:
     max_kv_len: int = 0
     max_kv_len_single: int = 0  # longest context among the single-token sequences
     forced_splits: int = 0  # key splits of decode attention fixed by the caller (0: chosen per step)
+    token_src: torch.Tensor | None = None  # [n] int32: row of the token source per token, -1 where token_ids holds the id
+    logits_all_rows: bool = False  # logit_rows is 0, 1, .., n - 1: the final norm's output needs no gather
     scratch: dict = field(default_factory=dict)  # per-step results that parts share across layers; cleared by each forward
 
     def group(self, index: int) -> GroupView:
@@ -112,6 +117,10 @@ def _check_entries(entries: Sequence[StepEntry], vocab_size: int) -> list[np.nda
         a = np.asarray(e.token_ids, dtype=np.int64)
         if a.ndim != 1 or a.size == 0:
             raise ValueError(f"request {e.request_id!r} brings no tokens")
+        if e.token_src >= 0:
+            if a.size != 1:
+                raise ValueError(f"request {e.request_id!r}: a token from the device comes alone")
+            a = np.zeros(1, dtype=np.int64)
         if a.min() < 0 or a.max() >= vocab_size:
             bad = int(a[(a < 0) | (a >= vocab_size)][0])
             raise ValueError(f"token id {bad} of request {e.request_id!r} is outside the vocabulary [0, {vocab_size})")
@@ -157,7 +166,14 @@ def gather_host(entries: Sequence[StepEntry], manager, vocab_size: int):
         slots.append(pages * ps + positions % ps)
         tables.append(table[rows, :width])
     logit_rows = [int(q_start[place[i]]) + w for i, e in enumerate(entries) for w in e.want]
+    token_src = None
+    if any(e.token_src >= 0 for e in entries):
+        token_src = np.full(n, -1, dtype=np.int64)
+        for i, e in enumerate(entries):
+            if e.token_src >= 0:
+                token_src[q_start[place[i]]] = e.token_src
     return dict(
+        token_src=token_src,
         token_ids=np.concatenate([arrays[old] for old in order]), positions=positions, seq_of_token=seq_of_token,
         q_start=q_start, kv_len=kv_len, state_slot=rows, logit_rows=np.asarray(logit_rows, dtype=np.int64),
         slots=slots, tables=tables, q_lens=q_lens, starts=starts, n=n, S=S, width=width, place=place,
@@ -171,6 +187,7 @@ def gather_single_tokens(entries: Sequence[StepEntry], manager, vocab_size: int)
     if S == 0:
         raise ValueError("a step needs at least one entry")
     tokens = np.empty(S, dtype=np.int64)
+    src = np.empty(S, dtype=np.int64)
     starts = np.empty(S, dtype=np.int64)
     rows = np.empty(S, dtype=np.int64)
     seen = set()
@@ -180,7 +197,8 @@ def gather_single_tokens(entries: Sequence[StepEntry], manager, vocab_size: int)
         if rid in seen:
             raise ValueError(f"request {rid!r} appears twice in one step")
         seen.add(rid)
-        tok = e.token_ids[0]
+        tok = e.token_ids[0] if e.token_src < 0 else 0
+        src[s] = e.token_src
         if not 0 <= tok < vocab_size:
             raise ValueError(f"token id {tok} of request {rid!r} is outside the vocabulary [0, {vocab_size})")
         for w in e.want:
@@ -207,7 +225,7 @@ def gather_single_tokens(entries: Sequence[StepEntry], manager, vocab_size: int)
         slots.append(pages * ps + offsets)
         tables.append(table[rows, :width])
     return dict(token_ids=tokens, positions=starts, kv_len=kv_len, state_slot=rows, logit_rows=np.asarray(logit_rows, dtype=np.int64),
-                slots=slots, tables=tables, S=S, width=width)
+                slots=slots, tables=tables, S=S, width=width, token_src=src if (src >= 0).any() else None)
 
 
 def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int, uploader: Uploader | None = None) -> tuple[StepBatch, list[int]]:
@@ -222,6 +240,8 @@ def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int, 
     pieces = [h["token_ids"], h["positions"], h["seq_of_token"], h["q_start"], h["kv_len"], h["state_slot"], h["logit_rows"]]
     for g in range(len(manager.pools)):
         pieces += [h["slots"][g], h["tables"][g].reshape(-1)]
+    if h["token_src"] is not None:
+        pieces.append(h["token_src"])
     flat = np.concatenate([np.asarray(p).reshape(-1) for p in pieces]).astype(np.int32)
     dev = (uploader or Uploader(device)).upload(flat)
     cut = 0
@@ -238,6 +258,7 @@ def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int, 
     for g in range(len(manager.pools)):
         gs = take(n)
         views.append(GroupView(take(S * width).view(S, width), gs))
+    b_src = take(n) if h["token_src"] is not None else None
     q_lens = h["q_lens"].tolist()
     kv = h["kv_len"].tolist()
     batch = StepBatch(
@@ -245,5 +266,7 @@ def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int, 
         seq_of_token=b_seq, q_start=b_qstart, kv_len=b_kvlen, state_slot=b_slot, logit_rows=b_rows, groups=views,
         q_lens=q_lens, starts=h["starts"].tolist(), state_slots=h["state_slot"].tolist(), max_q_len=max(q_lens), max_kv_len=max(kv),
         max_kv_len_single=max((k for k, q in zip(kv, q_lens) if q == 1), default=0),
+        logits_all_rows=h["logit_rows"].size == n and bool((h["logit_rows"] == np.arange(n)).all()),
+        token_src=b_src,
     )
     return batch, h["place"]

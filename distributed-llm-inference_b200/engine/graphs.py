@@ -34,7 +34,8 @@ class DecodeGraph:
         self.seqs, self.width, self.num_groups = seqs, width, num_groups
         dev = model.device
         per_group = seqs + seqs * width
-        self.size = 4 * seqs + num_groups * per_group
+        self.src_base = 4 * seqs + num_groups * per_group  # behind the groups: each row's place in the token source, or -1
+        self.size = self.src_base + seqs
         self.ints = torch.zeros(self.size, dtype=torch.int32, device=dev)
         pad = self.padding(scratch_pages, page_size)
         self.ints.copy_(torch.from_numpy(pad))
@@ -48,6 +49,7 @@ class DecodeGraph:
             seq_of_token=arange[:seqs], q_start=arange, kv_len=self.ints[2 * seqs : 3 * seqs], state_slot=self.ints[3 * seqs : 4 * seqs],
             logit_rows=arange[:seqs], groups=views, q_lens=[1] * seqs, starts=[0] * seqs, state_slots=[0] * seqs, max_q_len=1,
             max_kv_len=width * page_size, max_kv_len_single=width * page_size, forced_splits=splits,
+            logits_all_rows=True,
         )
         self._pad = pad
         # run eagerly first (kernels set their attributes, libraries pick their algorithms), then capture
@@ -75,6 +77,7 @@ class DecodeGraph:
             base = 4 * seqs + g * per_group
             flat[base : base + seqs] = page * page_size
             flat[base + seqs : base + per_group] = page
+        flat[self.src_base :] = -1
         return flat
 
     def fill(self, h: dict) -> np.ndarray:
@@ -91,9 +94,15 @@ class DecodeGraph:
             flat[base : base + S] = h["slots"][g]
             tables = flat[base + seqs : base + per_group].reshape(seqs, width)
             tables[:S, : h["width"]] = h["tables"][g]
+        if h.get("token_src") is not None:
+            flat[self.src_base : self.src_base + S] = h["token_src"]
         return flat
 
-    def replay(self) -> torch.Tensor:
+    def replay(self, token_source: torch.Tensor | None = None) -> torch.Tensor:
+        """Run the step whose integers are in ``ints``.  With ``token_source`` (ids sampled on the device
+        by the step before), rows that name a place in it take their token id from there first."""
+        if token_source is not None:
+            ops.patch_tokens(self.ints[0 : self.seqs], token_source, self.ints[self.src_base : self.size])
         self.graph.replay()
         ops.launch_count += self.kernels
         return self.logits

@@ -2,6 +2,15 @@
 
 Names and meanings follow src/dli/engine/engine.py:62-246 (for_model, add_request,
 step, generate, abort, has_unfinished, StepStats).  Token ids in, token ids out.
+
+One step ahead.  While every running request is decoding and nobody waits, the engine
+launches the next step before it reads the ids the current one sampled: the ids stay on the
+device, the next step takes them from there, and the host reads them one step late, while
+the device is already busy.  ``step()`` still returns the tokens of exactly one model step.
+A request that turns out to have ended (a stop token) has one surplus token computed, which
+is dropped; a request that ends by length is left out of the step ahead.  Whenever a request
+waits, a prompt is in portions, or a page is missing, the engine reads first and schedules
+then, as the reference does at every step.
 """
 
 from __future__ import annotations
@@ -13,6 +22,7 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Collection, Iterable, Protocol, Sequence
 
+from ..cache import UNKNOWN_TOKEN, OutOfPages
 from ..sampling import SamplingParams
 from .request import FinishReason, Request
 from .scheduler import ScheduledChunk, Scheduler, SchedulerConfig
@@ -61,9 +71,32 @@ class Runner(Protocol):
         manager.  Returns one logits row per chunk with ``needs_logits``, in the chunks' order."""
 
 
+class _Ready:
+    """Token ids that are already on the host (a sampler without ``sample_async``)."""
+
+    device_ids = None
+
+    def __init__(self, ids) -> None:
+        self._ids = list(ids)
+
+    def result(self) -> list[int]:
+        return self._ids
+
+
+@dataclass
+class _InFlight:
+    """A step that was launched and whose sampled ids have not been read."""
+
+    chunks: list[ScheduledChunk]
+    sampling: list[Request]  # who gets a token, in the order of the sampled rows
+    tokens: object  # PendingTokens or _Ready
+    num_preempted: int
+    launch_s: float
+
+
 class LLMEngine:
     def __init__(self, runner: Runner, config: SchedulerConfig | None = None, *, sampler=None,
-                 eos_token_ids: Collection[int] = (), seed: int = 0) -> None:
+                 eos_token_ids: Collection[int] = (), seed: int = 0, lookahead: bool = True) -> None:
         self.runner = runner
         self.manager = runner.manager
         self.scheduler = Scheduler(config or SchedulerConfig(), self.manager)
@@ -72,13 +105,18 @@ class LLMEngine:
         self._rng = random.Random(seed)
         self._arrivals = itertools.count()
         self.stats = _Counters()
+        # one step ahead needs a runner that takes token ids from the device and a sampler that leaves them there
+        self.lookahead = bool(lookahead and getattr(runner, "takes_token_source", False) and hasattr(sampler, "sample_async"))
+        self.steps_ahead = 0  # steps that were launched before the ids they run on were read
+        self._inflight: _InFlight | None = None
+        self._unknown: dict[str, int] = {}  # request -> position whose id the cache manager does not know yet
 
     # ------------------------------------------------------------ construction
 
     @classmethod
     def for_model(cls, model, *, num_blocks: int | None = None, kv_cache_gb: float | None = None, block_size: int = 16,
                   config: SchedulerConfig | None = None, enable_prefix_caching: bool = True, watermark: float = 0.01,
-                  eos_token_ids: Collection[int] = (), seed: int = 0) -> "LLMEngine":
+                  eos_token_ids: Collection[int] = (), seed: int = 0, lookahead: bool = True) -> "LLMEngine":
         """An engine around a loaded model.  The cache pool has ``num_blocks`` pages of
         ``block_size`` tokens, or as many as ``kv_cache_gb`` GiB hold (default 1 GiB)."""
         from ..sampling import Sampler
@@ -91,7 +129,7 @@ class LLMEngine:
             num_blocks = ModelRunner.pages_for_budget(model, (kv_cache_gb or 1.0) * 2**30, block_size)
         runner = ModelRunner(model, num_pages=num_blocks, page_size=block_size, max_requests=config.max_num_seqs,
                              enable_prefix_caching=enable_prefix_caching, watermark=watermark)
-        return cls(runner, config, sampler=Sampler(model.device), eos_token_ids=eos_token_ids, seed=seed)
+        return cls(runner, config, sampler=Sampler(model.device), eos_token_ids=eos_token_ids, seed=seed, lookahead=lookahead)
 
     @classmethod
     def from_model_dir(cls, model_dir: str | Path, *, dtype: str = "auto", device: str = "cuda:0", **kwargs) -> "LLMEngine":
@@ -118,31 +156,29 @@ class LLMEngine:
         return self.scheduler.has_unfinished
 
     def step(self) -> list[RequestOutput]:
+        """Advance by one model step; the tokens it produced, one RequestOutput per request."""
         t0 = time.perf_counter()
-        sched = self.scheduler.schedule()
+        flight, self._inflight = self._inflight, None
+        if flight is None:
+            flight = self._launch_scheduled()
         t1 = time.perf_counter()
-        outputs: list[RequestOutput] = []
-        if sched.chunks:
-            for req in sched.admitted:
-                self.runner.start_request(req.request_id, self.manager.state_slot(req.request_id))
-            logits = self.runner.execute(sched.chunks)
-            t2 = time.perf_counter()
-            for ch in sched.chunks:
-                ch.request.num_computed_tokens += ch.num_tokens
-                assert self.manager.num_computed_tokens(ch.request.request_id) == ch.request.num_computed_tokens
-            sampling = [c.request for c in sched.chunks if c.needs_logits]
-            tokens = self.sampler.sample(logits, [r.params for r in sampling], [r.seed for r in sampling],
-                                         [len(r.output_ids) for r in sampling])
-            for req, tok in zip(sampling, tokens):
-                outputs.append(self._append_token(req, int(tok)))
-        else:
-            t2 = t1
+        if flight is None:
+            self.stats.steps.append(StepStats(0, 0, 0, 0, 0, t1 - t0, 0.0, 0.0))
+            return []
+        ahead = self._launch_ahead(flight) if self.lookahead else None
+        t2 = time.perf_counter()
+        tokens = flight.tokens.result()
         t3 = time.perf_counter()
-        prefill = sum(c.num_tokens for c in sched.chunks if c.num_tokens > 1 or not c.needs_logits)
+        outputs = self._resolve(flight, tokens)
+        if ahead is not None and self.scheduler.running:
+            self._inflight = ahead  # (if nobody is left, its surplus tokens are simply never read)
+        t4 = time.perf_counter()
+        batched = sum(c.num_tokens for c in flight.chunks)
+        prefill = sum(c.num_tokens for c in flight.chunks if c.num_tokens > 1 or not c.needs_logits)
         self.stats.steps.append(StepStats(
-            num_seqs=len(sched.chunks), num_batched_tokens=sched.num_batched_tokens, num_prefill_tokens=prefill,
-            num_decode_tokens=sched.num_batched_tokens - prefill, num_preempted=len(sched.preempted),
-            schedule_s=t1 - t0, forward_s=t2 - t1, postprocess_s=t3 - t2,
+            num_seqs=len(flight.chunks), num_batched_tokens=batched, num_prefill_tokens=prefill,
+            num_decode_tokens=batched - prefill, num_preempted=flight.num_preempted,
+            schedule_s=(t1 - t0) + (t2 - t1 if ahead is not None else 0.0), forward_s=flight.launch_s + (t3 - t2), postprocess_s=t4 - t3,
         ))
         return outputs
 
@@ -157,6 +193,70 @@ class LLMEngine:
         return [r.output_ids for r in reqs]
 
     # ------------------------------------------------------------ internals
+
+    def _sample(self, logits, reqs: list[Request], ahead: int):
+        """Ids for ``reqs`` (row order); ``ahead``: tokens of each request that are sampled but not read."""
+        args = ([r.params for r in reqs], [r.seed for r in reqs], [len(r.output_ids) + ahead for r in reqs])
+        if hasattr(self.sampler, "sample_async"):
+            return self.sampler.sample_async(logits, *args)
+        return _Ready(self.sampler.sample(logits, *args))
+
+    def _run(self, chunks: list[ScheduledChunk], num_preempted: int, token_source=None, token_rows=None, ahead: int = 0) -> _InFlight:
+        t0 = time.perf_counter()
+        if token_source is None:
+            logits = self.runner.execute(chunks)
+        else:
+            logits = self.runner.execute(chunks, token_source, token_rows)
+        for ch in chunks:
+            ch.request.num_computed_tokens += ch.num_tokens
+            assert self.manager.num_computed_tokens(ch.request.request_id) == ch.request.num_computed_tokens
+        sampling = [c.request for c in chunks if c.needs_logits]
+        tokens = self._sample(logits, sampling, ahead) if sampling else _Ready([])
+        return _InFlight(chunks, sampling, tokens, num_preempted, time.perf_counter() - t0)
+
+    def _launch_scheduled(self) -> _InFlight | None:
+        """Ask the scheduler (every id is known to the host) and launch what it chose."""
+        sched = self.scheduler.schedule()
+        if not sched.chunks:
+            return None
+        for req in sched.admitted:
+            self.runner.start_request(req.request_id, self.manager.state_slot(req.request_id))
+        return self._run(sched.chunks, len(sched.preempted))
+
+    def _launch_ahead(self, flight: _InFlight) -> _InFlight | None:
+        """The decode step that follows ``flight``, launched on the ids it leaves on the device;
+        None whenever the scheduler has something to decide first."""
+        sch = self.scheduler
+        if sch.waiting or not flight.sampling or len(flight.sampling) != len(sch.running):
+            return None  # an admission is due, a prompt is still in portions, or someone was aborted
+        if flight.tokens.device_ids is None:
+            return None
+        chosen = [(i, r) for i, r in enumerate(flight.sampling)
+                  if not r.is_finished and len(r.output_ids) + 1 < r.params.max_tokens]  # the others end with the token in flight
+        if not chosen or len(chosen) > sch.config.max_num_batched_tokens:
+            return None
+        try:
+            for _, r in chosen:
+                position = r.num_tokens  # of the token in flight
+                if self.manager.num_tokens(r.request_id) <= position:
+                    self.manager.append_slots(r.request_id, [UNKNOWN_TOKEN])
+                    self._unknown[r.request_id] = position
+        except OutOfPages:
+            return None  # the scheduler will decide who yields; slots taken so far are kept and named when the ids arrive
+        chunks = [ScheduledChunk(r, r.num_computed_tokens, 1, True) for _, r in chosen]
+        self.steps_ahead += 1
+        return self._run(chunks, 0, flight.tokens, [i for i, _ in chosen], ahead=1)
+
+    def _resolve(self, flight: _InFlight, tokens: list[int]) -> list[RequestOutput]:
+        outputs = []
+        for req, tok in zip(flight.sampling, tokens):
+            position = self._unknown.pop(req.request_id, None)
+            if req.is_finished:
+                continue  # ended a step earlier (a stop token, an abort): this token is surplus
+            if position is not None and self.manager.has_request(req.request_id):
+                self.manager.set_token(req.request_id, position, int(tok))
+            outputs.append(self._append_token(req, int(tok)))
+        return outputs
 
     def _append_token(self, req: Request, tok: int) -> RequestOutput:
         req.output_ids.append(tok)

@@ -17,6 +17,7 @@ import torch
 from ..cache import CacheManager, CachePools, GroupSpec
 from ..cache.needs import PagedKVNeed, StateNeed
 from ..config.registry import load_config, resolve_architecture
+from ..kernels import ops
 from ..parts import DecoderModel
 from ..weights import load_tensors, random_tensors
 from .batch import StepEntry, Uploader, build_batch, gather_single_tokens
@@ -103,42 +104,54 @@ class ModelRunner:
             self.pools.reset_state(slot)
 
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], borrow: bool = False, token_source: torch.Tensor | None = None) -> torch.Tensor:
         """Logits [wanted, vocab] float32 on the device, in the order of ``entries`` and of
         each entry's ``want``.  Afterwards every entry's tokens count as computed.
-        With ``borrow`` the result may be a view of a buffer the next step overwrites."""
+        With ``borrow`` the result may be a view of a buffer the next step overwrites.
+        ``token_source``: int32 ids on the device (what the step before sampled); entries with
+        ``token_src >= 0`` take their token from that row of it, so a step can be launched before
+        the host has read the ids it runs on."""
+        if token_source is None and any(e.token_src >= 0 for e in entries):
+            raise ValueError("entries name rows of a token source, but none was given")
         logits = None
         if self.graphs is not None and all(len(e.token_ids) == 1 for e in entries):
-            logits = self._replay_decode(entries)
+            logits = self._replay_decode(entries, token_source)
             if logits is not None and not borrow:
                 logits = logits.clone()
         if logits is None:
             batch, _ = build_batch(entries, self.manager, self.model.device, self.model.spec.vocab_size, self.uploader)
+            if batch.token_src is not None:
+                ops.patch_tokens(batch.token_ids, token_source, batch.token_src)
             logits = self.model.forward(batch, self.pools.layer_caches)
         manager = self.manager
         for e in entries:
             manager.mark_computed(e.request_id, manager.progress(e.request_id)[0] + len(e.token_ids))
         return logits
 
-    def _replay_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+    def _replay_decode(self, entries: Sequence[StepEntry], token_source: torch.Tensor | None = None) -> torch.Tensor | None:
         """A step of single tokens through a captured graph; None if no graph takes its shape."""
         h = gather_single_tokens(entries, self.manager, self.model.spec.vocab_size)
         graph = self.graphs.lookup(h["S"], h["width"], int(h["kv_len"].max()))
         if graph is None:
             return None
         self.uploader.upload(graph.fill(h), out=graph.ints)
-        logits = graph.replay()
+        logits = graph.replay(token_source if h["token_src"] is not None else None)
         self.graph_steps += 1
         rows = h["logit_rows"]
         if rows.size == h["S"] and (rows == np.arange(h["S"])).all():
             return logits[: h["S"]]
         return logits[torch.from_numpy(rows).to(logits.device)]
 
-    def execute(self, chunks) -> torch.Tensor:
+    takes_token_source = True  # execute() accepts chunks whose token is still on the device
+
+    def execute(self, chunks, token_source=None, token_rows: Sequence[int] | None = None) -> torch.Tensor:
         """The engine's view of ``step``: one entry per scheduled chunk, logits at the last
-        token of the chunks that sample (src/dli/engine/runner.py:53-80)."""
+        token of the chunks that sample (src/dli/engine/runner.py:53-80).  ``token_rows[i] >= 0``:
+        chunk i is one token that the host has not read yet, row token_rows[i] of ``token_source``
+        (sampling.PendingTokens)."""
         entries = []
-        for ch in chunks:
-            tokens = ch.request.token_slice(ch.start, ch.start + ch.num_tokens)
-            entries.append(StepEntry(ch.request.request_id, tokens, [ch.num_tokens - 1] if ch.needs_logits else []))
-        return self.step(entries, borrow=True)
+        for i, ch in enumerate(chunks):
+            src = token_rows[i] if token_rows is not None else -1
+            tokens = [0] if src >= 0 else ch.request.token_slice(ch.start, ch.start + ch.num_tokens)
+            entries.append(StepEntry(ch.request.request_id, tokens, [ch.num_tokens - 1] if ch.needs_logits else [], src))
+        return self.step(entries, borrow=True, token_source=None if token_source is None else token_source.device_ids)

@@ -41,14 +41,27 @@ def fused_epilogue(x: torch.Tensor) -> bool:
     return decode_product(x) and x.shape[0] <= FUSED_EPILOGUE_MAX_TOKENS
 
 
-def project(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None, max_tokens: int = SKINNY_MAX_TOKENS) -> torch.Tensor:
-    """y = x W^T for a step's tokens, in x's dtype or in ``out_dtype`` (float32 for logits)."""
+def project(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, max_tokens: int = SKINNY_MAX_TOKENS) -> torch.Tensor:
+    """y = x W^T for a step's tokens, in x's dtype or in ``out_dtype`` (float32 for logits).  x may be
+    ops.ScaledRows (rows that still lack their norm's factor): those only exist for token counts that
+    the decode kernel serves, which applies the factor."""
     from . import ops
 
-    if decode_product(x, max_tokens):
+    if isinstance(x, ops.ScaledRows) or decode_product(x, max_tokens):
         return ops.skinny_gemm(x, weight, out_dtype or x.dtype)
     y = linear(x, weight)
     return y if out_dtype in (None, y.dtype) else y.to(out_dtype)
+
+
+def last_product(x: torch.Tensor, weight: torch.Tensor, defer: bool):
+    """The product that ends a mixer or feed-forward: x W^T, or — if the part's owner allowed it and
+    the decode kernel with its fused epilogues will serve these tokens — the product left
+    uncomputed for the norm behind it (parts.base.PendingProduct)."""
+    if defer and fused_epilogue(x):
+        from ..parts.base import PendingProduct
+
+        return PendingProduct(x, weight)
+    return project(x, weight)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

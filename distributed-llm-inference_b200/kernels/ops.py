@@ -95,6 +95,16 @@ def embedding(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
     _check(f(_ptr(h), _ptr(table), _ptr(ids), n, H, DT_CODE[table.dtype], _stream()), "embedding")
 
 
+def patch_tokens(ids: torch.Tensor, source: torch.Tensor, src: torch.Tensor) -> None:
+    """ids[i] = source[src[i]] wherever src[i] >= 0: the token ids of a step that were sampled on
+    the device by the step before and have not been read by the host."""
+    _need(ids, "ids", torch.int32), _need(source, "source", torch.int32), _need(src, "src", torch.int32)
+    if src.numel() != ids.numel():
+        raise KernelError("patch_tokens: one source row per token")
+    f = _fn("elementwise.cu", "dli_patch_tokens", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(ids), _ptr(source), _ptr(src), ids.numel(), _stream()), "patch_tokens")
+
+
 def add_rmsnorm(
     y: torch.Tensor,
     h: torch.Tensor,
@@ -453,6 +463,43 @@ def skinny_gemm_supported(tokens: int, in_features: int) -> bool:
     return 1 <= tokens <= 256 and in_features >= 8 and in_features % 8 == 0
 
 
+class ScaledRows:
+    """Activations whose rows still lack a factor: ``x`` [n, size] holds bfloat16(h * gain) of a
+    residual stream h, ``ssq`` [n, tiles] float32 the sums of h^2 over tiles of 128 features, and
+    the finished RMS norm is x[t] * rsqrt(sum(ssq[t]) / size + eps).  A factor per row commutes
+    with a matrix product, so the decode products take this as their input and apply the factor
+    to their float32 sums (``skinny_gemm*``); ``skinny_gemm_residual`` makes it."""
+
+    __slots__ = ("x", "ssq", "eps")
+
+    def __init__(self, x: torch.Tensor, ssq: torch.Tensor, eps: float) -> None:
+        self.x, self.ssq, self.eps = x, ssq, float(eps)
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    @property
+    def device(self):
+        return self.x.device
+
+
+def _row_scale(x, name: str):
+    """(activations, the four row-scaling arguments of the kernel) for a tensor or ScaledRows."""
+    if not isinstance(x, ScaledRows):
+        return x, (None, 0, 0.0, 0)
+    _need(x.ssq, name + ".ssq", torch.float32)
+    n, size = x.x.shape
+    if x.ssq.dim() != 2 or x.ssq.shape[0] != n or n > 64:
+        raise KernelError(f"{name}: row sums of squares must be [tokens <= 64, tiles]")
+    return x.x, (_ptr(x.ssq), x.ssq.shape[1], x.eps, size)
+
+
+_ROW_SCALE_ARGS = [c_void_p, c_int, c_float, c_int]
 _slices_cache: dict[tuple[int, int, int], int] = {}
 
 
@@ -470,6 +517,7 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
     """x [tokens <= 256, K] times weight [features, K] transposed, bfloat16 in, on tcgen05 tensor
     cores fed by TMA; returns [tokens, features] in bfloat16 or float32.  ``slices`` (1..8) cuts K
     across the CTAs of a cluster, which add their partial sums through distributed shared memory."""
+    x, scale = _row_scale(x, "skinny_gemm")
     _need(x, "x", torch.bfloat16), _need(weight, "weight", torch.bfloat16)
     tokens, K = x.shape
     features = weight.shape[0]
@@ -485,23 +533,46 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
         _need(out, "out", out_dtype)
         if tuple(out.shape) != (tokens, features):
             raise KernelError("skinny_gemm: out has the wrong shape")
-    f = _fn("skinny_gemm.cu", "dli_skinny_gemm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(out), int(out_dtype == torch.float32), _ptr(x), _ptr(weight), tokens, features, K, slices, max_stages, _stream()), "skinny_gemm")
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int] + _ROW_SCALE_ARGS + [c_void_p])
+    _check(f(_ptr(out), int(out_dtype == torch.float32), _ptr(x), _ptr(weight), tokens, features, K, slices, max_stages, *scale, _stream()), "skinny_gemm")
     return out
+
+
+def skinny_gemm_residual(x, weight: torch.Tensor, h: torch.Tensor, gain: torch.Tensor, eps: float, slices: int | None = None) -> ScaledRows:
+    """h += x W^T (float32, in place) and the first half of the RMS norm that follows, in the
+    product's epilogue: returns ScaledRows(bfloat16(h * gain), sums of h^2 per 128 features, eps).
+    x [tokens <= 64, K] may itself be ScaledRows."""
+    x, scale = _row_scale(x, "skinny_gemm_residual")
+    _need(x, "x", torch.bfloat16), _need(weight, "weight", torch.bfloat16), _need(h, "h", torch.float32), _need(gain, "gain", torch.float32)
+    tokens, K = x.shape
+    features = weight.shape[0]
+    if weight.shape[1] != K or not skinny_gemm_supported(tokens, K) or tokens > 64:
+        raise KernelError(f"skinny_gemm_residual: tokens {tokens} (1..64) or K {K} (a multiple of 8) not supported")
+    if tuple(h.shape) != (tokens, features) or gain.numel() != features:
+        raise KernelError("skinny_gemm_residual: h must be [tokens, features] and gain [features]")
+    if slices is None:
+        slices = skinny_gemm_slices(tokens, features, K)
+    out = torch.empty((tokens, features), dtype=torch.bfloat16, device=x.device)
+    ssq = torch.empty((tokens, (features + 127) // 128), dtype=torch.float32, device=x.device)
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_residual",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int] + _ROW_SCALE_ARGS + [c_void_p])
+    _check(f(_ptr(out), _ptr(h), _ptr(gain), _ptr(ssq), _ptr(x), _ptr(weight), tokens, features, K, slices, *scale, _stream()), "skinny_gemm_residual")
+    return ScaledRows(out, ssq, eps)
 
 
 def skinny_gemm_swiglu(x: torch.Tensor, weight_tiled: torch.Tensor) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) in one kernel: the decode matrix product with the activation in its
     epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate rows, then the 64 up rows of
     the same features.  Returns bfloat16 [tokens, I]."""
+    x, scale = _row_scale(x, "skinny_gemm_swiglu")
     _need(x, "x", torch.bfloat16), _need(weight_tiled, "weight", torch.bfloat16)
     tokens, K = x.shape
     features = weight_tiled.shape[0]
     if weight_tiled.shape[1] != K or features % 128 or not skinny_gemm_supported(tokens, K):
         raise KernelError("skinny_gemm_swiglu: sizes not supported")
     out = torch.empty((tokens, features // 2), dtype=torch.bfloat16, device=x.device)
-    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(out), _ptr(x), _ptr(weight_tiled), tokens, features, K, skinny_gemm_slices(tokens, features, K), _stream()), "skinny_gemm_swiglu")
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int] + _ROW_SCALE_ARGS + [c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(weight_tiled), tokens, features, K, skinny_gemm_slices(tokens, features, K), *scale, _stream()), "skinny_gemm_swiglu")
     return out
 
 
@@ -513,6 +584,7 @@ def skinny_gemm_rotary(x, wqkv, positions, inv_freq, slots, k_pool, v_pool, num_
                        rotary_dim: int, page_size: int, write_kv: bool) -> torch.Tensor:
     """q | k | v = x Wqkv^T with the rotary embedding and the write of keys and values into the
     cache pages done in the product's epilogue; returns the rotated queries [tokens, nh * d]."""
+    x, scale = _row_scale(x, "skinny_gemm_rotary")
     _need(x, "x", torch.bfloat16), _need(wqkv, "wqkv", torch.bfloat16), _need(positions, "positions", torch.int32)
     tokens, K = x.shape
     features = (num_heads + 2 * num_kv_heads) * head_dim
@@ -528,10 +600,11 @@ def skinny_gemm_rotary(x, wqkv, positions, inv_freq, slots, k_pool, v_pool, num_
             raise KernelError("skinny_gemm_rotary: pool layout must be [pages, kv_heads, page_size, head_dim]")
     q = torch.empty((tokens, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
     f = _fn("skinny_gemm.cu", "dli_skinny_gemm_rotary",
-            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6
+            + _ROW_SCALE_ARGS + [c_void_p])
     _check(f(_ptr(q), _ptr(x), _ptr(wqkv), tokens, K, skinny_gemm_slices(tokens, features, K), _ptr(positions),
              _ptr(inv_freq if rotary_dim else None), _ptr(slots if write_kv else None), _ptr(k_pool if write_kv else None),
-             _ptr(v_pool if write_kv else None), num_heads, num_kv_heads, head_dim, rotary_dim, page_size, int(write_kv), _stream()),
+             _ptr(v_pool if write_kv else None), num_heads, num_kv_heads, head_dim, rotary_dim, page_size, int(write_kv), *scale, _stream()),
            "skinny_gemm_rotary")
     return q
 

@@ -6,7 +6,7 @@ import torch
 
 from ..cache.needs import PagedKVNeed
 from ..kernels import attention as attn_kernels
-from ..kernels.gemm import project
+from ..kernels.gemm import last_product, project
 from ..weights.loader import TensorDecl
 from .base import Part, build_part, register_part
 
@@ -23,6 +23,8 @@ class GQAttention(Part):
     """
 
     graph_capturable = True
+    takes_scaled_rows = True  # the input only goes to the q | k | v product
+    defer_output = False
 
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
@@ -65,4 +67,4 @@ class GQAttention(Part):
             q = self.position.rotate_and_store(project(x, self.wqkv), batch, cache, self.nh, self.nkv, cache.writes)
         out = torch.empty((x.shape[0], self.nh * self.d), dtype=x.dtype, device=x.device)
         attn_kernels.paged_attention(out, q, cache, batch, self.nh, self.scale, self.window)
-        return project(out, self.wo)
+        return last_product(out, self.wo, self.defer_output)

@@ -24,6 +24,19 @@ Interfaces by category (what a new part of that category must provide):
                   and feed-forward around the residual ``stream`` (h plus a pending delta).
 ``embedding``     ``forward(token_ids) -> h`` float32 [n, H].
 ``head``          ``forward(y) -> logits`` float32 [k, V].
+
+Optional, for the fusion of a part's last matrix product with the residual addition and the
+norm behind it (a decode step's few tokens; see ``normed_input``).  A part that has none of
+these is served with plain tensors:
+
+* a mixer or feed-forward with an attribute ``defer_output`` (default False) may, when its owner
+  set it, return a ``PendingProduct`` (the delta x W^T, not yet computed) instead of a tensor;
+* a norm with ``add_product_norm(h, product) -> ScaledRows | None`` computes that product, adds it
+  to h and leaves the division by the row's RMS to the reader of its output (None: it declines);
+* a mixer, feed-forward or head with ``takes_scaled_rows`` true accepts such rows as its input
+  (it hands them to ``kernels.gemm.project`` or a decode product of ``kernels.ops``);
+* an arrangement with ``first_consumer() -> (norm, part)`` and ``defer_last_product(flag)`` lets
+  the model extend this across layer borders.
 """
 
 from __future__ import annotations
@@ -67,13 +80,60 @@ class Part:
         return []
 
 
-@dataclass
+class PendingProduct:
+    """The delta x W^T of a residual stream, not yet computed: the norm that adds it may compute it
+    in the same kernel.  ``materialize()`` computes it the plain way."""
+
+    __slots__ = ("x", "weight")
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor) -> None:
+        self.x, self.weight = x, weight
+
+    def materialize(self) -> torch.Tensor:
+        from ..kernels.gemm import project
+
+        return project(self.x, self.weight)
+
+
 class ResidualStream:
     """The float32 residual h [n, H] and a delta (activation dtype) not yet added to it.
-    Keeping the delta pending lets the next norm do the addition in the same kernel."""
+    Keeping the delta pending lets the next norm do the addition in the same kernel.  ``pending``
+    reads as a tensor (or None); ``take_pending()`` hands out a PendingProduct as it is."""
 
-    h: torch.Tensor
-    pending: torch.Tensor | None = None
+    def __init__(self, h: torch.Tensor, pending=None) -> None:
+        self.h = h
+        self._pending = pending
+
+    @property
+    def pending(self):
+        if isinstance(self._pending, PendingProduct):
+            self._pending = self._pending.materialize()
+        return self._pending
+
+    @pending.setter
+    def pending(self, value) -> None:
+        self._pending = value
+
+    def take_pending(self):
+        return self._pending
+
+
+def can_fuse(norm, consumer) -> bool:
+    """Whether ``norm`` can compute a PendingProduct itself and ``consumer`` reads what it then returns."""
+    return hasattr(norm, "add_product_norm") and bool(getattr(consumer, "takes_scaled_rows", False))
+
+
+def normed_input(norm, h: torch.Tensor, delta, consumer, rows: torch.Tensor | None = None):
+    """norm(h + delta) as ``consumer`` will read it.  A delta that is still a PendingProduct goes,
+    product and all, to a norm that can compute it (if the consumer reads ScaledRows and every row
+    is wanted); otherwise it is computed first and the norm gets a tensor."""
+    if isinstance(delta, PendingProduct):
+        if rows is None and can_fuse(norm, consumer):
+            y = norm.add_product_norm(h, delta)
+            if y is not None:  # None: the norm declines (sizes its kernel does not take)
+                return y
+        delta = delta.materialize()
+    return norm.add_norm(h, delta) if rows is None else norm.add_norm(h, delta, rows=rows)
 
 
 _REGISTRY: dict[tuple[str, str], Callable[..., Any]] = {}

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from .base import BuildEnv, Part, ResidualStream, build_part, register_part
+from .base import BuildEnv, Part, ResidualStream, build_part, can_fuse, normed_input, register_part
 
 
 @register_part("arrangement", "prenorm")
@@ -20,11 +20,23 @@ class PreNormBlock(Part):
         self.ffn_norm = build_part("norm", spec.parts["ffn_norm"], env)
         self.ffn = build_part("feed_forward", spec.parts["ffn"], env)
 
+        if hasattr(self.mixer, "defer_output"):
+            self.mixer.defer_output = can_fuse(self.ffn_norm, self.ffn)
+
     def children(self):
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
 
+    def first_consumer(self):
+        """The norm that takes the stream's pending delta, and the part that reads its output."""
+        return self.mixer_norm, self.mixer
+
+    def defer_last_product(self, flag: bool) -> None:
+        """Whether whoever runs after this layer can take the feed-forward's last product uncomputed."""
+        if hasattr(self.ffn, "defer_output"):
+            self.ffn.defer_output = bool(flag)
+
     def forward(self, stream: ResidualStream, batch, cache) -> None:
-        y = self.mixer_norm.add_norm(stream.h, stream.pending)
+        y = normed_input(self.mixer_norm, stream.h, stream.take_pending(), self.mixer)
         a = self.mixer.forward(y, batch, cache)
-        y = self.ffn_norm.add_norm(stream.h, a)
+        y = normed_input(self.ffn_norm, stream.h, a, self.ffn)
         stream.pending = self.ffn.forward(y)

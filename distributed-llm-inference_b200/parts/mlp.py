@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from ..kernels.gemm import fused_epilogue, project
+from ..kernels.gemm import fused_epilogue, last_product, project
 from ..weights.loader import TensorDecl
 from .base import Part, register_part
 
@@ -19,6 +19,8 @@ class SwiGLU(Part):
     params: hidden_size, intermediate_size."""
 
     graph_capturable = True
+    takes_scaled_rows = True  # the input only goes to the gate | up product
+    defer_output = False
 
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
@@ -54,4 +56,4 @@ class SwiGLU(Part):
             gate_up = project(x, self.w_gate_up)
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
             ops.silu_mul(act, gate_up, self.tiled)
-        return project(act, self.w_down)
+        return last_product(act, self.w_down, self.defer_output)

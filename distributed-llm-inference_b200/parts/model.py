@@ -8,7 +8,7 @@ from ..config.spec import ModelSpec
 from ..kernels import ops
 from ..kernels.gemm import SKINNY_MAX_TOKENS_HEAD, linear, project
 from ..weights.loader import TensorDecl
-from .base import BuildEnv, Part, ResidualStream, build_part, register_part
+from .base import BuildEnv, Part, ResidualStream, build_part, can_fuse, normed_input, register_part
 
 
 @register_part("embedding", "token_embedding")
@@ -42,6 +42,7 @@ class LMHead(Part):
     params: vocab_size, hidden_size, tied_to."""
 
     graph_capturable = True
+    takes_scaled_rows = True
 
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
@@ -78,6 +79,24 @@ class DecoderModel:
         self.layers = [build_part("arrangement", layer, self.env) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, self.env)
         self.head = build_part("head", spec.head, self.env)
+        self._wire_deferred_products()
+
+    def _wire_deferred_products(self) -> None:
+        """A layer may leave its last product to the norm of whatever runs after it, if every
+        successor it has in the run order (or the final norm and the head) can take it."""
+        order = [step.layer for step in self.spec.run_order]
+        ok: dict[int, bool] = {}
+        for i, layer in enumerate(order):
+            if i + 1 < len(order):
+                first = getattr(self.layers[order[i + 1]], "first_consumer", None)
+                able = first is not None and can_fuse(*first())
+            else:
+                able = can_fuse(self.final_norm, self.head)
+            ok[layer] = ok.get(layer, True) and able
+        for layer, able in ok.items():
+            defer = getattr(self.layers[layer], "defer_last_product", None)
+            if defer is not None:
+                defer(able)
 
     @property
     def dtype(self) -> torch.dtype:
@@ -122,7 +141,8 @@ class DecoderModel:
             self.layers[step.layer].forward(stream, batch, caches[i])
         if batch.logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
-        y = self.final_norm.add_norm(stream.h, stream.pending, rows=batch.logit_rows)
+        rows = None if getattr(batch, "logits_all_rows", False) else batch.logit_rows
+        y = normed_input(self.final_norm, stream.h, stream.take_pending(), self.head, rows=rows)
         return self.head.forward(y)
 
 

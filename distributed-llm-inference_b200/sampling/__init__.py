@@ -1,4 +1,4 @@
 from .params import SamplingParams
-from .sampler import Sampler
+from .sampler import PendingTokens, Sampler
 
-__all__ = ["Sampler", "SamplingParams"]
+__all__ = ["PendingTokens", "Sampler", "SamplingParams"]

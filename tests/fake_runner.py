@@ -33,18 +33,28 @@ class FakeRunner:
     def start_request(self, request_id, slot):
         self.started.append(request_id)
 
-    def execute(self, chunks):
+    def execute(self, chunks, token_source=None, token_rows=None):
         rows = []
         self.steps.append([(c.request.request_id, c.start, c.num_tokens, c.needs_logits) for c in chunks])
-        for c in chunks:
+        for i, c in enumerate(chunks):
             rid = c.request.request_id
             assert self.manager.num_computed_tokens(rid) == c.start, "a chunk does not start where the cache ends"
             assert self.manager.num_tokens(rid) >= c.start + c.num_tokens, "tokens without reserved slots"
             self.manager.mark_computed(rid, c.start + c.num_tokens)
+            history = c.request.all_token_ids[: c.start + c.num_tokens]
+            if token_rows is not None and token_rows[i] >= 0:  # the token the host has not read: the step before left it
+                assert c.num_tokens == 1 and c.start == len(history), "a token from the device is the one after the known ones"
+                history = history + [token_source.device_ids[token_rows[i]]]
             if c.needs_logits:
-                rows.append(next_token(c.request.all_token_ids[: c.start + c.num_tokens]))
+                rows.append(next_token(history))
         self.manager.check_invariants()
         return rows
+
+
+class AheadRunner(FakeRunner):
+    """Takes a step's tokens from what the step before sampled, as the real runner does on the device."""
+
+    takes_token_source = True
 
 
 class FakeSampler:
@@ -52,6 +62,21 @@ class FakeSampler:
         return list(logits)
 
 
-def fake_engine(num_pages=64, page_size=4, max_num_seqs=8, budget=32, **kw):
-    runner = FakeRunner(num_pages, page_size, max_requests=max_num_seqs, **kw)
-    return LLMEngine(runner, SchedulerConfig(max_num_seqs, budget), sampler=FakeSampler()), runner
+class FakeTokens:
+    def __init__(self, ids):
+        self.device_ids = list(ids)
+        self.reads = 0
+
+    def result(self):
+        self.reads += 1
+        return self.device_ids
+
+
+class AheadSampler(FakeSampler):
+    def sample_async(self, logits, params, seeds, draws):
+        return FakeTokens(logits)
+
+
+def fake_engine(num_pages=64, page_size=4, max_num_seqs=8, budget=32, ahead=False, **kw):
+    runner = (AheadRunner if ahead else FakeRunner)(num_pages, page_size, max_requests=max_num_seqs, **kw)
+    return LLMEngine(runner, SchedulerConfig(max_num_seqs, budget), sampler=AheadSampler() if ahead else FakeSampler()), runner

@@ -208,3 +208,27 @@ def test_random_orders_keep_every_invariant(seed, prefix_caching, window):
     m.check_invariants()
     for pool in m.pools:
         assert pool.available == pool.num_pages
+
+
+def test_unknown_token_is_not_indexed_until_named():
+    """A token appended before its id is known keeps its page out of the prefix index; once named,
+    the page is found by a request with the same tokens."""
+    from dli_b200.cache import UNKNOWN_TOKEN
+
+    m = CacheManager([GroupSpec(16)], 4, 4, enable_prefix_caching=True, watermark=0.0)
+    m.allocate("a", [1, 2, 3])
+    m.mark_computed("a", 3)
+    m.append_slots("a", [UNKNOWN_TOKEN])
+    m.mark_computed("a", 4)  # the page is full and written, but one id is unknown
+    m.check_invariants()
+    m.allocate("b", [1, 2, 3, 9, 5])
+    assert m.num_computed_tokens("b") == 0
+    m.free("b")
+    with pytest.raises(ValueError):
+        m.set_token("a", 2, 7)  # position 2 is known
+    m.set_token("a", 3, 9)
+    m.check_invariants()
+    m.allocate("c", [1, 2, 3, 9, 5])
+    assert m.num_computed_tokens("c") == 4
+    m.free("a"), m.free("c")
+    m.check_invariants()

@@ -78,6 +78,12 @@ def test_greedy_generation_equals_plain(models, name, dtype, setting):
         assert_same_tokens(got, want, gaps, TOL[dtype], f"{name} {dtype} {setting} prompt of {len(p)}")
     eng.manager.check_invariants()
     assert eng.manager.min_available_pages() == kwargs["num_blocks"]
+    # most decode steps were launched before the ids of the step before had been read; an engine
+    # that reads first produces the same tokens
+    assert eng.lookahead and eng.steps_ahead >= steps // 2
+    if setting == "roomy":
+        plain_eng = LLMEngine.from_model_dir(path, dtype=dtype, block_size=page, lookahead=False, **kwargs)
+        assert plain_eng.generate(prompts, SamplingParams(max_tokens=steps)) == outs and plain_eng.steps_ahead == 0
 
 
 def test_shared_prefix_is_reused_and_changes_nothing(models):
@@ -105,6 +111,7 @@ def test_seeded_sampling_alone_busy_and_across_preemption(models):
         alone.append(eng.generate([p], sp)[0])
     busy = LLMEngine.from_model_dir(path, dtype="float32", block_size=16, num_blocks=64).generate(prompts, params)
     assert busy == alone
+    assert LLMEngine.from_model_dir(path, dtype="float32", block_size=16, num_blocks=64, lookahead=False).generate(prompts, params) == alone
     tight = LLMEngine.from_model_dir(path, dtype="float32", block_size=16, num_blocks=8, watermark=0.0)
     assert tight.generate(prompts, params) == alone
     assert sum(s.num_preempted for s in tight.stats.steps) > 0

@@ -451,3 +451,49 @@ def test_skinny_gemm_with_rotary_epilogue(nh, nkv, d, rot, page):
     np.testing.assert_allclose(kp1.float().cpu().numpy(), kp2.float().cpu().numpy(), atol=t2)
     np.testing.assert_allclose(vp1.float().cpu().numpy(), vp2.float().cpu().numpy(), atol=t2)
     assert ops.skinny_gemm_error() == 0
+
+
+@pytest.mark.parametrize("tokens,H,K,slices", [(1, 128, 64, 1), (8, 2048, 2048, 8), (5, 200, 520, 3), (8, 264, 96, None), (33, 384, 1032, 2)])
+def test_skinny_gemm_with_residual_epilogue_and_row_scaling(tokens, H, K, slices):
+    """h += x W^T with the first half of the RMS norm in the epilogue, then the products that read
+    the result (plain, SiLU * up, float32 logits) and apply the norm's row factor, against the
+    formulas in float64.  One row of h is tiny and eps large, so a dropped eps would show."""
+    eps = 1e-3
+    x = rnd(tokens, K, dtype=torch.bfloat16, seed=tokens)
+    w = rnd(H, K, dtype=torch.bfloat16, seed=H, scale=0.05)
+    h0 = rnd(tokens, H, seed=K)
+    h0[0] *= 1e-3
+    x[0] *= 1e-3
+    gain = (1.0 + 0.3 * rnd(H, seed=3)).contiguous()
+    h = h0.clone()
+    got = ops.skinny_gemm_residual(x, w, h, gain, eps, slices)
+    want_h = h0.double() + x.double() @ w.double().T
+    np.testing.assert_allclose(h.double().cpu().numpy(), want_h.cpu().numpy(), atol=1e-4 * max(1.0, float(want_h.abs().max())))
+    assert tuple(got.ssq.shape) == (tokens, (H + 127) // 128)
+    np.testing.assert_allclose(got.ssq.double().sum(1).cpu().numpy(), (want_h ** 2).sum(1).cpu().numpy(), rtol=1e-4)
+    np.testing.assert_allclose(got.x.double().cpu().numpy(), (want_h * gain.double()).cpu().numpy(),
+                               atol=8e-3 * max(1.0, float((want_h * gain.double()).abs().max())))
+    # the readers: y = rmsnorm(h) * gain, then products of y
+    rstd = 1.0 / torch.sqrt((want_h ** 2).mean(1, keepdim=True) + eps)
+    y = want_h * rstd * gain.double()
+    w2 = rnd(136, H, dtype=torch.bfloat16, seed=7, scale=0.1)
+    for out_dtype, tol in ((torch.bfloat16, 2e-2), (torch.float32, 1e-2)):
+        for sl in (None, 1, 4):
+            out = ops.skinny_gemm(got, w2, out_dtype, sl)
+            want = (y @ w2.double().T).cpu().numpy()
+            np.testing.assert_allclose(out.double().cpu().numpy(), want, atol=tol * max(1.0, np.abs(want).max()))
+    I = 128
+    gate = rnd(I, H, dtype=torch.bfloat16, seed=8, scale=0.1)
+    up = rnd(I, H, dtype=torch.bfloat16, seed=9, scale=0.1)
+    tiled = torch.stack([gate.view(I // 64, 64, H), up.view(I // 64, 64, H)], 1).reshape(2 * I, H).contiguous()
+    act = ops.skinny_gemm_swiglu(got, tiled)
+    want = plain.silu((y @ gate.double().T).cpu().numpy()) * (y @ up.double().T).cpu().numpy()
+    np.testing.assert_allclose(act.double().cpu().numpy(), want, atol=2e-2 * max(1.0, np.abs(want).max()))
+    # a second residual product reading the first one's rows
+    w3 = rnd(H, H, dtype=torch.bfloat16, seed=11, scale=0.05)
+    h2 = h.clone()
+    nxt = ops.skinny_gemm_residual(got, w3, h2, gain, eps)
+    want_h2 = h.double() + y @ w3.double().T
+    np.testing.assert_allclose(h2.double().cpu().numpy(), want_h2.cpu().numpy(), atol=2e-2 * max(1.0, float(want_h2.abs().max())))
+    np.testing.assert_allclose(nxt.ssq.double().sum(1).cpu().numpy(), (h2.double() ** 2).sum(1).cpu().numpy(), rtol=1e-4)
+    assert ops.skinny_gemm_error() == 0

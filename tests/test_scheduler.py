@@ -13,10 +13,12 @@ def prompts(rng, n, lo=1, hi=30):
     return [[rng.randrange(50) for _ in range(rng.randrange(lo, hi))] for _ in range(n)]
 
 
-def test_batched_equals_sequential():
+@pytest.mark.parametrize("ahead", [False, True])
+def test_batched_equals_sequential(ahead):
     rng = random.Random(0)
     ps = prompts(rng, 12)
-    eng, runner = fake_engine()
+    eng, runner = fake_engine(ahead=ahead)
+    assert eng.lookahead == ahead
     outs = eng.generate(ps, SamplingParams(max_tokens=20))
     assert outs == [sequential(p, 20) for p in ps]
     assert eng.manager.min_available_pages() == 64 and not eng.has_unfinished()
@@ -79,10 +81,11 @@ def test_request_that_can_never_fit_is_refused():
         eng.add_request("empty", [])
 
 
-def test_stop_tokens_eos_and_length():
+@pytest.mark.parametrize("ahead", [False, True])
+def test_stop_tokens_eos_and_length(ahead):
     p = [3, 1, 4]
     full = sequential(p, 10)
-    eng, _ = fake_engine()
+    eng, _ = fake_engine(ahead=ahead)
     eng.eos = frozenset({full[4]})
     a = eng.add_request("a", p, SamplingParams(max_tokens=10))
     b = eng.add_request("b", p, SamplingParams(max_tokens=10, ignore_eos=True))
@@ -127,16 +130,18 @@ def test_head_of_queue_is_not_overtaken():
         eng.step()
 
 
+@pytest.mark.parametrize("ahead", [False, True])
 @pytest.mark.parametrize("seed", range(8))
-def test_random_scenarios(seed):
+def test_random_scenarios(seed, ahead):
     """Random pools, budgets, arrivals and aborts: outputs equal the sequential ones, every step
-    keeps the invariants (checked inside the fake runner), nothing leaks."""
+    keeps the invariants (checked inside the fake runner), nothing leaks.  With ``ahead`` the
+    engine launches decode steps before it has read the ids of the step before."""
     rng = random.Random(seed)
     page = rng.choice([1, 2, 4, 8])
     pages = rng.randrange(12, 40)
     eng, runner = fake_engine(num_pages=pages, page_size=page, max_num_seqs=rng.randrange(1, 6),
                               budget=rng.randrange(1, 24), watermark=rng.choice([0.0, 0.1]),
-                              prefix_caching=rng.random() < 0.7)
+                              prefix_caching=rng.random() < 0.7, ahead=ahead)
     pending = []
     for i in range(14):
         stem = [7] * rng.randrange(0, 10)
@@ -164,3 +169,34 @@ def test_random_scenarios(seed):
             assert req.output_ids == sequential(p, mt)
     eng.manager.check_invariants()
     assert eng.manager.min_available_pages() == pages
+    assert not eng._unknown
+
+
+def test_one_step_ahead_in_steady_decode():
+    """While everyone decodes and nobody waits, the next step is launched before the ids of the
+    current one are read; a stop token costs one surplus token that is dropped; a request that
+    ends by length is left out of the step ahead; an arrival makes the engine read first."""
+    p, q = [3, 1, 4], [2, 7]
+    eng, runner = fake_engine(ahead=True, page_size=2)
+    stop_at = sequential(q, 6)[3]
+    a = eng.add_request("a", p, SamplingParams(max_tokens=9))
+    b = eng.add_request("b", q, SamplingParams(max_tokens=9, stop_token_ids=(stop_at,)))
+    outs = eng.step()  # the prompts; the step after them is already launched
+    assert len(runner.steps) == 2 and eng.steps_ahead == 1 and {o.request_id for o in outs} == {"a", "b"}
+    assert all(n == 1 for _, _, n, _ in runner.steps[1])
+    while not b.is_finished:
+        eng.step()
+    assert b.output_ids == sequential(q, 9, stop=(stop_at,)) and b.finish_reason is FinishReason.STOP
+    surplus = [rid for rid, *_ in runner.steps[-1]]
+    assert "b" in surplus, "the step ahead was launched before the stop token was read"
+    late = eng.add_request("late", [9, 9, 9, 9, 9], SamplingParams(max_tokens=2))
+    launched = len(runner.steps)
+    eng.step()  # reads the step in flight; nothing new is launched ahead because a request waits
+    assert len(runner.steps) == launched
+    while eng.has_unfinished():
+        eng.step()
+    assert a.output_ids == sequential(p, 9) and late.output_ids == sequential([9] * 5, 2)
+    # 'a' ends by length: its last token's step had no step ahead for it
+    assert sum(1 for st in runner.steps for rid, *_ in st if rid == "a") == 9
+    eng.manager.check_invariants()
+    assert eng.manager.min_available_pages() == 64 and not eng._unknown
