@@ -14,10 +14,11 @@
 //     lies in the pages); the thread reads its row of O_tile and folds it into its float32
 //     accumulator with the usual rescaling.
 //
-// One thread issues all copies and matrix products and meets the softmax threads on mbarriers
-// only; loads run ahead (keys of the next tile as soon as S is done, values one tile ahead), and
-// two CTAs per SM overlap one's softmax with the other's matrix products.  Every mbarrier wait is bounded: after WAIT_LIMIT polls the kernel
-// sets *error_flag, stops using the tensor cores, frees its tensor memory and returns.
+// One warp issues the copies, one the matrix products; they meet each other and the softmax threads on mbarriers only.
+// Keys, values, scores, probabilities and the output tile are double-buffered, so the tensor cores
+// work one tile ahead of the softmax (one CTA per SM, 512 columns of tensor memory).  Every mbarrier
+// wait is bounded: after WAIT_LIMIT polls the kernel sets *error_flag, stops using the tensor
+// cores, frees its tensor memory and returns.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -33,9 +34,9 @@ constexpr int ROWS = 128;      // (token, head) rows per CTA
 constexpr int KEYS = 128;      // keys per tile
 constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 128 bytes (Q, K, V tiles and each half of P)
 constexpr int SOFTMAX_THREADS = 256;
-constexpr int THREADS = SOFTMAX_THREADS + 32;  // plus the warp whose first lane issues copies and matrix products
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 1 + 2 + 2) + 2 * ROWS * 4 + 256 + 1024;  // Q, K, V x2, P (two halves), row maxima, barriers, alignment
-constexpr int TMEM_COLS = 256;  // S: 128 columns, O_tile: 64 columns
+constexpr int THREADS = SOFTMAX_THREADS + 64;  // plus a warp that issues the matrix products and a warp that issues the copies
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 + 2 + 4) + 4 * ROWS * 4 + 256 + 1024;  // Q, K x2, V x2, P x2 (two halves each), row maxima x2, barriers, alignment
+constexpr int TMEM_COLS = 512;  // S: 2 x 128 columns, output tile: 2 x 64 columns (a power of two)
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
 struct Params {
@@ -80,7 +81,7 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
       "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -89,7 +90,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -115,31 +115,37 @@ __device__ __forceinline__ bool wait_or_fail(uint32_t bar, uint32_t parity, vola
   return false;
 }
 
-// 288 threads.  Warps 0..7 do the softmax: thread t works on row (t & 127); its half (t >> 7)
-// owns 64 of the tile's 128 key columns and 32 of the 64 output columns (warps w and w + 4 read
-// the same 32 lanes of tensor memory: the lane group is the warp index modulo 4).  Warp 8 issues
-// every TMA copy (one page per lane) and, from its first lane, every tcgen05.mma, so the softmax
-// warps never wait for serial work; the two sides meet on mbarriers only:
-//   k_full, v_full[2]   TMA -> controller          s_done, o_done   MMA -> softmax threads
-//   p_ready (256)       probabilities written, S read      o_read (256)   O_tile read
-__global__ void __launch_bounds__(THREADS, 2) paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+// 320 threads, one CTA per SM.  Warps 0..7 do the softmax: thread t works on row (t & 127); its half
+// (t >> 7) owns 64 of the tile's 128 key columns and 32 of the 64 output columns (warps w and w + 4
+// read the same 32 lanes of tensor memory: the lane group is the warp index modulo 4).  Warp 8 issues
+// every tcgen05.mma from its first lane; warp 9 issues every TMA copy, one page per lane.
+//
+// Everything a tile needs exists twice (key and value stages, the scores S and the output tile in
+// tensor memory, the probabilities P in shared memory), indexed by the tile's parity, so the tensor
+// cores run one tile ahead of the softmax: S(i + 1) = Q K(i + 1)^T is issued as soon as the threads
+// have read S(i - 1), and while they work on tile i the product P(i - 1) V(i - 1) finishes; a thread
+// folds that output tile into its accumulator after it has handed in P(i).  The two sides meet on
+// mbarriers only (two of each, by parity):
+//   k_full, v_full   TMA -> controller            s_done, o_done   MMA -> softmax threads
+//   p_ready (256)    P written, S read            o_read (256)     output tile read
+__global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                       const __grid_constant__ CUtensorMap map_v, const Params p) {
   pdl_launch_dependents();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sQ = smem;
-  unsigned char* sK = sQ + TILE_BYTES;          // one stage: refilled as soon as S = Q K^T is done
-  unsigned char* sV = sK + TILE_BYTES;          // two stages
-  unsigned char* sP = sV + 2 * TILE_BYTES;      // keys 0..63 | keys 64..127
-  float* row_max = (float*)(sP + 2 * TILE_BYTES);   // [2][128]: each half's maximum of the tile, later its sum
-  uint64_t* bars = (uint64_t*)(row_max + 2 * ROWS);  // k_full, v_full[2], s_done, o_done, p_ready, o_read
-  uint32_t* tmem_slot = (uint32_t*)(bars + 7);
+  unsigned char* sK = sQ + TILE_BYTES;          // two stages
+  unsigned char* sV = sK + 2 * TILE_BYTES;      // two stages
+  unsigned char* sP = sV + 2 * TILE_BYTES;      // two buffers of (keys 0..63 | keys 64..127)
+  float* row_max = (float*)(sP + 4 * TILE_BYTES);   // [2 (tile parity)][2 (half)][128]: each half's maximum of the tile, at the end its sum
+  uint64_t* bars = (uint64_t*)(row_max + 4 * ROWS);  // k_full[2], v_full[2], s_done[2], o_done[2], p_ready[2], o_read[2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = tid & (ROWS - 1), half = (tid >> 7) & 1;
-  const uint32_t k_full = smem_u32(bars), v_full = smem_u32(bars + 1), s_done = smem_u32(bars + 3), o_done = smem_u32(bars + 4),
-                 p_ready = smem_u32(bars + 5), o_read = smem_u32(bars + 6);
+  const uint32_t k_full = smem_u32(bars), v_full = smem_u32(bars + 2), s_done = smem_u32(bars + 4), o_done = smem_u32(bars + 6),
+                 p_ready = smem_u32(bars + 8), o_read = smem_u32(bars + 10);
 
   const int s = p.seq0 + blockIdx.y;
   const int tile = gridDim.x - 1 - blockIdx.x;  // the last tokens see the most keys: their CTAs start first
@@ -162,13 +168,8 @@ __global__ void __launch_bounds__(THREADS, 2) paged_prefill_tc_kernel(const __gr
   const int num_tiles = t_end - t_begin;
 
   if (tid == 0) {
-    mbar_init(k_full, 1);
-    mbar_init(v_full, 1);
-    mbar_init(v_full + 8, 1);
-    mbar_init(s_done, 1);
-    mbar_init(o_done, 1);
-    mbar_init(p_ready, SOFTMAX_THREADS);
-    mbar_init(o_read, SOFTMAX_THREADS);
+    for (int i = 0; i < 8; ++i) mbar_init(k_full + 8 * i, 1);  // k_full, v_full, s_done, o_done
+    for (int i = 0; i < 4; ++i) mbar_init(p_ready + 8 * i, SOFTMAX_THREADS);  // p_ready, o_read
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -196,66 +197,80 @@ __global__ void __launch_bounds__(THREADS, 2) paged_prefill_tc_kernel(const __gr
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + KEYS;
+  // tensor memory: S of even tiles, S of odd tiles, output tile of even tiles, of odd tiles
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 2 * KEYS;
 
-  if (warp == SOFTMAX_THREADS / 32) {
-    // ================================================================ controller warp
-    // Lane 0 waits and issues the matrix products.  The copies of a tile are issued by the whole
-    // warp, one page per lane (lanes 0..15 keys, lanes 16..31 values): a single thread would spend
-    // microseconds on sixteen table look-ups and address computations per tile.
+  if (warp == SOFTMAX_THREADS / 32 + 1) {
+    // ================================================================ the warp that copies
+    // The copies of a tile are issued by the whole warp, one page per lane (lanes 0..15 keys, lanes
+    // 16..31 values): a single thread would spend microseconds on sixteen table look-ups and
+    // address computations per tile.  A tile's stage is free once the product that read the tile
+    // two before it has finished; the table entry of the next tile is asked for a tile ahead.
     const int pages = KEYS / p.page_size;
     const int page_i = lane & 15;
-    auto page_row = [&](int t) -> int {  // first row of this lane's page in the pools, or -1 if it is not needed
+    auto lookup = [&](int t) -> int {  // this lane's page of tile t (absolute tile index), or -1 if it is not needed
       const int first = t * KEYS + page_i * p.page_size;
-      const bool need = page_i < pages && first < hi && first + p.page_size > lo;
-      return need ? (table[first / p.page_size] * p.nkv + kvh) * p.page_size : -1;
+      const bool need = t < t_end && page_i < pages && first < hi && first + p.page_size > lo;
+      return need ? table[first / p.page_size] : -1;
     };
-    auto issue = [&](bool keys, int stage, int row) {  // called by the sixteen lanes of one side
-      const uint32_t bar = keys ? k_full : v_full + 8 * stage;
-      unsigned char* dst = keys ? sK : sV + stage * TILE_BYTES;
+    auto issue = [&](bool keys, int stage, int page) {  // called by the sixteen lanes of one side
+      const uint32_t bar = (keys ? k_full : v_full) + 8 * stage;
+      unsigned char* dst = (keys ? sK : sV) + stage * TILE_BYTES;
       const unsigned side = keys ? 0x0000ffffu : 0xffff0000u;
-      const int count = __popc(__ballot_sync(side, row >= 0));
+      const int count = __popc(__ballot_sync(side, page >= 0));
       if (page_i == 0) mbar_expect_tx(bar, (uint32_t)(count * p.page_size * 128));
       __syncwarp(side);
-      if (row >= 0) tma_load_2d(smem_u32(dst + page_i * p.page_size * 128), keys ? &map_k : &map_v, 0, row, bar);
+      if (page >= 0) tma_load_2d(smem_u32(dst + page_i * p.page_size * 128), keys ? &map_k : &map_v, 0, (page * p.nkv + kvh) * p.page_size, bar);
     };
-    const uint32_t idesc_s = instr_desc(ROWS, KEYS, 0), idesc_o = instr_desc(ROWS, D, 1);
-    if (num_tiles > 0) {
-      const int row = page_row(t_begin);
-      if (lane < 16) issue(true, 0, row); else issue(false, 0, row);
-    }
-    for (int it = 0; it < num_tiles; ++it) {
-      const int stage = it & 1;
-      if (lane == 0 && wait_or_fail(k_full, it & 1, failed, 11, p.error_flag)) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a = smem_u32(sQ), b = smem_u32(sK);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma(tmem_s, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), idesc_s, k != 0);
-        umma_commit(s_done);
+    int page = lookup(t_begin);
+    for (int t = 0; t < num_tiles && !*failed; ++t) {
+      const int st = t & 1, par = ((t - 2) >> 1) & 1;
+      const int cur = page;
+      page = lookup(t_begin + t + 1);  // used an iteration from now
+      if (t >= 2) {
+        if (lane == 0) wait_or_fail(s_done + 8 * st, par, failed, 12, p.error_flag);  // Q K(t - 2)^T has read the stage
+        __syncwarp();
+        if (*failed) break;
       }
-      const int next_row = it + 1 < num_tiles ? page_row(t_begin + it + 1) : -1;  // looked up while the product runs
-      if (lane == 0) wait_or_fail(s_done, it & 1, failed, 12, p.error_flag);  // the key buffer is free again
-      __syncwarp();
-      if (*failed) break;
-      if (it + 1 < num_tiles && lane < 16) issue(true, 0, next_row);
-      // the other value stage was read by P V of tile it - 1
-      if (lane == 0 && it > 0) wait_or_fail(o_done, (it - 1) & 1, failed, 13, p.error_flag);
-      __syncwarp();
-      if (*failed) break;
-      if (it + 1 < num_tiles && lane >= 16) issue(false, stage ^ 1, next_row);
-      if (lane == 0 && wait_or_fail(p_ready, it & 1, failed, 15, p.error_flag) &&
-          wait_or_fail(v_full + 8 * stage, (it >> 1) & 1, failed, 14, p.error_flag) &&
-          (it == 0 || wait_or_fail(o_read, (it - 1) & 1, failed, 16, p.error_flag))) {  // O_tile of the tile before was read
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a = smem_u32(sP), b = smem_u32(sV + stage * TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < KEYS / 16; ++k)
-          umma(tmem_o, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(b + k * 2048), idesc_o, k != 0);
-        umma_commit(o_done);
+      if (lane < 16) issue(true, st, cur);
+      if (t >= 2) {
+        if (lane == 0) wait_or_fail(o_done + 8 * st, par, failed, 13, p.error_flag);  // P V(t - 2) has read the stage
+        __syncwarp();
+        if (*failed) break;
       }
-      __syncwarp();
-      if (*failed) break;
+      if (lane >= 16) issue(false, st, cur);
     }
+  } else if (warp == SOFTMAX_THREADS / 32) {
+    // ================================================================ the warp that issues the matrix products (its first lane)
+    if (lane == 0) {
+      const uint32_t idesc_s = instr_desc(ROWS, KEYS, 0), idesc_o = instr_desc(ROWS, D, 1);
+      auto qk = [&](int t) {  // S(t) = Q K(t)^T once the keys have arrived
+        const int b = t & 1;
+        if (!wait_or_fail(k_full + 8 * b, (t >> 1) & 1, failed, 11, p.error_flag)) return;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = smem_u32(sQ), k = smem_u32(sK + b * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) umma(tmem_s + b * KEYS, smem_desc_sw128(a + kk * 32), smem_desc_sw128(k + kk * 32), idesc_s, kk != 0);
+        umma_commit(s_done + 8 * b);
+      };
+      qk(0);
+      for (int it = 0; it < num_tiles && !*failed; ++it) {
+        const int b = it & 1, par = (it >> 1) & 1;
+        // S(it + 1): its buffer held S(it - 1), which every thread had read when p_ready(it - 1) was seen (last iteration)
+        if (it + 1 < num_tiles) qk(it + 1);
+        // O_tile(it) = P(it) V(it): the probabilities are written, the values have arrived, the output tile it - 2 was read
+        if (wait_or_fail(p_ready + 8 * b, par, failed, 15, p.error_flag) && wait_or_fail(v_full + 8 * b, par, failed, 14, p.error_flag) &&
+            (it < 2 || wait_or_fail(o_read + 8 * b, ((it - 2) >> 1) & 1, failed, 16, p.error_flag))) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a = smem_u32(sP + b * 2 * TILE_BYTES), v = smem_u32(sV + b * TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < KEYS / 16; ++k)
+            umma(tmem_o + b * D, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(v + k * 2048), idesc_o, k != 0);
+          umma_commit(o_done + 8 * b);
+        }
+      }
+    }
+    __syncwarp();
   } else {
     // ================================================================ softmax threads
     const int rtok = r / Gc;
@@ -264,97 +279,120 @@ __global__ void __launch_bounds__(THREADS, 2) paged_prefill_tc_kernel(const __gr
     const uint32_t lane_bits = (uint32_t)((warp & 3) * 32) << 16;
     const int col0 = half * 64;
     float m = -CUDART_INF_F, l = 0.f;  // m: running maximum of the raw scores; l: this half's share of the row sum
+    float corr_prev = 1.f;             // the factor that goes with the output tile not yet folded in
     float o[32];                       // output columns 32 * half .. 32 * half + 31 of the row
 #pragma unroll
     for (int j = 0; j < 32; ++j) o[j] = 0.f;
+    bool ok = true;
+    const int group = r >> 6;  // rows 0..63 (warps 0, 1, 4, 5) and rows 64..127 (warps 2, 3, 6, 7)
+
+    uint32_t ov[32];  // the output tile being folded in: asked for before the probabilities are computed, used after
+    auto fold_begin = [&](int t) {
+      const int b = t & 1;
+      ok = wait_or_fail(o_done + 8 * b, (t >> 1) & 1, failed, 13, p.error_flag) && ok;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (ok) tmem_ld32_nowait(tmem_o + b * D + lane_bits + half * 32, ov);  // (uniform: every thread waits on the same barriers)
+    };
+    auto fold_end = [&](int t, float corr) {  // o = o * corr + O_tile(t)
+      if (ok) {
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], corr, __uint_as_float(ov[j]));
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(o_read + 8 * (t & 1));
+    };
 
     for (int it = 0; it < num_tiles; ++it) {
+      const int b = it & 1;
       const int base = (t_begin + it) * KEYS;
-      bool ok = wait_or_fail(s_done, it & 1, failed, 12, p.error_flag);
+      ok = wait_or_fail(s_done + 8 * b, (it >> 1) & 1, failed, 12, p.error_flag) && ok;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // a tile that lies wholly at or before the first row's position, inside every row's window, needs no mask
       const bool full = base + KEYS - 1 <= pos0 && base >= lo && p.window <= 0;
-      auto masked = [&](uint32_t raw, int key) -> float {
-        const bool vis = key <= rpos && (p.window <= 0 || key > rpos - p.window);
-        return vis ? __uint_as_float(raw) : -CUDART_INF_F;
-      };
-      // ---- pass 1: the maximum of this thread's 64 raw scores
-      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-      if (ok) {  // every lane takes part in the aligned tensor-memory loads, also for rows that hold no query
+      // ---- this thread's 64 raw scores, read once; masked ones become -inf.  Rows that hold no query
+      //      (zeros in Q) are computed like the others and never written out.
+      float sc[64];
+      if (ok) {  // every lane takes part in the aligned tensor-memory loads
+        uint32_t v0[32], v1[32];
+        tmem_ld32_nowait(tmem_s + b * KEYS + lane_bits + col0, v0);
+        tmem_ld32_nowait(tmem_s + b * KEYS + lane_bits + col0 + 32, v1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (full) {
 #pragma unroll
-        for (int c = 0; c < 64; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_s + lane_bits + col0 + c, v);
-          if (full) {
+          for (int j = 0; j < 32; ++j) { sc[j] = __uint_as_float(v0[j]); sc[32 + j] = __uint_as_float(v1[j]); }
+        } else {
+          const int first = base + col0;  // visible: first + j in (rpos - window, rpos]
+          const int hi_j = rpos - first, lo_j = p.window > 0 ? rpos - p.window - first : -1;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(v[j]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], masked(v[j], base + col0 + c + j));
+          for (int j = 0; j < 32; ++j) {
+            sc[j] = (j <= hi_j && j > lo_j) ? __uint_as_float(v0[j]) : -CUDART_INF_F;
+            sc[32 + j] = (32 + j <= hi_j && 32 + j > lo_j) ? __uint_as_float(v1[j]) : -CUDART_INF_F;
           }
         }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) sc[j] = -CUDART_INF_F;
       }
-      if (!rvalid) mx[0] = mx[1] = mx[2] = mx[3] = -CUDART_INF_F;
-      row_max[half * ROWS + r] = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
-      const float mnew = fmaxf(m, fmaxf(row_max[r], row_max[ROWS + r]));
+      float mx[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx[j] = sc[j];
+#pragma unroll
+      for (int j = 8; j < 64; ++j) mx[j & 7] = fmaxf(mx[j & 7], sc[j]);
+      mx[0] = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      mx[4] = fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]));
+      float* rm = row_max + b * 2 * ROWS;  // by parity: a fast thread's next tile writes the other buffer
+      rm[half * ROWS + r] = fmaxf(mx[0], mx[4]);
+      if (group == 0) asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS / 2) : "memory");  // the two halves of this row's 64-row group
+      else asm volatile("bar.sync 2, %0;" ::"n"(SOFTMAX_THREADS / 2) : "memory");
+      const float mnew = fmaxf(m, fmaxf(rm[r], rm[ROWS + r]));
       const float msafe = (mnew == -CUDART_INF_F) ? 0.f : mnew;
       const float corr = ex2((m - msafe) * p.scale_log2);
       const float neg = -msafe * p.scale_log2;
       m = mnew;
-      // ---- pass 2: probabilities, their sum, and the bfloat16 tile for the P V product
+      // ---- probabilities, their sum, and the bfloat16 tile for the P V product.  P's buffer was read by
+      //      P V of tile it - 2, whose output this thread folded in an iteration ago.
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
-      if (ok) {
-        unsigned char* prow = sP + half * TILE_BYTES + r * 128;
+      unsigned char* prow = sP + b * 2 * TILE_BYTES + half * TILE_BYTES + r * 128;
+      // in three sweeps, so that the 64 exponentials follow each other without waiting for anything
 #pragma unroll
-        for (int c = 0; c < 64; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_s + lane_bits + col0 + c, v);
+      for (int j = 0; j < 64; ++j) sc[j] = fmaf(sc[j], p.scale_log2, neg);
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint32_t packed[4];
+      for (int j = 0; j < 64; ++j) sc[j] = ex2(sc[j]);  // masked: ex2(-inf) = 0
 #pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-              float a0, a1;
-              if (full) {
-                a0 = __uint_as_float(v[j + e]);
-                a1 = __uint_as_float(v[j + e + 1]);
-              } else {
-                a0 = masked(v[j + e], base + col0 + c + j + e);
-                a1 = masked(v[j + e + 1], base + col0 + c + j + e + 1);
-              }
-              const float p0 = rvalid ? ex2(fmaf(a0, p.scale_log2, neg)) : 0.f;  // masked: ex2(-inf) = 0
-              const float p1 = rvalid ? ex2(fmaf(a1, p.scale_log2, neg)) : 0.f;
-              sum[(e >> 1) & 3] += p0 + p1;
-              __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-              packed[e >> 1] = *reinterpret_cast<uint32_t*>(&b2);
-            }
-            *reinterpret_cast<uint4*>(prow + ((((c + j) >> 3) ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          }
+      for (int j = 0; j < 64; j += 8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          sum[(e >> 1) & 3] += sc[j + e] + sc[j + e + 1];
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(sc[j + e], sc[j + e + 1]);
+          packed[e >> 1] = *reinterpret_cast<uint32_t*>(&b2);
         }
+        *reinterpret_cast<uint4*>(prow + (((j >> 3) ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
       l = l * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor cores
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(p_ready);  // P is written and S has been read: the controller may issue P V, and later the next Q K^T
+      mbar_arrive(p_ready + 8 * b);  // P is written and S has been read: the controller may issue P V and the Q K^T of tile it + 2
 
-      ok = wait_or_fail(o_done, it & 1, failed, 13, p.error_flag) && ok;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (ok) {
-        uint32_t v[32];
-        tmem_ld32(tmem_o + lane_bits + half * 32, v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], corr, __uint_as_float(v[j]));
+      if (it > 0) {  // that product ran while this tile's probabilities were computed
+        fold_begin(it - 1);
+        fold_end(it - 1, corr_prev);
       }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(o_read);
+      corr_prev = corr;
+    }
+    if (num_tiles > 0) {
+      fold_begin(num_tiles - 1);
+      fold_end(num_tiles - 1, corr_prev);
     }
 
     // ---- the row sum is the two halves' sums; each half writes its 32 output columns
-    row_max[half * ROWS + r] = l;
-    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
+    float* rl = row_max + (num_tiles & 1) * 2 * ROWS;  // not the buffer of the last tile's maxima
+    rl[half * ROWS + r] = l;
+    if (group == 0) asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS / 2) : "memory");
+    else asm volatile("bar.sync 2, %0;" ::"n"(SOFTMAX_THREADS / 2) : "memory");
     if (!*failed && rvalid) {
-      const float inv = 1.f / (row_max[r] + row_max[ROWS + r]);
+      const float inv = 1.f / (rl[r] + rl[ROWS + r]);
       const size_t row = (size_t)(q0 + tok0 + rtok) * p.nh + head0 + (r - rtok * Gc);
       uint4* dst = reinterpret_cast<uint4*>(p.out + row * D + half * 32);
 #pragma unroll
