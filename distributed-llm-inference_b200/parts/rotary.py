@@ -34,7 +34,7 @@ def inverse_frequencies(params) -> torch.Tensor:
     return torch.where(medium, smoothed, scaled)
 
 
-def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq):
+def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq, table_key=None):
     """Runs the fused kernel and returns the tensor whose leading num_heads * head_dim columns
     are the encoded queries (qkv itself: queries are rotated in place)."""
     group = batch.group(cache.group)
@@ -44,7 +44,7 @@ def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head
         table = None
         if rotary_dim and qkv.dtype == torch.bfloat16 and qkv.shape[0] > 64:
             # many tokens: the sines and cosines of the step are computed once and shared by all layers
-            key = ("rotary_table", inv_freq.data_ptr())
+            key = ("rotary_table", table_key)
             table = batch.scratch.get(key)
             if table is None:
                 table = batch.scratch[key] = ops.rotary_table(batch.positions, inv_freq)
@@ -52,14 +52,14 @@ def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head
     return qkv
 
 
-def _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq):
+def _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq, table_key=None):
     """q | k | v projection followed by position encoding and cache write; for a decode step's few
     tokens both happen in one kernel (the product's epilogue rotates and writes the cache)."""
     if fused_epilogue(x) and ops.skinny_rotary_supported(head_dim):
         group = batch.group(cache.group)
         return ops.skinny_gemm_rotary(x, wqkv, batch.positions, inv_freq, group.slots, cache.k, cache.v, num_heads, num_kv_heads,
                                       head_dim, rotary_dim, cache.page_size, write_kv)
-    return _rotate_and_store(project(x, wqkv), batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq)
+    return _rotate_and_store(project(x, wqkv), batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq, table_key)
 
 
 @register_part("position", "rotary")
@@ -76,13 +76,16 @@ class Rotary(Part):
         self.rotary_dim = int(spec.params.get("rotary_dim", self.head_dim))
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim={self.rotary_dim} must be even and at most head_dim={self.head_dim}")
-        self.inv_freq = inverse_frequencies(spec.params).to(env.device) if self.rotary_dim else None
+        inv = inverse_frequencies(spec.params) if self.rotary_dim else None
+        self.inv_freq = inv.to(env.device) if inv is not None else None
+        # layers with the same frequencies share one table of sines and cosines per step
+        self.table_key = hash(tuple(inv.tolist())) if inv is not None else None
 
     def rotate_and_store(self, qkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
-        return _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, self.rotary_dim, self.inv_freq)
+        return _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, self.rotary_dim, self.inv_freq, self.table_key)
 
     def project_and_encode(self, x, wqkv, batch, cache, num_heads: int, num_kv_heads: int, write_kv: bool):
-        return _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, self.rotary_dim, self.inv_freq)
+        return _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, self.head_dim, self.rotary_dim, self.inv_freq, self.table_key)
 
 
 @register_part("position", "none")
