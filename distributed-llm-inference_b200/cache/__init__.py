@@ -1,4 +1,4 @@
-from .manager import UNKNOWN_TOKEN, Allocation, CacheManager, CacheStats, GroupSpec, UnknownRequest
+from .manager import UNKNOWN_TOKEN, Allocation, CacheManager, CacheStats, GroupSpec, PageCopy, UnknownRequest
 from .needs import PagedKVNeed, StateNeed
 from .page_pool import OutOfPages, PagePool, chain_hashes, page_hash
 from .pools import CachePools, LayerCache, plan_groups
@@ -6,5 +6,5 @@ from .pools import CachePools, LayerCache, plan_groups
 __all__ = [
     "UNKNOWN_TOKEN",
     "Allocation", "CacheManager", "CachePools", "CacheStats", "GroupSpec", "LayerCache", "OutOfPages",
-    "PagePool", "PagedKVNeed", "StateNeed", "UnknownRequest", "chain_hashes", "page_hash", "plan_groups",
+    "PageCopy", "PagePool", "PagedKVNeed", "StateNeed", "UnknownRequest", "chain_hashes", "page_hash", "plan_groups",
 ]

@@ -55,6 +55,15 @@ class CacheStats:
         return self.prompt_tokens_hit / self.prompt_tokens_queried if self.prompt_tokens_queried else 0.0
 
 
+@dataclass(frozen=True)
+class PageCopy:
+    """Copy page ``src`` to page ``dst`` in every layer of cache group ``group``."""
+
+    group: int
+    src: int
+    dst: int
+
+
 @dataclass
 class _Request:
     tables: list[list[int]]  # per group: page of block j, or -1 once the window passed it
@@ -77,6 +86,7 @@ class CacheManager:
         enable_prefix_caching: bool = True,
         has_state: bool = False,
         watermark: float = 0.01,
+        eviction_policy: str = "lru",
     ) -> None:
         if not 0.0 <= watermark < 1.0:
             raise ValueError("watermark must be in [0, 1)")
@@ -85,7 +95,7 @@ class CacheManager:
         self.page_size = page_size
         self.groups = list(groups)
         self.prefix_caching = bool(enable_prefix_caching and groups and not has_state and all(g.window is None for g in groups))
-        self.pools = [PagePool(g.num_pages, page_size, self.prefix_caching) for g in groups]
+        self.pools = [PagePool(g.num_pages, page_size, self.prefix_caching, eviction_policy) for g in groups]
         self._reserve = [int(watermark * g.num_pages) for g in groups]
         self.max_requests = max_requests
         self._has_window = any(g.window is not None for g in groups)
@@ -220,16 +230,29 @@ class CacheManager:
             self._mirror_write(g, req.slot, 0, table)
         return Allocation(cached, req.slot)
 
-    def append_slots(self, rid: Hashable, token_ids: Sequence[int]) -> None:
+    def append_slots(self, rid: Hashable, token_ids: Sequence[int]) -> list[PageCopy]:
         """Room for tokens appended to the request (a sampled token); ignores the watermark.
         A token whose id is not known yet (sampled on the device, not read) is UNKNOWN_TOKEN;
-        ``set_token`` names it later, and no page that holds one is indexed until then."""
+        ``set_token`` names it later, and no page that holds one is indexed until then.
+        If the request's last page is partly filled and shared with a fork, the request gets a page
+        of its own first: the returned copies must be carried out before the step that writes the
+        new tokens (src/dli/kv/block_manager.py:286-320)."""
         req = self._get(rid)
         ps = self.page_size
         first, last = req.num_tokens, req.num_tokens + len(token_ids)
         need = -(-last // ps) - -(-first // ps)  # positions in [first, last) that open a page
-        if need and any(need > pool.available for pool in self.pools):
-            raise OutOfPages(f"append needs {need} pages")
+        shared = [g for g, (pool, table) in enumerate(zip(self.pools, req.tables))
+                  if token_ids and first % ps and table[-1] >= 0 and pool.ref[table[-1]] > 1]
+        if any(need + (g in shared) > pool.available for g, pool in enumerate(self.pools)):
+            raise OutOfPages(f"append needs {need + bool(shared)} pages")
+        copies = []
+        for g in shared:
+            pool, table = self.pools[g], req.tables[g]
+            old, new = table[-1], pool.take()
+            pool.release(old)
+            table[-1] = new
+            self._mirror_write(g, req.slot, len(table) - 1, [new])
+            copies.append(PageCopy(g, old, new))
         if need:
             for g, (pool, table) in enumerate(zip(self.pools, req.tables)):
                 new = [pool.take() for _ in range(need)]
@@ -238,6 +261,26 @@ class CacheManager:
         req.num_tokens += len(token_ids)
         if self.prefix_caching:
             req.tail.extend(token_ids)
+        return copies
+
+    def fork(self, parent: Hashable, child: Hashable) -> None:
+        """A second request that shares every page of ``parent`` (several continuations of one
+        prompt).  The first append into the shared, partly filled last page gives the appender a
+        page of its own (src/dli/kv/block_manager.py:338-359)."""
+        src = self._get(parent)
+        if child in self._requests:
+            raise ValueError(f"request {child!r} already holds pages")
+        if not self._free_slots:
+            raise OutOfPages("no state slot free")
+        for pool, table in zip(self.pools, src.tables):
+            for page in table:
+                if page >= 0:
+                    pool.share(page)
+        req = _Request([list(t) for t in src.tables], src.num_tokens, src.num_computed, src.namespace, self._free_slots.pop(),
+                       list(src.hashes), list(src.tail), src.registered)
+        for g, table in enumerate(req.tables):
+            self._mirror_write(g, req.slot, 0, table)
+        self._requests[child] = req
 
     def mark_computed(self, rid: Hashable, num_computed: int) -> None:
         """Keys and values of the first ``num_computed`` tokens are written: full pages become

@@ -6,13 +6,16 @@ index: its contents stay valid and a later request with the same prefix can
 take it over, or it is evicted when memory is needed).  States and rules follow
 src/dli/kv/block_manager.py:9-29: only full pages are indexed, only after their
 keys were computed; the index is prefix-closed and only idle pages without an
-indexed child are evicted, least recently released first
-(src/dli/kv/eviction.py:59-90).
+indexed child are evicted: least recently released first, or — policy ``"cost"`` —
+lowest value first, a page's value growing with the hits it had and with its depth in
+its chain (src/dli/kv/eviction.py:59-164).
 """
 
 from __future__ import annotations
 
 import hashlib
+import heapq
+import itertools
 import struct
 from collections import OrderedDict, deque
 from dataclasses import dataclass
@@ -51,12 +54,81 @@ class _Indexed:
     digest: bytes
     parent: int | None
     children: int = 0
+    depth: int = 0  # pages before this one in its chain
+    hits: int = 1  # times its contents were wanted: once when computed, once per later request that found it
+
+
+class _OldestFirst:
+    """Candidates in the order in which they became evictable."""
+
+    def __init__(self) -> None:
+        self._order: OrderedDict[int, None] = OrderedDict()
+
+    def add(self, page: int, entry: _Indexed) -> None:
+        self._order[page] = None
+
+    def discard(self, page: int) -> None:
+        self._order.pop(page, None)
+
+    def pop(self, indexed: dict[int, _Indexed]) -> int:
+        return self._order.popitem(last=False)[0]
+
+    def pages(self) -> set[int]:
+        return set(self._order)
+
+    def __len__(self) -> int:
+        return len(self._order)
+
+
+class _LowestValueFirst:
+    """Greedy-dual with frequency (the scheme of src/dli/kv/eviction.py:93-164): a candidate's value
+    is ``floor + hits * (1 + depth_weight * depth)``; the lowest goes first and its value becomes the
+    floor, so pages that stop being hit age against newer ones.  All pages have the same size.  A deep
+    page of a chain that was wanted often (a shared system prompt) outlives one-off tails.
+    A heap with lazy deletion: an entry counts only while its stamp is the page's current one."""
+
+    def __init__(self, depth_weight: float = 0.05) -> None:
+        self.depth_weight = depth_weight
+        self.floor = 0.0
+        self._heap: list[tuple[float, int, int]] = []  # (value, stamp, page)
+        self._stamp: dict[int, int] = {}
+        self._stamps = itertools.count()
+
+    def add(self, page: int, entry: _Indexed) -> None:
+        stamp = self._stamp[page] = next(self._stamps)
+        heapq.heappush(self._heap, (self.floor + entry.hits * (1.0 + self.depth_weight * entry.depth), stamp, page))
+        if len(self._heap) > 4 * len(self._stamp) + 64:  # mostly stale entries: rebuild
+            self._heap = [e for e in self._heap if self._stamp.get(e[2]) == e[1]]
+            heapq.heapify(self._heap)
+
+    def discard(self, page: int) -> None:
+        self._stamp.pop(page, None)
+
+    def pop(self, indexed: dict[int, _Indexed]) -> int:
+        while self._heap:
+            value, stamp, page = heapq.heappop(self._heap)
+            if self._stamp.get(page) == stamp:
+                del self._stamp[page]
+                self.floor = value
+                return page
+        raise KeyError("no candidate")
+
+    def pages(self) -> set[int]:
+        return set(self._stamp)
+
+    def __len__(self) -> int:
+        return len(self._stamp)
+
+
+EVICTION_POLICIES = {"lru": _OldestFirst, "cost": _LowestValueFirst}
 
 
 class PagePool:
-    def __init__(self, num_pages: int, page_size: int, prefix_index: bool) -> None:
+    def __init__(self, num_pages: int, page_size: int, prefix_index: bool, eviction_policy: str = "lru") -> None:
         if num_pages < 1 or page_size < 1:
             raise ValueError("num_pages and page_size must be positive")
+        if eviction_policy not in EVICTION_POLICIES:
+            raise ValueError(f"eviction_policy must be one of {sorted(EVICTION_POLICIES)}, got {eviction_policy!r}")
         self.num_pages = num_pages
         self.page_size = page_size
         self.prefix_index = prefix_index
@@ -65,8 +137,9 @@ class PagePool:
         self.indexed: dict[int, _Indexed] = {}
         self.by_hash: dict[bytes, int] = {}
         self.num_idle = 0
-        # idle pages without an indexed child, oldest release first: the eviction order
-        self.evictable: OrderedDict[int, None] = OrderedDict()
+        # idle pages without an indexed child, in the policy's eviction order
+        self.evictable = EVICTION_POLICIES[eviction_policy]()
+        self.eviction_policy = eviction_policy
         self.evictions = 0
         self.duplicate_registrations = 0
 
@@ -93,8 +166,8 @@ class PagePool:
         """A page with ref 1: from the free list, else the least recently released evictable one."""
         if self.free:
             page = self.free.popleft()
-        elif self.evictable:
-            page, _ = self.evictable.popitem(last=False)
+        elif len(self.evictable):
+            page = self.evictable.pop(self.indexed)
             self._evict(page)
         else:
             raise OutOfPages("no free or evictable page")
@@ -107,7 +180,10 @@ class PagePool:
             if page not in self.indexed:
                 raise AssertionError(f"share of free page {page}")
             self.num_idle -= 1
-            self.evictable.pop(page, None)
+            self.evictable.discard(page)
+        entry = self.indexed.get(page)
+        if entry is not None:
+            entry.hits += 1
         self.ref[page] += 1
 
     def release(self, page: int) -> None:
@@ -122,7 +198,7 @@ class PagePool:
             return
         self.num_idle += 1
         if entry.children == 0:
-            self.evictable[page] = None
+            self.evictable.add(page, entry)
 
     def _evict(self, page: int) -> None:
         entry = self.indexed.pop(page)
@@ -133,13 +209,13 @@ class PagePool:
             parent = self.indexed[entry.parent]
             parent.children -= 1
             if parent.children == 0 and self.ref[entry.parent] == 0:
-                self.evictable[entry.parent] = None  # the parent is now a leaf
+                self.evictable.add(entry.parent, parent)  # the parent is now a leaf
 
     def drop_index(self) -> int:
         """Evict every idle page (its contents are forgotten).  Returns how many."""
         n = 0
-        while self.evictable:
-            page, _ = self.evictable.popitem(last=False)
+        while len(self.evictable):
+            page = self.evictable.pop(self.indexed)
             self._evict(page)
             self.free.append(page)
             n += 1
@@ -167,9 +243,9 @@ class PagePool:
                 return
             pentry = self.indexed[parent]
             if pentry.children == 0 and self.ref[parent] == 0:
-                self.evictable.pop(parent, None)
+                self.evictable.discard(parent)
             pentry.children += 1
-        self.indexed[page] = _Indexed(digest, parent)
+        self.indexed[page] = _Indexed(digest, parent, depth=0 if parent is None else self.indexed[parent].depth + 1)
         self.by_hash[digest] = page
 
     # ------------------------------------------------------------ verification
@@ -199,4 +275,4 @@ class PagePool:
             if page in used:
                 assert e.parent is None or self.ref[e.parent] > 0, f"used page {page} has an idle parent"
         leaves = {p for p in idle if self.indexed[p].children == 0}
-        assert set(self.evictable) == leaves, "evictable set is not the idle leaves"
+        assert self.evictable.pages() == leaves and len(self.evictable) == len(leaves), "evictable set is not the idle leaves"

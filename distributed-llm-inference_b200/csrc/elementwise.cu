@@ -63,6 +63,25 @@ DLI_EXPORT int dli_patch_tokens(int* ids, const int* source, const int* src, int
   return (int)cudaGetLastError();
 }
 
+// One page copied to another in every layer of a cache group (a forked request gets its own last
+// page before it appends): pool [layers, pages, page_bytes]; 16-byte units.
+__global__ void copy_page_kernel(uint4* __restrict__ pool, long long layer_units, long long page_units, int src, int dst) {
+  pdl_launch_dependents();
+  pdl_wait();
+  uint4* base = pool + (size_t)blockIdx.y * layer_units;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < page_units; i += (long long)gridDim.x * blockDim.x)
+    base[(size_t)dst * page_units + i] = base[(size_t)src * page_units + i];
+}
+
+DLI_EXPORT int dli_copy_page(void* pool, long long layer_bytes, long long page_bytes, int layers, int src, int dst, cudaStream_t stream) {
+  if (layers == 0 || src == dst) return 0;
+  if ((page_bytes % 16) || (layer_bytes % 16) || ((uintptr_t)pool % 16)) return DLI_ERR_UNSUPPORTED;
+  const long long units = page_bytes / 16;
+  const int blocks = (int)((units + 255) / 256 < 64 ? (units + 255) / 256 : 64);
+  launch_pdl(copy_page_kernel, dim3(blocks, layers), dim3(256), 0, stream, 1, (uint4*)pool, layer_bytes / 16, units, src, dst);
+  return (int)cudaGetLastError();
+}
+
 // ---------------------------------------------------------------- add + rmsnorm
 // For output row r (source row s = rows ? rows[r] : r):
 //   v = h[s] + delta[s]            (float32; written back to h[s] when rows == nullptr)

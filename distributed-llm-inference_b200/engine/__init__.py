@@ -1,4 +1,5 @@
 from .batch import StepBatch, StepEntry, build_batch
+from .generate import greedy_generate
 from .llm_engine import LLMEngine, RequestOutput, StepStats
 from .request import FinishReason, Request, RequestStatus
 from .runner import ModelRunner, load_model, random_model, resolve_dtype
@@ -7,5 +8,5 @@ from .scheduler import ScheduledChunk, Scheduler, SchedulerConfig, SchedulerOutp
 __all__ = [
     "FinishReason", "LLMEngine", "ModelRunner", "Request", "RequestOutput", "RequestStatus", "ScheduledChunk",
     "Scheduler", "SchedulerConfig", "SchedulerOutput", "StepBatch", "StepEntry", "StepStats", "build_batch",
-    "load_model", "random_model", "resolve_dtype",
+    "greedy_generate", "load_model", "random_model", "resolve_dtype",
 ]

@@ -116,9 +116,12 @@ class LLMEngine:
     @classmethod
     def for_model(cls, model, *, num_blocks: int | None = None, kv_cache_gb: float | None = None, block_size: int = 16,
                   config: SchedulerConfig | None = None, enable_prefix_caching: bool = True, watermark: float = 0.01,
-                  eos_token_ids: Collection[int] = (), seed: int = 0, lookahead: bool = True) -> "LLMEngine":
+                  eos_token_ids: Collection[int] = (), seed: int = 0, lookahead: bool = True,
+                  eviction_policy: str = "lru") -> "LLMEngine":
         """An engine around a loaded model.  The cache pool has ``num_blocks`` pages of
-        ``block_size`` tokens, or as many as ``kv_cache_gb`` GiB hold (default 1 GiB)."""
+        ``block_size`` tokens, or as many as ``kv_cache_gb`` GiB hold (default 1 GiB).
+        ``eviction_policy``: which idle prefix page goes first, "lru" or "cost"
+        (src/dli/engine/engine.py:92-107, src/dli/kv/eviction.py:167)."""
         from ..sampling import Sampler
         from .runner import ModelRunner
 
@@ -128,7 +131,7 @@ class LLMEngine:
         if num_blocks is None:
             num_blocks = ModelRunner.pages_for_budget(model, (kv_cache_gb or 1.0) * 2**30, block_size)
         runner = ModelRunner(model, num_pages=num_blocks, page_size=block_size, max_requests=config.max_num_seqs,
-                             enable_prefix_caching=enable_prefix_caching, watermark=watermark)
+                             enable_prefix_caching=enable_prefix_caching, watermark=watermark, eviction_policy=eviction_policy)
         return cls(runner, config, sampler=Sampler(model.device), eos_token_ids=eos_token_ids, seed=seed, lookahead=lookahead)
 
     @classmethod
@@ -221,6 +224,8 @@ class LLMEngine:
             return None
         for req in sched.admitted:
             self.runner.start_request(req.request_id, self.manager.state_slot(req.request_id))
+        if sched.copies:
+            self.runner.copy_pages(sched.copies)
         return self._run(sched.chunks, len(sched.preempted))
 
     def _launch_ahead(self, flight: _InFlight) -> _InFlight | None:
@@ -239,8 +244,10 @@ class LLMEngine:
             for _, r in chosen:
                 position = r.num_tokens  # of the token in flight
                 if self.manager.num_tokens(r.request_id) <= position:
-                    self.manager.append_slots(r.request_id, [UNKNOWN_TOKEN])
+                    copies = self.manager.append_slots(r.request_id, [UNKNOWN_TOKEN])
                     self._unknown[r.request_id] = position
+                    if copies:
+                        self.runner.copy_pages(copies)
         except OutOfPages:
             return None  # the scheduler will decide who yields; slots taken so far are kept and named when the ids arrive
         chunks = [ScheduledChunk(r, r.num_computed_tokens, 1, True) for _, r in chosen]

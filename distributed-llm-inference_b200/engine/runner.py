@@ -73,7 +73,8 @@ class ModelRunner:
     """A model with its cache pools and cache manager."""
 
     def __init__(self, model: DecoderModel, *, num_pages: int | Sequence[int], page_size: int = 16, max_requests: int = 64,
-                 enable_prefix_caching: bool = True, watermark: float = 0.01, cuda_graphs: bool = True) -> None:
+                 enable_prefix_caching: bool = True, watermark: float = 0.01, cuda_graphs: bool = True,
+                 eviction_policy: str = "lru") -> None:
         self.model = model
         needs = model.cache_needs()
         order = model.spec.run_order
@@ -83,7 +84,7 @@ class ModelRunner:
         self.manager = CacheManager(
             [GroupSpec(p, need.window) for p, need in zip(pages, self.pools.group_needs)],
             page_size, max_requests, enable_prefix_caching=enable_prefix_caching,
-            has_state=any(isinstance(n, StateNeed) for n in needs), watermark=watermark,
+            has_state=any(isinstance(n, StateNeed) for n in needs), watermark=watermark, eviction_policy=eviction_policy,
         )
         self.page_size = page_size
         self.uploader = Uploader(model.device)
@@ -102,6 +103,13 @@ class ModelRunner:
     def start_request(self, request_id, slot: int) -> None:
         if self.pools.has_state:
             self.pools.reset_state(slot)
+
+    def copy_pages(self, copies) -> None:
+        """Carry out the cache manager's page copies (``append_slots`` of a forked request) in every
+        layer of their groups, before the step that writes the appended tokens."""
+        for c in copies:
+            ops.copy_page(self.pools.k[c.group], c.src, c.dst)
+            ops.copy_page(self.pools.v[c.group], c.src, c.dst)
 
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry], borrow: bool = False, token_source: torch.Tensor | None = None) -> torch.Tensor:

@@ -55,6 +55,7 @@ class SchedulerOutput:
     chunks: list[ScheduledChunk] = field(default_factory=list)
     preempted: list[Request] = field(default_factory=list)
     admitted: list[Request] = field(default_factory=list)
+    copies: list = field(default_factory=list)  # cache.PageCopy: to carry out before the step runs
 
     @property
     def num_batched_tokens(self) -> int:
@@ -119,7 +120,7 @@ class Scheduler:
             n = min(total - req.num_computed_tokens, budget)
             if n <= 0:
                 continue
-            while not self._reserve(req, total):
+            while not self._reserve(req, total, out):
                 victim = next((c for c in reversed(self.running) if c.request_id not in in_batch and c is not req), None)
                 if victim is None:
                     victim = req  # nobody else can yield
@@ -156,13 +157,13 @@ class Scheduler:
         start = req.num_computed_tokens
         return ScheduledChunk(req, start, n, needs_logits=start + n == req.num_tokens)
 
-    def _reserve(self, req: Request, total: int) -> bool:
+    def _reserve(self, req: Request, total: int, out: SchedulerOutput) -> bool:
         """Slots for tokens the cache manager has not seen yet (the newly sampled one)."""
         missing = total - self.manager.num_tokens(req.request_id)
         if missing <= 0:
             return True
         try:
-            self.manager.append_slots(req.request_id, req.token_slice(total - missing, total))
+            out.copies.extend(self.manager.append_slots(req.request_id, req.token_slice(total - missing, total)) or ())
             return True
         except OutOfPages:
             return False

@@ -105,6 +105,17 @@ def patch_tokens(ids: torch.Tensor, source: torch.Tensor, src: torch.Tensor) -> 
     _check(f(_ptr(ids), _ptr(source), _ptr(src), ids.numel(), _stream()), "patch_tokens")
 
 
+def copy_page(pool: torch.Tensor, src: int, dst: int) -> None:
+    """pool[:, dst] = pool[:, src] for a cache pool [layers, pages, ...] (copy-on-write of a forked
+    request's last page)."""
+    _need(pool, "pool")
+    if pool.dim() < 2 or not (0 <= src < pool.shape[1] and 0 <= dst < pool.shape[1]):
+        raise KernelError("copy_page: pool must be [layers, pages, ...] and the pages inside it")
+    page_bytes = pool[0, 0].numel() * pool.element_size()
+    f = _fn("elementwise.cu", "dli_copy_page", [c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(pool), pool.shape[1] * page_bytes, page_bytes, pool.shape[0], src, dst, _stream()), "copy_page")
+
+
 def add_rmsnorm(
     y: torch.Tensor,
     h: torch.Tensor,

@@ -24,14 +24,17 @@ def sequential(prompt, max_tokens, stop=()):
 
 
 class FakeRunner:
-    def __init__(self, num_pages, page_size, max_requests=64, prefix_caching=True, watermark=0.01):
+    def __init__(self, num_pages, page_size, max_requests=64, prefix_caching=True, watermark=0.01, eviction_policy="lru"):
         self.manager = CacheManager([GroupSpec(num_pages)], page_size, max_requests,
-                                    enable_prefix_caching=prefix_caching, watermark=watermark)
+                                    enable_prefix_caching=prefix_caching, watermark=watermark, eviction_policy=eviction_policy)
         self.started = []
         self.steps = []
 
     def start_request(self, request_id, slot):
         self.started.append(request_id)
+
+    def copy_pages(self, copies):
+        self.copied = getattr(self, "copied", []) + list(copies)
 
     def execute(self, chunks, token_source=None, token_rows=None):
         rows = []

@@ -155,7 +155,7 @@ def test_random_orders_keep_every_invariant(seed, prefix_caching, window):
     rng = random.Random(seed)
     page = rng.choice([1, 3, 4])
     groups = [GroupSpec(24)] + ([GroupSpec(20, window=window)] if window else [])
-    m = CacheManager(groups, page, 5, enable_prefix_caching=prefix_caching, watermark=0.0)
+    m = CacheManager(groups, page, 5, enable_prefix_caching=prefix_caching, watermark=0.0, eviction_policy=rng.choice(["lru", "cost"]))
     shadow = [dict() for _ in groups]  # per group: slot -> prefix tuple
     tokens: dict[int, list[int]] = {}
     stems = [[rng.randrange(5) for _ in range(12)] for _ in range(3)]
@@ -231,4 +231,64 @@ def test_unknown_token_is_not_indexed_until_named():
     m.allocate("c", [1, 2, 3, 9, 5])
     assert m.num_computed_tokens("c") == 4
     m.free("a"), m.free("c")
+    m.check_invariants()
+
+
+def test_cost_policy_keeps_the_prefix_that_is_wanted_often():
+    """A shared stem that many requests hit survives a burst of one-off prompts under the "cost"
+    policy (its pages have many hits and lie deep in their chain); least-recently-released evicts it."""
+    stem = list(range(100, 112))  # three full pages of 4
+
+    def run(policy):
+        m = CacheManager([GroupSpec(8)], 4, 4, enable_prefix_caching=True, watermark=0.0, eviction_policy=policy)
+        for i in range(4):  # the stem is computed once and found three times
+            toks = stem + [i]
+            m.allocate(f"s{i}", toks)
+            m.mark_computed(f"s{i}", len(toks))
+            m.free(f"s{i}")
+        for i in range(5):  # one-off prompts of one full page each: 5 more pages than the 5 that are free
+            toks = [200 + i] * 4 + [7]
+            m.allocate(f"u{i}", toks)
+            m.mark_computed(f"u{i}", len(toks))
+            m.free(f"u{i}")
+            m.check_invariants()
+        return m.allocate("again", stem + [9]).num_cached_tokens
+
+    assert run("cost") == 12
+    assert run("lru") < 12
+    with pytest.raises(ValueError):
+        CacheManager([GroupSpec(8)], 4, 4, eviction_policy="random")
+
+
+def test_fork_shares_pages_and_the_first_append_copies_the_last_one():
+    m = make(pages=8)  # page size 4
+    m.allocate("a", list(range(6)))  # one full page, one with two tokens
+    m.mark_computed("a", 6)
+    m.fork("a", "b")
+    assert m.block_table("a") == m.block_table("b") and m.state_slot("a") != m.state_slot("b")
+    m.check_invariants()
+    with pytest.raises(ValueError):
+        m.fork("a", "b")
+    copies = m.append_slots("b", [40])
+    assert len(copies) == 1 and copies[0].src == m.block_table("a")[1] and copies[0].dst == m.block_table("b")[1]
+    assert m.block_table("a")[0] == m.block_table("b")[0] and m.block_table("a")[1] != m.block_table("b")[1]
+    assert m.append_slots("a", [41]) == []  # the last page is a's own again
+    assert m.append_slots("b", [42, 43, 44]) == []  # b fills its page and opens the next
+    m.check_invariants()
+    m.free("a")
+    m.check_invariants()
+    m.free("b")
+    m.check_invariants()
+    assert m.min_available_pages() == 8
+
+
+def test_fork_without_room_for_the_copy_changes_nothing():
+    m = make(pages=2, watermark=0.0)
+    m.allocate("a", list(range(6)))
+    m.mark_computed("a", 6)
+    m.fork("a", "b")
+    before = (m.block_table("a"), m.block_table("b"), m.num_tokens("b"))
+    with pytest.raises(OutOfPages):
+        m.append_slots("b", [9])
+    assert (m.block_table("a"), m.block_table("b"), m.num_tokens("b")) == before
     m.check_invariants()

@@ -177,3 +177,55 @@ def test_command_line_generates(models, tmp_path):
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr
     assert (tmp_path / "m" / "model.safetensors").exists()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generate_with_and_without_cache(models, dtype):
+    """The plain entry point: the cached path, the path that runs the whole sequence again for every
+    token, and the plain implementation agree; a stop id ends the generation and is kept."""
+    import dli_b200
+
+    path, cfg, weights, page = models["tiny_a"]
+    model = dli_b200.load_model(path, dtype)
+    prompt = random_tokens(cfg["vocab_size"], 21, seed=5)
+    cached = dli_b200.greedy_generate(model, prompt, 12, page_size=page)
+    want, gaps = plain_greedy_with_margin(cfg, plain_weights_for(weights, dtype), prompt, 12)
+    assert_same_tokens(cached, want, gaps, TOL[dtype], f"greedy_generate {dtype}")
+    again = dli_b200.greedy_generate(model, prompt, 12, use_cache=False, page_size=page)
+    assert_same_tokens(again, want, gaps, TOL[dtype], f"greedy_generate without cache {dtype}")
+    assert dli_b200.greedy_generate(model, prompt, 12, eos_token_ids=[cached[3]], page_size=page) == cached[: cached.index(cached[3]) + 1]
+    assert dli_b200.greedy_generate(model, prompt, 0) == []
+    with pytest.raises(ValueError):
+        dli_b200.greedy_generate(model, [], 3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_forked_requests_continue_apart(models, dtype):
+    """Two continuations of one prompt share its pages; the first append into the shared, partly
+    filled last page copies it (all layers), after which each request's logits are those of its own
+    sequence, in one batch and step by step."""
+    path, cfg, weights, page = models["tiny_b"]
+    w = plain_weights_for(weights, dtype)
+    model = dli_b200.load_model(path, dtype)
+    runner = ModelRunner(model, num_pages=16, page_size=page, max_requests=4, enable_prefix_caching=False, watermark=0.0)
+    prompt = random_tokens(cfg["vocab_size"], page + page // 2 + 1, seed=9)  # ends inside its second page
+    runner.manager.allocate("a", prompt)
+    runner.step([StepEntry("a", prompt, [len(prompt) - 1])])
+    runner.manager.fork("a", "b")
+    seqs = {"a": list(prompt), "b": list(prompt)}
+    for step in range(page):  # long enough to leave the copied page and open a new one
+        entries = []
+        for rid in ("a", "b"):
+            tok = (7 + 3 * step) % cfg["vocab_size"] if rid == "a" else (11 + 5 * step) % cfg["vocab_size"]
+            copies = runner.manager.append_slots(rid, [tok])
+            assert bool(copies) == (step == 0 and rid == "a"), "exactly the first appender gets a page of its own"
+            runner.copy_pages(copies)
+            seqs[rid].append(tok)
+            entries.append(StepEntry(rid, [tok], [0]))
+        got = runner.step(entries).float().cpu().numpy()
+        for row, rid in enumerate(("a", "b")):
+            want = plain.forward(cfg, w, seqs[rid])[-1]
+            np.testing.assert_allclose(got[row], want, atol=TOL[dtype], err_msg=f"{rid} step {step}")
+    runner.manager.check_invariants()
+    runner.manager.free("a"), runner.manager.free("b")
+    assert runner.manager.min_available_pages() == 16

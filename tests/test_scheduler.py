@@ -141,7 +141,7 @@ def test_random_scenarios(seed, ahead):
     pages = rng.randrange(12, 40)
     eng, runner = fake_engine(num_pages=pages, page_size=page, max_num_seqs=rng.randrange(1, 6),
                               budget=rng.randrange(1, 24), watermark=rng.choice([0.0, 0.1]),
-                              prefix_caching=rng.random() < 0.7, ahead=ahead)
+                              prefix_caching=rng.random() < 0.7, ahead=ahead, eviction_policy=rng.choice(["lru", "cost"]))
     pending = []
     for i in range(14):
         stem = [7] * rng.randrange(0, 10)
