@@ -15,8 +15,8 @@ import sys
 from pathlib import Path
 
 
-def _engine_options(p: argparse.ArgumentParser) -> None:
-    p.add_argument("--model", required=True, help="model folder (config.json + *.safetensors)")
+def _engine_options(p: argparse.ArgumentParser, model_required: bool = True) -> None:
+    p.add_argument("--model", required=model_required, default=None, help="model folder (config.json + *.safetensors)")
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--dtype", default="auto", choices=["auto", "float32", "bfloat16"], help="auto = bfloat16")
     kv = p.add_mutually_exclusive_group()
@@ -58,6 +58,57 @@ def cmd_generate(args) -> int:
     return 0
 
 
+def cmd_bench(args) -> int:
+    """Steady decode steps of ``--batch`` requests through the engine, as a user would drive it
+    (the measurement of benchmarks/scripts/engine_profile.py:36-117: random prompts, warm-up past the
+    prompts, timed steps, the split of a step, and the floor that memory bandwidth sets)."""
+    import statistics
+    import time
+
+    import torch
+
+    from . import LLMEngine, SamplingParams, SchedulerConfig, load_model, random_model
+
+    if not args.random_config and not args.model:
+        raise SystemExit("give --model DIR or --random-config JSON")
+    if args.random_config:
+        model = random_model(json.loads(Path(args.random_config).read_text()), args.seed, "bfloat16" if args.dtype == "auto" else args.dtype, args.device)
+    else:
+        model = load_model(args.model, "bfloat16" if args.dtype == "auto" else args.dtype, args.device)
+    total = args.input_len + args.output_len
+    blocks = args.num_blocks or args.batch * (-(-total // args.block_size) + 1)
+    eng = LLMEngine.for_model(model, num_blocks=blocks, block_size=args.block_size, enable_prefix_caching=not args.no_prefix_caching,
+                              config=SchedulerConfig(args.batch, max(args.max_num_batched_tokens, args.batch)), seed=args.seed)
+    g = torch.Generator().manual_seed(0)
+    for i in range(args.batch):
+        ids = torch.randint(min(1000, model.spec.vocab_size - 1), model.spec.vocab_size, (args.input_len,), generator=g).tolist()
+        eng.add_request(f"r{i}", ids, SamplingParams(max_tokens=args.output_len, ignore_eos=True))
+    while any(r.num_computed_tokens < args.input_len for r in eng.scheduler.running + list(eng.scheduler.waiting)):
+        eng.step()
+    for _ in range(args.warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    first = len(eng.stats.steps)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        eng.step()
+    torch.cuda.synchronize()
+    step_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    st = eng.stats.steps[first:]
+    weights = sum(t.numel() * t.element_size() for t in {id(t): t for part in model.parts() for t in vars(part).values() if isinstance(t, torch.Tensor)}.values())
+    ctx = statistics.mean(r.num_computed_tokens for r in eng.scheduler.running) if eng.scheduler.running else 0
+    kv = args.batch * ctx * sum(eng.runner.pools.bytes_per_page(model.cache_needs(), model.spec.run_order, args.block_size, model.dtype)) / args.block_size
+    print(json.dumps({
+        "batch": args.batch, "input_len": args.input_len, "steps": args.steps, "step_ms": step_ms, "tokens_per_s": args.batch / step_ms * 1e3,
+        "schedule_ms_mean": statistics.mean(s.schedule_s for s in st) * 1e3, "forward_ms_mean": statistics.mean(s.forward_s for s in st) * 1e3,
+        "postprocess_ms_mean": statistics.mean(s.postprocess_s for s in st) * 1e3, "steps_launched_ahead": eng.steps_ahead,
+        "graph_steps": eng.runner.graph_steps, "weight_bytes": weights, "kv_bytes_read_per_step": kv,
+        "bandwidth_floor_ms": (weights + kv) / (args.bandwidth_gbs * 1e9) * 1e3, "bandwidth_gbs": args.bandwidth_gbs,
+        "max_memory_allocated_mib": torch.cuda.max_memory_allocated() >> 20,
+    }))
+    return 0
+
+
 def cmd_init(args) -> int:
     import torch
 
@@ -93,6 +144,17 @@ def main(argv: list[str] | None = None) -> int:
     i.add_argument("--out", required=True)
     i.add_argument("--storage-dtype", default="float32", choices=["float32", "bfloat16"])
     i.set_defaults(fn=cmd_init)
+
+    b = sub.add_parser("bench", help="time steady decode steps of a batch through the engine")
+    _engine_options(b, model_required=False)
+    b.add_argument("--random-config", default=None, help="a config.json: run with seeded random weights instead of --model")
+    b.add_argument("--batch", type=int, default=8)
+    b.add_argument("--input-len", type=int, default=256)
+    b.add_argument("--output-len", type=int, default=128)
+    b.add_argument("--steps", type=int, default=20)
+    b.add_argument("--warmup", type=int, default=8)
+    b.add_argument("--bandwidth-gbs", type=float, default=6650.0, help="memory bandwidth for the floor, GB/s")
+    b.set_defaults(fn=cmd_bench)
 
     r = sub.add_parser("replay", help="trace replay (see bin/trace_run)", add_help=False)
     r.set_defaults(fn=None)

@@ -177,6 +177,13 @@ def test_command_line_generates(models, tmp_path):
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr
     assert (tmp_path / "m" / "model.safetensors").exists()
+    # and `dli bench` times decode steps of a batch on random weights
+    out = subprocess.run([sys.executable, str(ROOT / "bin" / "dli"), "bench", "--random-config", str(tmp_path / "c.json"), "--batch", "3",
+                          "--input-len", "20", "--output-len", "40", "--steps", "5", "--warmup", "2", "--block-size", "8"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    rec = json.loads(out.stdout.strip().splitlines()[-1])
+    assert rec["batch"] == 3 and rec["tokens_per_s"] > 0 and rec["steps_launched_ahead"] >= 5 and rec["bandwidth_floor_ms"] > 0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
