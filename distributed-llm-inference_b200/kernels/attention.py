@@ -22,20 +22,33 @@ CLUSTER_SPLITS_MAX = ops.DECODE_TMA_CLUSTER_SPLITS  # splits that the TMA decode
 CLUSTER_SPLITS_KV_LIMIT = 16384
 
 
-def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int = ONE_WAVE) -> int:
+def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int = ONE_WAVE, fill_last_wave: bool = True) -> int:
     """Key splits for single-token sequences: as many as still fit the GPU in one wave (a second,
     partly filled wave costs more than the extra parallelism brings), none shorter than
     MIN_TILES_PER_SPLIT key tiles (the role of src/dli/model/paged_attention.py:63-74)."""
     pairs = max(1, num_seqs * ctas_per_seq)
     tiles = -(-max_kv_len // 64)
-    return max(1, min(wave // pairs, tiles // MIN_TILES_PER_SPLIT))
+    most = max(1, tiles // MIN_TILES_PER_SPLIT)
+    if pairs <= wave:
+        return max(1, min(wave // pairs, most))
+    if not fill_last_wave:
+        return 1
+    # More CTAs than one wave holds even without splits: a few splits can still fill the last wave
+    # (512 CTAs on 296 places leave the second wave 27 % empty; 2,048 fill seven waves to 99 %).  Each
+    # split costs merging, so it has to buy three points of occupancy.  (Measured: the mma.sync
+    # kernel at head size 128 gains a fifth at 64 sequences; the TMA-fed kernel loses, so it opts out.)
+    def score(s: int) -> float:
+        ctas = pairs * s
+        return ctas / (-(-ctas // wave) * wave) - 0.03 * (s - 1)
+
+    return max(range(1, min(4, most) + 1), key=score)
 
 
 def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_size: int, max_kv_len: int) -> int:
     """Key splits of the decode kernel that will serve these sizes."""
     ctas_per_seq = nkv * -(-(num_heads // nkv) // 16)
     tma = ops.decode_tma_supported(head_dim, page_size)
-    splits = choose_splits(num_seqs, ctas_per_seq, max_kv_len, ONE_WAVE_TMA if tma else ONE_WAVE)
+    splits = choose_splits(num_seqs, ctas_per_seq, max_kv_len, ONE_WAVE_TMA if tma else ONE_WAVE, fill_last_wave=not tma)
     if tma and splits > CLUSTER_SPLITS_MAX and max_kv_len <= CLUSTER_SPLITS_KV_LIMIT:
         splits = CLUSTER_SPLITS_MAX  # merged on the chip by one cluster: measured faster than more splits and a merge kernel
     return splits

@@ -316,7 +316,8 @@ def test_one_key_stands_out(kernel, where):
 
 
 def test_choose_splits():
-    assert choose_splits(64, 8, 4096) == 1
+    assert choose_splits(64, 8, 4096) == 4  # 512 CTAs would leave the second wave of 296 places 27 % empty; 2,048 fill seven
+    assert choose_splits(64, 8, 4096, fill_last_wave=False) == 1
     assert choose_splits(8, 8, 4096) == 4
     assert choose_splits(1, 8, 4096) == 32
     assert choose_splits(1, 8, 100) == 1
