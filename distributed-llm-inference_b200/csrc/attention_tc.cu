@@ -484,21 +484,31 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
 namespace {
 
 constexpr int DN = 16;                 // keys per tile of one warp
-constexpr int DSTAGES = 3;
 constexpr int DWARPS = 4;
-constexpr int DTILE = DN * 128;        // one K or V tile: 16 rows of 128 bytes, swizzled
-constexpr int QROW = D * 2 + 16;       // padded query rows (read once)
-static_assert(DWARPS * 16 * (D + 2) * 4 <= DWARPS * DSTAGES * 2 * DTILE, "the merge buffer reuses the key/value stages");
-// Splits merged inside a cluster: row r of the 16 belongs to CTA (r mod splits); every CTA pushes its
-// partial (sums[D], maximum, denominator) of a row into the owner's memory.  At most 16 + 7 rows arrive
-// at one CTA (splits * ceil(16 / splits)).  The region starts where the query rows lay: they are in
-// registers by then.  With it the kernel still fits four CTAs per SM.
 constexpr int CLUSTER_SPLITS_MAX = 8;
-constexpr int RECV_ROW = D + 2;
-constexpr int RECV_BYTES = (16 + CLUSTER_SPLITS_MAX - 1) * RECV_ROW * 4;
-static_assert(RECV_BYTES >= 16 * QROW, "the received partial results lie over the query rows");
-constexpr int DSMEM = 1024 + DWARPS * DSTAGES * 2 * DTILE + RECV_BYTES + DWARPS * DSTAGES * 8 + 64;
-static_assert(4 * (DSMEM + 1024) <= 227 * 1024, "four CTAs per SM");
+
+// Sizes that depend on the head size HD (64 or 128).  A row of keys or values is HD * 2 bytes; the
+// 128-byte swizzle covers 64 elements, so a tile of 16 rows lies in shared memory as HD / 64 slabs of
+// [16 rows x 128 bytes], each filled by its own TMA box (the columns 64 s .. 64 s + 63 of the rows).
+template <int HD>
+struct DecodeCfg {
+  static_assert(HD == 64 || HD == 128, "head sizes with whole 128-byte slabs");
+  static constexpr int SLABS = HD / 64;
+  static constexpr int SLAB = DN * 128;                 // bytes of one slab
+  static constexpr int TILE = SLABS * SLAB;             // one K or V tile
+  static constexpr int STAGES = HD == 64 ? 3 : 2;
+  static constexpr int QROW = HD * 2 + 16;              // padded query rows (read once)
+  // Splits merged inside a cluster: row r of the 16 belongs to CTA (r mod splits); every CTA pushes its
+  // partial (sums[HD], maximum, denominator) of a row into the owner's memory.  At most 16 + 7 rows arrive
+  // at one CTA (splits * ceil(16 / splits)).  The region starts where the query rows lay: they are in
+  // registers by then.
+  static constexpr int RECV_ROW = HD + 2;
+  static constexpr int RECV_BYTES = (16 + CLUSTER_SPLITS_MAX - 1) * RECV_ROW * 4;
+  static constexpr int SMEM = 1024 + DWARPS * STAGES * 2 * TILE + RECV_BYTES + DWARPS * STAGES * 8 + 64;
+  static_assert(RECV_BYTES >= 16 * QROW, "the received partial results lie over the query rows");
+  static_assert(DWARPS * 16 * (HD + 2) * 4 <= DWARPS * STAGES * 2 * TILE, "the merge buffer reuses the key/value stages");
+  static_assert((HD == 64 ? 4 : 2) * (SMEM + 1024) <= 227 * 1024, "four CTAs per SM at head size 64, two at 128");
+};
 
 struct DecodeParams {
   bf16* out;
@@ -544,8 +554,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // are the query heads of one KV head; each warp walks its own share of the 16-key tiles.  A tile's
 // keys and values arrive by TMA (one box per page piece, 128-byte swizzle), four tiles ahead, on the
 // warp's own mbarriers: no thread spends instructions on addresses of individual 16-byte copies.
+template <int HD>
 __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
+  using Cfg = DecodeCfg<HD>;
+  constexpr int DSTAGES = Cfg::STAGES, DTILE = Cfg::TILE, QROW = Cfg::QROW, RECV_BYTES = Cfg::RECV_BYTES, RECV_ROW = Cfg::RECV_ROW;
+  constexpr int D = HD;  // shadows the prefill kernel's head size within this kernel
   pdl_launch_dependents();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -614,8 +628,11 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
         const int key = key0 + b * box_rows;
         // a row coordinate beyond the pool makes the copy fill the box with zeros
         const int row = page < 0 ? 0x3fffff00 : (page * p.nkv + kvh) * p.page_size + (key % p.page_size);
-        tma_load_2d(smem_u32(wbuf + st * 2 * DTILE + b * box_rows * 128), &map_k, 0, row, bar);
-        tma_load_2d(smem_u32(wbuf + st * 2 * DTILE + DTILE + b * box_rows * 128), &map_v, 0, row, bar);
+#pragma unroll
+        for (int sl = 0; sl < Cfg::SLABS; ++sl) {
+          tma_load_2d(smem_u32(wbuf + st * 2 * DTILE + sl * Cfg::SLAB + b * box_rows * 128), &map_k, sl * 64, row, bar);
+          tma_load_2d(smem_u32(wbuf + st * 2 * DTILE + DTILE + sl * Cfg::SLAB + b * box_rows * 128), &map_v, sl * 64, row, bar);
+        }
       }
     }
   };
@@ -640,8 +657,8 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
   pdl_wait();
   if (deferred >= 0) issue(deferred);
 
-  for (int idx = tid; idx < 16 * 8; idx += DWARPS * 32) {
-    const int r = idx >> 3, c = idx & 7;
+  for (int idx = tid; idx < 16 * (D / 8); idx += DWARPS * 32) {
+    const int r = idx / (D / 8), c = idx - r * (D / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < nheads) v = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)(head0 + r) * D + c * 8);
     *reinterpret_cast<uint4*>(sQ + r * QROW + c * 16) = v;
@@ -669,8 +686,8 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
       for (int kk = 0; kk < D / 16; ++kk) {
         uint32_t b[4];
         const int key = (lane & 7) + (lane >> 4) * 8;
-        const int chunk = kk * 2 + ((lane >> 3) & 1);
-        ldsm_x4(b, tK + key * 128 + ((chunk ^ (key & 7)) << 4));
+        const int chunk = (kk & 3) * 2 + ((lane >> 3) & 1);
+        ldsm_x4(b, tK + (kk >> 2) * Cfg::SLAB + key * 128 + ((chunk ^ (key & 7)) << 4));
         mma16816(sc[0], qf[kk], b[0], b[1]);
         mma16816(sc[1], qf[kk], b[2], b[3]);
       }
@@ -716,8 +733,8 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
       for (int jp = 0; jp < D / 16; ++jp) {
         uint32_t b[4];
         const int key = (lane & 7) + ((lane >> 3) & 1) * 8;
-        const int chunk = jp * 2 + (lane >> 4);
-        ldsm_x4_trans(b, tV + key * 128 + ((chunk ^ (key & 7)) << 4));
+        const int chunk = (jp & 3) * 2 + (lane >> 4);
+        ldsm_x4_trans(b, tV + (jp >> 2) * Cfg::SLAB + key * 128 + ((chunk ^ (key & 7)) << 4));
         mma16816(o[2 * jp], a, b[0], b[1]);
         mma16816(o[2 * jp + 1], a, b[2], b[3]);
       }
@@ -811,7 +828,7 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
 
 // out[row] = sum_i acc_i 2^(m_i - max m) / sum_i l_i 2^(m_i - max m); one block per (token, head) row.
 __global__ void merge_decode_splits_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                           int row0, int splits) {
+                                           int row0, int splits, int d) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = (size_t)row0 + blockIdx.x;
@@ -824,26 +841,58 @@ __global__ void merge_decode_splits_kernel(bf16* __restrict__ out, const float* 
     if (mi != -CUDART_INF_F) L += ml[2 * i + 1] * exp2f(mi - mmax);
   }
   const float inv = 1.f / L;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float acc = 0.f;
     for (int i = 0; i < splits; ++i) {
       const float mi = ml[2 * i];
-      if (mi != -CUDART_INF_F) acc += part_acc[(row * splits + i) * D + d] * exp2f(mi - mmax);
+      if (mi != -CUDART_INF_F) acc += part_acc[(row * splits + i) * d + c] * exp2f(mi - mmax);
     }
-    out[row * D + d] = __float2bfloat16_rn(acc * inv);
+    out[row * d + c] = __float2bfloat16_rn(acc * inv);
   }
+}
+
+// a pool [pages, nkv, page_size, d] seen as rows of d elements; boxes of box_rows rows x 64 elements
+bool make_decode_map(CUtensorMap* map, const void* base, long long rows, int box_rows, int d) {
+  EncodeTiled fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)d * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HD>
+int launch_decode(const CUtensorMap& map_k, const CUtensorMap& map_v, const DecodeParams& p, int num_seqs, int first_row, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<HD>::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int G = p.nh / p.nkv;
+  cudaError_t e = launch_pdl(paged_decode_tma_kernel<HD>, dim3(num_seqs, p.splits, p.nkv * ((G + 15) / 16)), dim3(DWARPS * 32),
+                             (size_t)DecodeCfg<HD>::SMEM, stream, p.cluster_merge ? p.splits : 1, map_k, map_v, p);
+  if (e != cudaSuccess) return (int)e;
+  if (p.splits > 1 && !p.cluster_merge)
+    e = launch_pdl(merge_decode_splits_kernel, dim3(num_seqs * p.nh), dim3(64), 0, stream, 1, p.out, (const float*)p.part_acc,
+                   (const float*)p.part_ml, first_row * p.nh, p.splits, HD);
+  return (int)e;
 }
 
 }  // namespace
 
-// Attention of num_seqs single-token sequences (head size 64; page size a multiple of 8, and of 16
-// if larger than 8).  Up to 8 splits are one cluster and merge on the chip; more go through
+// Attention of num_seqs single-token sequences (head size 64 or 128; page size a multiple of 8, and
+// of 16 if larger than 8).  Up to 8 splits are one cluster and merge on the chip; more go through
 // part_acc / part_ml (scratch, as for dli_paged_attention_mma) and a second kernel.
 DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                     long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
-                                    const int* kv_len, int seq0, int num_seqs, int first_row, int nh, int nkv, int page_size,
-                                    int window, float scale, int splits, float* part_acc, float* part_ml, cudaStream_t stream) {
+                                    const int* kv_len, int seq0, int num_seqs, int first_row, int nh, int nkv, int head_dim,
+                                    int page_size, int window, float scale, int splits, float* part_acc, float* part_ml,
+                                    cudaStream_t stream) {
   if (num_seqs == 0) return 0;
+  if (head_dim != 64 && head_dim != 128) return DLI_ERR_UNSUPPORTED;
   if (nkv < 1 || nh % nkv || splits < 1 || (splits > 1 && (!part_acc || !part_ml))) return DLI_ERR_UNSUPPORTED;
   if (page_size < 8 || (page_size % 8) || (page_size > 8 && (page_size % 16)) || page_size > 256) return DLI_ERR_UNSUPPORTED;
   if (((uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)q) & 15) return DLI_ERR_UNSUPPORTED;
@@ -852,16 +901,11 @@ DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride
     *error_flag_host = 0;
     if (cudaHostGetDevicePointer((void**)&error_flag_device, error_flag_host, 0) != cudaSuccess) return (int)cudaGetLastError();
   }
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(paged_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DSMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
   CUtensorMap map_k, map_v;
   const long long rows = num_pages * nkv * page_size;
   const int box_rows = page_size < DN ? page_size : DN;
-  if (!make_pool_map(&map_k, k_pool, rows, box_rows) || !make_pool_map(&map_v, v_pool, rows, box_rows)) return DLI_ERR_UNSUPPORTED;
+  if (!make_decode_map(&map_k, k_pool, rows, box_rows, head_dim) || !make_decode_map(&map_v, v_pool, rows, box_rows, head_dim))
+    return DLI_ERR_UNSUPPORTED;
   DecodeParams p;
   p.out = (bf16*)out; p.q = (const bf16*)q; p.q_stride = q_stride;
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.q_start = q_start; p.kv_len = kv_len; p.seq0 = seq0;
@@ -869,14 +913,8 @@ DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride
   p.scale_log2 = scale * 1.4426950408889634f;
   p.part_acc = part_acc; p.part_ml = part_ml; p.error_flag = error_flag_device;
   p.cluster_merge = splits > 1 && splits <= CLUSTER_SPLITS_MAX;
-  const int G = nh / nkv;
-  cudaError_t e = launch_pdl(paged_decode_tma_kernel, dim3(num_seqs, splits, nkv * ((G + 15) / 16)), dim3(DWARPS * 32), (size_t)DSMEM, stream,
-                             p.cluster_merge ? splits : 1, map_k, map_v, p);
-  if (e != cudaSuccess) return (int)e;
-  if (splits > 1 && !p.cluster_merge)
-    e = launch_pdl(merge_decode_splits_kernel, dim3(num_seqs * nh), dim3(64), 0, stream, 1, (bf16*)out, (const float*)part_acc,
-                   (const float*)part_ml, first_row * nh, splits);
-  return (int)e;
+  return head_dim == 64 ? launch_decode<64>(map_k, map_v, p, num_seqs, first_row, stream)
+                        : launch_decode<128>(map_k, map_v, p, num_seqs, first_row, stream);
 }
 
 // 0, or the code of the first bounded wait that ran out (11 keys, 12 scores, 13 output tile, 14 values,

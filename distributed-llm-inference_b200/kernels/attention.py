@@ -14,7 +14,7 @@ import torch
 from . import ops
 
 ONE_WAVE = 148 * 2  # CTAs of the mma.sync decode kernel resident at once (two per SM in its few-sequences shape)
-ONE_WAVE_TMA = 148 * 4  # ... of the TMA-fed decode kernel (four per SM)
+ONE_WAVE_TMA = 148 * 4  # ... of the TMA-fed decode kernel (four per SM at head size 64; two at head size 128)
 MIN_TILES_PER_SPLIT = 2  # key tiles (of 64) a split should at least cover
 
 
@@ -48,7 +48,8 @@ def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_s
     """Key splits of the decode kernel that will serve these sizes."""
     ctas_per_seq = nkv * -(-(num_heads // nkv) // 16)
     tma = ops.decode_tma_supported(head_dim, page_size)
-    splits = choose_splits(num_seqs, ctas_per_seq, max_kv_len, ONE_WAVE_TMA if tma else ONE_WAVE, fill_last_wave=not tma)
+    wave = (ONE_WAVE_TMA if head_dim <= 64 else ONE_WAVE_TMA // 2) if tma else ONE_WAVE
+    splits = choose_splits(num_seqs, ctas_per_seq, max_kv_len, wave, fill_last_wave=not tma)
     if tma and splits > CLUSTER_SPLITS_MAX and max_kv_len <= CLUSTER_SPLITS_KV_LIMIT:
         splits = CLUSTER_SPLITS_MAX  # merged on the chip by one cluster: measured faster than more splits and a merge kernel
     return splits

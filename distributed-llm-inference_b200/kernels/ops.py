@@ -304,7 +304,7 @@ def paged_prefill_tc(
 
 
 def decode_tma_supported(head_dim: int, page_size: int) -> bool:
-    return head_dim == 64 and page_size % 8 == 0 and (page_size == 8 or page_size % 16 == 0) and page_size <= 256
+    return head_dim in (64, 128) and page_size % 8 == 0 and (page_size == 8 or page_size % 16 == 0) and page_size <= 256
 
 
 def paged_decode_tma(
@@ -325,13 +325,13 @@ def paged_decode_tma(
     scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
 ) -> None:
     """bfloat16 attention of single-token sequences whose keys and values arrive by TMA (head size
-    64; page sizes 8, 16, 32, ...).  Arguments as paged_attention_mma with max_q_len = 1."""
+    64 or 128; page sizes 8, 16, 32, ...).  Arguments as paged_attention_mma with max_q_len = 1."""
     for t, name in ((out, "out"), (qkv, "qkv"), (k_pool, "k_pool"), (v_pool, "v_pool")):
         _need(t, name, torch.bfloat16)
     _need(block_tables, "block_tables", torch.int32), _need(q_start, "q_start", torch.int32), _need(kv_len, "kv_len", torch.int32)
     pages, nkv, page_size, d = k_pool.shape
     if not decode_tma_supported(d, page_size):
-        raise KernelError(f"paged_decode_tma: head_dim {d} (64) or page size {page_size} not supported")
+        raise KernelError(f"paged_decode_tma: head_dim {d} (64 or 128) or page size {page_size} not supported")
     if out.shape[1] != num_heads * d or qkv.shape[0] != out.shape[0] or qkv.shape[1] < num_heads * d or num_heads % nkv or k_pool.shape != v_pool.shape:
         raise KernelError("paged_decode_tma: shapes do not agree")
     if seq0 + num_seqs > kv_len.numel() or q_start.numel() != kv_len.numel() + 1:
@@ -347,12 +347,12 @@ def paged_decode_tma(
             raise KernelError("paged_decode_tma: scratch too small")
     f = _fn(
         "attention_tc.cu", "dli_paged_decode_tma",
-        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7
+        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 8
         + [c_float, c_int, c_void_p, c_void_p, c_void_p],
     )
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_tables), block_tables.shape[1],
-          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, first_row, num_heads, nkv, page_size, int(window or 0), scale, splits,
+          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, first_row, num_heads, nkv, d, page_size, int(window or 0), scale, splits,
           _ptr(acc), _ptr(ml), _stream()),
         "paged_decode_tma",
     )

@@ -245,12 +245,16 @@ def test_paged_prefill_tc(nh, nkv, page, window):
     assert ops.paged_prefill_tc_error() == 0
 
 
-@pytest.mark.parametrize("nh,nkv,page", [(8, 2, 16), (3, 1, 8), (5, 5, 32), (32, 8, 64), (40, 1, 16)])
-@pytest.mark.parametrize("window", [None, 70])
-@pytest.mark.parametrize("splits", [1, 3, 8])
-def test_paged_decode_tma(nh, nkv, page, window, splits):
-    """The TMA-fed decode kernel: contexts from 1 to 1500 keys, ends on and off tile and page edges."""
-    d = 64
+DECODE_TMA_CASES = [(64, nh, nkv, page, window, splits)
+                    for nh, nkv, page in [(8, 2, 16), (3, 1, 8), (5, 5, 32), (32, 8, 64), (40, 1, 16)] for window in (None, 70) for splits in (1, 3, 8)]
+DECODE_TMA_CASES += [(64, 8, 2, 16, None, 11), (128, 24, 8, 16, None, 1), (128, 24, 8, 16, 70, 8), (128, 3, 1, 8, None, 3), (128, 3, 1, 8, 70, 1),
+                     (128, 20, 1, 32, None, 11), (128, 4, 4, 128, None, 8)]
+
+
+@pytest.mark.parametrize("d,nh,nkv,page,window,splits", DECODE_TMA_CASES)
+def test_paged_decode_tma(nh, nkv, page, window, splits, d):
+    """The TMA-fed decode kernel at both head sizes: contexts from 1 to 1500 keys, ends on and off tile
+    and page edges; splits merged inside a cluster (up to 8) and by the merge kernel (11)."""
     seqs = [(0, 1), (15, 1), (16, 1), (199, 1), (63, 1), (255, 1), (1499, 1), (700, 1)]
     t = attention_case(nh, nkv, d, page, seqs, torch.bfloat16, seed=nh + page)
     out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
