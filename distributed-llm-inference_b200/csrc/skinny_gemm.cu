@@ -17,7 +17,8 @@
 //     the residual addition with the first half of the next RMS norm (see Epilogue).
 //
 // The grid is (feature tiles, K slices).  Slices exist to fill the GPU when a matrix has few
-// feature tiles.  The CTAs of one tile's slices form a thread-block cluster (up to 8): each
+// feature tiles.  The CTAs of one tile's slices form a thread-block cluster (up to 16, the largest this
+// GPU takes; more than 8 is the kernel's opt-in): each
 // pushes its partial sums of a token into the shared memory of the CTA that owns the token
 // (distributed shared memory), and after one cluster barrier the owner adds them, slice 0
 // first, so the order is fixed, and writes the output.  No partial sum ever leaves the chip,
@@ -42,6 +43,7 @@ constexpr int WSUM_OFFSET = 192;    // four warp sums,
 constexpr int RSTD_OFFSET = 256;    // and the row factors of up to RSTD_MAX_TOKENS tokens
 constexpr int RSTD_MAX_TOKENS = 64;
 constexpr unsigned WAIT_LIMIT = 1u << 24;
+constexpr int MAX_SLICES = 16;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -421,14 +423,14 @@ int* error_flag_host = nullptr;
 }  // namespace
 
 // Number of K slices recommended for the given sizes: enough CTAs to fill the GPU, no slice
-// shorter than four k-tiles, at most 8 (the portable cluster size).
+// shorter than four k-tiles, at most 16 (the largest cluster of this GPU; 8 is the portable size).
 DLI_EXPORT int dli_skinny_gemm_slices(int tokens, int features, int K) {
   const int tiles = (features + BM - 1) / BM;
   const int k_tiles = (K + BK - 1) / BK;
   int want = (148 * 2 + tiles - 1) / tiles;
   int most = k_tiles / 4;
   if (most < 1) most = 1;
-  if (most > 8) most = 8;
+  if (most > MAX_SLICES) most = MAX_SLICES;
   int slices = want < most ? want : most;
   if (slices < 1) slices = 1;
   const int per = (k_tiles + slices - 1) / slices;
@@ -437,7 +439,7 @@ DLI_EXPORT int dli_skinny_gemm_slices(int tokens, int features, int K) {
 
 static int launch_skinny(void* out, int out_f32, const void* x, const void* w, int tokens, int features, int K, int slices,
                          int max_stages, const Epilogue& ep, cudaStream_t stream) {
-  if (tokens < 1 || tokens > 256 || features < 1 || K < 8 || K % 8 || slices < 1 || slices > 8) return DLI_ERR_UNSUPPORTED;
+  if (tokens < 1 || tokens > 256 || features < 1 || K < 8 || K % 8 || slices < 1 || slices > MAX_SLICES) return DLI_ERR_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return DLI_ERR_UNSUPPORTED;
   if (!error_flag_host) {
     if (cudaHostAlloc((void**)&error_flag_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return (int)cudaGetLastError();
@@ -468,6 +470,12 @@ static int launch_skinny(void* out, int out_f32, const void* x, const void* w, i
   if (smem > 227 * 1024) return DLI_ERR_UNSUPPORTED;
   int tmem_cols = 32;
   while (tmem_cols < npad) tmem_cols <<= 1;
+  static bool big_clusters = false;
+  if (slices > 8 && !big_clusters) {
+    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return (int)e;
+    big_clusters = true;
+  }
   static int configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -526,7 +526,7 @@ def skinny_gemm_slices(tokens: int, features: int, in_features: int) -> int:
 def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, slices: int | None = None,
                 out: torch.Tensor | None = None, max_stages: int = 0) -> torch.Tensor:
     """x [tokens <= 256, K] times weight [features, K] transposed, bfloat16 in, on tcgen05 tensor
-    cores fed by TMA; returns [tokens, features] in bfloat16 or float32.  ``slices`` (1..8) cuts K
+    cores fed by TMA; returns [tokens, features] in bfloat16 or float32.  ``slices`` (1..16) cuts K
     across the CTAs of a cluster, which add their partial sums through distributed shared memory."""
     x, scale = _row_scale(x, "skinny_gemm")
     _need(x, "x", torch.bfloat16), _need(weight, "weight", torch.bfloat16)
@@ -534,8 +534,8 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
     features = weight.shape[0]
     if weight.shape[1] != K or not skinny_gemm_supported(tokens, K) or out_dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"skinny_gemm: tokens {tokens} (1..256), K {K} (a multiple of 8) or output {out_dtype} not supported")
-    if slices is not None and not 1 <= slices <= 8:
-        raise KernelError("skinny_gemm: 1 to 8 K slices")
+    if slices is not None and not 1 <= slices <= 16:
+        raise KernelError("skinny_gemm: 1 to 16 K slices")
     if slices is None:
         slices = skinny_gemm_slices(tokens, features, K)
     if out is None:

@@ -399,7 +399,7 @@ def test_skinny_gemm(tokens, features, K, out_dtype):
     w = rnd(features, K, dtype=torch.bfloat16, seed=features, scale=0.1)
     want = (x.double() @ w.double().T).cpu().numpy()
     scale = np.abs(want).max()
-    for slices in (None, 1, 2, 5, 8):
+    for slices in (None, 1, 2, 5, 8, 13, 16):
         for _ in range(2):
             got = ops.skinny_gemm(x, w, out_dtype, slices)
             assert got.dtype == out_dtype and tuple(got.shape) == (tokens, features)
