@@ -485,7 +485,8 @@ namespace {
 
 constexpr int DN = 16;                 // keys per tile of one warp
 constexpr int DWARPS = 4;
-constexpr int CLUSTER_SPLITS_MAX = 8;
+constexpr int CLUSTER_SPLITS_MAX = 16;  // the largest cluster of this GPU (more than 8 is the kernel's opt-in)
+constexpr int CLUSTER_ROWS_MAX = 23;    // rows of partial results that may arrive at one CTA
 
 // Sizes that depend on the head size HD (64 or 128).  A row of keys or values is HD * 2 bytes; the
 // 128-byte swizzle covers 64 elements, so a tile of 16 rows lies in shared memory as HD / 64 slabs of
@@ -499,11 +500,11 @@ struct DecodeCfg {
   static constexpr int STAGES = HD == 64 ? 3 : 2;
   static constexpr int QROW = HD * 2 + 16;              // padded query rows (read once)
   // Splits merged inside a cluster: row r of the 16 belongs to CTA (r mod splits); every CTA pushes its
-  // partial (sums[HD], maximum, denominator) of a row into the owner's memory.  At most 16 + 7 rows arrive
-  // at one CTA (splits * ceil(16 / splits)).  The region starts where the query rows lay: they are in
-  // registers by then.
+  // partial (sums[HD], maximum, denominator) of a row into the owner's memory: splits * ceil(rows / splits)
+  // rows arrive at one CTA, and the launcher merges in the cluster only if that is at most
+  // CLUSTER_ROWS_MAX.  The region starts where the query rows lay: they are in registers by then.
   static constexpr int RECV_ROW = HD + 2;
-  static constexpr int RECV_BYTES = (16 + CLUSTER_SPLITS_MAX - 1) * RECV_ROW * 4;
+  static constexpr int RECV_BYTES = CLUSTER_ROWS_MAX * RECV_ROW * 4;
   static constexpr int SMEM = 1024 + DWARPS * STAGES * 2 * TILE + RECV_BYTES + DWARPS * STAGES * 8 + 64;
   static_assert(RECV_BYTES >= 16 * QROW, "the received partial results lie over the query rows");
   static_assert(DWARPS * 16 * (HD + 2) * 4 <= DWARPS * STAGES * 2 * TILE, "the merge buffer reuses the key/value stages");
@@ -767,7 +768,7 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
   const bool bad = *failed != 0;
   if (bad && !p.cluster_merge) return;
   float* recv = reinterpret_cast<float*>(sQ);  // [split][owned row][sums | maximum | denominator]
-  const int owned_max = (16 + p.splits - 1) / p.splits;
+  const int owned_max = (nheads + p.splits - 1) / p.splits;
   if (p.cluster_merge) cluster_wait();  // every CTA of the cluster has its query in registers: the region may be written
   for (int idx = tid; idx < nheads * D; idx += DWARPS * 32) {
     const int r = idx / D, dcol = idx - r * D;
@@ -863,11 +864,19 @@ bool make_decode_map(CUtensorMap* map, const void* base, long long rows, int box
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// whether the key splits of these sizes merge inside one cluster (else: scratch and the merge kernel)
+bool merges_in_cluster(int nh, int nkv, int splits) {
+  const int G = nh / nkv, rows = G < 16 ? G : 16;
+  // (clusters of 9 to 15 CTAs were measured slower than 8 splits, or than more splits and the merge kernel)
+  return splits > 1 && (splits <= 8 || splits == CLUSTER_SPLITS_MAX) && splits * ((rows + splits - 1) / splits) <= CLUSTER_ROWS_MAX;
+}
+
 template <int HD>
 int launch_decode(const CUtensorMap& map_k, const CUtensorMap& map_v, const DecodeParams& p, int num_seqs, int first_row, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<HD>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -884,7 +893,7 @@ int launch_decode(const CUtensorMap& map_k, const CUtensorMap& map_v, const Deco
 }  // namespace
 
 // Attention of num_seqs single-token sequences (head size 64 or 128; page size a multiple of 8, and
-// of 16 if larger than 8).  Up to 8 splits are one cluster and merge on the chip; more go through
+// of 16 if larger than 8).  Up to 16 splits are one cluster and merge on the chip; more go through
 // part_acc / part_ml (scratch, as for dli_paged_attention_mma) and a second kernel.
 DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                     long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
@@ -912,10 +921,12 @@ DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride
   p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.window = window; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.part_acc = part_acc; p.part_ml = part_ml; p.error_flag = error_flag_device;
-  p.cluster_merge = splits > 1 && splits <= CLUSTER_SPLITS_MAX;
+  p.cluster_merge = merges_in_cluster(nh, nkv, splits);
   return head_dim == 64 ? launch_decode<64>(map_k, map_v, p, num_seqs, first_row, stream)
                         : launch_decode<128>(map_k, map_v, p, num_seqs, first_row, stream);
 }
+
+DLI_EXPORT int dli_decode_tma_merges_in_cluster(int nh, int nkv, int splits) { return merges_in_cluster(nh, nkv, splits) ? 1 : 0; }
 
 // 0, or the code of the first bounded wait that ran out (11 keys, 12 scores, 13 output tile, 14 values,
 // 15 probabilities, 16 output tile read; 21: a decode warp's keys and values)

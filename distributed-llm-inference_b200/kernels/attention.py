@@ -50,8 +50,13 @@ def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_s
     tma = ops.decode_tma_supported(head_dim, page_size)
     wave = (ONE_WAVE_TMA if head_dim <= 64 else ONE_WAVE_TMA // 2) if tma else ONE_WAVE
     splits = choose_splits(num_seqs, ctas_per_seq, max_kv_len, wave, fill_last_wave=not tma)
-    if tma and splits > CLUSTER_SPLITS_MAX and max_kv_len <= CLUSTER_SPLITS_KV_LIMIT:
-        splits = CLUSTER_SPLITS_MAX  # merged on the chip by one cluster: measured faster than more splits and a merge kernel
+    if tma and max_kv_len <= CLUSTER_SPLITS_KV_LIMIT:
+        # short contexts: a split count that one cluster merges on the chip (up to 8 CTAs, or 16) is faster than
+        # a few more splits and a merge kernel
+        if splits > CLUSTER_SPLITS_MAX:
+            splits = CLUSTER_SPLITS_MAX
+        elif 8 < splits < CLUSTER_SPLITS_MAX:
+            splits = 8
     return splits
 
 

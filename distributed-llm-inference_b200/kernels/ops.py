@@ -19,7 +19,7 @@ DT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 # number of this package's kernels launched since import (a graph replay adds its node count)
 launch_count = 0
-DECODE_TMA_CLUSTER_SPLITS = 8  # CLUSTER_SPLITS_MAX of csrc/attention_tc.cu
+DECODE_TMA_CLUSTER_SPLITS = 16  # CLUSTER_SPLITS_MAX of csrc/attention_tc.cu
 
 
 class KernelError(RuntimeError):
@@ -357,8 +357,8 @@ def paged_decode_tma(
         "paged_decode_tma",
     )
     global launch_count
-    if splits > DECODE_TMA_CLUSTER_SPLITS:
-        launch_count += 1  # the merge kernel; up to that many splits merge inside the kernel, as one cluster
+    if splits > 1 and not _fn("attention_tc.cu", "dli_decode_tma_merges_in_cluster", [c_int, c_int, c_int])(num_heads, nkv, splits):
+        launch_count += 1  # the merge kernel; otherwise the splits merge inside the kernel, as one cluster
 
 
 def paged_prefill_tc_error() -> int:
