@@ -10,15 +10,15 @@
 //   * two threads share a row: each reads 64 of its 128 scores with tcgen05.ld, masks by absolute
 //     position, keeps running maximum and sum in float32 (the halves meet through shared memory
 //     once per tile), and writes its probabilities as bfloat16 into a swizzled shared-memory tile;
-//   * O_tile = P V is a second group of tcgen05.mma (V is the MN-major operand, exactly as it
-//     lies in the pages); the thread reads its row of O_tile and folds it into its float32
-//     accumulator with the usual rescaling.
+//   * O += P V is a second group of tcgen05.mma (V is the MN-major operand, exactly as it lies in
+//     the pages), accumulated in tensor memory over all tiles; the threads rescale it in place only
+//     when a row's maximum has grown by more than 2^8, and read it once, at the end.
 //
-// One warp issues the copies, one the matrix products; they meet each other and the softmax threads on mbarriers only.
-// Keys, values, scores, probabilities and the output tile are double-buffered, so the tensor cores
-// work one tile ahead of the softmax (one CTA per SM, 512 columns of tensor memory).  Every mbarrier
-// wait is bounded: after WAIT_LIMIT polls the kernel sets *error_flag, stops using the tensor
-// cores, frees its tensor memory and returns.
+// One warp issues the copies, one the matrix products; they meet each other and the softmax threads on
+// mbarriers only.  Keys, values, scores and probabilities are double-buffered, so the tensor cores work
+// one tile ahead of the softmax (one CTA per SM, 512 columns of tensor memory).  Every mbarrier wait is
+// bounded: after WAIT_LIMIT polls the kernel sets *error_flag, stops using the tensor cores, frees its
+// tensor memory and returns.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -92,6 +92,16 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
       : "r"(taddr));
 }
 
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+      "%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -120,14 +130,15 @@ __device__ __forceinline__ bool wait_or_fail(uint32_t bar, uint32_t parity, vola
 // read the same 32 lanes of tensor memory: the lane group is the warp index modulo 4).  Warp 8 issues
 // every tcgen05.mma from its first lane; warp 9 issues every TMA copy, one page per lane.
 //
-// Everything a tile needs exists twice (key and value stages, the scores S and the output tile in
-// tensor memory, the probabilities P in shared memory), indexed by the tile's parity, so the tensor
-// cores run one tile ahead of the softmax: S(i + 1) = Q K(i + 1)^T is issued as soon as the threads
-// have read S(i - 1), and while they work on tile i the product P(i - 1) V(i - 1) finishes; a thread
-// folds that output tile into its accumulator after it has handed in P(i).  The two sides meet on
-// mbarriers only (two of each, by parity):
+// Keys, values, the scores S (tensor memory) and the probabilities P (shared memory) exist twice,
+// indexed by the tile's parity, so the tensor cores run one tile ahead of the softmax: S(i + 1) =
+// Q K(i + 1)^T is issued as soon as the threads have read S(i - 1).  The output accumulates in tensor
+// memory over all tiles: O += P(i) V(i).  The probabilities of a row are scaled by a reference maximum
+// that follows the row's running maximum only when that has grown by more than 2^8; only then the
+// threads multiply their part of O by 2^(old - new) in place (tcgen05.ld / tcgen05.st), which after the
+// first tiles is rare.  The sides meet on mbarriers only (two of each, by parity):
 //   k_full, v_full   TMA -> controller            s_done, o_done   MMA -> softmax threads
-//   p_ready (256)    P written, S read            o_read (256)     output tile read
+//   p_ready (256)    P written, output rescaled, S read
 __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                       const __grid_constant__ CUtensorMap map_v, const Params p) {
   pdl_launch_dependents();
@@ -138,14 +149,14 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
   unsigned char* sV = sK + 2 * TILE_BYTES;      // two stages
   unsigned char* sP = sV + 2 * TILE_BYTES;      // two buffers of (keys 0..63 | keys 64..127)
   float* row_max = (float*)(sP + 4 * TILE_BYTES);   // [2 (tile parity)][2 (half)][128]: each half's maximum of the tile, at the end its sum
-  uint64_t* bars = (uint64_t*)(row_max + 4 * ROWS);  // k_full[2], v_full[2], s_done[2], o_done[2], p_ready[2], o_read[2]
-  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+  uint64_t* bars = (uint64_t*)(row_max + 4 * ROWS);  // k_full[2], v_full[2], s_done[2], o_done[2], p_ready[2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 10);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = tid & (ROWS - 1), half = (tid >> 7) & 1;
   const uint32_t k_full = smem_u32(bars), v_full = smem_u32(bars + 2), s_done = smem_u32(bars + 4), o_done = smem_u32(bars + 6),
-                 p_ready = smem_u32(bars + 8), o_read = smem_u32(bars + 10);
+                 p_ready = smem_u32(bars + 8);
 
   const int s = p.seq0 + blockIdx.y;
   const int tile = gridDim.x - 1 - blockIdx.x;  // the last tokens see the most keys: their CTAs start first
@@ -169,7 +180,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
 
   if (tid == 0) {
     for (int i = 0; i < 8; ++i) mbar_init(k_full + 8 * i, 1);  // k_full, v_full, s_done, o_done
-    for (int i = 0; i < 4; ++i) mbar_init(p_ready + 8 * i, SOFTMAX_THREADS);  // p_ready, o_read
+    for (int i = 0; i < 2; ++i) mbar_init(p_ready + 8 * i, SOFTMAX_THREADS);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -258,14 +269,14 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
         const int b = it & 1, par = (it >> 1) & 1;
         // S(it + 1): its buffer held S(it - 1), which every thread had read when p_ready(it - 1) was seen (last iteration)
         if (it + 1 < num_tiles) qk(it + 1);
-        // O_tile(it) = P(it) V(it): the probabilities are written, the values have arrived, the output tile it - 2 was read
-        if (wait_or_fail(p_ready + 8 * b, par, failed, 15, p.error_flag) && wait_or_fail(v_full + 8 * b, par, failed, 14, p.error_flag) &&
-            (it < 2 || wait_or_fail(o_read + 8 * b, ((it - 2) >> 1) & 1, failed, 16, p.error_flag))) {
+        // O += P(it) V(it): the probabilities are written (and the output rescaled where a row's maximum grew),
+        // the values have arrived.  The output stays in tensor memory over all tiles.
+        if (wait_or_fail(p_ready + 8 * b, par, failed, 15, p.error_flag) && wait_or_fail(v_full + 8 * b, par, failed, 14, p.error_flag)) {
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a = smem_u32(sP + b * 2 * TILE_BYTES), v = smem_u32(sV + b * TILE_BYTES);
 #pragma unroll
           for (int k = 0; k < KEYS / 16; ++k)
-            umma(tmem_o + b * D, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(v + k * 2048), idesc_o, k != 0);
+            umma(tmem_o, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(v + k * 2048), idesc_o, (it | k) != 0);
           umma_commit(o_done + 8 * b);
         }
       }
@@ -278,30 +289,17 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
     const int rpos = pos0 + rtok;
     const uint32_t lane_bits = (uint32_t)((warp & 3) * 32) << 16;
     const int col0 = half * 64;
-    float m = -CUDART_INF_F, l = 0.f;  // m: running maximum of the raw scores; l: this half's share of the row sum
-    float corr_prev = 1.f;             // the factor that goes with the output tile not yet folded in
-    float o[32];                       // output columns 32 * half .. 32 * half + 31 of the row
-#pragma unroll
-    for (int j = 0; j < 32; ++j) o[j] = 0.f;
+    // m: running maximum of the row's raw scores; m_ref: the maximum that the probabilities and the output
+    // are scaled by at present; l: this half's share of the row sum (in that scale).  m_ref follows m only
+    // when m has grown by more than RESCALE_STEP (in powers of two): the output, which accumulates in
+    // tensor memory over all tiles, then has to be multiplied by 2^(old - new), and that is rare after the
+    // first tiles.  Probabilities thus reach at most 2^RESCALE_STEP, which bfloat16 and the float32 sums hold
+    // with the same relative precision.
+    constexpr float RESCALE_STEP = 8.f;
+    float m = -CUDART_INF_F, m_ref = -CUDART_INF_F, l = 0.f;
     bool ok = true;
     const int group = r >> 6;  // rows 0..63 (warps 0, 1, 4, 5) and rows 64..127 (warps 2, 3, 6, 7)
-
-    uint32_t ov[32];  // the output tile being folded in: asked for before the probabilities are computed, used after
-    auto fold_begin = [&](int t) {
-      const int b = t & 1;
-      ok = wait_or_fail(o_done + 8 * b, (t >> 1) & 1, failed, 13, p.error_flag) && ok;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (ok) tmem_ld32_nowait(tmem_o + b * D + lane_bits + half * 32, ov);  // (uniform: every thread waits on the same barriers)
-    };
-    auto fold_end = [&](int t, float corr) {  // o = o * corr + O_tile(t)
-      if (ok) {
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], corr, __uint_as_float(ov[j]));
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(o_read + 8 * (t & 1));
-    };
+    const uint32_t my_o = tmem_o + lane_bits + half * 32;  // output columns 32 * half .. 32 * half + 31 of the row
 
     for (int it = 0; it < num_tiles; ++it) {
       const int b = it & 1;
@@ -345,13 +343,33 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
       rm[half * ROWS + r] = fmaxf(mx[0], mx[4]);
       if (group == 0) asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS / 2) : "memory");  // the two halves of this row's 64-row group
       else asm volatile("bar.sync 2, %0;" ::"n"(SOFTMAX_THREADS / 2) : "memory");
-      const float mnew = fmaxf(m, fmaxf(rm[r], rm[ROWS + r]));
-      const float msafe = (mnew == -CUDART_INF_F) ? 0.f : mnew;
-      const float corr = ex2((m - msafe) * p.scale_log2);
-      const float neg = -msafe * p.scale_log2;
-      m = mnew;
-      // ---- probabilities, their sum, and the bfloat16 tile for the P V product.  P's buffer was read by
-      //      P V of tile it - 2, whose output this thread folded in an iteration ago.
+      m = fmaxf(m, fmaxf(rm[r], rm[ROWS + r]));
+      float corr = 1.f;
+      const bool grown = (m - m_ref) * p.scale_log2 > RESCALE_STEP;  // also the first finite maximum (m_ref = -inf)
+      if (grown) {
+        corr = (m_ref == -CUDART_INF_F) ? 0.f : ex2((m_ref - m) * p.scale_log2);  // nothing finite was accumulated before
+        m_ref = m;
+      }
+      const float neg = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref * p.scale_log2;
+      // P's buffer was read by the product of tile it - 2
+      if (it >= 2) ok = wait_or_fail(o_done + 8 * b, ((it - 2) >> 1) & 1, failed, 13, p.error_flag) && ok;
+      // the output so far, multiplied by 2^(old - new) in the rows whose reference moved (the whole warp
+      // reads and writes tensor memory together, rows that did not move with factor 1)
+      if (it > 0 && __any_sync(0xffffffffu, grown)) {
+        ok = wait_or_fail(o_done + 8 * (b ^ 1), ((it - 1) >> 1) & 1, failed, 13, p.error_flag) && ok;  // the product of tile it - 1 has finished
+        ok = __all_sync(0xffffffffu, ok);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+          uint32_t v[32];
+          tmem_ld32_nowait(my_o, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+          tmem_st32(my_o, v);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      // ---- probabilities, their sum, and the bfloat16 tile for the P V product
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
       unsigned char* prow = sP + b * 2 * TILE_BYTES + half * TILE_BYTES + r * 128;
       // in three sweeps, so that the 64 exponentials follow each other without waiting for anything
@@ -373,17 +391,23 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
       l = l * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor cores
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(p_ready + 8 * b);  // P is written and S has been read: the controller may issue P V and the Q K^T of tile it + 2
+      mbar_arrive(p_ready + 8 * b);  // P is written, the output rescaled and S read: P V and the Q K^T of tile it + 2 may be issued
 
-      if (it > 0) {  // that product ran while this tile's probabilities were computed
-        fold_begin(it - 1);
-        fold_end(it - 1, corr_prev);
-      }
-      corr_prev = corr;
     }
-    if (num_tiles > 0) {
-      fold_begin(num_tiles - 1);
-      fold_end(num_tiles - 1, corr_prev);
+    // ---- the finished output, once the last product is done
+    float o[32];
+    ok = wait_or_fail(o_done + 8 * ((num_tiles - 1) & 1), ((num_tiles - 1) >> 1) & 1, failed, 13, p.error_flag) && ok;
+    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      uint32_t v[32];
+      tmem_ld32_nowait(my_o, v);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(v[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o[j] = 0.f;
     }
 
     // ---- the row sum is the two halves' sums; each half writes its 32 output columns

@@ -119,10 +119,12 @@ def test_silu_mul(dtype):
 # ------------------------------------------------------------------ attention
 
 
-def attention_case(nh, nkv, d, page, seqs, dtype, seed=0, sharp=None):
+def attention_case(nh, nkv, d, page, seqs, dtype, seed=0, sharp=None, ramp=0.0):
     """seqs: [(start, q_len)].  Builds pools with shuffled pages, tables whose unused entries
     point at a poisoned page (NaN: a stray read shows without faulting), qkv rows, and the plain
-    result.  sharp = (seq, token, key): that query and key are scaled so the score stands out."""
+    result.  sharp = (seq, token, key): that query and key are scaled so the score stands out.
+    ramp: every query gets a component along one direction and key u one of ramp * u along it, so
+    scores grow with the key's position and a row's maximum rises from tile to tile."""
     rng = np.random.default_rng(seed)
     kv_lens = [s + q for s, q in seqs]
     blocks = [-(-k // page) for k in kv_lens]
@@ -143,6 +145,12 @@ def attention_case(nh, nkv, d, page, seqs, dtype, seed=0, sharp=None):
         direction /= np.linalg.norm(direction)
         Q[si][ti] = direction * 6.0 * math.sqrt(math.sqrt(d))
         K[si][ki] = direction * 6.0 * math.sqrt(math.sqrt(d))
+    if ramp:
+        direction = rng.standard_normal(d)
+        direction /= np.linalg.norm(direction)
+        for i in range(len(seqs)):
+            Q[i] = 0.3 * Q[i] + direction * math.sqrt(d)
+            K[i] = 0.3 * K[i] + direction[None, None, :] * (ramp * np.arange(kv_lens[i]))[:, None, None]
     tt = torch.float32 if dtype == torch.float32 else torch.bfloat16
     cast = lambda a: torch.from_numpy(a).to(tt)
     K, V, Q = [[cast(a) for a in L] for L in (K, V, Q)]
@@ -263,6 +271,21 @@ def test_paged_decode_tma(nh, nkv, page, window, splits, d):
         scratch = (torch.full((len(seqs) * nh * splits * d,), float("nan"), device=DEV), torch.full((len(seqs) * nh * splits * 2,), float("nan"), device=DEV))
     ops.paged_decode_tma(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(seqs), 0, nh, d**-0.5, window, splits, scratch)
     want = plain_attention(t, seqs, nh, window)
+    np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2))
+    assert ops.paged_prefill_tc_error() == 0
+
+
+@pytest.mark.parametrize("ramp", [0.02, 0.3])
+def test_prefill_tc_when_row_maxima_keep_rising(ramp):
+    """Scores that grow with the key's position: the row maxima rise by a little (0.02: about four powers
+    of two per tile, below the kernel's step for rescaling its accumulated output) or by a lot (0.3: about
+    55 per tile, a rescaling at every tile)."""
+    nh, nkv, d, page = 8, 2, 64, 16
+    seqs = [(0, 700), (300, 260), (1000, 3)]
+    t = attention_case(nh, nkv, d, page, seqs, torch.bfloat16, seed=5, ramp=ramp)
+    out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_prefill_tc(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(seqs), max(q for _, q in seqs), nh, d**-0.5, None)
+    want = plain_attention(t, seqs, nh, None)
     np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2))
     assert ops.paged_prefill_tc_error() == 0
 
