@@ -434,6 +434,316 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
+// ================================================================ two query tiles per CTA
+// The same products, arranged so that the special-function units (16 exponentials per clock per SM,
+// a quarter of them per scheduler) never wait: a CTA owns two query tiles of 128 rows, A and B, that
+// read the same keys and values.  A row belongs to one thread (warps 0..3: tile A, warps 4..7: tile B;
+// a scheduler holds one warp of each), which reads its 128 scores into registers at once, so a
+// tile's S is free for the next product at once, and needs no other thread for its maximum.  The two
+// groups take turns at the exponentials (named barriers): while A computes its probabilities, B
+// reads scores, takes maxima, rescales its output and hands in P, and the other way round.  The
+// warp that issues the matrix products serves whichever product has become possible.
+//   k_full, v_full [2]     TMA -> products              k_free, v_free [2]   products done -> TMA
+//   s_done [A, B]          S there                      s_read [A, B] (128)  S in registers
+//   p_ready [A, B] (128)   P written, output rescaled   o_done [A, B]        O += P V finished
+constexpr int T2_THREADS = 2 * ROWS + 128;  // two softmax warpgroups and one of which two warps work (products, copies): whole warpgroups trade registers
+constexpr int T2_SMEM = TILE_BYTES * (2 + 2 + 2 + 4) + 256 + 1024;  // Q x2, K x2, V x2, P x2 (two halves each), barriers, alignment
+
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+
+__global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                         const __grid_constant__ CUtensorMap map_v, const Params p) {
+  pdl_launch_dependents();
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sQ = smem;                     // tile A, tile B
+  unsigned char* sK = sQ + 2 * TILE_BYTES;      // two stages
+  unsigned char* sV = sK + 2 * TILE_BYTES;      // two stages
+  unsigned char* sP = sV + 2 * TILE_BYTES;      // per query tile (keys 0..63 | keys 64..127)
+  uint64_t* bars = (uint64_t*)(sP + 4 * TILE_BYTES);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+  volatile int* failed = (volatile int*)(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t k_full = smem_u32(bars), v_full = smem_u32(bars + 2), k_free = smem_u32(bars + 4), v_free = smem_u32(bars + 6),
+                 s_done = smem_u32(bars + 8), s_read = smem_u32(bars + 10), p_ready = smem_u32(bars + 12), o_done = smem_u32(bars + 14);
+
+  const int s = p.seq0 + blockIdx.y;
+  const int tile = gridDim.x - 1 - blockIdx.x;  // the last tokens see the most keys: their CTAs start first
+  const int kvh = blockIdx.z / p.head_chunks, hc = blockIdx.z - kvh * p.head_chunks;
+  const int q0 = p.q_start[s];
+  const int qlen = p.q_start[s + 1] - q0;
+  const int tpt = p.tokens_per_tile;
+  const int tok0 = tile * 2 * tpt;
+  if (tok0 >= qlen) return;  // the whole CTA: nothing was set up yet
+  const int kvlen = p.kv_len[s];
+  const int ntok = min(2 * tpt, qlen - tok0);  // tokens of both tiles
+  const int G = p.nh / p.nkv, Gc = p.heads_per_chunk;
+  const int head0 = kvh * G + hc * Gc;
+  const int nheads = min(Gc, G - hc * Gc);
+  const int pos0 = kvlen - qlen + tok0;
+  const int* table = p.block_tables + (size_t)s * p.max_blocks;
+  const int hi = pos0 + ntok;
+  const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+  const int t_begin = lo / KEYS, t_end = (hi + KEYS - 1) / KEYS;
+  const int num_tiles = t_end - t_begin;  // both query tiles walk all of them (the later tile sees at most one more)
+
+  if (tid == 0) {
+    for (int i = 0; i < 10; ++i) mbar_init(k_full + 8 * i, 1);  // k_full, v_full, k_free, v_free, s_done
+    for (int i = 10; i < 14; ++i) mbar_init(k_full + 8 * i, ROWS);  // s_read, p_ready
+    for (int i = 14; i < 16; ++i) mbar_init(k_full + 8 * i, 1);  // o_done
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pdl_wait();  // queries and the cache are the work of the kernels before this one
+
+  // ---- both Q tiles, swizzled by hand (rows beyond the used ones are zero); the value stages start as zeros
+  for (int idx = tid; idx < 2 * ROWS * 8; idx += T2_THREADS) {
+    const int rr = idx >> 3, c = idx & 7;  // rr: row among the 256 of both tiles
+    const int rt = rr & (ROWS - 1), tok = (rr >> 7) * tpt + rt / Gc, hd = rt % Gc;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (rt / Gc < tpt && tok < ntok && hd < nheads)
+      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + tok0 + tok) * p.q_stride + (size_t)(head0 + hd) * D + c * 8);
+    *reinterpret_cast<uint4*>(sQ + rr * 128 + ((c ^ (rr & 7)) << 4)) = v;
+  }
+  for (int idx = tid; idx < 2 * TILE_BYTES / 16; idx += T2_THREADS) reinterpret_cast<uint4*>(sV)[idx] = make_uint4(0, 0, 0, 0);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 2 * KEYS;  // S of A, S of B, O of A, O of B
+
+  // The softmax threads hold a row of 128 scores in registers; the third warpgroup needs few and gives its
+  // share away (a scheduler then holds two warps of 224 registers and one of 40).
+  if (warp >= 2 * ROWS / 32) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp == 2 * ROWS / 32 + 1) {
+    // ================================================================ the warp that copies
+    const int pages = KEYS / p.page_size;
+    const int page_i = lane & 15;
+    auto lookup = [&](int t) -> int {
+      const int first = t * KEYS + page_i * p.page_size;
+      const bool need = t < t_end && page_i < pages && first < hi && first + p.page_size > lo;
+      return need ? table[first / p.page_size] : -1;
+    };
+    auto issue = [&](bool keys, int stage, int page) {
+      const uint32_t bar = (keys ? k_full : v_full) + 8 * stage;
+      unsigned char* dst = (keys ? sK : sV) + stage * TILE_BYTES;
+      const unsigned side = keys ? 0x0000ffffu : 0xffff0000u;
+      const int count = __popc(__ballot_sync(side, page >= 0));
+      if (page_i == 0) mbar_expect_tx(bar, (uint32_t)(count * p.page_size * 128));
+      __syncwarp(side);
+      if (page >= 0) tma_load_2d(smem_u32(dst + page_i * p.page_size * 128), keys ? &map_k : &map_v, 0, (page * p.nkv + kvh) * p.page_size, bar);
+    };
+    int page = lookup(t_begin);
+    for (int t = 0; t < num_tiles && !*failed; ++t) {
+      const int st = t & 1, par = ((t - 2) >> 1) & 1;
+      const int cur = page;
+      page = lookup(t_begin + t + 1);
+      if (t >= 2) {
+        if (lane == 0) wait_or_fail(k_free + 8 * st, par, failed, 12, p.error_flag);
+        __syncwarp();
+        if (*failed) break;
+      }
+      if (lane < 16) issue(true, st, cur);
+      if (t >= 2) {
+        if (lane == 0) wait_or_fail(v_free + 8 * st, par, failed, 13, p.error_flag);
+        __syncwarp();
+        if (*failed) break;
+      }
+      if (lane >= 16) issue(false, st, cur);
+    }
+  } else if (warp == 2 * ROWS / 32) {
+    // ================================================================ the warp that issues the matrix products (its first lane)
+    if (lane == 0) {
+      const uint32_t idesc_s = instr_desc(ROWS, KEYS, 0), idesc_o = instr_desc(ROWS, D, 1);
+      int next_qk[2] = {0, 0}, next_pv[2] = {0, 0};
+      unsigned spins = 0;
+      while ((next_pv[0] < num_tiles || next_pv[1] < num_tiles) && !*failed) {
+        bool progress = false;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          // S_q(t) = Q_q K(t)^T: the keys are there and the thread of every row has S_q(t - 1) in registers
+          int t = next_qk[q];
+          if (t < num_tiles && mbar_test(k_full + 8 * (t & 1), (t >> 1) & 1) && (t == 0 || mbar_test(s_read + 8 * q, (t - 1) & 1))) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a = smem_u32(sQ + q * TILE_BYTES), k = smem_u32(sK + (t & 1) * TILE_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) umma(tmem_s + q * KEYS, smem_desc_sw128(a + kk * 32), smem_desc_sw128(k + kk * 32), idesc_s, kk != 0);
+            umma_commit(s_done + 8 * q);
+            next_qk[q] = t + 1;
+            if (next_qk[q ^ 1] > t) umma_commit(k_free + 8 * (t & 1));  // both tiles' products with K(t) are issued
+            progress = true;
+          }
+          // O_q += P_q(t) V(t)
+          t = next_pv[q];
+          if (t < num_tiles && mbar_test(p_ready + 8 * q, t & 1) && mbar_test(v_full + 8 * (t & 1), (t >> 1) & 1)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a = smem_u32(sP + q * 2 * TILE_BYTES), v = smem_u32(sV + (t & 1) * TILE_BYTES);
+#pragma unroll
+            for (int k = 0; k < KEYS / 16; ++k)
+              umma(tmem_o + q * D, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(v + k * 2048), idesc_o, (t | k) != 0);
+            umma_commit(o_done + 8 * q);
+            next_pv[q] = t + 1;
+            if (next_pv[q ^ 1] > t) umma_commit(v_free + 8 * (t & 1));  // both tiles' products with V(t) are issued
+            progress = true;
+          }
+        }
+        if (progress) spins = 0;
+        else if (++spins > WAIT_LIMIT) {
+          *failed = 17;
+          atomicExch(p.error_flag, 17);
+        }
+      }
+    }
+    __syncwarp();
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    // ================================================================ softmax threads: one per row
+    const int q = warp >> 2;                 // query tile A or B
+    const int r = tid & (ROWS - 1);          // row of the tile
+    const int rtok = q * tpt + r / Gc;       // token among the CTA's
+    const bool rvalid = rtok < ntok && (r % Gc) < nheads && r / Gc < tpt;
+    const int rpos = pos0 + rtok;
+    const uint32_t lane_bits = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t my_s = tmem_s + q * KEYS + lane_bits, my_o = tmem_o + q * D + lane_bits;
+    const uint32_t my_s_done = s_done + 8 * q, my_s_read = s_read + 8 * q, my_p_ready = p_ready + 8 * q, my_o_done = o_done + 8 * q;
+    constexpr float RESCALE_STEP = 8.f;
+    float m = -CUDART_INF_F, m_ref = -CUDART_INF_F, l = 0.f;
+    bool ok = true;
+    const int first_pos = pos0 + q * tpt;  // position of the tile's first row
+    if (q == 1 && num_tiles > 0) asm volatile("bar.arrive 1, %0;" ::"n"(2 * ROWS) : "memory");  // tile A takes the first turn
+
+    for (int t = 0; t < num_tiles; ++t) {
+      const int base = (t_begin + t) * KEYS;
+      ok = wait_or_fail(my_s_done, t & 1, failed, 12, p.error_flag) && ok;
+      ok = __all_sync(0xffffffffu, ok);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float sc[128];
+      if (ok) {
+#pragma unroll
+        for (int c = 0; c < 128; c += 64) {
+          uint32_t v0[32], v1[32];
+          tmem_ld32_nowait(my_s + c, v0);
+          tmem_ld32_nowait(my_s + c + 32, v1);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { sc[c + j] = __uint_as_float(v0[j]); sc[c + 32 + j] = __uint_as_float(v1[j]); }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 128; ++j) sc[j] = -CUDART_INF_F;
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(my_s_read);  // S is in registers: the next product of this tile may overwrite it
+      // a tile that lies wholly at or before the first row's position, inside every row's window, needs no mask
+      const bool full = base + KEYS - 1 <= first_pos && base >= lo && p.window <= 0;
+      if (ok && !full) {
+        const int hi_j = rpos - base, lo_j = p.window > 0 ? rpos - p.window - base : -1;
+#pragma unroll
+        for (int j = 0; j < 128; ++j) sc[j] = (j <= hi_j && j > lo_j) ? sc[j] : -CUDART_INF_F;
+      }
+      float mx[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx[j] = sc[j];
+#pragma unroll
+      for (int j = 8; j < 128; ++j) mx[j & 7] = fmaxf(mx[j & 7], sc[j]);
+      m = fmaxf(m, fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))));
+      float corr = 1.f;
+      const bool grown = (m - m_ref) * p.scale_log2 > RESCALE_STEP;  // also the first finite maximum (m_ref = -inf)
+      if (grown) {
+        corr = (m_ref == -CUDART_INF_F) ? 0.f : ex2((m_ref - m) * p.scale_log2);
+        m_ref = m;
+      }
+      const float neg = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref * p.scale_log2;
+      // P and O of this tile are free once its product of the key tile before has finished
+      if (t > 0) {
+        ok = wait_or_fail(my_o_done, (t - 1) & 1, failed, 13, p.error_flag) && ok;
+        ok = __all_sync(0xffffffffu, ok);
+        if (__any_sync(0xffffffffu, grown)) {  // the output so far times 2^(old - new) in the rows whose reference moved
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (ok) {
+#pragma unroll
+            for (int c = 0; c < D; c += 32) {
+              uint32_t v[32];
+              tmem_ld32_nowait(my_o + c, v);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+              tmem_st32(my_o + c, v);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          }
+        }
+      }
+      // ---- this group's turn at the exponentials (measured: 562 us at 8,192 tokens with turns, 694 without)
+      if (q == 0) asm volatile("bar.sync 1, %0;" ::"n"(2 * ROWS) : "memory");
+      else asm volatile("bar.sync 2, %0;" ::"n"(2 * ROWS) : "memory");
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned char* prow = sP + q * 2 * TILE_BYTES + r * 128;
+#pragma unroll
+      for (int j = 0; j < 128; j += 8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const float p0 = ex2(fmaf(sc[j + e], p.scale_log2, neg));  // masked: ex2(-inf) = 0
+          const float p1 = ex2(fmaf(sc[j + e + 1], p.scale_log2, neg));
+          sum[(e >> 1) & 3] += p0 + p1;
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+          packed[e >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+        }
+        *reinterpret_cast<uint4*>(prow + (j >> 6) * TILE_BYTES + ((((j >> 3) & 7) ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+      if (q == 0) asm volatile("bar.arrive 2, %0;" ::"n"(2 * ROWS) : "memory");
+      else if (t + 1 < num_tiles) asm volatile("bar.arrive 1, %0;" ::"n"(2 * ROWS) : "memory");
+      l = l * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor cores
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(my_p_ready);
+    }
+    // ---- the finished row, once the last product is done
+    ok = wait_or_fail(my_o_done, (num_tiles - 1) & 1, failed, 13, p.error_flag) && ok;
+    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const float inv = 1.f / l;
+    const size_t row = (size_t)(q0 + tok0 + rtok) * p.nh + head0 + (r % Gc);
+#pragma unroll
+    for (int c = 0; c < D; c += 32) {
+      uint32_t v[32];
+      if (ok) {
+        tmem_ld32_nowait(my_o + c, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      }
+      if (ok && !*failed && rvalid) {
+        uint4* dst = reinterpret_cast<uint4*>(p.out + row * D + c);
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 w;
+          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]) * inv, __uint_as_float(v[j + 2 * e + 1]) * inv);
+          dst[j >> 3] = w;
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -466,10 +776,11 @@ int* error_flag_host = nullptr;
 
 // Sequences [seq0, seq0 + num_seqs) of a batch, each bringing at most max_q_len tokens.
 // Head size 64 only; page_size must be 8, 16, 32, 64 or 128; num_pages is the pools' first extent.
+// query_tiles: 1 or 2 tiles of 128 rows per CTA, 0 to let the launcher choose.
 DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                     long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
                                     const int* kv_len, int seq0, int num_seqs, int max_q_len, int nh, int nkv, int page_size,
-                                    int window, float scale, cudaStream_t stream) {
+                                    int window, float scale, int query_tiles, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (nkv < 1 || nh % nkv || page_size < 8 || page_size > 128 || (KEYS % page_size) != 0) return DLI_ERR_UNSUPPORTED;
   if (((uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)q) & 15) return DLI_ERR_UNSUPPORTED;
@@ -497,6 +808,19 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
   p.head_chunks = (G + p.heads_per_chunk - 1) / p.heads_per_chunk;
   p.tokens_per_tile = ROWS / p.heads_per_chunk;
   p.error_flag = error_flag_device;
+  // two query tiles per CTA when a sequence brings more tokens than one tile holds, unless the caller chose
+  const bool two = query_tiles == 2 || (query_tiles != 1 && max_q_len > p.tokens_per_tile);
+  if (two) {
+    static bool configured2 = false;
+    if (!configured2) {
+      cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM);
+      if (e != cudaSuccess) return (int)e;
+      configured2 = true;
+    }
+    const int tiles = (max_q_len + 2 * p.tokens_per_tile - 1) / (2 * p.tokens_per_tile);
+    return (int)launch_pdl(paged_prefill_tc2_kernel, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(T2_THREADS), (size_t)T2_SMEM, stream, 1,
+                           map_k, map_v, p);
+  }
   const int tiles = (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
   cudaError_t e = launch_pdl(paged_prefill_tc_kernel, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(THREADS), (size_t)SMEM_BYTES, stream, 1,
                              map_k, map_v, p);

@@ -279,9 +279,12 @@ def paged_prefill_tc(
     num_heads: int,
     scale: float,
     window: int | None = None,
+    query_tiles: int = 0,
 ) -> None:
     """bfloat16 attention for prompt portions on tcgen05 tensor cores with TMA-fed pages
-    (head size 64; page sizes 8, 16, 32, 64, 128).  Arguments as paged_attention_mma."""
+    (head size 64; page sizes 8, 16, 32, 64, 128).  Arguments as paged_attention_mma.
+    ``query_tiles``: 1 or 2 tiles of 128 (token, head) rows per CTA; 0 lets the launcher choose (two
+    when a sequence brings more tokens than one tile holds)."""
     for t, name in ((out, "out"), (qkv, "qkv"), (k_pool, "k_pool"), (v_pool, "v_pool")):
         _need(t, name, torch.bfloat16)
     _need(block_tables, "block_tables", torch.int32), _need(q_start, "q_start", torch.int32), _need(kv_len, "kv_len", torch.int32)
@@ -294,11 +297,13 @@ def paged_prefill_tc(
         raise KernelError("paged_prefill_tc: sequence range outside the batch")
     f = _fn(
         "attention_tc.cu", "dli_paged_prefill_tc",
-        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p],
+        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_int, c_void_p],
     )
+    if query_tiles not in (0, 1, 2):
+        raise KernelError("paged_prefill_tc: query_tiles is 0 (choose), 1 or 2")
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_tables), block_tables.shape[1],
-          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, num_heads, nkv, page_size, int(window or 0), scale, _stream()),
+          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, num_heads, nkv, page_size, int(window or 0), scale, query_tiles, _stream()),
         "paged_prefill_tc",
     )
 

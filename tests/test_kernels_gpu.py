@@ -241,15 +241,16 @@ PREFILL_MIX = [(0, 37), (40, 2), (64, 64), (3, 130), (255, 300), (16, 17), (700,
 @pytest.mark.parametrize("nh,nkv,page", [(8, 2, 16), (3, 1, 8), (5, 5, 32), (4, 4, 128), (32, 8, 64), (130, 1, 16)])
 @pytest.mark.parametrize("window", [None, 70, 200])
 def test_paged_prefill_tc(nh, nkv, page, window):
-    """The tcgen05 + TMA prefill kernel: portions that start anywhere, cross tile and page edges,
-    with GQA groups from 1 to 130 heads per KV head."""
+    """The tcgen05 + TMA prefill kernels (one and two query tiles per CTA): portions that start anywhere,
+    cross tile and page edges, with GQA groups from 1 to 130 heads per KV head."""
     d = 64
     t = attention_case(nh, nkv, d, page, PREFILL_MIX, torch.bfloat16, seed=nh + page)
-    out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.paged_prefill_tc(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(PREFILL_MIX),
-                         max(q for _, q in PREFILL_MIX), nh, d**-0.5, window)
     want = plain_attention(t, PREFILL_MIX, nh, window)
-    np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2))
+    for tiles in (1, 2, 0):
+        out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.paged_prefill_tc(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(PREFILL_MIX),
+                             max(q for _, q in PREFILL_MIX), nh, d**-0.5, window, tiles)
+        np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2), err_msg=f"{tiles} query tiles")
     assert ops.paged_prefill_tc_error() == 0
 
 
@@ -283,10 +284,11 @@ def test_prefill_tc_when_row_maxima_keep_rising(ramp):
     nh, nkv, d, page = 8, 2, 64, 16
     seqs = [(0, 700), (300, 260), (1000, 3)]
     t = attention_case(nh, nkv, d, page, seqs, torch.bfloat16, seed=5, ramp=ramp)
-    out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.paged_prefill_tc(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(seqs), max(q for _, q in seqs), nh, d**-0.5, None)
     want = plain_attention(t, seqs, nh, None)
-    np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2))
+    for tiles in (1, 2):
+        out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.paged_prefill_tc(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(seqs), max(q for _, q in seqs), nh, d**-0.5, None, tiles)
+        np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2), err_msg=f"{tiles} query tiles")
     assert ops.paged_prefill_tc_error() == 0
 
 
