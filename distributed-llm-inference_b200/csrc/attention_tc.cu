@@ -1,5 +1,5 @@
 // Paged causal GQA attention for prompt portions on the fifth-generation tensor cores
-// (bfloat16, head size 64, page sizes 8..128 that divide 128).
+// (bfloat16, head size 64 — and 128 in the kernel with a thread per row —, page sizes 8..128 that divide 128).
 //
 // A CTA owns 128 rows — (token, query head) pairs that share one KV head — and walks the keys
 // of its sequence in tiles of 128:
@@ -446,8 +446,19 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
 //   k_full, v_full [2]     TMA -> products              k_free, v_free [2]   products done -> TMA
 //   s_done [A, B]          S there                      s_read [A, B] (128)  S in registers
 //   p_ready [A, B] (128)   P written, output rescaled   o_done [A, B]        O += P V finished
-constexpr int T2_THREADS = 2 * ROWS + 128;  // two softmax warpgroups and one of which two warps work (products, copies): whole warpgroups trade registers
-constexpr int T2_SMEM = TILE_BYTES * (2 + 2 + 2 + 4) + 256 + 1024;  // Q x2, K x2, V x2, P x2 (two halves each), barriers, alignment
+// Head size 64: two query tiles per CTA.  Head size 128: one (its Q, K and V tiles are twice as large), so the
+// group has no partner; a row of keys or values is then two 128-byte slabs, each with its own TMA box, the
+// score product runs over both, and the output product is one group of tcgen05.mma per slab of 64 columns.
+template <int HD>
+struct T2Cfg {
+  static_assert(HD == 64 || HD == 128, "head sizes with whole 128-byte slabs");
+  static constexpr int QT = HD == 64 ? 2 : 1;             // query tiles per CTA
+  static constexpr int SLABS = HD / 64;
+  static constexpr int THREADS = QT * ROWS + 128;         // softmax warpgroups and one of which two warps work (products, copies)
+  static constexpr int KV_BYTES = SLABS * TILE_BYTES;     // one stage of keys or of values; also one Q tile
+  static constexpr int SMEM = QT * KV_BYTES + 4 * KV_BYTES + QT * 2 * TILE_BYTES + 256 + 1024;  // Q, K x2, V x2, P per query tile, barriers, alignment
+  static constexpr int TMEM = QT * KEYS + QT * HD <= 256 ? 256 : 512;
+};
 
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t done;
@@ -456,16 +467,20 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
-__global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k,
-                                                                         const __grid_constant__ CUtensorMap map_v, const Params p) {
+template <int HD>
+__global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                                  const __grid_constant__ CUtensorMap map_v, const Params p) {
+  using Cfg = T2Cfg<HD>;
+  constexpr int QT = Cfg::QT, SLABS = Cfg::SLABS, KV_BYTES = Cfg::KV_BYTES, T2_THREADS = Cfg::THREADS;
+  constexpr int D = HD;  // shadows the one-tile kernel's head size within this kernel
   pdl_launch_dependents();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  unsigned char* sQ = smem;                     // tile A, tile B
-  unsigned char* sK = sQ + 2 * TILE_BYTES;      // two stages
-  unsigned char* sV = sK + 2 * TILE_BYTES;      // two stages
-  unsigned char* sP = sV + 2 * TILE_BYTES;      // per query tile (keys 0..63 | keys 64..127)
-  uint64_t* bars = (uint64_t*)(sP + 4 * TILE_BYTES);
+  unsigned char* sQ = smem;                     // tile A (, tile B); a tile is SLABS slabs of [128 rows x 128 bytes]
+  unsigned char* sK = sQ + QT * KV_BYTES;       // two stages
+  unsigned char* sV = sK + 2 * KV_BYTES;        // two stages
+  unsigned char* sP = sV + 2 * KV_BYTES;        // per query tile (keys 0..63 | keys 64..127)
+  uint64_t* bars = (uint64_t*)(sP + QT * 2 * TILE_BYTES);
   uint32_t* tmem_slot = (uint32_t*)(bars + 16);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
@@ -479,10 +494,10 @@ __global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const 
   const int q0 = p.q_start[s];
   const int qlen = p.q_start[s + 1] - q0;
   const int tpt = p.tokens_per_tile;
-  const int tok0 = tile * 2 * tpt;
+  const int tok0 = tile * QT * tpt;
   if (tok0 >= qlen) return;  // the whole CTA: nothing was set up yet
   const int kvlen = p.kv_len[s];
-  const int ntok = min(2 * tpt, qlen - tok0);  // tokens of both tiles
+  const int ntok = min(QT * tpt, qlen - tok0);  // tokens of the CTA's tiles
   const int G = p.nh / p.nkv, Gc = p.heads_per_chunk;
   const int head0 = kvh * G + hc * Gc;
   const int nheads = min(Gc, G - hc * Gc);
@@ -502,34 +517,35 @@ __global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const 
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::TMEM) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   pdl_wait();  // queries and the cache are the work of the kernels before this one
 
   // ---- both Q tiles, swizzled by hand (rows beyond the used ones are zero); the value stages start as zeros
-  for (int idx = tid; idx < 2 * ROWS * 8; idx += T2_THREADS) {
-    const int rr = idx >> 3, c = idx & 7;  // rr: row among the 256 of both tiles
+  for (int idx = tid; idx < QT * ROWS * (D / 8); idx += T2_THREADS) {
+    const int rr = idx / (D / 8), c = idx - rr * (D / 8);  // rr: row among those of all tiles; c: 16-byte chunk of the row
     const int rt = rr & (ROWS - 1), tok = (rr >> 7) * tpt + rt / Gc, hd = rt % Gc;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (rt / Gc < tpt && tok < ntok && hd < nheads)
       v = *reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + tok0 + tok) * p.q_stride + (size_t)(head0 + hd) * D + c * 8);
-    *reinterpret_cast<uint4*>(sQ + rr * 128 + ((c ^ (rr & 7)) << 4)) = v;
+    *reinterpret_cast<uint4*>(sQ + (rr >> 7) * KV_BYTES + (c >> 3) * TILE_BYTES + rt * 128 + (((c & 7) ^ (rt & 7)) << 4)) = v;
   }
-  for (int idx = tid; idx < 2 * TILE_BYTES / 16; idx += T2_THREADS) reinterpret_cast<uint4*>(sV)[idx] = make_uint4(0, 0, 0, 0);
+  for (int idx = tid; idx < 2 * KV_BYTES / 16; idx += T2_THREADS) reinterpret_cast<uint4*>(sV)[idx] = make_uint4(0, 0, 0, 0);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + 2 * KEYS;  // S of A, S of B, O of A, O of B
+  const uint32_t tmem_s = tmem, tmem_o = tmem + QT * KEYS;  // S of each query tile, then O of each
 
   // The softmax threads hold a row of 128 scores in registers; the third warpgroup needs few and gives its
   // share away (a scheduler then holds two warps of 224 registers and one of 40).
-  if (warp >= 2 * ROWS / 32) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-  if (warp == 2 * ROWS / 32 + 1) {
+  if (warp >= QT * ROWS / 32) {
+    if (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp == QT * ROWS / 32 + 1) {
     // ================================================================ the warp that copies
+    // a lane copies one page (lanes 0..15 keys, lanes 16..31 values), all its slabs of 64 columns
     const int pages = KEYS / p.page_size;
     const int page_i = lane & 15;
     auto lookup = [&](int t) -> int {
@@ -539,12 +555,16 @@ __global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const 
     };
     auto issue = [&](bool keys, int stage, int page) {
       const uint32_t bar = (keys ? k_full : v_full) + 8 * stage;
-      unsigned char* dst = (keys ? sK : sV) + stage * TILE_BYTES;
+      unsigned char* dst = (keys ? sK : sV) + stage * KV_BYTES;
       const unsigned side = keys ? 0x0000ffffu : 0xffff0000u;
       const int count = __popc(__ballot_sync(side, page >= 0));
-      if (page_i == 0) mbar_expect_tx(bar, (uint32_t)(count * p.page_size * 128));
+      if (page_i == 0) mbar_expect_tx(bar, (uint32_t)(count * p.page_size * 128 * SLABS));
       __syncwarp(side);
-      if (page >= 0) tma_load_2d(smem_u32(dst + page_i * p.page_size * 128), keys ? &map_k : &map_v, 0, (page * p.nkv + kvh) * p.page_size, bar);
+      if (page >= 0) {
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl)
+          tma_load_2d(smem_u32(dst + sl * TILE_BYTES + page_i * p.page_size * 128), keys ? &map_k : &map_v, sl * 64, (page * p.nkv + kvh) * p.page_size, bar);
+      }
     };
     int page = lookup(t_begin);
     for (int t = 0; t < num_tiles && !*failed; ++t) {
@@ -564,39 +584,42 @@ __global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const 
       }
       if (lane >= 16) issue(false, st, cur);
     }
-  } else if (warp == 2 * ROWS / 32) {
+  } else if (warp == QT * ROWS / 32) {
     // ================================================================ the warp that issues the matrix products (its first lane)
     if (lane == 0) {
-      const uint32_t idesc_s = instr_desc(ROWS, KEYS, 0), idesc_o = instr_desc(ROWS, D, 1);
-      int next_qk[2] = {0, 0}, next_pv[2] = {0, 0};
+      const uint32_t idesc_s = instr_desc(ROWS, KEYS, 0), idesc_o = instr_desc(ROWS, 64, 1);
+      int next_qk[2] = {0, QT == 2 ? 0 : num_tiles}, next_pv[2] = {0, QT == 2 ? 0 : num_tiles};  // a tile that does not exist is finished
       unsigned spins = 0;
       while ((next_pv[0] < num_tiles || next_pv[1] < num_tiles) && !*failed) {
         bool progress = false;
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
+        for (int q = 0; q < QT; ++q) {
           // S_q(t) = Q_q K(t)^T: the keys are there and the thread of every row has S_q(t - 1) in registers
           int t = next_qk[q];
           if (t < num_tiles && mbar_test(k_full + 8 * (t & 1), (t >> 1) & 1) && (t == 0 || mbar_test(s_read + 8 * q, (t - 1) & 1))) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a = smem_u32(sQ + q * TILE_BYTES), k = smem_u32(sK + (t & 1) * TILE_BYTES);
+            const uint32_t a = smem_u32(sQ + q * KV_BYTES), k = smem_u32(sK + (t & 1) * KV_BYTES);
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) umma(tmem_s + q * KEYS, smem_desc_sw128(a + kk * 32), smem_desc_sw128(k + kk * 32), idesc_s, kk != 0);
+            for (int kk = 0; kk < D / 16; ++kk)
+              umma(tmem_s + q * KEYS, smem_desc_sw128(a + (kk >> 2) * TILE_BYTES + (kk & 3) * 32), smem_desc_sw128(k + (kk >> 2) * TILE_BYTES + (kk & 3) * 32), idesc_s, kk != 0);
             umma_commit(s_done + 8 * q);
             next_qk[q] = t + 1;
-            if (next_qk[q ^ 1] > t) umma_commit(k_free + 8 * (t & 1));  // both tiles' products with K(t) are issued
+            if (next_qk[q ^ 1] > t) umma_commit(k_free + 8 * (t & 1));  // every tile's product with K(t) is issued
             progress = true;
           }
           // O_q += P_q(t) V(t)
           t = next_pv[q];
           if (t < num_tiles && mbar_test(p_ready + 8 * q, t & 1) && mbar_test(v_full + 8 * (t & 1), (t >> 1) & 1)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a = smem_u32(sP + q * 2 * TILE_BYTES), v = smem_u32(sV + (t & 1) * TILE_BYTES);
+            const uint32_t a = smem_u32(sP + q * 2 * TILE_BYTES), v = smem_u32(sV + (t & 1) * KV_BYTES);
 #pragma unroll
-            for (int k = 0; k < KEYS / 16; ++k)
-              umma(tmem_o + q * D, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(v + k * 2048), idesc_o, (t | k) != 0);
+            for (int sl = 0; sl < SLABS; ++sl)  // 64 output columns at a time: the values' slab is the MN-major operand
+#pragma unroll
+              for (int k = 0; k < KEYS / 16; ++k)
+                umma(tmem_o + q * D + sl * 64, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(v + sl * TILE_BYTES + k * 2048), idesc_o, (t | k) != 0);
             umma_commit(o_done + 8 * q);
             next_pv[q] = t + 1;
-            if (next_pv[q ^ 1] > t) umma_commit(v_free + 8 * (t & 1));  // both tiles' products with V(t) are issued
+            if (next_pv[q ^ 1] > t) umma_commit(v_free + 8 * (t & 1));  // every tile's product with V(t) is issued
             progress = true;
           }
         }
@@ -610,7 +633,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const 
     __syncwarp();
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    if (QT == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     // ================================================================ softmax threads: one per row
     const int q = warp >> 2;                 // query tile A or B
     const int r = tid & (ROWS - 1);          // row of the tile
@@ -624,7 +647,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const 
     float m = -CUDART_INF_F, m_ref = -CUDART_INF_F, l = 0.f;
     bool ok = true;
     const int first_pos = pos0 + q * tpt;  // position of the tile's first row
-    if (q == 1 && num_tiles > 0) asm volatile("bar.arrive 1, %0;" ::"n"(2 * ROWS) : "memory");  // tile A takes the first turn
+    if (QT == 2 && q == 1 && num_tiles > 0) asm volatile("bar.arrive 1, %0;" ::"n"(2 * ROWS) : "memory");  // tile A takes the first turn
 
     for (int t = 0; t < num_tiles; ++t) {
       const int base = (t_begin + t) * KEYS;
@@ -689,8 +712,10 @@ __global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const 
         }
       }
       // ---- this group's turn at the exponentials (measured: 562 us at 8,192 tokens with turns, 694 without)
-      if (q == 0) asm volatile("bar.sync 1, %0;" ::"n"(2 * ROWS) : "memory");
-      else asm volatile("bar.sync 2, %0;" ::"n"(2 * ROWS) : "memory");
+      if (QT == 2) {
+        if (q == 0) asm volatile("bar.sync 1, %0;" ::"n"(2 * ROWS) : "memory");
+        else asm volatile("bar.sync 2, %0;" ::"n"(2 * ROWS) : "memory");
+      }
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
       unsigned char* prow = sP + q * 2 * TILE_BYTES + r * 128;
 #pragma unroll
@@ -706,8 +731,10 @@ __global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const 
         }
         *reinterpret_cast<uint4*>(prow + (j >> 6) * TILE_BYTES + ((((j >> 3) & 7) ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
-      if (q == 0) asm volatile("bar.arrive 2, %0;" ::"n"(2 * ROWS) : "memory");
-      else if (t + 1 < num_tiles) asm volatile("bar.arrive 1, %0;" ::"n"(2 * ROWS) : "memory");
+      if (QT == 2) {
+        if (q == 0) asm volatile("bar.arrive 2, %0;" ::"n"(2 * ROWS) : "memory");
+        else if (t + 1 < num_tiles) asm volatile("bar.arrive 1, %0;" ::"n"(2 * ROWS) : "memory");
+      }
       l = l * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor cores
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -741,7 +768,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) paged_prefill_tc2_kernel(const 
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM) : "memory");
 }
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -757,13 +784,13 @@ EncodeTiled encode_fn() {
   }
   return fn;
 }
-// a pool [pages, nkv, page_size, 64] seen as rows of 64 elements; boxes of one page of one head
-bool make_pool_map(CUtensorMap* map, const void* base, long long rows, int page_size) {
+// a pool [pages, nkv, page_size, d] seen as rows of d elements; boxes of one page of one head, 64 columns wide
+bool make_pool_map(CUtensorMap* map, const void* base, long long rows, int page_size, int d = D) {
   EncodeTiled fn = encode_fn();
   if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-  cuuint32_t box[2] = {(cuuint32_t)D, (cuuint32_t)page_size};
+  cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)d * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
   cuuint32_t elem[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -775,13 +802,14 @@ int* error_flag_host = nullptr;
 }  // namespace
 
 // Sequences [seq0, seq0 + num_seqs) of a batch, each bringing at most max_q_len tokens.
-// Head size 64 only; page_size must be 8, 16, 32, 64 or 128; num_pages is the pools' first extent.
-// query_tiles: 1 or 2 tiles of 128 rows per CTA, 0 to let the launcher choose.
+// Head size 64 or 128; page_size must be 8, 16, 32, 64 or 128; num_pages is the pools' first extent.
+// query_tiles (head size 64): 1 or 2 tiles of 128 rows per CTA, 0 to let the launcher choose.
 DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                     long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
-                                    const int* kv_len, int seq0, int num_seqs, int max_q_len, int nh, int nkv, int page_size,
-                                    int window, float scale, int query_tiles, cudaStream_t stream) {
+                                    const int* kv_len, int seq0, int num_seqs, int max_q_len, int nh, int nkv, int head_dim,
+                                    int page_size, int window, float scale, int query_tiles, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
+  if (head_dim != 64 && head_dim != 128) return DLI_ERR_UNSUPPORTED;
   if (nkv < 1 || nh % nkv || page_size < 8 || page_size > 128 || (KEYS % page_size) != 0) return DLI_ERR_UNSUPPORTED;
   if (((uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)q) & 15) return DLI_ERR_UNSUPPORTED;
   if (!error_flag_host) {
@@ -797,7 +825,7 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
   }
   CUtensorMap map_k, map_v;
   const long long rows = num_pages * nkv * page_size;
-  if (!make_pool_map(&map_k, k_pool, rows, page_size) || !make_pool_map(&map_v, v_pool, rows, page_size)) return DLI_ERR_UNSUPPORTED;
+  if (!make_pool_map(&map_k, k_pool, rows, page_size, head_dim) || !make_pool_map(&map_v, v_pool, rows, page_size, head_dim)) return DLI_ERR_UNSUPPORTED;
   Params p;
   p.out = (bf16*)out; p.q = (const bf16*)q; p.q_stride = q_stride;
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.q_start = q_start; p.kv_len = kv_len; p.seq0 = seq0;
@@ -808,18 +836,29 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
   p.head_chunks = (G + p.heads_per_chunk - 1) / p.heads_per_chunk;
   p.tokens_per_tile = ROWS / p.heads_per_chunk;
   p.error_flag = error_flag_device;
+  if (head_dim == 128) {  // one query tile per CTA, a thread per row
+    static bool configured128 = false;
+    if (!configured128) {
+      cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2Cfg<128>::SMEM);
+      if (e != cudaSuccess) return (int)e;
+      configured128 = true;
+    }
+    const int tiles = (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
+    return (int)launch_pdl(paged_prefill_tc2_kernel<128>, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(T2Cfg<128>::THREADS),
+                           (size_t)T2Cfg<128>::SMEM, stream, 1, map_k, map_v, p);
+  }
   // two query tiles per CTA when a sequence brings more tokens than one tile holds, unless the caller chose
   const bool two = query_tiles == 2 || (query_tiles != 1 && max_q_len > p.tokens_per_tile);
   if (two) {
     static bool configured2 = false;
     if (!configured2) {
-      cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM);
+      cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2Cfg<64>::SMEM);
       if (e != cudaSuccess) return (int)e;
       configured2 = true;
     }
     const int tiles = (max_q_len + 2 * p.tokens_per_tile - 1) / (2 * p.tokens_per_tile);
-    return (int)launch_pdl(paged_prefill_tc2_kernel, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(T2_THREADS), (size_t)T2_SMEM, stream, 1,
-                           map_k, map_v, p);
+    return (int)launch_pdl(paged_prefill_tc2_kernel<64>, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(T2Cfg<64>::THREADS),
+                           (size_t)T2Cfg<64>::SMEM, stream, 1, map_k, map_v, p);
   }
   const int tiles = (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
   cudaError_t e = launch_pdl(paged_prefill_tc_kernel, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(THREADS), (size_t)SMEM_BYTES, stream, 1,

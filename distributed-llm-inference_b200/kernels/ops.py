@@ -262,7 +262,7 @@ def paged_attention_simt(
 
 
 def prefill_tc_supported(head_dim: int, page_size: int) -> bool:
-    return head_dim == 64 and page_size in (8, 16, 32, 64, 128)
+    return head_dim in (64, 128) and page_size in (8, 16, 32, 64, 128)
 
 
 def paged_prefill_tc(
@@ -282,28 +282,28 @@ def paged_prefill_tc(
     query_tiles: int = 0,
 ) -> None:
     """bfloat16 attention for prompt portions on tcgen05 tensor cores with TMA-fed pages
-    (head size 64; page sizes 8, 16, 32, 64, 128).  Arguments as paged_attention_mma.
-    ``query_tiles``: 1 or 2 tiles of 128 (token, head) rows per CTA; 0 lets the launcher choose (two
+    (head size 64 or 128; page sizes 8, 16, 32, 64, 128).  Arguments as paged_attention_mma.
+    ``query_tiles`` (head size 64): 1 or 2 tiles of 128 (token, head) rows per CTA; 0 lets the launcher choose (two
     when a sequence brings more tokens than one tile holds)."""
     for t, name in ((out, "out"), (qkv, "qkv"), (k_pool, "k_pool"), (v_pool, "v_pool")):
         _need(t, name, torch.bfloat16)
     _need(block_tables, "block_tables", torch.int32), _need(q_start, "q_start", torch.int32), _need(kv_len, "kv_len", torch.int32)
     pages, nkv, page_size, d = k_pool.shape
     if not prefill_tc_supported(d, page_size):
-        raise KernelError(f"paged_prefill_tc: head_dim {d} (64) or page size {page_size} (8..128, dividing 128) not supported")
+        raise KernelError(f"paged_prefill_tc: head_dim {d} (64 or 128) or page size {page_size} (8..128, dividing 128) not supported")
     if out.shape[1] != num_heads * d or qkv.shape[0] != out.shape[0] or qkv.shape[1] < num_heads * d or num_heads % nkv or k_pool.shape != v_pool.shape:
         raise KernelError("paged_prefill_tc: shapes do not agree")
     if seq0 + num_seqs > kv_len.numel() or q_start.numel() != kv_len.numel() + 1:
         raise KernelError("paged_prefill_tc: sequence range outside the batch")
     f = _fn(
         "attention_tc.cu", "dli_paged_prefill_tc",
-        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_int, c_void_p],
+        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 8 + [c_float, c_int, c_void_p],
     )
     if query_tiles not in (0, 1, 2):
         raise KernelError("paged_prefill_tc: query_tiles is 0 (choose), 1 or 2")
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_tables), block_tables.shape[1],
-          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, num_heads, nkv, page_size, int(window or 0), scale, query_tiles, _stream()),
+          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, num_heads, nkv, d, page_size, int(window or 0), scale, query_tiles, _stream()),
         "paged_prefill_tc",
     )
 

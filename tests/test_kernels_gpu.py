@@ -276,6 +276,19 @@ def test_paged_decode_tma(nh, nkv, page, window, splits, d):
     assert ops.paged_prefill_tc_error() == 0
 
 
+@pytest.mark.parametrize("nh,nkv,page,window", [(6, 2, 16, None), (3, 1, 8, 70), (4, 4, 128, None), (24, 8, 32, 200), (9, 1, 16, None)])
+def test_paged_prefill_tc_head_size_128(nh, nkv, page, window):
+    """Head size 128 goes to the kernel with a thread per row: two 128-byte slabs per row of keys and values."""
+    d = 128
+    t = attention_case(nh, nkv, d, page, PREFILL_MIX, torch.bfloat16, seed=nh + page)
+    want = plain_attention(t, PREFILL_MIX, nh, window)
+    out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_prefill_tc(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(PREFILL_MIX),
+                         max(q for _, q in PREFILL_MIX), nh, d**-0.5, window)
+    np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2))
+    assert ops.paged_prefill_tc_error() == 0
+
+
 @pytest.mark.parametrize("ramp", [0.02, 0.3])
 def test_prefill_tc_when_row_maxima_keep_rising(ramp):
     """Scores that grow with the key's position: the row maxima rise by a little (0.02: about four powers
