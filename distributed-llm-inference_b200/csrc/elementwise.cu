@@ -323,13 +323,14 @@ __global__ void rotary_store_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, co
   const int t = blockIdx.x;
   const int half = rot >> 1;
   __nv_bfloat16* base = qkv + (size_t)t * (nh + 2 * nkv) * d;
-  if (table) {
-    for (int i = threadIdx.x; i < rot; i += blockDim.x) trig[i] = table[(size_t)t * rot + i];
-  } else {
+  // with a table of the step's cosines and sines every thread reads its eight of each straight from it (one
+  // round of loads, no barrier); without one the block computes the token's into shared memory first
+  const float* trig_row = table ? table + (size_t)t * rot : trig;
+  if (!table) {
     const float pos = (float)positions[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &trig[half + i], &trig[i]);
+    __syncthreads();
   }
-  __syncthreads();
   const int slot = slots ? slots[t] : -1;
   const bool store = write_kv && slot >= 0;
   const int page = store ? slot / page_size : 0, off = store ? slot % page_size : 0;
@@ -341,13 +342,17 @@ __global__ void rotary_store_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, co
     if (idx < rot_items) {
       const int head = idx / hc, i = (idx - head * hc) << 3;
       __nv_bfloat16* x = base + (size_t)head * d;
-      float a[8], b[8];
+      float a[8], b[8], cs8[8], sn8[8];
       load8(x + i, a);
       load8(x + i + half, b);
+      *reinterpret_cast<float4*>(cs8) = *reinterpret_cast<const float4*>(trig_row + i);
+      *reinterpret_cast<float4*>(cs8 + 4) = *reinterpret_cast<const float4*>(trig_row + i + 4);
+      *reinterpret_cast<float4*>(sn8) = *reinterpret_cast<const float4*>(trig_row + half + i);
+      *reinterpret_cast<float4*>(sn8 + 4) = *reinterpret_cast<const float4*>(trig_row + half + i + 4);
       float ra[8], rb[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const float cs = trig[i + k], sn = trig[half + i + k];
+        const float cs = cs8[k], sn = sn8[k];
         ra[k] = a[k] * cs - b[k] * sn;
         rb[k] = b[k] * cs + a[k] * sn;
       }
