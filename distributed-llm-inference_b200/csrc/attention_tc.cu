@@ -36,7 +36,7 @@ constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 128 bytes (Q, K, V tiles a
 constexpr int SOFTMAX_THREADS = 256;
 constexpr int THREADS = SOFTMAX_THREADS + 64;  // plus a warp that issues the matrix products and a warp that issues the copies
 constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 + 2 + 4) + 4 * ROWS * 4 + 256 + 1024;  // Q, K x2, V x2, P x2 (two halves each), row maxima x2, barriers, alignment
-constexpr int TMEM_COLS = 512;  // S: 2 x 128 columns, output tile: 2 x 64 columns (a power of two)
+constexpr int TMEM_COLS = 512;  // S: 2 x 128 columns, the output: 64 columns (320, rounded up to a power of two)
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
 struct Params {
@@ -137,7 +137,7 @@ __device__ __forceinline__ bool wait_or_fail(uint32_t bar, uint32_t parity, vola
 // that follows the row's running maximum only when that has grown by more than 2^8; only then the
 // threads multiply their part of O by 2^(old - new) in place (tcgen05.ld / tcgen05.st), which after the
 // first tiles is rare.  The sides meet on mbarriers only (two of each, by parity):
-//   k_full, v_full   TMA -> controller            s_done, o_done   MMA -> softmax threads
+//   k_full, v_full   TMA -> products             s_done, o_done   products -> softmax threads and TMA
 //   p_ready (256)    P written, output rescaled, S read
 __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                       const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  // tensor memory: S of even tiles, S of odd tiles, output tile of even tiles, of odd tiles
+  // tensor memory: S of even tiles, S of odd tiles, the output
   const uint32_t tmem_s = tmem, tmem_o = tmem + 2 * KEYS;
 
   if (warp == SOFTMAX_THREADS / 32 + 1) {
@@ -1315,6 +1315,6 @@ DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride
 
 DLI_EXPORT int dli_decode_tma_merges_in_cluster(int nh, int nkv, int splits) { return merges_in_cluster(nh, nkv, splits) ? 1 : 0; }
 
-// 0, or the code of the first bounded wait that ran out (11 keys, 12 scores, 13 output tile, 14 values,
-// 15 probabilities, 16 output tile read; 21: a decode warp's keys and values)
+// 0, or the code of the first bounded wait that ran out (11 keys, 12 scores or a key stage, 13 an output product or a
+// value stage, 14 values, 15 probabilities, 17 the product warp found nothing to issue; 21: a decode warp's keys and values)
 DLI_EXPORT int dli_paged_prefill_tc_error() { return error_flag_host ? *error_flag_host : 0; }
