@@ -11,5 +11,5 @@ __version__ = "0.1.0"
 
 from .config import LlamaConfig, UnsupportedModelError, load_config, register_architecture  # noqa: E402,F401
 from .weights import CheckpointError, write_model_dir  # noqa: E402,F401
-from .engine import LLMEngine, SchedulerConfig, greedy_generate, load_model, random_model  # noqa: E402,F401
+from .engine import LLMEngine, Priority, SchedulerConfig, greedy_generate, load_model, random_model  # noqa: E402,F401
 from .sampling import SamplingParams  # noqa: E402,F401

@@ -24,7 +24,7 @@ from typing import Collection, Iterable, Protocol, Sequence
 
 from ..cache import UNKNOWN_TOKEN, OutOfPages
 from ..sampling import SamplingParams
-from .request import FinishReason, Request
+from .request import FinishReason, Priority, Request
 from .scheduler import ScheduledChunk, Scheduler, SchedulerConfig
 
 
@@ -142,13 +142,16 @@ class LLMEngine:
 
     # ------------------------------------------------------------ API
 
-    def add_request(self, request_id: str, prompt_ids: Sequence[int], params: SamplingParams | None = None) -> Request:
-        """Queue a request.  One that can never fit finishes at once with reason ``capacity``."""
+    def add_request(self, request_id: str, prompt_ids: Sequence[int], params: SamplingParams | None = None, *,
+                    priority: Priority = Priority.INTERACTIVE, tenant: str = "default") -> Request:
+        """Queue a request.  One that can never fit finishes at once with reason ``capacity``.
+        ``priority`` and ``tenant`` decide its place among the others (see the scheduler)."""
         if not prompt_ids:
             raise ValueError("prompt must be non-empty")
         params = params or SamplingParams()
         seed = params.seed if params.seed is not None else self._rng.getrandbits(63)
-        req = Request(request_id, [int(t) for t in prompt_ids], params, next(self._arrivals), seed=seed)
+        req = Request(request_id, [int(t) for t in prompt_ids], params, next(self._arrivals), seed=seed,
+                      priority=Priority(priority), tenant=tenant)
         self.scheduler.add(req)
         return req
 
@@ -251,6 +254,7 @@ class LLMEngine:
         except OutOfPages:
             return None  # the scheduler will decide who yields; slots taken so far are kept and named when the ids arrive
         chunks = [ScheduledChunk(r, r.num_computed_tokens, 1, True) for _, r in chosen]
+        sch.step_launched_ahead([r for _, r in chosen])
         self.steps_ahead += 1
         return self._run(chunks, 0, flight.tokens, [i for i, _ in chosen], ahead=1)
 

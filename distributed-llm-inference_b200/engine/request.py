@@ -3,7 +3,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from enum import Enum
+from enum import Enum, IntEnum
 
 from ..sampling.params import SamplingParams
 
@@ -21,6 +21,13 @@ class FinishReason(str, Enum):
     CAPACITY = "capacity"  # can never fit in the cache pool; never ran
 
 
+class Priority(IntEnum):
+    """Scheduling class of a request; the lower value is served first (src/dli/engine/request.py:27-31)."""
+
+    INTERACTIVE = 0
+    BATCH = 1
+
+
 @dataclass(eq=False)
 class Request:
     """``num_computed_tokens`` counts tokens whose keys and values are in the cache; it equals
@@ -31,6 +38,9 @@ class Request:
     params: SamplingParams
     arrival: int
     seed: int = 0
+    priority: Priority = Priority.INTERACTIVE
+    tenant: str = "default"  # whose share of the engine the request's tokens are charged to
+    arrival_step: int = 0  # the scheduler's step count when the request was queued (for aging)
     output_ids: list[int] = field(default_factory=list)
     status: RequestStatus = RequestStatus.WAITING
     finish_reason: FinishReason | None = None

@@ -15,17 +15,25 @@ A request whose prompt plus ``max_tokens`` can never fit in the pool is finished
 at once with reason ``capacity``, so the oldest running request can always
 finish and the engine cannot livelock.  (src/dli/engine/scheduler.py:102-120,255-267.)
 
-The reference's priority classes and tenant fair-share (its HTTP server's
-concern) are not kept: the order is arrival, preempted requests first.
+Order among requests (src/dli/engine/scheduler.py:218-242).  Running requests are
+served by (class, arrival): an INTERACTIVE request before a BATCH one, and a
+request that has been in the system for ``aging_steps`` steps counts as
+INTERACTIVE, so BATCH work cannot starve for ever.  Victims of preemption come
+from the end of that order.  Admission takes, within the best class, a preempted
+request before a new one, then the request of the tenant that is furthest behind.
+Every tenant has a virtual clock that advances by tokens / weight for each token
+scheduled for it; a tenant that turns up (again) starts at the smallest clock of
+the tenants that have work, so an idle spell earns no credit.
 """
 
 from __future__ import annotations
 
 from collections import deque
+from collections.abc import Mapping
 from dataclasses import dataclass, field
 
 from ..cache import CacheManager, OutOfPages
-from .request import FinishReason, Request, RequestStatus
+from .request import FinishReason, Priority, Request, RequestStatus
 
 
 @dataclass(frozen=True)
@@ -33,10 +41,16 @@ class SchedulerConfig:
     max_num_seqs: int = 64  # requests holding pages at once
     max_num_batched_tokens: int = 512  # tokens per step, prompt portions and decoded tokens together
     namespace: bytes = b""  # scope of prefix reuse (identity of model and weights)
+    tenant_weights: Mapping[str, float] = field(default_factory=dict)  # share of a tenant (default 1.0): weight 2 gets about twice the tokens
+    aging_steps: int = 200  # a request this many steps in the system counts as INTERACTIVE
 
     def __post_init__(self) -> None:
         if self.max_num_seqs < 1 or self.max_num_batched_tokens < 1:
             raise ValueError("max_num_seqs and max_num_batched_tokens must be >= 1")
+        if self.aging_steps < 1:
+            raise ValueError("aging_steps must be >= 1")
+        if any(not w > 0 for w in self.tenant_weights.values()):
+            raise ValueError("tenant weights must be positive")
 
 
 @dataclass(frozen=True)
@@ -69,6 +83,8 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self._known: dict[str, Request] = {}
+        self.num_steps = 0  # batches decided so far; a request's age is counted in these
+        self._clock: dict[str, float] = {}  # tenant -> tokens scheduled for it / its weight
 
     # ------------------------------------------------------------ life of a request
 
@@ -80,6 +96,8 @@ class Scheduler:
             req.status, req.finish_reason = RequestStatus.FINISHED, FinishReason.CAPACITY
             return False
         self._known[req.request_id] = req
+        req.arrival_step = self.num_steps
+        self._enter_tenant(req.tenant)
         self.waiting.append(req)
         return True
 
@@ -109,7 +127,7 @@ class Scheduler:
         out = SchedulerOutput()
         budget = self.config.max_num_batched_tokens
         in_batch: set[str] = set()
-        self.running.sort(key=lambda r: r.arrival)
+        self.running.sort(key=lambda r: (self.effective_priority(r), r.arrival))
 
         for req in list(self.running):
             if budget == 0:
@@ -133,10 +151,11 @@ class Scheduler:
             start = req.num_computed_tokens
             out.chunks.append(ScheduledChunk(req, start, n, start + n == total))
             in_batch.add(req.request_id)
+            self.charge(req, n)
             budget -= n
 
         while not out.preempted and self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
-            req = min(self.waiting, key=lambda r: (0 if r.num_preemptions else 1, r.arrival))
+            req = min(self.waiting, key=self._admission_key)
             tokens = req.all_token_ids
             if not self.manager.can_allocate(tokens, self.config.namespace):
                 break  # the head of the queue waits for memory; nobody jumps past it
@@ -148,8 +167,40 @@ class Scheduler:
             out.admitted.append(req)
             n = min(len(tokens) - alloc.num_cached_tokens, budget)
             out.chunks.append(self._chunk(req, n))
+            self.charge(req, n)
             budget -= n
+        self.num_steps += 1
         return out
+
+    # ------------------------------------------------------------ order and shares
+
+    def effective_priority(self, req: Request) -> int:
+        if self.num_steps - req.arrival_step >= self.config.aging_steps:
+            return int(Priority.INTERACTIVE)
+        return int(req.priority)
+
+    def charge(self, req: Request, tokens: int) -> None:
+        """Advance the clock of the request's tenant by ``tokens`` scheduled for it."""
+        self._clock[req.tenant] = self._clock.get(req.tenant, 0.0) + tokens / self.config.tenant_weights.get(req.tenant, 1.0)
+
+    def step_launched_ahead(self, reqs) -> None:
+        """A decode step of ``reqs`` that the engine launched without asking ``schedule``: it
+        counts as a step and its tokens are charged, as if it had been scheduled."""
+        for req in reqs:
+            self.charge(req, 1)
+        self.num_steps += 1
+
+    def tenant_clock(self, tenant: str) -> float:
+        return self._clock.get(tenant, 0.0)
+
+    def _admission_key(self, req: Request):
+        return (self.effective_priority(req), 0 if req.num_preemptions else 1, self._clock.get(req.tenant, 0.0), req.arrival)
+
+    def _enter_tenant(self, tenant: str) -> None:
+        busy = {r.tenant for r in self.waiting} | {r.tenant for r in self.running}
+        busy.discard(tenant)
+        now = min((self._clock.get(t, 0.0) for t in busy), default=0.0)
+        self._clock[tenant] = max(self._clock.get(tenant, 0.0), now)
 
     # ------------------------------------------------------------ internals
 

@@ -80,6 +80,7 @@ class AheadSampler(FakeSampler):
         return FakeTokens(logits)
 
 
-def fake_engine(num_pages=64, page_size=4, max_num_seqs=8, budget=32, ahead=False, **kw):
+def fake_engine(num_pages=64, page_size=4, max_num_seqs=8, budget=32, ahead=False, tenant_weights=None, aging_steps=200, **kw):
     runner = (AheadRunner if ahead else FakeRunner)(num_pages, page_size, max_requests=max_num_seqs, **kw)
-    return LLMEngine(runner, SchedulerConfig(max_num_seqs, budget), sampler=AheadSampler() if ahead else FakeSampler()), runner
+    config = SchedulerConfig(max_num_seqs, budget, tenant_weights=tenant_weights or {}, aging_steps=aging_steps)
+    return LLMEngine(runner, config, sampler=AheadSampler() if ahead else FakeSampler()), runner

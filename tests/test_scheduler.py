@@ -5,7 +5,7 @@ import random
 import pytest
 
 from dli_b200 import SamplingParams
-from dli_b200.engine import FinishReason
+from dli_b200.engine import FinishReason, Priority, SchedulerConfig
 from tests.fake_runner import fake_engine, sequential
 
 
@@ -141,7 +141,8 @@ def test_random_scenarios(seed, ahead):
     pages = rng.randrange(12, 40)
     eng, runner = fake_engine(num_pages=pages, page_size=page, max_num_seqs=rng.randrange(1, 6),
                               budget=rng.randrange(1, 24), watermark=rng.choice([0.0, 0.1]),
-                              prefix_caching=rng.random() < 0.7, ahead=ahead, eviction_policy=rng.choice(["lru", "cost"]))
+                              prefix_caching=rng.random() < 0.7, ahead=ahead, eviction_policy=rng.choice(["lru", "cost"]),
+                              tenant_weights={"t1": 2.0}, aging_steps=rng.choice([3, 200]))
     pending = []
     for i in range(14):
         stem = [7] * rng.randrange(0, 10)
@@ -151,7 +152,8 @@ def test_random_scenarios(seed, ahead):
     while pending or eng.has_unfinished():
         if pending and rng.random() < 0.5:
             rid, p, mt = pending.pop()
-            req = eng.add_request(rid, p, SamplingParams(max_tokens=mt))
+            req = eng.add_request(rid, p, SamplingParams(max_tokens=mt), priority=rng.choice(list(Priority)),
+                                  tenant=rng.choice(["t0", "t1", "t2"]))
             live[rid] = (req, p, mt)
         if live and rng.random() < 0.05:
             rid = rng.choice(sorted(live))
@@ -200,3 +202,113 @@ def test_one_step_ahead_in_steady_decode():
     assert sum(1 for st in runner.steps for rid, *_ in st if rid == "a") == 9
     eng.manager.check_invariants()
     assert eng.manager.min_available_pages() == 64 and not eng._unknown
+
+
+# ---- order among requests: classes, aging, tenants' shares
+
+
+def tokens_by_tenant(runner, steps):
+    served = {}
+    for step in steps:
+        for rid, _, n, _ in step:
+            served[rid[0]] = served.get(rid[0], 0) + n
+    return served
+
+
+def test_tenants_with_queued_work_share_the_engine_whatever_the_order_of_arrival():
+    eng, runner = fake_engine(max_num_seqs=2, budget=64)
+    for i in range(12):  # all of A's requests arrive before any of B's
+        eng.add_request(f"A{i}", [1, 2, i], SamplingParams(max_tokens=5), tenant="A")
+    for i in range(12):
+        eng.add_request(f"B{i}", [3, 4, i], SamplingParams(max_tokens=5), tenant="B")
+    for _ in range(40):
+        eng.step()
+    served = tokens_by_tenant(runner, runner.steps)
+    assert abs(served["A"] - served["B"]) <= 8, served  # one request's worth at most
+    while eng.has_unfinished():
+        eng.step()
+
+
+def test_a_tenant_of_weight_two_gets_about_twice_the_tokens():
+    eng, runner = fake_engine(max_num_seqs=3, budget=64, tenant_weights={"A": 2.0, "B": 1.0})
+    for i in range(30):
+        eng.add_request(f"A{i}", [1, i], SamplingParams(max_tokens=8), tenant="A")
+        eng.add_request(f"B{i}", [2, i], SamplingParams(max_tokens=8), tenant="B")
+    for _ in range(60):
+        eng.step()
+    served = tokens_by_tenant(runner, runner.steps)
+    assert 1.5 < served["A"] / served["B"] < 2.6, served
+    assert eng.scheduler.tenant_clock("A") == pytest.approx(served["A"] / 2.0)
+    while eng.has_unfinished():
+        eng.step()
+
+
+def test_an_idle_spell_earns_no_credit():
+    eng, runner = fake_engine(max_num_seqs=2, budget=64)
+    for i in range(10):
+        eng.add_request(f"A{i}", [1, i], SamplingParams(max_tokens=4), tenant="A")
+    for _ in range(12):
+        eng.step()  # B has been idle all this time
+    for i in range(10):
+        eng.add_request(f"B{i}", [2, i], SamplingParams(max_tokens=4), tenant="B")
+        eng.add_request(f"A{10 + i}", [1, 10 + i], SamplingParams(max_tokens=4), tenant="A")
+    assert eng.scheduler.tenant_clock("B") == eng.scheduler.tenant_clock("A") > 0
+    mark = len(runner.steps)
+    for _ in range(20):
+        eng.step()
+    served = tokens_by_tenant(runner, runner.steps[mark:])
+    assert abs(served["A"] - served["B"]) <= 12, served  # B does not take the engine over to catch up
+    while eng.has_unfinished():
+        eng.step()
+
+
+def test_interactive_goes_before_batch_and_aging_ends_the_wait():
+    eng, runner = fake_engine(max_num_seqs=1, budget=64, aging_steps=6)
+    eng.add_request("old_batch", [5, 5], SamplingParams(max_tokens=2), priority=Priority.BATCH)
+    order = []
+    for i in range(12):  # an interactive request arrives before every step
+        eng.add_request(f"i{i}", [i, 1], SamplingParams(max_tokens=1))
+        eng.step()
+        order += [rid for rid, *_ in runner.steps[-1] if rid not in order]
+    assert order[0] == "i0", "a batch request was admitted in front of an interactive one"
+    assert "old_batch" in order, "the batch request starved"
+    assert 5 <= order.index("old_batch") <= 7  # after aging_steps steps it counts as interactive, and it is the oldest
+    while eng.has_unfinished():
+        eng.step()
+
+
+def test_running_interactive_requests_get_the_budget_before_running_batch_ones():
+    eng, runner = fake_engine(max_num_seqs=4, budget=2)
+    eng.add_request("b0", [1], SamplingParams(max_tokens=30), priority=Priority.BATCH)
+    eng.add_request("b1", [2], SamplingParams(max_tokens=30), priority=Priority.BATCH)
+    eng.step()
+    eng.add_request("i0", [3], SamplingParams(max_tokens=6))
+    eng.step()  # no room in the budget: the two batch requests take it, i0 waits
+    eng.step()
+    for step in runner.steps[3:6]:
+        assert step[0][0] == "i0", step  # once it runs, it is served first, and one batch request sits out
+        assert len(step) == 2
+    while eng.has_unfinished():
+        eng.step()
+
+
+def test_a_preempted_request_comes_back_before_new_ones_of_its_class():
+    eng, runner = fake_engine(num_pages=6, page_size=4, max_num_seqs=4, budget=64, watermark=0.0, prefix_caching=False)
+    a = eng.add_request("a", list(range(8)), SamplingParams(max_tokens=14))
+    b = eng.add_request("b", list(range(20, 28)), SamplingParams(max_tokens=14))
+    while not b.num_preemptions:
+        eng.step()
+    eng.add_request("new", [9], SamplingParams(max_tokens=1))
+    assert eng.scheduler._admission_key(b) < eng.scheduler._admission_key(eng.scheduler._known["new"])
+    while eng.has_unfinished():
+        eng.step()
+    assert a.output_ids == sequential(list(range(8)), 14) and b.output_ids == sequential(list(range(20, 28)), 14)
+
+
+def test_scheduler_config_checks_its_values():
+    with pytest.raises(ValueError, match="aging_steps"):
+        SchedulerConfig(aging_steps=0)
+    with pytest.raises(ValueError, match="positive"):
+        SchedulerConfig(tenant_weights={"A": 0.0})
+    with pytest.raises(ValueError, match=">= 1"):
+        SchedulerConfig(max_num_seqs=0)
