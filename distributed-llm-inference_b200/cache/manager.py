@@ -17,6 +17,7 @@ do not restore a request, so reuse is off.
 
 from __future__ import annotations
 
+import threading
 from dataclasses import dataclass, field
 from typing import Hashable, Sequence
 
@@ -87,7 +88,12 @@ class CacheManager:
         has_state: bool = False,
         watermark: float = 0.01,
         eviction_policy: str = "lru",
+        debug_checks: bool = False,
     ) -> None:
+        # The manager is not locked: it belongs to the one thread that runs the engine's loop.
+        # With ``debug_checks`` every call that changes it verifies that
+        # (src/dli/kv/block_manager.py:177-183,447-449).
+        self._owner = threading.get_ident() if debug_checks else None
         if not 0.0 <= watermark < 1.0:
             raise ValueError("watermark must be in [0, 1)")
         if max_requests < 1:
@@ -110,6 +116,10 @@ class CacheManager:
 
     def has_request(self, rid: Hashable) -> bool:
         return rid in self._requests
+
+    def _confine(self) -> None:
+        if self._owner is not None and threading.get_ident() != self._owner:
+            raise RuntimeError("the cache manager was called from a thread other than the one that made it")
 
     def _get(self, rid: Hashable) -> _Request:
         try:
@@ -203,6 +213,7 @@ class CacheManager:
     def allocate(self, rid: Hashable, token_ids: Sequence[int], *, namespace: bytes = b"", respect_watermark: bool = True) -> Allocation:
         """Admit a request: pages for all its tokens in every group (indexed prefix pages are
         shared, the rest are taken), and a state slot."""
+        self._confine()
         if rid in self._requests:
             raise ValueError(f"request {rid!r} already holds pages")
         if not token_ids:
@@ -237,6 +248,7 @@ class CacheManager:
         If the request's last page is partly filled and shared with a fork, the request gets a page
         of its own first: the returned copies must be carried out before the step that writes the
         new tokens (src/dli/kv/block_manager.py:286-320)."""
+        self._confine()
         req = self._get(rid)
         ps = self.page_size
         first, last = req.num_tokens, req.num_tokens + len(token_ids)
@@ -267,6 +279,7 @@ class CacheManager:
         """A second request that shares every page of ``parent`` (several continuations of one
         prompt).  The first append into the shared, partly filled last page gives the appender a
         page of its own (src/dli/kv/block_manager.py:338-359)."""
+        self._confine()
         src = self._get(parent)
         if child in self._requests:
             raise ValueError(f"request {child!r} already holds pages")
@@ -285,6 +298,7 @@ class CacheManager:
     def mark_computed(self, rid: Hashable, num_computed: int) -> None:
         """Keys and values of the first ``num_computed`` tokens are written: full pages become
         shareable, and windowed groups give back the pages no later token can read."""
+        self._confine()
         req = self._get(rid)
         if not req.num_computed <= num_computed <= req.num_tokens:
             raise ValueError(f"computed must be in [{req.num_computed}, {req.num_tokens}], got {num_computed}")
@@ -323,6 +337,7 @@ class CacheManager:
 
     def set_token(self, rid: Hashable, position: int, token_id: int) -> None:
         """Name the token at ``position`` that was appended as UNKNOWN_TOKEN."""
+        self._confine()
         req = self._get(rid)
         if not self.prefix_caching:
             return
@@ -334,6 +349,7 @@ class CacheManager:
 
     def free(self, rid: Hashable) -> None:
         """Give back everything a finished, aborted or preempted request holds."""
+        self._confine()
         req = self._requests.pop(rid, None)
         if req is None:
             raise UnknownRequest(f"unknown request {rid!r}")
@@ -344,6 +360,7 @@ class CacheManager:
         self._free_slots.append(req.slot)
 
     def reset_prefix_cache(self) -> int:
+        self._confine()
         return sum(pool.drop_index() for pool in self.pools)
 
     # ------------------------------------------------------------ verification

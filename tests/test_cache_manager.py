@@ -292,3 +292,26 @@ def test_fork_without_room_for_the_copy_changes_nothing():
         m.append_slots("b", [9])
     assert (m.block_table("a"), m.block_table("b"), m.num_tokens("b")) == before
     m.check_invariants()
+
+
+def test_debug_checks_refuse_calls_from_another_thread():
+    import threading
+
+    m = CacheManager([GroupSpec(8)], 4, 4, debug_checks=True)
+    m.allocate("a", [1, 2, 3])
+    caught = []
+
+    def elsewhere():
+        for call in (lambda: m.append_slots("a", [4]), lambda: m.free("a"), lambda: m.allocate("b", [1])):
+            try:
+                call()
+            except RuntimeError as e:
+                caught.append(str(e))
+
+    t = threading.Thread(target=elsewhere)
+    t.start()
+    t.join()
+    assert len(caught) == 3 and all("thread" in c for c in caught)
+    assert m.num_tokens("a") == 3 and not m.has_request("b")  # nothing happened
+    m.free("a")  # the owner may
+    m.check_invariants()
