@@ -1,4 +1,4 @@
-"""Command line of the engine: ``dli generate``, ``dli init``, ``dli replay``.
+"""Command line of the engine: ``dli generate``, ``dli init``, ``dli bench``, ``dli workload``, ``dli replay``.
 
 Option names and meanings are those of the reference's only command line, its
 server (src/dli/server/__main__.py:65-124): --model, --device, --dtype,
@@ -67,14 +67,9 @@ def cmd_bench(args) -> int:
 
     import torch
 
-    from . import LLMEngine, SamplingParams, SchedulerConfig, load_model, random_model
+    from . import LLMEngine, SamplingParams, SchedulerConfig
 
-    if not args.random_config and not args.model:
-        raise SystemExit("give --model DIR or --random-config JSON")
-    if args.random_config:
-        model = random_model(json.loads(Path(args.random_config).read_text()), args.seed, "bfloat16" if args.dtype == "auto" else args.dtype, args.device)
-    else:
-        model = load_model(args.model, "bfloat16" if args.dtype == "auto" else args.dtype, args.device)
+    model = _model_for(args)
     total = args.input_len + args.output_len
     blocks = args.num_blocks or args.batch * (-(-total // args.block_size) + 1)
     eng = LLMEngine.for_model(model, num_blocks=blocks, block_size=args.block_size, enable_prefix_caching=not args.no_prefix_caching,
@@ -105,6 +100,82 @@ def cmd_bench(args) -> int:
         "graph_steps": eng.runner.graph_steps, "weight_bytes": weights, "kv_bytes_read_per_step": kv,
         "bandwidth_floor_ms": (weights + kv) / (args.bandwidth_gbs * 1e9) * 1e3, "bandwidth_gbs": args.bandwidth_gbs,
         "max_memory_allocated_mib": torch.cuda.max_memory_allocated() >> 20,
+    }))
+    return 0
+
+
+def _model_for(args):
+    from . import load_model, random_model
+
+    if not args.random_config and not args.model:
+        raise SystemExit("give --model DIR or --random-config JSON")
+    dtype = "bfloat16" if args.dtype == "auto" else args.dtype
+    if args.random_config:
+        return random_model(json.loads(Path(args.random_config).read_text()), args.seed, dtype, args.device)
+    return load_model(args.model, dtype, args.device)
+
+
+def cmd_workload(args) -> int:
+    """A closed set of requests, all queued at the start and run to the end through the engine:
+    prompts of seeded random ids with lengths uniform in [--min-input, --max-input], a share of
+    them opening with the same --shared-prefix-len ids, --output-len tokens generated for each
+    (end-of-sequence ignored, temperature 0, as the reference's load generator sends them:
+    benchmarks/methodology.md:55-67).  Prompt portions and decoded tokens share the steps."""
+    import random
+    import statistics
+    import time
+
+    import torch
+
+    from . import LLMEngine, SamplingParams, SchedulerConfig
+
+    model = _model_for(args)
+    rng = random.Random(args.seed)
+    vocab = model.spec.vocab_size
+    low = min(1000, vocab - 1)
+    stem = [rng.randrange(low, vocab) for _ in range(args.shared_prefix_len)]
+    prompts = []
+    for i in range(args.num_requests):
+        n = rng.randint(args.min_input, args.max_input)
+        shared = args.shared_prefix_len > 0 and rng.random() < args.shared_fraction
+        head = stem[:n] if shared else []
+        prompts.append(head + [rng.randrange(low, vocab) for _ in range(n - len(head))])
+    longest = max(len(p) for p in prompts) + args.output_len
+    per_request = -(-longest // args.block_size) + 1
+    blocks = args.num_blocks or (None if args.kv_cache_gb else args.max_num_seqs * per_request)
+    eng = LLMEngine.for_model(model, num_blocks=blocks, kv_cache_gb=args.kv_cache_gb, block_size=args.block_size,
+                              enable_prefix_caching=not args.no_prefix_caching,
+                              config=SchedulerConfig(args.max_num_seqs, args.max_num_batched_tokens), seed=args.seed)
+    params = SamplingParams(max_tokens=args.output_len, ignore_eos=True)
+    for rep in range(args.warmup_runs + 1):  # warm-up runs compile nothing new later: same lengths, other ids
+        if rep:
+            eng.manager.reset_prefix_cache()
+        timed = rep == args.warmup_runs
+        reqs = [eng.add_request(f"w{rep}-{i}", p if timed else [(t + 1 + rep) % vocab for t in p], params) for i, p in enumerate(prompts)]
+        first_token = {}
+        first_step = len(eng.stats.steps)
+        hit_before = eng.manager.stats.prompt_tokens_hit
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while eng.has_unfinished():
+            for out in eng.step():
+                first_token.setdefault(out.request_id, time.perf_counter() - t0)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+    st = eng.stats.steps[first_step:]
+    generated = sum(len(r.output_ids) for r in reqs)
+    prompt_tokens = sum(len(p) for p in prompts)
+    ttft = sorted(first_token.values())
+    print(json.dumps({
+        "requests": len(reqs), "prompt_tokens": prompt_tokens, "generated_tokens": generated, "seconds": seconds,
+        "generated_tokens_per_s": generated / seconds, "total_tokens_per_s": (prompt_tokens + generated) / seconds,
+        "steps": len(st), "prefill_tokens_run": sum(s.num_prefill_tokens for s in st), "decode_tokens_run": sum(s.num_decode_tokens for s in st),
+        "prompt_tokens_reused": eng.manager.stats.prompt_tokens_hit - hit_before,
+        "preemptions": sum(s.num_preempted for s in st), "mean_batched_tokens": statistics.mean(s.num_batched_tokens for s in st),
+        "first_token_s_median": ttft[len(ttft) // 2], "first_token_s_max": ttft[-1],
+        "schedule_ms_mean": statistics.mean(s.schedule_s for s in st) * 1e3, "forward_ms_mean": statistics.mean(s.forward_s for s in st) * 1e3,
+        "steps_launched_ahead": eng.steps_ahead, "graph_steps": eng.runner.graph_steps,
+        "pages": eng.manager.groups[0].num_pages, "max_memory_allocated_mib": torch.cuda.max_memory_allocated() >> 20,
     }))
     return 0
 
@@ -155,6 +226,18 @@ def main(argv: list[str] | None = None) -> int:
     b.add_argument("--warmup", type=int, default=8)
     b.add_argument("--bandwidth-gbs", type=float, default=6650.0, help="memory bandwidth for the floor, GB/s")
     b.set_defaults(fn=cmd_bench)
+
+    w = sub.add_parser("workload", help="run a closed set of requests of mixed lengths, part of them sharing a prefix, to the end")
+    _engine_options(w, model_required=False)
+    w.add_argument("--random-config", default=None, help="a config.json: run with seeded random weights instead of --model")
+    w.add_argument("--num-requests", type=int, default=64)
+    w.add_argument("--min-input", type=int, default=128)
+    w.add_argument("--max-input", type=int, default=2048)
+    w.add_argument("--output-len", type=int, default=256)
+    w.add_argument("--shared-prefix-len", type=int, default=512, help="ids that the sharing requests open with (0: nobody shares)")
+    w.add_argument("--shared-fraction", type=float, default=0.5, help="share of the requests that open with the shared ids")
+    w.add_argument("--warmup-runs", type=int, default=1, help="untimed runs of the same lengths before the timed one")
+    w.set_defaults(fn=cmd_workload)
 
     r = sub.add_parser("replay", help="trace replay (see bin/trace_run)", add_help=False)
     r.set_defaults(fn=None)

@@ -184,6 +184,15 @@ def test_command_line_generates(models, tmp_path):
     assert out.returncode == 0, out.stderr
     rec = json.loads(out.stdout.strip().splitlines()[-1])
     assert rec["batch"] == 3 and rec["tokens_per_s"] > 0 and rec["steps_launched_ahead"] >= 5 and rec["bandwidth_floor_ms"] > 0
+    # and `dli workload` runs a closed set of requests, half of them behind a shared prefix, in a pool that makes some wait
+    out = subprocess.run([sys.executable, str(ROOT / "bin" / "dli"), "workload", "--random-config", str(tmp_path / "c.json"), "--num-requests", "9",
+                          "--min-input", "5", "--max-input", "40", "--output-len", "12", "--shared-prefix-len", "16", "--shared-fraction", "0.6",
+                          "--block-size", "4", "--max-num-seqs", "4", "--max-num-batched-tokens", "24", "--num-blocks", "40"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    rec = json.loads(out.stdout.strip().splitlines()[-1])
+    assert rec["requests"] == 9 and rec["generated_tokens"] == 9 * 12 and rec["prompt_tokens_reused"] > 0
+    assert rec["decode_tokens_run"] >= 9 * 11 and rec["generated_tokens_per_s"] > 0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
