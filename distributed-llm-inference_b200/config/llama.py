@@ -22,7 +22,7 @@ class RopeConfig:
     """Rotary embedding constants (src/dli/model/config.py:22-39)."""
 
     theta: float
-    rope_type: str = "default"  # "default" | "llama3"
+    rope_type: str = "default"  # "default" | "linear" | "llama3"
     factor: float = 1.0
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
@@ -121,8 +121,8 @@ def _parse_rope(cfg: dict[str, Any]) -> RopeConfig:
     merged = {**dict(cfg.get("rope_scaling") or {}), **dict(cfg.get("rope_parameters") or {})}
     theta = float(merged.get("rope_theta", cfg.get("rope_theta", 10000.0)))
     rope_type = merged.get("rope_type", merged.get("type", "default"))
-    if rope_type not in ("default", "llama3"):
-        raise UnsupportedModelError(f"rope_type={rope_type!r} is not supported (default, llama3)")
+    if rope_type not in ("default", "linear", "llama3"):
+        raise UnsupportedModelError(f"rope_type={rope_type!r} is not supported (default, linear, llama3)")
     if rope_type == "default":
         return RopeConfig(theta=theta)
     if "factor" not in merged:

@@ -1,4 +1,4 @@
-"""Rotary position encoding (rotate-half pairing), default and llama3 frequency scaling."""
+"""Rotary position encoding (rotate-half pairing) with default, linear and llama3 frequency scaling."""
 
 from __future__ import annotations
 
@@ -13,7 +13,8 @@ from .base import Part, register_part
 
 def inverse_frequencies(params) -> torch.Tensor:
     """[rotary_dim / 2] float32 on the CPU, every step in float32 as the reference does it
-    (src/dli/model/rope.py:21-47): exponents 2j/d, 1 / theta**e; for ``llama3`` wavelengths
+    (src/dli/model/rope.py:21-47): exponents 2j/d, 1 / theta**e; ``linear`` divides every
+    frequency by ``factor`` (positions are interpolated); for ``llama3`` wavelengths
     beyond original_max / low_freq_factor are divided by ``factor``, those under
     original_max / high_freq_factor kept, and the band between interpolated."""
     d = int(params["rotary_dim"])
@@ -22,8 +23,10 @@ def inverse_frequencies(params) -> torch.Tensor:
     scaling = params.get("scaling", "default")
     if scaling == "default":
         return inv
+    if scaling == "linear":
+        return inv / float(params["factor"])
     if scaling != "llama3":
-        raise ValueError(f"rotary scaling {scaling!r} is not supported (default, llama3)")
+        raise ValueError(f"rotary scaling {scaling!r} is not supported (default, linear, llama3)")
     old = params["original_max_position_embeddings"]
     factor, low, high = float(params["factor"]), float(params["low_freq_factor"]), float(params["high_freq_factor"])
     wavelen = 2 * math.pi / inv

@@ -104,6 +104,8 @@ def inverse_frequencies(c: dict) -> np.ndarray:
     inv = (f32(1.0) / np.power(f32(c["theta"]), exponents, dtype=f32)).astype(f32)
     if c["rope_type"] == "default":
         return inv
+    if c["rope_type"] == "linear":
+        return (inv / f32(c["factor"])).astype(f32)
     if c["rope_type"] != "llama3":
         raise ValueError(c["rope_type"])
     old = c["old_ctx"]

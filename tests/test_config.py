@@ -2,6 +2,7 @@
 
 import copy
 
+import numpy as np
 import pytest
 
 from dli_b200.config import (Architecture, LlamaConfig, UnsupportedModelError, llama_model_spec, register_architecture,
@@ -57,7 +58,7 @@ def test_rope_parameters_win_and_legacy_type_key():
     ({"attention_bias": True}, "attention_bias"),
     ({"mlp_bias": True}, "mlp_bias"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "rope_type"),
-    ({"rope_scaling": {"rope_type": "linear", "factor": 2.0}}, "rope_type"),
+    ({"rope_scaling": {"rope_type": "dynamic", "factor": 2.0}}, "rope_type"),
     ({"num_key_value_heads": 3}, "num_key_value_heads"),
     ({"head_dim": 15}, "head_dim"),
     ({"model_type": "qwen2"}, "model_type"),
@@ -107,3 +108,19 @@ def test_run_order_is_validated():
     ok = ModelSpec(spec.hidden_size, spec.vocab_size, spec.embedding, spec.layers,
                    (RunStep(0), RunStep(1), RunStep(0), RunStep(1, cache_of=1)), spec.final_norm, spec.head)
     assert len(ok.run_order) == 4
+
+
+def test_linear_rope_scaling_divides_every_frequency():
+    from tests.plain import llama_plain as plain
+    from tests.tiny_configs import TINY_C
+
+    c = LlamaConfig.from_hf_dict(TINY_C)
+    assert c.rope.rope_type == "linear" and c.rope.factor == 2.5
+    position = llama_model_spec(c).layers[0].parts["mixer"].params["position"]
+    assert position.params["scaling"] == "linear" and position.params["factor"] == 2.5
+    pc = plain.read_config(TINY_C)
+    base = plain.inverse_frequencies({**pc, "rope_type": "default"})
+    assert np.allclose(plain.inverse_frequencies(pc), base / np.float32(2.5), rtol=1e-7)
+    with pytest.raises(KeyError):
+        LlamaConfig.from_hf_dict({**TINY_C, "rope_scaling": {"type": "linear"}})
+    assert LlamaConfig.from_hf_dict(c.to_hf_dict()).rope == c.rope  # survives the round trip through config.json

@@ -65,7 +65,7 @@ def test_norm_part(dtype):
     np.testing.assert_allclose(np32(y), want, atol=TOL[dtype])
 
 
-@pytest.mark.parametrize("cfg", [TINY_A, TINY_B, TINY_C], ids=["default", "llama3", "default48"])
+@pytest.mark.parametrize("cfg", [TINY_A, TINY_B, TINY_C], ids=["default", "llama3", "linear48"])
 def test_rotary_part_frequencies(cfg):
     spec = llama_model_spec(LlamaConfig.from_hf_dict(cfg))
     pos = build_part("position", spec.layers[0].parts["mixer"].params["position"], env(torch.float32))

@@ -3,7 +3,7 @@
 They differ in every size and option: head counts and groups (GQA 4/2, MQA 3/1,
 MHA 5/5), head sizes 16/32/48, widths and vocabularies that are no power of
 two, number of layers, eps, rope (default / llama3 with all three frequency
-bands inside 256 positions), tied and untied heads, and the KV page size the
+bands inside 256 positions / linear), tied and untied heads, and the KV page size the
 tests pair with each.
 """
 
@@ -49,7 +49,7 @@ TINY_B = {
 }
 
 # A third one: MHA, head_dim 48 (a multiple of 16 that is no power of two),
-# head_dim * heads != hidden, odd vocabulary.
+# head_dim * heads != hidden, odd vocabulary, linear rope scaling (legacy spelling of the key).
 TINY_C = {
     "architectures": ["LlamaForCausalLM"],
     "model_type": "llama",
@@ -61,6 +61,7 @@ TINY_C = {
     "intermediate_size": 144,
     "vocab_size": 517,
     "rope_theta": 130000.0,
+    "rope_scaling": {"type": "linear", "factor": 2.5},
     "tie_word_embeddings": True,
     "rms_norm_eps": 3e-6,
     "max_position_embeddings": 512,
