@@ -29,14 +29,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-LLAMA_3_2_1B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 16, "hidden_size": 2048,
-    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256,
-    "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                     "original_max_position_embeddings": 8192},
-    "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "hidden_act": "silu",
-}
+LLAMA_3_2_1B = json.loads((ROOT / "distributed-llm-inference_b200" / "config" / "shapes" / "llama-3.2-1b.json").read_text())
 PROMPT_LEN = 2048
 CONTEXT = 4096
 PAGE = 16

@@ -104,6 +104,20 @@ def cmd_bench(args) -> int:
     return 0
 
 
+SHAPES = Path(__file__).resolve().parent / "config" / "shapes"  # config.json files of the models that benchmarks name
+
+
+def shape_config(name_or_path: str) -> dict:
+    """A config.json given as a path, or as the name of one of the shapes kept with the package."""
+    path = Path(name_or_path)
+    if not path.exists():
+        path = SHAPES / f"{name_or_path}.json"
+    if not path.exists():
+        known = ", ".join(sorted(p.stem for p in SHAPES.glob("*.json")))
+        raise SystemExit(f"{name_or_path!r} is neither a config.json nor one of the shapes {known}")
+    return json.loads(path.read_text())
+
+
 def _model_for(args):
     from . import load_model, random_model
 
@@ -111,7 +125,7 @@ def _model_for(args):
         raise SystemExit("give --model DIR or --random-config JSON")
     dtype = "bfloat16" if args.dtype == "auto" else args.dtype
     if args.random_config:
-        return random_model(json.loads(Path(args.random_config).read_text()), args.seed, dtype, args.device)
+        return random_model(shape_config(args.random_config), args.seed, dtype, args.device)
     return load_model(args.model, dtype, args.device)
 
 
@@ -218,7 +232,7 @@ def main(argv: list[str] | None = None) -> int:
 
     b = sub.add_parser("bench", help="time steady decode steps of a batch through the engine")
     _engine_options(b, model_required=False)
-    b.add_argument("--random-config", default=None, help="a config.json: run with seeded random weights instead of --model")
+    b.add_argument("--random-config", default=None, help="a config.json, or the name of a shape kept with the package (llama-3.2-1b, smollm2-1.7b, llama-3.2-3b): run with seeded random weights instead of --model")
     b.add_argument("--batch", type=int, default=8)
     b.add_argument("--input-len", type=int, default=256)
     b.add_argument("--output-len", type=int, default=128)
@@ -229,7 +243,7 @@ def main(argv: list[str] | None = None) -> int:
 
     w = sub.add_parser("workload", help="run a closed set of requests of mixed lengths, part of them sharing a prefix, to the end")
     _engine_options(w, model_required=False)
-    w.add_argument("--random-config", default=None, help="a config.json: run with seeded random weights instead of --model")
+    w.add_argument("--random-config", default=None, help="a config.json, or the name of a shape kept with the package (llama-3.2-1b, smollm2-1.7b, llama-3.2-3b): run with seeded random weights instead of --model")
     w.add_argument("--num-requests", type=int, default=64)
     w.add_argument("--min-input", type=int, default=128)
     w.add_argument("--max-input", type=int, default=2048)
