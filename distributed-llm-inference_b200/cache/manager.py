@@ -206,9 +206,9 @@ class CacheManager:
                 return False
         return True
 
-    def can_allocate(self, token_ids: Sequence[int], namespace: bytes = b"") -> bool:
+    def can_allocate(self, token_ids: Sequence[int], namespace: bytes = b"", respect_watermark: bool = True) -> bool:
         hits, _ = self._hits(token_ids, namespace)
-        return self._admissible(len(token_ids), hits, True)
+        return self._admissible(len(token_ids), hits, respect_watermark)
 
     def allocate(self, rid: Hashable, token_ids: Sequence[int], *, namespace: bytes = b"", respect_watermark: bool = True) -> Allocation:
         """Admit a request: pages for all its tokens in every group (indexed prefix pages are

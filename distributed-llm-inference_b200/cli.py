@@ -72,14 +72,19 @@ def cmd_bench(args) -> int:
     model = _model_for(args)
     total = args.input_len + args.output_len
     blocks = args.num_blocks or args.batch * (-(-total // args.block_size) + 1)
+    # no pages are held back: the pool is sized so that all requests run at once, to their last token
     eng = LLMEngine.for_model(model, num_blocks=blocks, block_size=args.block_size, enable_prefix_caching=not args.no_prefix_caching,
-                              config=SchedulerConfig(args.batch, max(args.max_num_batched_tokens, args.batch)), seed=args.seed)
+                              config=SchedulerConfig(args.batch, max(args.max_num_batched_tokens, args.batch)), seed=args.seed, watermark=0.0)
     g = torch.Generator().manual_seed(0)
     for i in range(args.batch):
         ids = torch.randint(min(1000, model.spec.vocab_size - 1), model.spec.vocab_size, (args.input_len,), generator=g).tolist()
         eng.add_request(f"r{i}", ids, SamplingParams(max_tokens=args.output_len, ignore_eos=True))
     while any(r.num_computed_tokens < args.input_len for r in eng.scheduler.running + list(eng.scheduler.waiting)):
         eng.step()
+        if eng.stats.steps[-1].num_batched_tokens == 0:
+            raise SystemExit("the prompts make no progress: the pool (--num-blocks) is too small for one of them")
+    if len(eng.scheduler.running) != args.batch:
+        raise SystemExit(f"only {len(eng.scheduler.running)} of {args.batch} requests run at once: the steps timed would not be steps of the whole batch")
     for _ in range(args.warmup):
         eng.step()
     torch.cuda.synchronize()
@@ -89,6 +94,8 @@ def cmd_bench(args) -> int:
         eng.step()
     torch.cuda.synchronize()
     step_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    if len(eng.scheduler.running) != args.batch:
+        raise SystemExit(f"requests ended before the {args.warmup} + {args.steps} steps were over: raise --output-len (now {args.output_len})")
     st = eng.stats.steps[first:]
     weights = sum(t.numel() * t.element_size() for t in {id(t): t for part in model.parts() for t in vars(part).values() if isinstance(t, torch.Tensor)}.values())
     ctx = statistics.mean(r.num_computed_tokens for r in eng.scheduler.running) if eng.scheduler.running else 0

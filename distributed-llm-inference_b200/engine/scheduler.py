@@ -14,6 +14,9 @@ yield, the requester itself is preempted.  A step that preempted admits nobody.
 A request whose prompt plus ``max_tokens`` can never fit in the pool is finished
 at once with reason ``capacity``, so the oldest running request can always
 finish and the engine cannot livelock.  (src/dli/engine/scheduler.py:102-120,255-267.)
+One case the reference leaves open is closed here: a request that fits the pool but
+not the pool less its watermark is admitted when nobody runs (the reference would
+keep it waiting for ever).
 
 Order among requests (src/dli/engine/scheduler.py:218-242).  Running requests are
 served by (class, arrival): an INTERACTIVE request before a BATCH one, and a
@@ -157,9 +160,13 @@ class Scheduler:
         while not out.preempted and self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
             req = min(self.waiting, key=self._admission_key)
             tokens = req.all_token_ids
-            if not self.manager.can_allocate(tokens, self.config.namespace):
+            # The pages held back by the watermark are room for running requests to grow into.
+            # With nobody running there is nobody to keep them for, and a request that needs
+            # them would otherwise wait for ever (it passed the capacity check, so it fits alone).
+            hold_back = bool(self.running)
+            if not self.manager.can_allocate(tokens, self.config.namespace, hold_back):
                 break  # the head of the queue waits for memory; nobody jumps past it
-            alloc = self.manager.allocate(req.request_id, tokens, namespace=self.config.namespace)
+            alloc = self.manager.allocate(req.request_id, tokens, namespace=self.config.namespace, respect_watermark=hold_back)
             self.waiting.remove(req)
             req.status = RequestStatus.RUNNING
             req.num_computed_tokens = alloc.num_cached_tokens

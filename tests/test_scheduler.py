@@ -312,3 +312,20 @@ def test_scheduler_config_checks_its_values():
         SchedulerConfig(tenant_weights={"A": 0.0})
     with pytest.raises(ValueError, match=">= 1"):
         SchedulerConfig(max_num_seqs=0)
+
+
+def test_a_request_that_needs_the_watermark_pages_runs_when_it_is_alone():
+    """10 pages, 2 of them held back for running requests: a request of 9 pages passes the
+    capacity check, can never be admitted beside the watermark, and must still run."""
+    eng, runner = fake_engine(num_pages=10, page_size=4, budget=64, watermark=0.2)
+    small = eng.add_request("small", [1, 2, 3], SamplingParams(max_tokens=4))
+    big = eng.add_request("big", list(range(30)), SamplingParams(max_tokens=6))  # 36 tokens = 9 pages
+    steps = 0
+    while eng.has_unfinished():
+        eng.step()
+        steps += 1
+        assert steps < 100, "the big request waits for ever"
+    assert big.output_ids == sequential(list(range(30)), 6) and small.output_ids == sequential([1, 2, 3], 4)
+    first_big = next(i for i, st in enumerate(runner.steps) if any(rid == "big" for rid, *_ in st))
+    assert all(rid != "small" for rid, *_ in runner.steps[first_big]), "it was admitted beside a running request"
+    eng.manager.check_invariants()
