@@ -1,12 +1,12 @@
 from .batch import StepBatch, StepEntry, build_batch
-from .generate import greedy_generate
+from .generate import PagedGeneration, PagedSequence, greedy_generate, paged_greedy_generate
 from .llm_engine import LLMEngine, RequestOutput, StepStats
 from .request import FinishReason, Priority, Request, RequestStatus
 from .runner import ModelRunner, load_model, random_model, resolve_dtype
 from .scheduler import ScheduledChunk, Scheduler, SchedulerConfig, SchedulerOutput
 
 __all__ = [
-    "FinishReason", "LLMEngine", "ModelRunner", "Priority", "Request", "RequestOutput", "RequestStatus", "ScheduledChunk",
+    "FinishReason", "LLMEngine", "ModelRunner", "PagedGeneration", "PagedSequence", "Priority", "Request", "RequestOutput", "RequestStatus", "ScheduledChunk",
     "Scheduler", "SchedulerConfig", "SchedulerOutput", "StepBatch", "StepEntry", "StepStats", "build_batch",
-    "greedy_generate", "load_model", "random_model", "resolve_dtype",
+    "greedy_generate", "load_model", "paged_greedy_generate", "random_model", "resolve_dtype",
 ]

@@ -29,6 +29,7 @@ class FakeRunner:
                                     enable_prefix_caching=prefix_caching, watermark=watermark, eviction_policy=eviction_policy)
         self.started = []
         self.steps = []
+        self.prompts, self.histories, self.stepped = {}, {}, []
 
     def start_request(self, request_id, slot):
         self.started.append(request_id)
@@ -52,6 +53,30 @@ class FakeRunner:
                 rows.append(next_token(history))
         self.manager.check_invariants()
         return rows
+
+
+    def step(self, entries):
+        """The step function's side of the fake: rows of 50 "logits" whose maximum is the hash of the
+        history up to the wanted token.  ``self.prompts[rid]`` must hold the request's prompt, so that
+        tokens served by the prefix index (which a step never sees) are part of the history."""
+        import numpy as np
+
+        rows = []
+        for e in entries:
+            rid = e.request_id
+            done = self.manager.num_computed_tokens(rid)
+            hist = self.histories.setdefault(rid, list(self.prompts[rid][:done]))
+            assert len(hist) == done, "a step does not start where the cache ends"
+            assert self.manager.num_tokens(rid) >= done + len(e.token_ids), "tokens without reserved slots"
+            for w in e.want:
+                row = np.zeros(50, dtype=np.float32)
+                row[next_token(hist + list(e.token_ids[: w + 1]))] = 1.0
+                rows.append(row)
+            hist.extend(e.token_ids)
+            self.manager.mark_computed(rid, done + len(e.token_ids))
+            self.stepped.append((rid, done, len(e.token_ids)))
+        self.manager.check_invariants()
+        return np.stack(rows) if rows else np.zeros((0, 50), dtype=np.float32)
 
 
 class AheadRunner(FakeRunner):

@@ -329,3 +329,40 @@ def test_a_request_that_needs_the_watermark_pages_runs_when_it_is_alone():
     first_big = next(i for i, st in enumerate(runner.steps) if any(rid == "big" for rid, *_ in st))
     assert all(rid != "small" for rid, *_ in runner.steps[first_big]), "it was admitted beside a running request"
     eng.manager.check_invariants()
+
+
+# ---- one request stepped by hand on a shared runner
+
+
+def test_paged_sequence_and_paged_greedy_generate_reuse_the_prefix():
+    import numpy as np
+
+    from dli_b200.engine import PagedSequence, paged_greedy_generate
+    from tests.fake_runner import FakeRunner
+
+    runner = FakeRunner(num_pages=40, page_size=4, watermark=0.0)
+    pick = lambda row: int(np.argmax(row))  # noqa: E731
+    stem = list(range(10, 23))  # 13 tokens: three full pages
+    p1, p2 = stem + [1, 2], stem + [3]
+    runner.prompts.update(a=p1, b=p2)
+    first = paged_greedy_generate(runner, "a", p1, 7, pick=pick)
+    assert first.tokens == sequential(p1, 7) and first.num_cached_prompt_tokens == 0 and not runner.manager.has_request("a")
+    second = paged_greedy_generate(runner, "b", p2, 5, pick=pick, release=False)
+    assert second.tokens == sequential(p2, 5) and second.num_cached_prompt_tokens == 12
+    assert ("b", 12, 2) in runner.stepped, "the prompt's rest did not start behind the reused pages"
+    # an end-of-sequence id ends the generation and is kept
+    stop = sequential(p1, 7)[2]
+    runner.prompts["c"] = p1
+    assert paged_greedy_generate(runner, "c", p1, 7, eos_token_ids={stop}, pick=pick).tokens == sequential(p1, 7)[:3]
+    # feeding forced tokens by hand: the logits after each are those of the history so far
+    seq = PagedSequence(runner, "b")
+    hist = p2 + second.tokens[:-1]  # the last sampled token was never fed
+    for forced in (7, 7, 9):
+        row = seq.feed(forced)
+        hist.append(forced)
+        assert pick(row) == sequential(hist, 1)[0]
+    with pytest.raises(KeyError):
+        PagedSequence(runner, "nobody")
+    runner.manager.free("b")
+    runner.manager.check_invariants()
+    assert runner.manager.min_available_pages() == 40
