@@ -1,4 +1,4 @@
-"""Command line of the engine: ``dli generate``, ``dli init``, ``dli bench``, ``dli workload``, ``dli replay``.
+"""Command line of the engine: ``dli generate``, ``dli init``, ``dli bench``, ``dli workload``, ``dli env``, ``dli replay``.
 
 Option names and meanings are those of the reference's only command line, its
 server (src/dli/server/__main__.py:65-124): --model, --device, --dtype,
@@ -108,6 +108,7 @@ def cmd_bench(args) -> int:
         "bandwidth_floor_ms": (weights + kv) / (args.bandwidth_gbs * 1e9) * 1e3, "bandwidth_gbs": args.bandwidth_gbs,
         "max_memory_allocated_mib": torch.cuda.max_memory_allocated() >> 20,
     }))
+    _note_env(args)
     return 0
 
 
@@ -201,6 +202,20 @@ def cmd_workload(args) -> int:
     return 0
 
 
+def cmd_env(args) -> int:
+    from . import envinfo
+
+    return envinfo.main([args.out] if args.out else [])
+
+
+def _note_env(args) -> None:
+    """``--env-json PATH``: the machine and the code a result came from, written beside it."""
+    if getattr(args, "env_json", None):
+        from . import envinfo
+
+        envinfo.write(args.env_json)
+
+
 def cmd_init(args) -> int:
     import torch
 
@@ -246,6 +261,7 @@ def main(argv: list[str] | None = None) -> int:
     b.add_argument("--steps", type=int, default=20)
     b.add_argument("--warmup", type=int, default=8)
     b.add_argument("--bandwidth-gbs", type=float, default=6650.0, help="memory bandwidth for the floor, GB/s")
+    b.add_argument("--env-json", default=None, help="also write what the run ran on (hardware, driver, libraries, revision) to this file")
     b.set_defaults(fn=cmd_bench)
 
     w = sub.add_parser("workload", help="run a closed set of requests of mixed lengths, part of them sharing a prefix, to the end")
@@ -258,7 +274,12 @@ def main(argv: list[str] | None = None) -> int:
     w.add_argument("--shared-prefix-len", type=int, default=512, help="ids that the sharing requests open with (0: nobody shares)")
     w.add_argument("--shared-fraction", type=float, default=0.5, help="share of the requests that open with the shared ids")
     w.add_argument("--warmup-runs", type=int, default=1, help="untimed runs of the same lengths before the timed one")
+    w.add_argument("--env-json", default=None, help="also write what the run ran on (hardware, driver, libraries, revision) to this file")
     w.set_defaults(fn=cmd_workload)
+
+    e = sub.add_parser("env", help="print what a measurement would run on: hardware, driver, libraries, revision of the code")
+    e.add_argument("--out", default=None, help="write it to this file instead")
+    e.set_defaults(fn=cmd_env)
 
     r = sub.add_parser("replay", help="trace replay (see bin/trace_run)", add_help=False)
     r.set_defaults(fn=None)

@@ -39,19 +39,27 @@ def _say(msg: str) -> None:
     print(f"[dli_b200] {msg}", file=sys.stderr, flush=True)
 
 
+_build_dir: Path | None = None
+
+
 def build_dir() -> Path:
-    env = os.environ.get("DLI_B200_BUILD_DIR")
-    cand = Path(env) if env else SRC_DIR / "_build"
-    try:
-        cand.mkdir(parents=True, exist_ok=True)
-        probe = cand / f".w{os.getpid()}"
-        probe.write_text("")
-        probe.unlink()
-        return cand
-    except OSError:
-        fallback = Path(tempfile.gettempdir()) / f"dli_b200_build_{os.getuid()}"
-        fallback.mkdir(parents=True, exist_ok=True)
-        return fallback
+    """Where the libraries go: decided once per process (several threads may ask at the same time)."""
+    global _build_dir
+    with _lock:
+        if _build_dir is None:
+            env = os.environ.get("DLI_B200_BUILD_DIR")
+            cand = Path(env) if env else SRC_DIR / "_build"
+            try:
+                cand.mkdir(parents=True, exist_ok=True)
+                probe = cand / f".w{os.getpid()}_{threading.get_ident()}"
+                probe.write_text("")
+                probe.unlink()
+                _build_dir = cand
+            except OSError:
+                fallback = Path(tempfile.gettempdir()) / f"dli_b200_build_{os.getuid()}"
+                fallback.mkdir(parents=True, exist_ok=True)
+                _build_dir = fallback
+        return _build_dir
 
 
 def _nvcc() -> str:
