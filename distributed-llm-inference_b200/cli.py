@@ -138,18 +138,19 @@ def _model_for(args):
 
 
 def cmd_workload(args) -> int:
-    """A closed set of requests, all queued at the start and run to the end through the engine:
+    """A closed set of requests run to the end through the engine, all queued at the start or
+    --concurrency of them in flight (the next is submitted when one finishes):
     prompts of seeded random ids with lengths uniform in [--min-input, --max-input], a share of
     them opening with the same --shared-prefix-len ids, --output-len tokens generated for each
     (end-of-sequence ignored, temperature 0, as the reference's load generator sends them:
     benchmarks/methodology.md:55-67).  Prompt portions and decoded tokens share the steps."""
     import random
     import statistics
-    import time
 
     import torch
 
     from . import LLMEngine, SamplingParams, SchedulerConfig
+    from .engine import percentile, run_closed_loop
 
     model = _model_for(args)
     rng = random.Random(args.seed)
@@ -173,32 +174,28 @@ def cmd_workload(args) -> int:
         if rep:
             eng.manager.reset_prefix_cache()
         timed = rep == args.warmup_runs
-        reqs = [eng.add_request(f"w{rep}-{i}", p if timed else [(t + 1 + rep) % vocab for t in p], params) for i, p in enumerate(prompts)]
-        first_token = {}
+        run_prompts = prompts if timed else [[(t + 1 + rep) % vocab for t in p] for p in prompts]
         first_step = len(eng.stats.steps)
         hit_before = eng.manager.stats.prompt_tokens_hit
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        while eng.has_unfinished():
-            for out in eng.step():
-                first_token.setdefault(out.request_id, time.perf_counter() - t0)
-        torch.cuda.synchronize()
-        seconds = time.perf_counter() - t0
+        run = run_closed_loop(eng, run_prompts, params, concurrency=args.concurrency, name=f"w{rep}", synchronize=torch.cuda.synchronize)
     st = eng.stats.steps[first_step:]
+    reqs, seconds = run.requests, run.seconds
     generated = sum(len(r.output_ids) for r in reqs)
     prompt_tokens = sum(len(p) for p in prompts)
-    ttft = sorted(first_token.values())
+    ttft, tpot = run.time_to_first_token(), run.time_per_output_token()
     print(json.dumps({
-        "requests": len(reqs), "prompt_tokens": prompt_tokens, "generated_tokens": generated, "seconds": seconds,
-        "generated_tokens_per_s": generated / seconds, "total_tokens_per_s": (prompt_tokens + generated) / seconds,
+        "requests": len(reqs), "concurrency": args.concurrency or len(reqs), "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+        "seconds": seconds, "generated_tokens_per_s": generated / seconds, "total_tokens_per_s": (prompt_tokens + generated) / seconds,
         "steps": len(st), "prefill_tokens_run": sum(s.num_prefill_tokens for s in st), "decode_tokens_run": sum(s.num_decode_tokens for s in st),
         "prompt_tokens_reused": eng.manager.stats.prompt_tokens_hit - hit_before,
         "preemptions": sum(s.num_preempted for s in st), "mean_batched_tokens": statistics.mean(s.num_batched_tokens for s in st),
-        "first_token_s_median": ttft[len(ttft) // 2], "first_token_s_max": ttft[-1],
+        "first_token_s_median": percentile(ttft, 0.5), "first_token_s_p99": percentile(ttft, 0.99), "first_token_s_max": ttft[-1] if ttft else None,
+        "per_output_token_s_median": percentile(tpot, 0.5), "per_output_token_s_p99": percentile(tpot, 0.99),
         "schedule_ms_mean": statistics.mean(s.schedule_s for s in st) * 1e3, "forward_ms_mean": statistics.mean(s.forward_s for s in st) * 1e3,
         "steps_launched_ahead": eng.steps_ahead, "graph_steps": eng.runner.graph_steps,
         "pages": eng.manager.groups[0].num_pages, "max_memory_allocated_mib": torch.cuda.max_memory_allocated() >> 20,
     }))
+    _note_env(args)
     return 0
 
 
@@ -274,6 +271,7 @@ def main(argv: list[str] | None = None) -> int:
     w.add_argument("--shared-prefix-len", type=int, default=512, help="ids that the sharing requests open with (0: nobody shares)")
     w.add_argument("--shared-fraction", type=float, default=0.5, help="share of the requests that open with the shared ids")
     w.add_argument("--warmup-runs", type=int, default=1, help="untimed runs of the same lengths before the timed one")
+    w.add_argument("--concurrency", type=int, default=None, help="requests in flight: the next is submitted when one finishes (default: all are queued at the start)")
     w.add_argument("--env-json", default=None, help="also write what the run ran on (hardware, driver, libraries, revision) to this file")
     w.set_defaults(fn=cmd_workload)
 

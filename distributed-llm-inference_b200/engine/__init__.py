@@ -4,9 +4,10 @@ from .llm_engine import LLMEngine, RequestOutput, StepStats
 from .request import FinishReason, Priority, Request, RequestStatus
 from .runner import ModelRunner, load_model, random_model, resolve_dtype
 from .scheduler import ScheduledChunk, Scheduler, SchedulerConfig, SchedulerOutput
+from .workload import ClosedLoopResult, percentile, run_closed_loop
 
 __all__ = [
-    "FinishReason", "LLMEngine", "ModelRunner", "PagedGeneration", "PagedSequence", "Priority", "Request", "RequestOutput", "RequestStatus", "ScheduledChunk",
+    "ClosedLoopResult", "FinishReason", "LLMEngine", "ModelRunner", "PagedGeneration", "PagedSequence", "Priority", "Request", "RequestOutput", "RequestStatus", "ScheduledChunk",
     "Scheduler", "SchedulerConfig", "SchedulerOutput", "StepBatch", "StepEntry", "StepStats", "build_batch",
-    "greedy_generate", "load_model", "paged_greedy_generate", "random_model", "resolve_dtype",
+    "greedy_generate", "load_model", "paged_greedy_generate", "random_model", "resolve_dtype", "run_closed_loop",
 ]
