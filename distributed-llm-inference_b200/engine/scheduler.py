@@ -18,15 +18,8 @@ One case the reference leaves open is closed here: a request that fits the pool 
 not the pool less its watermark is admitted when nobody runs (the reference would
 keep it waiting for ever).
 
-Order among requests (src/dli/engine/scheduler.py:218-242).  Running requests are
-served by (class, arrival): an INTERACTIVE request before a BATCH one, and a
-request that has been in the system for ``aging_steps`` steps counts as
-INTERACTIVE, so BATCH work cannot starve for ever.  Victims of preemption come
-from the end of that order.  Admission takes, within the best class, a preempted
-request before a new one, then the request of the tenant that is furthest behind.
-Every tenant has a virtual clock that advances by tokens / weight for each token
-scheduled for it; a tenant that turns up (again) starts at the smallest clock of
-the tenants that have work, so an idle spell earns no credit.
+Who is served first among equals in need (classes of service with aging, tenants'
+weighted shares) is decided by ``ordering.ServiceOrder``.
 """
 
 from __future__ import annotations
@@ -36,7 +29,8 @@ from collections.abc import Mapping
 from dataclasses import dataclass, field
 
 from ..cache import CacheManager, OutOfPages
-from .request import FinishReason, Priority, Request, RequestStatus
+from .ordering import ServiceOrder
+from .request import FinishReason, Request, RequestStatus
 
 
 @dataclass(frozen=True)
@@ -83,11 +77,10 @@ class Scheduler:
     def __init__(self, config: SchedulerConfig, manager: CacheManager) -> None:
         self.config = config
         self.manager = manager
+        self.order = ServiceOrder(config.tenant_weights, config.aging_steps)
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self._known: dict[str, Request] = {}
-        self.num_steps = 0  # batches decided so far; a request's age is counted in these
-        self._clock: dict[str, float] = {}  # tenant -> tokens scheduled for it / its weight
 
     # ------------------------------------------------------------ life of a request
 
@@ -99,8 +92,8 @@ class Scheduler:
             req.status, req.finish_reason = RequestStatus.FINISHED, FinishReason.CAPACITY
             return False
         self._known[req.request_id] = req
-        req.arrival_step = self.num_steps
-        self._enter_tenant(req.tenant)
+        req.arrival_step = self.order.steps
+        self.order.arrive(req.tenant, (r.tenant for r in (*self.waiting, *self.running)))
         self.waiting.append(req)
         return True
 
@@ -124,14 +117,34 @@ class Scheduler:
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
 
+    @property
+    def num_steps(self) -> int:
+        return self.order.steps
+
+    def tenant_clock(self, tenant: str) -> float:
+        return self.order.clock(tenant)
+
     # ------------------------------------------------------------ one step's batch
 
     def schedule(self) -> SchedulerOutput:
         out = SchedulerOutput()
-        budget = self.config.max_num_batched_tokens
-        in_batch: set[str] = set()
-        self.running.sort(key=lambda r: (self.effective_priority(r), r.arrival))
+        left = self._serve_running(out, self.config.max_num_batched_tokens)
+        if not out.preempted:  # a step that had to take pages away gives none out
+            self._admit_waiting(out, left)
+        self.order.tick()
+        return out
 
+    def step_launched_ahead(self, reqs) -> None:
+        """A decode step of ``reqs`` that the engine launched without asking ``schedule``: it
+        counts as a step and its tokens are charged, as if it had been scheduled."""
+        for req in reqs:
+            self.order.charge(req.tenant, 1)
+        self.order.tick()
+
+    def _serve_running(self, out: SchedulerOutput, budget: int) -> int:
+        """Every running request's next token or next portion, in service order; returns the budget left."""
+        in_batch: set[str] = set()
+        self.running.sort(key=self.order.running_key)
         for req in list(self.running):
             if budget == 0:
                 break
@@ -154,11 +167,14 @@ class Scheduler:
             start = req.num_computed_tokens
             out.chunks.append(ScheduledChunk(req, start, n, start + n == total))
             in_batch.add(req.request_id)
-            self.charge(req, n)
+            self.order.charge(req.tenant, n)
             budget -= n
+        return budget
 
-        while not out.preempted and self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
-            req = min(self.waiting, key=self._admission_key)
+    def _admit_waiting(self, out: SchedulerOutput, budget: int) -> None:
+        """Waiting requests, the most deserving first, while budget, request cap and pages allow."""
+        while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
+            req = min(self.waiting, key=self.order.admission_key)
             tokens = req.all_token_ids
             # The pages held back by the watermark are room for running requests to grow into.
             # With nobody running there is nobody to keep them for, and a request that needs
@@ -173,47 +189,11 @@ class Scheduler:
             self.running.append(req)
             out.admitted.append(req)
             n = min(len(tokens) - alloc.num_cached_tokens, budget)
-            out.chunks.append(self._chunk(req, n))
-            self.charge(req, n)
+            out.chunks.append(ScheduledChunk(req, req.num_computed_tokens, n, req.num_computed_tokens + n == len(tokens)))
+            self.order.charge(req.tenant, n)
             budget -= n
-        self.num_steps += 1
-        return out
-
-    # ------------------------------------------------------------ order and shares
-
-    def effective_priority(self, req: Request) -> int:
-        if self.num_steps - req.arrival_step >= self.config.aging_steps:
-            return int(Priority.INTERACTIVE)
-        return int(req.priority)
-
-    def charge(self, req: Request, tokens: int) -> None:
-        """Advance the clock of the request's tenant by ``tokens`` scheduled for it."""
-        self._clock[req.tenant] = self._clock.get(req.tenant, 0.0) + tokens / self.config.tenant_weights.get(req.tenant, 1.0)
-
-    def step_launched_ahead(self, reqs) -> None:
-        """A decode step of ``reqs`` that the engine launched without asking ``schedule``: it
-        counts as a step and its tokens are charged, as if it had been scheduled."""
-        for req in reqs:
-            self.charge(req, 1)
-        self.num_steps += 1
-
-    def tenant_clock(self, tenant: str) -> float:
-        return self._clock.get(tenant, 0.0)
-
-    def _admission_key(self, req: Request):
-        return (self.effective_priority(req), 0 if req.num_preemptions else 1, self._clock.get(req.tenant, 0.0), req.arrival)
-
-    def _enter_tenant(self, tenant: str) -> None:
-        busy = {r.tenant for r in self.waiting} | {r.tenant for r in self.running}
-        busy.discard(tenant)
-        now = min((self._clock.get(t, 0.0) for t in busy), default=0.0)
-        self._clock[tenant] = max(self._clock.get(tenant, 0.0), now)
 
     # ------------------------------------------------------------ internals
-
-    def _chunk(self, req: Request, n: int) -> ScheduledChunk:
-        start = req.num_computed_tokens
-        return ScheduledChunk(req, start, n, needs_logits=start + n == req.num_tokens)
 
     def _reserve(self, req: Request, total: int, out: SchedulerOutput) -> bool:
         """Slots for tokens the cache manager has not seen yet (the newly sampled one)."""

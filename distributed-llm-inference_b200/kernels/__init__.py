@@ -1,0 +1,1 @@
+"""ctypes wrappers of the compiled kernels (ops, attention, gemm)."""

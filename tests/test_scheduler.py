@@ -299,7 +299,7 @@ def test_a_preempted_request_comes_back_before_new_ones_of_its_class():
     while not b.num_preemptions:
         eng.step()
     eng.add_request("new", [9], SamplingParams(max_tokens=1))
-    assert eng.scheduler._admission_key(b) < eng.scheduler._admission_key(eng.scheduler._known["new"])
+    assert eng.scheduler.order.admission_key(b) < eng.scheduler.order.admission_key(eng.scheduler._known["new"])
     while eng.has_unfinished():
         eng.step()
     assert a.output_ids == sequential(list(range(8)), 14) and b.output_ids == sequential(list(range(20, 28)), 14)
