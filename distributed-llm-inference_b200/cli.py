@@ -95,7 +95,8 @@ def cmd_bench(args) -> int:
     torch.cuda.synchronize()
     step_ms = (time.perf_counter() - t0) / args.steps * 1e3
     if len(eng.scheduler.running) != args.batch:
-        raise SystemExit(f"requests ended before the {args.warmup} + {args.steps} steps were over: raise --output-len (now {args.output_len})")
+        raise SystemExit(f"the batch did not stay whole for {args.warmup} + {args.steps} steps: requests ended (raise --output-len, now "
+                         f"{args.output_len}) or were preempted (raise --num-blocks)")
     st = eng.stats.steps[first:]
     weights = sum(t.numel() * t.element_size() for t in {id(t): t for part in model.parts() for t in vars(part).values() if isinstance(t, torch.Tensor)}.values())
     ctx = statistics.mean(r.num_computed_tokens for r in eng.scheduler.running) if eng.scheduler.running else 0

@@ -81,3 +81,51 @@ def test_workload_command_with_a_fake_engine(monkeypatch, capsys, tmp_path):
     assert (tmp_path / "env.json").exists()
     made["engine"].manager.check_invariants()
     assert len(made["engine"].stats.steps) > rec["steps"]  # the warm-up run came first and is not counted
+
+
+def _fake_factory(made):
+    def make(*args, num_blocks=None, block_size=16, config=None, **kw):
+        eng, runner = fake_engine(num_pages=num_blocks or 64, page_size=block_size, max_num_seqs=config.max_num_seqs,
+                                  budget=config.max_num_batched_tokens, watermark=kw.get("watermark", 0.01))
+        runner.graph_steps = 0
+        runner.pools = types.SimpleNamespace(bytes_per_page=lambda *a: [64])
+        made["engine"] = eng
+        return eng
+
+    return make
+
+
+def test_generate_command_with_a_fake_engine(monkeypatch, capsys, tmp_path):
+    made = {}
+    monkeypatch.setattr(LLMEngine, "from_model_dir", staticmethod(_fake_factory(made)))
+    (tmp_path / "prompts.txt").write_text("7 8 9\n\n4,5\n")
+    rc = cli.main(["generate", "--model", "unused", "--prompt-ids", "1,2,3", "--prompt-file", str(tmp_path / "prompts.txt"), "--max-tokens", "5",
+                   "--num-blocks", "32", "--block-size", "4", "--max-num-batched-tokens", "8", "--stop-token-ids", "", "--ignore-eos"])
+    lines = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
+    assert rc == 0 and [rec["prompt_ids"] for rec in lines] == [[1, 2, 3], [7, 8, 9], [4, 5]]
+    assert [rec["output_ids"] for rec in lines] == [sequential(p, 5) for p in ([1, 2, 3], [7, 8, 9], [4, 5])]
+    assert {rec["finish_reason"] for rec in lines} == {"length"}
+    with pytest.raises(SystemExit):
+        cli.main(["generate", "--model", "unused"])  # no prompt at all
+
+
+def test_bench_command_refuses_a_batch_that_is_not_whole(monkeypatch, capsys):
+    import torch
+
+    made = {}
+    monkeypatch.setattr(cli, "_model_for", lambda args: types.SimpleNamespace(
+        spec=types.SimpleNamespace(vocab_size=50, run_order=()), parts=lambda: [], cache_needs=lambda: [], dtype=None))
+    monkeypatch.setattr(LLMEngine, "for_model", staticmethod(_fake_factory(made)))
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a: None)
+    monkeypatch.setattr(torch.cuda, "max_memory_allocated", lambda *a: 0)
+    args = ["bench", "--random-config", "llama-3.2-1b", "--batch", "3", "--input-len", "10", "--block-size", "4", "--warmup", "2"]
+    assert cli.main(args + ["--output-len", "30", "--steps", "5"]) == 0
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["batch"] == 3 and rec["steps"] == 5 and rec["tokens_per_s"] > 0
+    assert made["engine"].manager._reserve == [0], "pages were held back in a pool sized for exactly this batch"
+    with pytest.raises(SystemExit, match="output-len"):
+        cli.main(args + ["--output-len", "6", "--steps", "20"])  # the requests end during the timed steps
+    with pytest.raises(SystemExit, match="only 0 of 3"):
+        cli.main(args + ["--output-len", "30", "--steps", "5", "--num-blocks", "2"])  # no request fits the pool at all
+    with pytest.raises(SystemExit, match="preempted"):
+        cli.main(args + ["--output-len", "30", "--steps", "25", "--num-blocks", "14"])  # all start, but they cannot all grow
