@@ -315,3 +315,101 @@ def test_debug_checks_refuse_calls_from_another_thread():
     assert m.num_tokens("a") == 3 and not m.has_request("b")  # nothing happened
     m.free("a")  # the owner may
     m.check_invariants()
+
+
+# ---- mutants: every kind of damage is noticed by check_invariants
+
+
+def _busy_manager():
+    """Two live requests sharing two indexed pages, one finished request whose pages idle in the index."""
+    m = CacheManager([GroupSpec(16)], 4, 4, watermark=0.0)
+    stem = list(range(8))
+    for rid, tail in (("gone", [50, 51, 52, 53, 54]), ("a", [20, 21, 22]), ("b", [30])):
+        m.allocate(rid, stem + tail)
+        m.mark_computed(rid, len(stem + tail))
+    m.free("gone")
+    m.check_invariants()
+    assert m.pools[0].num_idle >= 1 and m.pools[0].ref[m.block_table("a")[0]] == 2
+    return m
+
+
+def _lose_a_free_page(m):
+    m.pools[0].free.pop()
+
+
+def _free_a_page_twice(m):
+    m.pools[0].free.append(m.pools[0].free[0])
+
+
+def _free_a_page_that_is_held(m):
+    m.pools[0].free.append(m.block_table("a")[-1])
+
+
+def _hold_a_page_twice_without_counting(m):
+    m._requests["b"].tables[0][-1] = m.block_table("a")[-1]
+    m._mirror[0][m.state_slot("b"), len(m.block_table("b")) - 1] = m.block_table("a")[-1]
+
+
+def _drop_a_reference(m):
+    m.pools[0].ref[m.block_table("a")[0]] -= 1
+
+
+def _table_of_the_wrong_length(m):
+    m._requests["a"].tables[0].append(m.pools[0].take())
+
+
+def _table_array_out_of_step(m):
+    m._mirror[0][m.state_slot("a"), 0] += 1
+
+
+def _lose_a_state_slot(m):
+    m._free_slots.pop()
+
+
+def _give_a_held_slot_away(m):
+    m._free_slots.append(m.state_slot("a"))
+
+
+def _forget_a_hash(m):
+    pool = m.pools[0]
+    del pool.by_hash[pool.indexed[m.block_table("a")[1]].digest]
+
+
+def _miscount_children(m):
+    m.pools[0].indexed[m.block_table("a")[0]].children += 1
+
+
+def _miscount_idle(m):
+    m.pools[0].num_idle += 1
+
+
+def _hide_an_idle_leaf_from_eviction(m):
+    pool = m.pools[0]
+    pool.evictable.discard(next(iter(pool.evictable.pages())))
+
+
+def _computed_beyond_tokens(m):
+    m._requests["a"].num_computed = m._requests["a"].num_tokens + 1
+
+
+MUTANTS = [_lose_a_free_page, _free_a_page_twice, _free_a_page_that_is_held, _hold_a_page_twice_without_counting, _drop_a_reference,
+           _table_of_the_wrong_length, _table_array_out_of_step, _lose_a_state_slot, _give_a_held_slot_away, _forget_a_hash,
+           _miscount_children, _miscount_idle, _hide_an_idle_leaf_from_eviction, _computed_beyond_tokens]
+
+
+@pytest.mark.parametrize("damage", MUTANTS, ids=lambda f: f.__name__.strip("_"))
+def test_check_invariants_notices(damage):
+    m = _busy_manager()
+    damage(m)
+    with pytest.raises(AssertionError):
+        m.check_invariants()
+
+
+def test_double_free_and_release_of_a_free_page_raise_at_once():
+    m = _busy_manager()
+    m.free("a")
+    with pytest.raises(UnknownRequest):
+        m.free("a")
+    with pytest.raises(AssertionError):
+        m.pools[0].release(m.pools[0].free[0])
+    m.check_invariants()
