@@ -110,6 +110,7 @@ class LLMEngine:
         self.steps_ahead = 0  # steps that were launched before the ids they run on were read
         self._inflight: _InFlight | None = None
         self._unknown: dict[str, int] = {}  # request -> position whose id the cache manager does not know yet
+        self._preempted_for_nothing = 0  # requests preempted by a scheduling round that produced no batch
 
     # ------------------------------------------------------------ construction
 
@@ -165,11 +166,12 @@ class LLMEngine:
         """Advance by one model step; the tokens it produced, one RequestOutput per request."""
         t0 = time.perf_counter()
         flight, self._inflight = self._inflight, None
+        self._preempted_for_nothing = 0
         if flight is None:
             flight = self._launch_scheduled()
         t1 = time.perf_counter()
         if flight is None:
-            self.stats.steps.append(StepStats(0, 0, 0, 0, 0, t1 - t0, 0.0, 0.0))
+            self.stats.steps.append(StepStats(0, 0, 0, 0, self._preempted_for_nothing, t1 - t0, 0.0, 0.0))
             return []
         ahead = self._launch_ahead(flight) if self.lookahead else None
         t2 = time.perf_counter()
@@ -196,7 +198,17 @@ class LLMEngine:
         reqs = [self.add_request(f"gen-{base}-{i}", p, per[i]) for i, p in enumerate(prompts)]
         while self.has_unfinished():
             self.step()
+            if self.is_stalled():
+                raise RuntimeError("the engine makes no progress: requests wait, nothing runs and nothing could be scheduled")
         return [r.output_ids for r in reqs]
+
+    def is_stalled(self) -> bool:
+        """Requests wait, but the last step scheduled nothing, preempted nobody and none is in flight.  Nothing
+        changes between steps by itself, so the next step would do the same: whoever owns the
+        loop should stop instead of stepping for ever.  (The scheduler's rules exclude this; the
+        check is there so that a fault in them ends a run instead of hanging it.)"""
+        return (self.has_unfinished() and self._inflight is None and bool(self.stats.steps)
+                and self.stats.steps[-1].num_seqs == 0 and self.stats.steps[-1].num_preempted == 0)
 
     # ------------------------------------------------------------ internals
 
@@ -224,6 +236,7 @@ class LLMEngine:
         """Ask the scheduler (every id is known to the host) and launch what it chose."""
         sched = self.scheduler.schedule()
         if not sched.chunks:
+            self._preempted_for_nothing = len(sched.preempted)  # (a lone request that gave up its own pages)
             return None
         for req in sched.admitted:
             self.runner.start_request(req.request_id, self.manager.state_slot(req.request_id))

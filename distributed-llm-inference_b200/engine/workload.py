@@ -93,6 +93,8 @@ def run_closed_loop(engine, prompts: Sequence[Sequence[int]], params: SamplingPa
             res.done_s.setdefault(rid, now)
             live.discard(rid)
         submit_some()
+        if getattr(engine, "is_stalled", lambda: False)():
+            raise RuntimeError("the engine makes no progress: requests wait, nothing runs and nothing could be scheduled")
     if synchronize:
         synchronize()
     res.seconds = clock() - t0

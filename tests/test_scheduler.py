@@ -366,3 +366,18 @@ def test_paged_sequence_and_paged_greedy_generate_reuse_the_prefix():
     runner.manager.free("b")
     runner.manager.check_invariants()
     assert runner.manager.min_available_pages() == 40
+
+
+def test_a_stalled_engine_ends_the_loop_instead_of_stepping_for_ever():
+    from dli_b200.engine import run_closed_loop
+
+    for drive in (lambda e: e.generate([[1, 2, 3]], SamplingParams(max_tokens=2)),
+                  lambda e: run_closed_loop(e, [[1, 2, 3]], SamplingParams(max_tokens=2))):
+        eng, _ = fake_engine()
+        eng.manager.can_allocate = lambda *a, **k: False  # a fault in the rules of admission, made up for the test
+        with pytest.raises(RuntimeError, match="no progress"):
+            drive(eng)
+    eng, _ = fake_engine()
+    assert not eng.is_stalled()
+    eng.generate([[1, 2, 3]], SamplingParams(max_tokens=2))
+    assert not eng.is_stalled()
