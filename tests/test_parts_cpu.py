@@ -1,0 +1,64 @@
+"""The tests of tests/test_parts_gpu.py once more, in float32 on the CPU with torch stand-ins for the
+kernels (tests/cpu_ops.py): each part alone, a block against the plain layer, and the generality of the
+assembly (a layer run twice, a shared cache, a windowed group that gives pages back, other position
+encodings, the toy mixer with state, the toy routed feed-forward).  What they check here is the Python
+above the kernels; the kernels themselves are checked on the GPU."""
+
+import functools
+
+import pytest
+import torch
+
+from dli_b200.engine import random_model
+from tests import cpu_ops
+from tests import test_parts_gpu as g
+from tests.tiny_configs import TINY_A, TINY_B, TINY_C
+
+F32 = torch.float32
+
+
+@pytest.fixture(autouse=True)
+def on_the_cpu(monkeypatch):
+    monkeypatch.setattr(g, "DEV", torch.device("cpu"))
+    monkeypatch.setattr(g, "random_model", functools.partial(random_model, device="cpu"))
+    with cpu_ops.patched():
+        yield
+
+
+def test_norm_feed_forward_embedding_and_head():
+    g.test_norm_part(F32)
+    g.test_feed_forward_part(F32)
+    g.test_embedding_and_head_parts(F32, True)
+    g.test_embedding_and_head_parts(F32, False)
+
+
+@pytest.mark.parametrize("cfg", [TINY_A, TINY_B, TINY_C], ids=["a", "b", "c"])
+def test_frequencies_and_block(cfg):
+    g.test_rotary_part_frequencies(cfg)
+    g.test_block_of_parts_equals_plain_layer(F32, cfg)
+
+
+@pytest.mark.parametrize("rotary_dim", [0, 16])
+def test_other_position_encodings(rotary_dim):
+    g.test_other_position_encodings(F32, rotary_dim)
+
+
+def test_run_order_and_window():
+    g.test_run_order_names_a_layer_twice_and_shares_a_cache(F32)
+    g.test_windowed_layer_has_pages_of_its_own_and_gives_them_back(F32)
+    g.test_unknown_part_kind_is_named()
+
+
+@pytest.fixture
+def toy_architecture():
+    """As the fixture of the same name in tests/test_parts_gpu.py."""
+    g.register_part("mixer", "toy_running_mean")(g.RunningMean)
+    g.register_architecture(g.Architecture("ToyStateLM", g.LlamaConfig.from_hf_dict, lambda cfg: g.toy_spec(cfg.to_hf_dict())))
+    yield {**TINY_B, "architectures": ["ToyStateLM"]}
+    g.unregister_architecture("ToyStateLM")
+    g.unregister_part("mixer", "toy_running_mean")
+
+
+def test_toy_parts(toy_architecture):
+    g.test_toy_mixer_with_state_is_registered_built_and_stepped(toy_architecture)
+    g.test_toy_routed_feed_forward_is_registered_and_stepped()
