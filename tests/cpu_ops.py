@@ -1,4 +1,4 @@
-"""Stand-ins for the float32 kernels, written with torch on the CPU, for tests of the engine's host side.
+"""Stand-ins for the kernels, written with torch on the CPU, for tests of the engine's host side.
 
 The product has no CPU path.  These functions exist only so that the Python above the kernels
 (parts and their wiring, batch building, cache pools, the step function, scheduler, engine, the
@@ -98,6 +98,91 @@ def paged_attention_simt(out, qkv, k_pool, v_pool, block_tables, seq_of_token, p
         out[t] = torch.einsum("hk,khd->hd", w, v).reshape(-1).to(out.dtype)
 
 
+def _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window):
+    """The bfloat16 attention kernels' common contract: sequences [seq0, seq0 + num_seqs); a sequence's
+    tokens sit in rows q_start[s] .. q_start[s + 1] at positions kv_len[s] - q_len .. kv_len[s] - 1."""
+    rows, seqs, pos = [], [], []
+    for s in range(seq0, seq0 + num_seqs):
+        lo, hi = int(q_start[s]), int(q_start[s + 1])
+        rows += range(lo, hi)
+        seqs += [s] * (hi - lo)
+        pos += range(int(kv_len[s]) - (hi - lo), int(kv_len[s]))
+    if not rows:
+        return
+    idx = torch.tensor(rows)
+    part = torch.empty((len(rows), out.shape[1]), dtype=out.dtype)
+    paged_attention_simt(part, qkv[idx], k_pool, v_pool, block_tables, torch.tensor(seqs, dtype=torch.int32),
+                         torch.tensor(pos, dtype=torch.int32), num_heads, scale, window)
+    out[idx] = part
+
+
+def paged_attention_mma(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, max_q_len, first_row, num_heads, scale,
+                        window=None, splits=1, scratch=None):
+    assert splits == 1 or (max_q_len == 1 and scratch is not None)
+    _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window)
+
+
+def paged_decode_tma(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, first_row, num_heads, scale,
+                     window=None, splits=1, scratch=None):
+    assert splits == 1 or scratch is not None
+    _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window)
+
+
+def paged_prefill_tc(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, max_q_len, num_heads, scale,
+                     window=None, query_tiles=0):
+    _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window)
+
+
+# ---- the decode matrix product and its epilogues (bfloat16 in, float32 sums)
+
+
+def _sums(x, weight):
+    """float32 sums of x W^T; x may be ops.ScaledRows, whose row factor is applied to the sums."""
+    if isinstance(x, ops.ScaledRows):
+        factor = torch.rsqrt(x.ssq.sum(-1, keepdim=True) / x.x.shape[1] + x.eps)
+        return (x.x.float() @ weight.float().t()) * factor
+    return x.float() @ weight.float().t()
+
+
+def skinny_gemm_slices(tokens, features, in_features):
+    return 1
+
+
+def skinny_gemm(x, weight, out_dtype=torch.bfloat16, slices=None, out=None, max_stages=0):
+    y = _sums(x, weight).to(out_dtype)
+    if out is None:
+        return y
+    out.copy_(y)
+    return out
+
+
+def skinny_gemm_residual(x, weight, h, gain, eps, slices=None):
+    h += _sums(x, weight)
+    tokens, features = h.shape
+    tiles = -(-features // 128)
+    sq = torch.zeros((tokens, tiles * 128))
+    sq[:, :features] = h * h
+    return ops.ScaledRows((h * gain).to(torch.bfloat16), sq.view(tokens, tiles, 128).sum(-1), eps)
+
+
+def skinny_gemm_swiglu(x, weight_tiled):
+    y = _sums(x, weight_tiled)
+    out = torch.empty((y.shape[0], y.shape[1] // 2), dtype=torch.bfloat16)
+    silu_mul(out, y, tiled=True)
+    return out
+
+
+def skinny_gemm_rotary(x, wqkv, positions, inv_freq, slots, k_pool, v_pool, num_heads, num_kv_heads, head_dim, rotary_dim, page_size, write_kv):
+    qkv = _sums(x, wqkv)  # rotated in float32, rounded once (as the kernel's epilogue does)
+    pools = (torch.empty_like(k_pool, dtype=torch.float32), torch.empty_like(v_pool, dtype=torch.float32)) if write_kv else (None, None)
+    rotary_store(qkv, positions, inv_freq, slots, pools[0], pools[1], num_heads, num_kv_heads, head_dim, rotary_dim, page_size, write_kv)
+    if write_kv:
+        page, off = (slots // page_size).long(), (slots % page_size).long()
+        k_pool[page, :, off, :] = pools[0][page, :, off, :].to(k_pool.dtype)
+        v_pool[page, :, off, :] = pools[1][page, :, off, :].to(v_pool.dtype)
+    return qkv[:, : num_heads * head_dim].to(torch.bfloat16)
+
+
 def sample(out, logits, temperature=None, top_k=None, top_p=None, seed=None, draw=None):
     rows = logits.shape[0]
     for r in range(rows):
@@ -143,19 +228,34 @@ class CpuSampler:
 
 OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_page, "add_rmsnorm": add_rmsnorm,
        "rotary_table": rotary_table, "rotary_store": rotary_store, "silu_mul": silu_mul, "paged_attention_simt": paged_attention_simt,
-       "sample": sample}
+       "paged_attention_mma": paged_attention_mma, "paged_decode_tma": paged_decode_tma, "paged_prefill_tc": paged_prefill_tc,
+       "skinny_gemm_slices": skinny_gemm_slices, "skinny_gemm": skinny_gemm, "skinny_gemm_residual": skinny_gemm_residual,
+       "skinny_gemm_swiglu": skinny_gemm_swiglu, "skinny_gemm_rotary": skinny_gemm_rotary, "sample": sample}
+
+
+calls: dict[str, int] = {}  # how often each stand-in ran since patched() was entered
+
+
+def _counted(name, fn):
+    def run(*args, **kwargs):
+        calls[name] = calls.get(name, 0) + 1
+        return fn(*args, **kwargs)
+
+    return run
 
 
 @contextlib.contextmanager
 def patched():
-    """Inside: float32 models on ``device='cpu'`` build, load and step through the stand-ins."""
+    """Inside: models on ``device='cpu'`` build, load and step through the stand-ins (float32, and bfloat16
+    with the decode products' fused epilogues)."""
     saved = {name: getattr(ops, name) for name in OPS}
     saved_linear, saved_model_linear, saved_require = gemm.linear, model_mod.linear, runner_mod._require_cuda
     saved_lookup = graphs_mod.DecodeGraphs.lookup
     try:
         graphs_mod.DecodeGraphs.lookup = lambda self, *a, **k: None  # no captured steps without a device
+        calls.clear()
         for name, fn in OPS.items():
-            setattr(ops, name, fn)
+            setattr(ops, name, _counted(name, fn))
         gemm.linear = model_mod.linear = linear
         runner_mod._require_cuda = lambda device: None
         yield

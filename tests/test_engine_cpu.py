@@ -11,9 +11,10 @@ from dli_b200 import LLMEngine, SamplingParams, SchedulerConfig
 from dli_b200.engine import ModelRunner, PagedSequence, StepEntry, paged_greedy_generate
 from tests import cpu_ops
 from tests.plain import llama_plain as plain
-from tests.util import make_model_dir, random_tokens
+from tests.util import make_model_dir, plain_weights_for, random_tokens
 
 TOL = 2e-4
+TOLS = {"float32": 2e-4, "bfloat16": 5e-2}
 
 
 @pytest.fixture(scope="module")
@@ -32,8 +33,8 @@ def cpu_kernels():
         yield
 
 
-def engine_for(path, page, num_blocks, config=None, **kw):
-    model = dli_b200.load_model(path, "float32", "cpu")
+def engine_for(path, page, num_blocks, config=None, dtype="float32", **kw):
+    model = dli_b200.load_model(path, dtype, "cpu")
     config = config or SchedulerConfig(8, 512)
     runner = ModelRunner(model, num_pages=num_blocks, page_size=page, max_requests=config.max_num_seqs, cuda_graphs=False,
                          enable_prefix_caching=kw.pop("enable_prefix_caching", True), watermark=kw.pop("watermark", 0.01))
@@ -51,10 +52,10 @@ def plain_greedy(cfg, w, prompt, n):
     return out, gaps
 
 
-def same_tokens(got, want, gaps, what):
+def same_tokens(got, want, gaps, what, tol=TOL):
     for i, (g, w_, gap) in enumerate(zip(got, want, gaps)):
         if g != w_:
-            assert gap < 2 * TOL, f"{what}: token {i} is {g}, plain says {w_} with a gap of {gap:.3g}"
+            assert gap < 2 * tol, f"{what}: token {i} is {g}, plain says {w_} with a gap of {gap:.3g}"
             return
     assert len(got) == len(want)
 
@@ -209,3 +210,78 @@ def test_trace_run_in_process(models, tmp_path, monkeypatch, capsys):
         got = np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(len(rows), -1)
         want = np.stack([full[k][r] for k, r in rows])
         np.testing.assert_allclose(got, want, atol=TOL, err_msg=f"step {step}")
+
+
+# ---- bfloat16: the decode products with their fused epilogues, and the choice of attention kernels
+
+
+TINY_D64 = {  # head size 64, so that the dispatch takes the TMA-fed decode kernel and the tcgen05 prefill kernel
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 192, "vocab_size": 300, "rope_theta": 10000.0,
+    "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 256, "hidden_act": "silu",
+}
+
+
+@pytest.fixture(scope="module")
+def model_d64(tmp_path_factory):
+    import torch as _torch
+
+    from dli_b200.weights import write_safetensors
+
+    path = tmp_path_factory.mktemp("tiny_d64")
+    dli_b200.write_model_dir(path, TINY_D64, seed=7)
+    w = {k: _torch.from_numpy(v.copy()) for k, v in plain.read_safetensors(path / "model.safetensors").items()}
+    for k in w:
+        if k.endswith("q_proj.weight") or k.endswith("k_proj.weight"):
+            w[k] = w[k] * 6.0
+    write_safetensors(path / "model.safetensors", w)
+    return path, TINY_D64, plain.read_safetensors(path / "model.safetensors"), 16
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "d64"])
+def test_bfloat16_logits_whole_in_portions_and_token_by_token(models, model_d64, name):
+    """In bfloat16 a step of up to 8 tokens takes the decode products (rotary and cache write, SiLU * up,
+    residual + the first half of the next norm in their epilogues; the norm's factor applied by the product
+    that reads the rows); longer portions take the library's products and the separate kernels.  Both, and
+    every way of cutting, give the plain logits."""
+    path, cfg, weights, page = model_d64 if name == "d64" else models[name]
+    w = plain_weights_for(weights, "bfloat16")
+    model = dli_b200.load_model(path, "bfloat16", "cpu")
+    toks = random_tokens(cfg["vocab_size"], 41, seed=6)
+    want = plain.forward(cfg, w, toks)
+    runner = ModelRunner(model, num_pages=12, page_size=page, cuda_graphs=False, enable_prefix_caching=False, watermark=0.0)
+    runner.manager.allocate("x", toks)
+    got = runner.step([StepEntry("x", toks, list(range(len(toks))))]).numpy()
+    np.testing.assert_allclose(got, want, atol=TOLS["bfloat16"])
+    runner.manager.free("x")
+    runner.manager.allocate("y", toks[:30])
+    rows, at = [], 0
+    for n in (9, 2, 12, 4, 3):  # portions above and below the 8 tokens that the decode products take
+        rows.append(runner.step([StepEntry("y", toks[at : at + n], list(range(n)))]))
+        at += n
+    for t in toks[30:]:
+        runner.manager.append_slots("y", [t])
+        rows.append(runner.step([StepEntry("y", [t], [0])]))
+    np.testing.assert_allclose(torch.cat(rows).numpy(), want, atol=TOLS["bfloat16"])
+    # the paths that were meant to run did run
+    ran = cpu_ops.calls
+    assert ran.get("skinny_gemm_residual", 0) > 0 and ran.get("add_rmsnorm", 0) > 0 and ran.get("silu_mul", 0) > 0
+    assert ran.get("skinny_gemm_rotary", 0) > 0 or cfg["head_dim"] == 48  # a head of 48 does not divide the product's tile
+    assert (ran.get("skinny_gemm_swiglu", 0) > 0) == (cfg["intermediate_size"] % 64 == 0)
+    if name == "d64":
+        assert ran.get("paged_decode_tma", 0) > 0 and ran.get("paged_prefill_tc", 0) > 0 and "paged_attention_mma" not in ran
+    else:
+        assert ran.get("paged_attention_mma", 0) > 0 and "paged_decode_tma" not in ran
+
+
+@pytest.mark.parametrize("lookahead", [True, False])
+def test_bfloat16_generation_mixed_batches(models, lookahead):
+    path, cfg, weights, page = models["tiny_a"]
+    w = plain_weights_for(weights, "bfloat16")
+    prompts = [random_tokens(256, n, seed=n) for n in (5, 17, 33, 2)]
+    eng = engine_for(path, page, 200, config=SchedulerConfig(8, 20), dtype="bfloat16", lookahead=lookahead)
+    outs = eng.generate(prompts, SamplingParams(max_tokens=8))
+    for p, got in zip(prompts, outs):
+        want, gaps = plain_greedy(cfg, w, p, 8)
+        same_tokens(got, want, gaps, f"prompt of {len(p)}", TOLS["bfloat16"])
+    eng.manager.check_invariants()

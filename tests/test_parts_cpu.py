@@ -1,4 +1,4 @@
-"""The tests of tests/test_parts_gpu.py once more, in float32 on the CPU with torch stand-ins for the
+"""The tests of tests/test_parts_gpu.py once more, on the CPU with torch stand-ins for the
 kernels (tests/cpu_ops.py): each part alone, a block against the plain layer, and the generality of the
 assembly (a layer run twice, a shared cache, a windowed group that gives pages back, other position
 encodings, the toy mixer with state, the toy routed feed-forward).  What they check here is the Python
@@ -15,6 +15,7 @@ from tests import test_parts_gpu as g
 from tests.tiny_configs import TINY_A, TINY_B, TINY_C
 
 F32 = torch.float32
+DTYPES = [torch.float32, torch.bfloat16]
 
 
 @pytest.fixture(autouse=True)
@@ -25,27 +26,31 @@ def on_the_cpu(monkeypatch):
         yield
 
 
-def test_norm_feed_forward_embedding_and_head():
-    g.test_norm_part(F32)
-    g.test_feed_forward_part(F32)
-    g.test_embedding_and_head_parts(F32, True)
-    g.test_embedding_and_head_parts(F32, False)
+@pytest.mark.parametrize("dtype", DTYPES, ids=["float32", "bfloat16"])
+def test_norm_feed_forward_embedding_and_head(dtype):
+    g.test_norm_part(dtype)
+    g.test_feed_forward_part(dtype)
+    g.test_embedding_and_head_parts(dtype, True)
+    g.test_embedding_and_head_parts(dtype, False)
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=["float32", "bfloat16"])
 @pytest.mark.parametrize("cfg", [TINY_A, TINY_B, TINY_C], ids=["a", "b", "c"])
-def test_frequencies_and_block(cfg):
+def test_frequencies_and_block(cfg, dtype):
     g.test_rotary_part_frequencies(cfg)
-    g.test_block_of_parts_equals_plain_layer(F32, cfg)
+    g.test_block_of_parts_equals_plain_layer(dtype, cfg)
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=["float32", "bfloat16"])
 @pytest.mark.parametrize("rotary_dim", [0, 16])
-def test_other_position_encodings(rotary_dim):
-    g.test_other_position_encodings(F32, rotary_dim)
+def test_other_position_encodings(rotary_dim, dtype):
+    g.test_other_position_encodings(dtype, rotary_dim)
 
 
-def test_run_order_and_window():
-    g.test_run_order_names_a_layer_twice_and_shares_a_cache(F32)
-    g.test_windowed_layer_has_pages_of_its_own_and_gives_them_back(F32)
+@pytest.mark.parametrize("dtype", DTYPES, ids=["float32", "bfloat16"])
+def test_run_order_and_window(dtype):
+    g.test_run_order_names_a_layer_twice_and_shares_a_cache(dtype)
+    g.test_windowed_layer_has_pages_of_its_own_and_gives_them_back(dtype)
     g.test_unknown_part_kind_is_named()
 
 
