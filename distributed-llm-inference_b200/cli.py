@@ -286,11 +286,9 @@ def main(argv: list[str] | None = None) -> int:
     if argv is None:
         argv = sys.argv[1:]
     if argv[:1] == ["replay"]:
-        import runpy
+        from . import replay
 
-        sys.argv = ["trace_run", *argv[1:]]
-        runpy.run_path(str(Path(__file__).resolve().parents[1] / "bin" / "trace_run"), run_name="__main__")
-        return 0
+        return replay.main(argv[1:])
     args = ap.parse_args(argv)
     return args.fn(args)
 

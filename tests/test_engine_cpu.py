@@ -159,7 +159,8 @@ def test_paged_sequence_on_the_real_runner(models):
     runner.manager.check_invariants()
 
 
-def test_trace_run_in_process(models, tmp_path, monkeypatch, capsys):
+@pytest.mark.parametrize("how", ["script", "command"])
+def test_trace_run_in_process(models, tmp_path, monkeypatch, capsys, how):
     """bin/trace_run itself (its arguments, the order of the wanted rows, requests that end and whose
     pages are used again), run in this process on the stand-ins: up to four live requests, portions of
     some beside single tokens of others, in a pool of 128 tokens."""
@@ -200,11 +201,17 @@ def test_trace_run_in_process(models, tmp_path, monkeypatch, capsys):
         lines.append(json.dumps({"step": step, "entries": recs, "end": end}))
         expected.append(rows)
     out_dir = tmp_path / "logits"
-    monkeypatch.setattr(sys, "argv", ["trace_run", "--model", str(path), "--dtype", "float32", "--out", str(out_dir), "--max-tokens", "128", "--device", "cpu"])
+    argv = ["--model", str(path), "--dtype", "float32", "--out", str(out_dir), "--max-tokens", "128", "--device", "cpu"]
     monkeypatch.setattr(sys, "stdin", io.StringIO("\n".join(lines) + "\n"))
-    with pytest.raises(SystemExit) as done:
-        runpy.run_path(str(ROOT / "bin" / "trace_run"), run_name="__main__")
-    assert done.value.code == 0
+    if how == "script":  # bin/trace_run, as its own program
+        monkeypatch.setattr(sys, "argv", ["trace_run", *argv])
+        with pytest.raises(SystemExit) as done:
+            runpy.run_path(str(ROOT / "bin" / "trace_run"), run_name="__main__")
+        assert done.value.code == 0
+    else:  # the same through the command line's `dli replay`
+        from dli_b200 import cli
+
+        assert cli.main(["replay", *argv]) == 0
     assert capsys.readouterr().out.split() == [w for step in range(len(plan)) for w in ("done", str(step))]
     for step, rows in enumerate(expected):
         got = np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(len(rows), -1)
