@@ -48,12 +48,44 @@ class Allocation:
 
 @dataclass
 class CacheStats:
+    """Counters since construction.  Calling the object (``manager.stats()``, the reference's
+    spelling: src/dli/kv/block_manager.py:84-105,222-234) gives a snapshot that also holds the
+    pages' states, per cache group."""
+
     prompt_tokens_queried: int = 0
     prompt_tokens_hit: int = 0
+    page_copies: int = 0  # copy-on-write of a forked request's last page
+    _pools: list = field(default_factory=list, repr=False)
 
     @property
     def hit_rate(self) -> float:
         return self.prompt_tokens_hit / self.prompt_tokens_queried if self.prompt_tokens_queried else 0.0
+
+    def __call__(self) -> "CacheSnapshot":
+        groups = [GroupPages(p.num_pages, len(p.free), p.num_idle, p.num_pages - len(p.free) - p.num_idle, p.evictions,
+                             p.duplicate_registrations) for p in self._pools]
+        return CacheSnapshot(self.prompt_tokens_queried, self.prompt_tokens_hit, self.hit_rate, self.page_copies, groups)
+
+
+@dataclass(frozen=True)
+class GroupPages:
+    """Pages of one cache group by state: free, idle in the prefix index (evictable in the end), used."""
+
+    num_pages: int
+    free_pages: int
+    cached_idle_pages: int
+    used_pages: int
+    evictions: int
+    duplicate_registrations: int
+
+
+@dataclass(frozen=True)
+class CacheSnapshot:
+    prompt_tokens_queried: int
+    prompt_tokens_hit: int
+    hit_rate: float
+    page_copies: int
+    groups: list[GroupPages]
 
 
 @dataclass(frozen=True)
@@ -107,7 +139,7 @@ class CacheManager:
         self._has_window = any(g.window is not None for g in groups)
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._requests: dict[Hashable, _Request] = {}
-        self.stats = CacheStats()
+        self.stats = CacheStats(_pools=self.pools)
         # per group, a copy of every live request's block table as rows of one array (row =
         # state slot), so a step's tables and slots are gathered with array operations
         self._mirror = [np.full((max_requests, 16), -1, dtype=np.int32) for _ in groups]
@@ -206,6 +238,12 @@ class CacheManager:
                 return False
         return True
 
+    def pages_needed_for_prompt(self, token_ids: Sequence[int], namespace: bytes = b"") -> int:
+        """New pages per group that ``allocate`` would take for this prompt, after prefix hits
+        (src/dli/kv/block_manager.py:212-215)."""
+        hits, _ = self._hits(token_ids, namespace)
+        return self.pages_for(len(token_ids)) - (len(hits[0]) if hits else 0)
+
     def can_allocate(self, token_ids: Sequence[int], namespace: bytes = b"", respect_watermark: bool = True) -> bool:
         hits, _ = self._hits(token_ids, namespace)
         return self._admissible(len(token_ids), hits, respect_watermark)
@@ -265,6 +303,7 @@ class CacheManager:
             table[-1] = new
             self._mirror_write(g, req.slot, len(table) - 1, [new])
             copies.append(PageCopy(g, old, new))
+            self.stats.page_copies += 1
         if need:
             for g, (pool, table) in enumerate(zip(self.pools, req.tables)):
                 new = [pool.take() for _ in range(need)]

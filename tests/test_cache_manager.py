@@ -413,3 +413,19 @@ def test_double_free_and_release_of_a_free_page_raise_at_once():
     with pytest.raises(AssertionError):
         m.pools[0].release(m.pools[0].free[0])
     m.check_invariants()
+
+
+def test_stats_snapshot_counts_pages_by_state_and_copies():
+    m = _busy_manager()  # two live requests on a shared stem, one finished request idling in the index
+    snap = m.stats()
+    g = snap.groups[0]
+    assert g.num_pages == 16 and g.free_pages + g.cached_idle_pages + g.used_pages == 16
+    assert g.cached_idle_pages == m.pools[0].num_idle >= 1 and g.used_pages == sum(1 for r in m.pools[0].ref if r > 0)
+    assert snap.prompt_tokens_hit == m.stats.prompt_tokens_hit == 16 and 0 < snap.hit_rate < 1 and snap.page_copies == 0
+    stem = list(range(8))
+    assert m.pages_needed_for_prompt(stem + [70, 71]) == 1  # two pages of the stem are in the index
+    assert m.pages_needed_for_prompt([9] * 10) == 3
+    m.fork("a", "a2")
+    m.append_slots("a2", [5])  # the shared last page is partly filled: it is copied first
+    assert m.stats().page_copies == 1
+    m.check_invariants()
