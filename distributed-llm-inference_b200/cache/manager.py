@@ -327,7 +327,7 @@ class CacheManager:
         for pool, table in zip(self.pools, src.tables):
             for page in table:
                 if page >= 0:
-                    pool.share(page)
+                    pool.share(page, found_by_hash=False)
         req = _Request([list(t) for t in src.tables], src.num_tokens, src.num_computed, src.namespace, self._free_slots.pop(),
                        list(src.hashes), list(src.tail), src.registered)
         for g, table in enumerate(req.tables):

@@ -174,15 +174,17 @@ class PagePool:
         self.ref[page] = 1
         return page
 
-    def share(self, page: int) -> None:
-        """One more reference to a used or idle page (a prefix hit)."""
+    def share(self, page: int, found_by_hash: bool = True) -> None:
+        """One more reference to a used or idle page: a prefix hit (which counts towards the page's
+        value for the cost-aware policy, as in src/dli/kv/block_manager.py:265-268), or a fork of the
+        request that holds it (which does not)."""
         if self.ref[page] == 0:
             if page not in self.indexed:
                 raise AssertionError(f"share of free page {page}")
             self.num_idle -= 1
             self.evictable.discard(page)
         entry = self.indexed.get(page)
-        if entry is not None:
+        if entry is not None and found_by_hash:
             entry.hits += 1
         self.ref[page] += 1
 
