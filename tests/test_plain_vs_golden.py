@@ -61,3 +61,18 @@ def test_llama3_bands():
     ratio = scaled / base
     assert np.allclose(ratio[:2], 1.0) and np.allclose(ratio[3:], 1 / 8, rtol=1e-6)
     assert 1 / 8 < ratio[2] < 1.0
+
+
+def test_sampling_distribution_matches_reference():
+    """The probabilities the reference's sampler draws from (tests/golden/make_sampling_golden.py), row by
+    row, against the plain sampler's; and its greedy choices, ties included."""
+    data = np.load(GOLDEN / "sampling_probs.npz")
+    logits, settings = data["logits"], data["settings"]
+    for i, want in zip(data["rows"], data["probs"]):
+        t, k, p = settings[i % len(settings)]
+        got = plain.filtered_probabilities(logits[i], float(t), int(k), float(p))
+        assert (got > 0).tolist() == (want > 0).tolist(), f"row {i}: another set of tokens survives"
+        np.testing.assert_allclose(got, want, atol=2e-6, err_msg=f"row {i}")
+    for i, token in data["greedy"]:
+        t, k, p = settings[i % len(settings)]
+        assert plain.sample_token(logits[i], float(t), int(k), float(p), seed=1, draw=0) == token
