@@ -429,3 +429,16 @@ def test_stats_snapshot_counts_pages_by_state_and_copies():
     m.append_slots("a2", [5])  # the shared last page is partly filled: it is copied first
     assert m.stats().page_copies == 1
     m.check_invariants()
+
+
+def test_page_hashes_equal_the_reference():
+    """Chains of page hashes recorded from the reference's dli.kv.hashing.chain_hashes
+    (tests/golden/make_config_hash_golden.py): the same bytes here, so a prefix index could be shared."""
+    import json
+    from pathlib import Path
+
+    golden = json.loads((Path(__file__).parent / "golden" / "config_and_hash.json").read_text())
+    for case in golden["hashes"]:
+        got = chain_hashes(bytes.fromhex(case["namespace"]), case["tokens"], case["page_size"])
+        assert [h.hex() for h in got] == case["chain"]
+        assert len(got) == len(case["tokens"]) // case["page_size"]

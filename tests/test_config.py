@@ -124,3 +124,33 @@ def test_linear_rope_scaling_divides_every_frequency():
     with pytest.raises(KeyError):
         LlamaConfig.from_hf_dict({**TINY_C, "rope_scaling": {"type": "linear"}})
     assert LlamaConfig.from_hf_dict(c.to_hf_dict()).rope == c.rope  # survives the round trip through config.json
+
+
+def test_same_outcomes_as_the_reference_parser():
+    """tests/golden/config_and_hash.json (made by tests/golden/make_config_hash_golden.py from the reference's
+    ModelConfig.from_hf_dict): every config.json there parses to the same fields here, or is refused in the
+    same way (a key that is missing, a feature that is not supported)."""
+    import dataclasses
+    import json
+    from pathlib import Path
+
+    golden = json.loads((Path(__file__).parent / "golden" / "config_and_hash.json").read_text())
+    for i, case in enumerate(golden["configs"]):
+        cfg, outcome = case["config"], case["outcome"]
+        try:
+            parsed = LlamaConfig.from_hf_dict(cfg)
+        except UnsupportedModelError:
+            assert outcome == {"error": "unsupported"}, f"config {i}: refused here, the reference gives {outcome}"
+            continue
+        except KeyError:
+            assert outcome == {"error": "missing key"}, f"config {i}: a key is missed here, the reference gives {outcome}"
+            continue
+        assert "ok" in outcome, f"config {i}: parsed here, the reference gives {outcome}"
+        want = outcome["ok"]
+        got = dataclasses.asdict(parsed)
+        for key in ("vocab_size", "hidden_size", "intermediate_size", "num_layers", "num_heads", "num_kv_heads", "head_dim",
+                    "max_position_embeddings", "tie_word_embeddings"):
+            assert got[key] == want[key], f"config {i}: {key}"
+        assert got["rms_norm_eps"] == pytest.approx(want["rms_norm_eps"])
+        for key in ("theta", "rope_type", "factor", "low_freq_factor", "high_freq_factor", "original_max_position_embeddings"):
+            assert got["rope"][key] == want["rope"][key], f"config {i}: rope.{key}"
