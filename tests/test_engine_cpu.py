@@ -292,3 +292,22 @@ def test_bfloat16_generation_mixed_batches(models, lookahead):
         want, gaps = plain_greedy(cfg, w, p, 8)
         same_tokens(got, want, gaps, f"prompt of {len(p)}", TOLS["bfloat16"])
     eng.manager.check_invariants()
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+def test_engine_tokens_equal_the_reference_engine_run(name, tmp_path):
+    """tests/golden/<name>.npz holds 16 greedy tokens that the reference's own model produced from the first 9
+    ids of its sequence, on the weights this repository's writer makes for the configuration's seed.  The engine
+    (float32, CPU stand-ins), alone and in a batch with other requests, produces the same tokens."""
+    from pathlib import Path
+
+    from tests.tiny_configs import TINY
+
+    cfg, seed, page = TINY[name]
+    gold = np.load(Path(__file__).parent / "golden" / f"{name}.npz")
+    dli_b200.write_model_dir(tmp_path, cfg, seed)
+    prompt = gold["token_ids"][:9].tolist()
+    eng = engine_for(tmp_path, page, 64, config=SchedulerConfig(4, 7))
+    others = [random_tokens(cfg["vocab_size"], n, seed=n) for n in (3, 20)]
+    outs = eng.generate([others[0], prompt, others[1]], SamplingParams(max_tokens=16))
+    assert outs[1] == gold["greedy"].tolist()
