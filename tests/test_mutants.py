@@ -18,6 +18,7 @@ import tests.test_scheduler as scheduler_tests
 from dli_b200.cache.manager import CacheManager
 from dli_b200.cache.page_pool import PagePool
 from dli_b200.engine import batch as batch_mod
+from dli_b200.engine.llm_engine import LLMEngine
 from dli_b200.engine.ordering import ServiceOrder
 from dli_b200.engine.scheduler import Scheduler
 
@@ -69,6 +70,12 @@ def reference_schedules():
             schedule_golden.test_same_steps_as_the_reference(case, False, mp)
 
 
+def reference_schedules_ahead():
+    for case in schedule_golden.CASES:
+        with _Patch() as mp:
+            schedule_golden.test_same_steps_as_the_reference(case, True, mp)
+
+
 def scheduler_rules():
     scheduler_tests.test_pages_run_out_newest_is_preempted_and_recomputed()
     scheduler_tests.test_head_of_queue_is_not_overtaken()
@@ -84,6 +91,17 @@ def gathered_arrays():
         batch_tests.test_gather_host_equals_a_per_token_restatement(seed)
     for seed in range(4):
         batch_tests.test_single_token_gather_equals_the_general_one(seed)
+
+
+def engine_loop():
+    scheduler_tests.test_one_step_ahead_in_steady_decode()
+    scheduler_tests.test_an_arrival_stops_the_step_ahead()
+    scheduler_tests.test_pages_written_by_steps_launched_ahead_are_found_again()
+    for ahead in (False, True):
+        scheduler_tests.test_stop_tokens_eos_and_length(ahead)
+        scheduler_tests.test_batched_equals_sequential(ahead)
+        for seed in range(8):
+            scheduler_tests.test_random_scenarios(seed, ahead)
 
 
 MUTANTS = {
@@ -110,6 +128,12 @@ MUTANTS = {
     "aging never happens": (ServiceOrder, "service_class", "aged = self.steps - req.arrival_step >= self.aging_steps", "aged = False", [scheduler_rules, reference_schedules]),
     "weights are ignored": (ServiceOrder, "charge", "tokens / self.weights.get(tenant, 1.0)", "tokens", [scheduler_rules, reference_schedules]),
     "an idle tenant keeps its old clock": (ServiceOrder, "arrive", "max(self.clock(tenant), floor)", "self.clock(tenant)", [scheduler_rules, reference_schedules]),
+    # the engine loop and the step launched ahead
+    "a request that ends by length still gets a step ahead": (LLMEngine, "_launch_ahead", "len(r.output_ids) + 1 < r.params.max_tokens", "len(r.output_ids) < r.params.max_tokens + 1", [engine_loop]),
+    "the surplus token of a finished request is kept": (LLMEngine, "_resolve", "if req.is_finished:\n            continue", "if False:\n            continue", [engine_loop]),
+    "a step is launched ahead although a request waits": (LLMEngine, "_launch_ahead", "if sch.waiting or not flight.sampling", "if not flight.sampling", [engine_loop, reference_schedules_ahead]),
+    "an unknown token is never named": (LLMEngine, "_resolve", "self.manager.set_token(req.request_id, position, int(tok))", "pass", [engine_loop]),
+    "the stop token is dropped from the output": (LLMEngine, "_append_token", "req.output_ids.append(tok)\n", "req.output_ids.append(tok)\n    if tok in req.params.stop_token_ids: req.output_ids.pop()\n", [engine_loop, reference_schedules]),
     # batch gathering
     "a slot at a page's edge is off by one": (batch_mod, "gather_host", "slots.append(pages * ps + positions % ps)",
                                               "slots.append(pages * ps + (positions + (positions % ps == ps - 1)) % ps)", [gathered_arrays]),
@@ -134,5 +158,5 @@ def test_mutant_is_noticed(name, monkeypatch):
 
 
 def test_without_a_mutant_the_detectors_are_quiet():
-    for detect in (shadow_store, reference_traces, fork_and_window, reference_schedules, scheduler_rules, gathered_arrays):
+    for detect in (shadow_store, reference_traces, fork_and_window, reference_schedules, reference_schedules_ahead, scheduler_rules, engine_loop, gathered_arrays):
         detect()

@@ -381,3 +381,30 @@ def test_a_stalled_engine_ends_the_loop_instead_of_stepping_for_ever():
     assert not eng.is_stalled()
     eng.generate([[1, 2, 3]], SamplingParams(max_tokens=2))
     assert not eng.is_stalled()
+
+
+def test_an_arrival_stops_the_step_ahead():
+    eng, runner = fake_engine(ahead=True)
+    eng.add_request("a", [1, 2, 3], SamplingParams(max_tokens=20))
+    eng.step(), eng.step()  # steady decoding: every step is launched before the ids of the one before are read
+    assert eng.steps_ahead == 2
+    launched = len(runner.steps)
+    eng.add_request("late", [4, 5], SamplingParams(max_tokens=3))
+    eng.step()  # reads the step in flight; nothing is launched ahead, because a request waits
+    assert len(runner.steps) == launched
+    eng.step()  # the scheduler decides again: the newcomer's prompt beside the decoded token
+    assert {rid for rid, *_ in runner.steps[-1]} == {"a", "late"}
+    while eng.has_unfinished():
+        eng.step()
+
+
+def test_pages_written_by_steps_launched_ahead_are_found_again():
+    """Tokens that ran before the host knew their ids are named afterwards (set_token), so their pages
+    enter the prefix index like any others."""
+    eng, _ = fake_engine(ahead=True, page_size=4, budget=64)
+    prompt = [1, 2, 3]
+    out = eng.generate([prompt], SamplingParams(max_tokens=14))[0]  # 16 tokens computed: four full pages
+    assert eng.steps_ahead > 5
+    before = eng.manager.stats.prompt_tokens_hit
+    eng.generate([prompt + out], SamplingParams(max_tokens=1))
+    assert eng.manager.stats.prompt_tokens_hit - before == 16
