@@ -1318,3 +1318,5 @@ DLI_EXPORT int dli_decode_tma_merges_in_cluster(int nh, int nkv, int splits) { r
 // 0, or the code of the first bounded wait that ran out (11 keys, 12 scores or a key stage, 13 an output product or a
 // value stage, 14 values, 15 probabilities, 17 the product warp found nothing to issue; 21: a decode warp's keys and values)
 DLI_EXPORT int dli_paged_prefill_tc_error() { return error_flag_host ? *error_flag_host : 0; }
+// Forget a recorded code (the host has read it); call with no launch of this library in flight.
+DLI_EXPORT int dli_paged_prefill_tc_clear_error() { if (error_flag_host) *error_flag_host = 0; return 0; }

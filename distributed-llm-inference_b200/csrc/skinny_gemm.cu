@@ -549,3 +549,5 @@ DLI_EXPORT int dli_skinny_gemm_residual(void* x_out, float* h, const float* gain
 
 // 0, or the code of the first wait that ran out (1 producer, 2 MMA issuer, 3 epilogue)
 DLI_EXPORT int dli_skinny_gemm_error() { return error_flag_host ? *error_flag_host : 0; }
+// Forget a recorded code (the host has read it); call with no launch of this library in flight.
+DLI_EXPORT int dli_skinny_gemm_clear_error() { if (error_flag_host) *error_flag_host = 0; return 0; }

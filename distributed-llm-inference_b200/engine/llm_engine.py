@@ -176,6 +176,7 @@ class LLMEngine:
         ahead = self._launch_ahead(flight) if self.lookahead else None
         t2 = time.perf_counter()
         tokens = flight.tokens.result()
+        self._check_device(flight, ahead)
         t3 = time.perf_counter()
         outputs = self._resolve(flight, tokens)
         if ahead is not None and self.scheduler.running:
@@ -211,6 +212,24 @@ class LLMEngine:
                 and self.stats.steps[-1].num_seqs == 0 and self.stats.steps[-1].num_preempted == 0)
 
     # ------------------------------------------------------------ internals
+
+    def _check_device(self, flight: _InFlight, ahead: _InFlight | None) -> None:
+        """The step's ids are on the host, so its kernels have ended: ask the runner whether one of them
+        gave up a bounded wait.  If so, nothing the step (or the one launched behind it) computed is
+        used: its requests are aborted, no page any of them wrote stays in the prefix index, and the
+        error goes to the caller.  The engine itself stays usable."""
+        check = getattr(self.runner, "check_device_errors", None)
+        if check is None:
+            return
+        try:
+            check()
+        except Exception:
+            for fl in (flight, ahead):
+                for ch in (fl.chunks if fl is not None else []):
+                    self._unknown.pop(ch.request.request_id, None)
+                    self.scheduler.abort(ch.request.request_id)
+            self.manager.reset_prefix_cache()
+            raise
 
     def _sample(self, logits, reqs: list[Request], ahead: int):
         """Ids for ``reqs`` (row order); ``ahead``: tokens of each request that are sampled but not read."""

@@ -150,6 +150,14 @@ class ModelRunner:
             return logits[: h["S"]]
         return logits[torch.from_numpy(rows).to(logits.device)]
 
+    def check_device_errors(self) -> None:
+        """Raise if a bounded wait inside one of the kernels gave up since this was last asked: what
+        such a step computed is not to be trusted.  Call it once the step's results are on the host."""
+        errors = ops.device_wait_errors()
+        if errors:
+            raise ops.KernelError("a device-side wait ran out; the step's results are invalid: "
+                                  + ", ".join(f"{lib} code {code}" for lib, code in sorted(errors.items())))
+
     takes_token_source = True  # execute() accepts chunks whose token is still on the device
 
     def execute(self, chunks, token_source=None, token_rows: Sequence[int] | None = None) -> torch.Tensor:

@@ -367,8 +367,31 @@ def paged_decode_tma(
 
 
 def paged_prefill_tc_error() -> int:
-    """0, or which bounded wait of the tcgen05 prefill attention ran out since the library was loaded."""
+    """0, or which bounded wait of the tcgen05 / TMA attention kernels ran out since the library was loaded
+    (or since the code was last cleared)."""
     return _fn("attention_tc.cu", "dli_paged_prefill_tc_error", [])()
+
+
+def _library_in_use(source: str) -> bool:
+    return any(key.startswith(source + ":") for key in _fns)
+
+
+def device_wait_errors(clear: bool = True) -> dict[str, int]:
+    """Bounded device waits that ran out: {library: code} for the libraries this process has used
+    (a library nobody called has recorded nothing and is not built for the question).  The flags live
+    in mapped host memory, so reading them costs no copy; read them once the step's results have
+    reached the host.  With ``clear`` a code that was read is forgotten."""
+    found = {}
+    for source, read, forget in (("skinny_gemm.cu", "dli_skinny_gemm_error", "dli_skinny_gemm_clear_error"),
+                                 ("attention_tc.cu", "dli_paged_prefill_tc_error", "dli_paged_prefill_tc_clear_error")):
+        if not _library_in_use(source):
+            continue
+        code = _fn(source, read, [])()
+        if code:
+            found[source] = int(code)
+            if clear:
+                _fn(source, forget, [])()
+    return found
 
 
 # ------------------------------------------------------------------ sampling

@@ -2,6 +2,8 @@
 and LLMEngine in float32, with torch stand-ins for the kernels (tests/cpu_ops.py), against the plain
 implementation.  The GPU tests make the same comparisons with the real kernels."""
 
+import sys
+
 import numpy as np
 import pytest
 import torch
@@ -217,6 +219,36 @@ def test_trace_run_in_process(models, tmp_path, monkeypatch, capsys, how):
         got = np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(len(rows), -1)
         want = np.stack([full[k][r] for k, r in rows])
         np.testing.assert_allclose(got, want, atol=TOL, err_msg=f"step {step}")
+
+
+def test_trace_run_with_the_prefix_index_on(models, tmp_path, monkeypatch, capsys):
+    """--prefix-caching: a request whose tokens begin like an earlier one's (ended, or still live) is not run over
+    the shared pages again, and its logits are what they are without the index."""
+    import io
+    import json
+
+    from dli_b200 import replay
+
+    path, cfg, weights, page = models["tiny_b"]  # pages of 16 tokens
+    stem = random_tokens(1000, 50, seed=70)
+    seqs = {"a": stem + random_tokens(1000, 9, seed=71), "b": stem + random_tokens(1000, 14, seed=72), "c": stem[:40] + random_tokens(1000, 20, seed=73)}
+    full = {k: plain.forward(cfg, weights, v) for k, v in seqs.items()}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": seqs["a"], "want": list(range(59))}], "end": ["a"]},
+        # b: the stem's three full pages are idle in the index; places 50.. are wanted
+        {"step": 1, "entries": [{"id": "b", "tokens": seqs["b"][:60], "want": list(range(50, 60))}], "end": []},
+        # c shares two pages with b while b is live; b goes on beside it
+        {"step": 2, "entries": [{"id": "c", "tokens": seqs["c"], "want": list(range(40, 60))}, {"id": "b", "tokens": seqs["b"][60:], "want": [0, 3]}], "end": ["b", "c"]},
+    ]
+    rows = [[("a", i) for i in range(59)], [("b", i) for i in range(50, 60)], [("c", i) for i in range(40, 60)] + [("b", 60), ("b", 63)]]
+    out_dir = tmp_path / "logits"
+    monkeypatch.setattr(sys, "stdin", io.StringIO("\n".join(json.dumps(s) for s in steps) + "\n"))
+    assert replay.main(["--model", str(path), "--dtype", "float32", "--out", str(out_dir), "--max-tokens", "192", "--device", "cpu", "--prefix-caching"]) == 0
+    err = capsys.readouterr().err
+    assert "request b: 48 tokens found" in err and "request c: 32 tokens found" in err
+    for step, want_rows in enumerate(rows):
+        got = np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(len(want_rows), -1)
+        np.testing.assert_allclose(got, np.stack([full[k][r] for k, r in want_rows]), atol=TOL, err_msg=f"step {step}")
 
 
 # ---- bfloat16: the decode products with their fused epilogues, and the choice of attention kernels

@@ -133,3 +133,35 @@ def test_want_may_be_empty_and_partial(case):
     ref = case["ref"][rid]
     tol = TOL[case["dtype"]]
     assert np.abs(out - ref[[59, 40, 47]]).max() < tol and np.abs(tail - ref[-1:]).max() < tol
+
+
+def test_prefix_hits_change_nothing(case):
+    """The prefix index on: requests that begin like an earlier one (ended, its pages idle in the index; or live,
+    its pages shared) skip the shared pages, in a pool so small that idle pages are evicted and used again; the
+    logits at every place computed are those of the plain implementation."""
+    cfg, page = case["cfg"], case["page"]
+    tol = TOL[case["dtype"]]
+    w = plain_weights_for(plain.read_safetensors(case["path"] / "model.safetensors"), case["dtype"])
+    stem = random_tokens(cfg["vocab_size"], 70, seed=501)
+    seqs = {k: stem[:n] + random_tokens(cfg["vocab_size"], m, seed=502 + i) for i, (k, n, m) in
+            enumerate((("a", 70, 12), ("b", 70, 25), ("c", 45, 30), ("d", 0, 126), ("e", 70, 5)))}
+    ref = {k: plain.forward(cfg, w, v) for k, v in seqs.items()}
+    run = TraceRun(case["path"], case["dtype"], case["tmp"].mktemp("out"), 2 * rounded(100, page), page, prefix_caching=True)
+    got = {}
+    got["a"] = (0, run.step([("a", seqs["a"], range(len(seqs["a"])))], end=["a"]))
+    b = seqs["b"]
+    first = run.step([("b", b[:80], range(70, 80))])  # the stem's full pages are idle in the index
+    c = seqs["c"]
+    both = run.step([("c", c, range(45, len(c))), ("b", b[80:], range(len(b) - 80))], end=["c"])  # c shares pages with the live b
+    got["b"] = (70, np.concatenate([first, both[len(c) - 45:]]))
+    got["c"] = (45, both[: len(c) - 45])
+    d = seqs["d"]
+    got["d"] = (0, run.step([("d", d, range(len(d)))], end=["d", "b"]))  # more pages than are free: idle ones are evicted for it
+    e = seqs["e"]
+    got["e"] = (70, run.step([("e", e, range(70, len(e)))], end=["e"]))
+    assert run.close() == 0
+    found = run.found_in_cache()
+    assert found.get("b") == 70 // page * page and found.get("c") == 45 // page * page, found
+    for rid, (start, logits) in got.items():
+        err = np.abs(logits - ref[rid][start:]).max(axis=1)
+        assert err.max() < tol, f"request {rid}: first wrong position {start + int(np.argmax(err > tol))} (error {err.max():.3g})"

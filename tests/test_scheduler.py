@@ -408,3 +408,36 @@ def test_pages_written_by_steps_launched_ahead_are_found_again():
     before = eng.manager.stats.prompt_tokens_hit
     eng.generate([prompt + out], SamplingParams(max_tokens=1))
     assert eng.manager.stats.prompt_tokens_hit - before == 16
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_a_device_wait_that_ran_out_fails_the_steps_requests_and_leaves_the_engine_usable(ahead):
+    """The runner reports that a kernel gave up a bounded wait: the step's tokens are not handed out, its
+    requests are aborted, no page they wrote stays in the prefix index, the error reaches the caller,
+    and requests that come afterwards run as if nothing had happened."""
+    eng, runner = fake_engine(num_pages=64, page_size=4, ahead=ahead)
+    failing = {"now": False}
+
+    def check_device_errors():
+        if failing["now"]:
+            failing["now"] = False
+            raise RuntimeError("a device-side wait ran out")
+
+    runner.check_device_errors = check_device_errors
+    prompts = [[1, 2, 3, 4, 5, 6, 7, 8, 9], [11, 12, 13]]
+    reqs = [eng.add_request(f"r{i}", p, SamplingParams(max_tokens=12)) for i, p in enumerate(prompts)]
+    for _ in range(3):
+        eng.step()
+    before = [list(r.output_ids) for r in reqs]
+    failing["now"] = True
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        eng.step()
+    assert [r.output_ids for r in reqs] == before, "tokens of the failed step were handed out"
+    assert all(r.finish_reason is FinishReason.ABORTED for r in reqs) and not eng.has_unfinished()
+    runner.manager.check_invariants()
+    group = runner.manager.stats().groups[0]
+    assert group.used_pages == 0 and group.cached_idle_pages == 0, "pages of the failed step stayed indexed"
+    # the engine goes on: the same prompt again is computed from its first token (no prefix hit) and is right
+    steps_before = len(runner.steps)
+    assert eng.generate([prompts[0]], SamplingParams(max_tokens=6)) == [sequential(prompts[0], 6)]
+    assert runner.steps[steps_before][0][1:3] == (0, len(prompts[0])), "the prompt was served from pages of the failed step"

@@ -49,13 +49,22 @@ def random_tokens(vocab: int, n: int, seed: int) -> list[int]:
 class TraceRun:
     """bin/trace_run as a child process, fed one step at a time."""
 
-    def __init__(self, model_dir, dtype: str, out_dir, max_tokens: int, page_size: int | None = None, cwd=None, env=None):
+    def __init__(self, model_dir, dtype: str, out_dir, max_tokens: int, page_size: int | None = None, cwd=None, env=None,
+                 prefix_caching: bool = False):
         self.out_dir = Path(out_dir)
         cmd = [str((Path(cwd) if cwd else ROOT) / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
                "--out", str(out_dir), "--max-tokens", str(max_tokens)]
         if page_size:
             cmd += ["--page-size", str(page_size)]
-        self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, cwd=cwd, env=env)
+        self.err_path = None
+        stderr = None
+        if prefix_caching:
+            cmd.append("--prefix-caching")
+            self.err_path = Path(out_dir) / "stderr.txt"  # where trace_run says what it found in the cache
+            stderr = open(self.err_path, "w")
+        self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=stderr, text=True, cwd=cwd, env=env)
+        if stderr is not None:
+            stderr.close()
         self.step_no = 0
 
     def step(self, entries, end=()):
@@ -77,3 +86,12 @@ class TraceRun:
     def close(self) -> int:
         self.proc.stdin.close()
         return self.proc.wait(timeout=120)
+
+    def found_in_cache(self) -> dict[str, int]:
+        """request -> tokens that trace_run reported as found in the prefix index (after close)."""
+        out = {}
+        for line in self.err_path.read_text().splitlines():
+            if "tokens found in the cache" in line:
+                words = line.split()
+                out[words[2].rstrip(":")] = int(words[3])
+        return out
