@@ -516,15 +516,15 @@ DLI_EXPORT int dli_paged_attention_mma(void* out, const void* q, long long q_str
                                        cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (nkv < 1 || nh % nkv || splits < 1 || (splits > 1 && (max_q_len != 1 || !part_acc || !part_ml))) return DLI_ERR_UNSUPPORTED;
-  static bool configured = false;
-  if (!configured) {
+  static OncePerDevice configured;
+  if (!configured.here()) {
     cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(paged_decode_mma_kernel<DecodeMany>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeMany::SMEM);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(paged_decode_mma_kernel<DecodeFew>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeFew::SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.here() = true;
   }
   Params p;
   p.out = (bf16*)out; p.q = (const bf16*)q; p.q_stride = q_stride;
@@ -539,7 +539,7 @@ DLI_EXPORT int dli_paged_attention_mma(void* out, const void* q, long long q_str
   p.splits = splits; p.part_acc = part_acc; p.part_ml = part_ml;
   if (max_q_len == 1) {
     const dim3 grid(splits, num_seqs, nkv * ((G + 15) / 16));
-    if ((long long)num_seqs * grid.z >= 2 * 148)
+    if ((long long)num_seqs * grid.z >= 2 * sm_count())
       launch_pdl((paged_decode_mma_kernel<DecodeMany>), grid, dim3(THREADS), DecodeMany::SMEM, stream, 1, p);
     else
       launch_pdl((paged_decode_mma_kernel<DecodeFew>), grid, dim3(THREADS), DecodeFew::SMEM, stream, 1, p);

@@ -817,11 +817,11 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
     *error_flag_host = 0;
     if (cudaHostGetDevicePointer((void**)&error_flag_device, error_flag_host, 0) != cudaSuccess) return (int)cudaGetLastError();
   }
-  static bool configured = false;
-  if (!configured) {
+  static OncePerDevice configured;
+  if (!configured.here()) {
     cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.here() = true;
   }
   CUtensorMap map_k, map_v;
   const long long rows = num_pages * nkv * page_size;
@@ -837,11 +837,11 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
   p.tokens_per_tile = ROWS / p.heads_per_chunk;
   p.error_flag = error_flag_device;
   if (head_dim == 128) {  // one query tile per CTA, a thread per row
-    static bool configured128 = false;
-    if (!configured128) {
+    static OncePerDevice configured128;
+    if (!configured128.here()) {
       cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2Cfg<128>::SMEM);
       if (e != cudaSuccess) return (int)e;
-      configured128 = true;
+      configured128.here() = true;
     }
     const int tiles = (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
     return (int)launch_pdl(paged_prefill_tc2_kernel<128>, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(T2Cfg<128>::THREADS),
@@ -850,11 +850,11 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
   // two query tiles per CTA when a sequence brings more tokens than one tile holds, unless the caller chose
   const bool two = query_tiles == 2 || (query_tiles != 1 && max_q_len > p.tokens_per_tile);
   if (two) {
-    static bool configured2 = false;
-    if (!configured2) {
+    static OncePerDevice configured2;
+    if (!configured2.here()) {
       cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2Cfg<64>::SMEM);
       if (e != cudaSuccess) return (int)e;
-      configured2 = true;
+      configured2.here() = true;
     }
     const int tiles = (max_q_len + 2 * p.tokens_per_tile - 1) / (2 * p.tokens_per_tile);
     return (int)launch_pdl(paged_prefill_tc2_kernel<64>, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(T2Cfg<64>::THREADS),
@@ -1260,12 +1260,12 @@ bool merges_in_cluster(int nh, int nkv, int splits) {
 
 template <int HD>
 int launch_decode(const CUtensorMap& map_k, const CUtensorMap& map_v, const DecodeParams& p, int num_seqs, int first_row, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static OncePerDevice configured;
+  if (!configured.here()) {
     cudaError_t e = cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<HD>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.here() = true;
   }
   const int G = p.nh / p.nkv;
   cudaError_t e = launch_pdl(paged_decode_tma_kernel<HD>, dim3(num_seqs, p.splits, p.nkv * ((G + 15) / 16)), dim3(DWARPS * 32),

@@ -71,7 +71,7 @@ def _nvcc() -> str:
 
 def _digest(source: str, defines: dict[str, object]) -> str:
     h = hashlib.sha256()
-    for path in [SRC_DIR / source, *sorted(SRC_DIR.glob("*.cuh"))]:
+    for path in [SRC_DIR / source, *sorted(SRC_DIR.glob("*.cuh")), *sorted(SRC_DIR.glob("*.h"))]:  # every header a source may include
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(repr(sorted(defines.items())).encode())

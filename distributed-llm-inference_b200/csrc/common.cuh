@@ -33,6 +33,33 @@ inline bool pdl_enabled() {
   return on == 1;
 }
 
+// The current device (indices wrap at 64) and its number of SMs, asked once per device.
+inline int current_device() {
+  int d = 0;
+  cudaGetDevice(&d);
+  return d & 63;
+}
+inline int sm_count() {
+  static int count[64] = {};
+  const int d = current_device();
+  if (!count[d]) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, d);
+    count[d] = v > 0 ? v : 1;
+  }
+  return count[d];
+}
+// Attributes of a kernel (dynamic shared memory, cluster size) are set per device: each device has its own
+// copy of the kernel.  `here()` is the current device's flag (or largest value set so far).
+struct OncePerDevice {
+  bool done[64] = {};
+  bool& here() { return done[current_device()]; }
+};
+struct MaxPerDevice {
+  int value[64] = {};
+  int& here() { return value[current_device()]; }
+};
+
 // Launch with the programmatic-serialization attribute (and, if cluster_y > 1, a cluster of
 // that many CTAs along y).
 template <typename... KArgs, typename... Args>

@@ -464,7 +464,7 @@ DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int tiled, 
   }
   const size_t total = (size_t)n * I;
   const int threads = 256;
-  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  const int blocks = (int)((total + threads - 1) / threads < (size_t)sm_count() * 16 ? (total + threads - 1) / threads : (size_t)sm_count() * 16);
   if (dtype == DLI_F32)
     launch_pdl((silu_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, 1, (float*)out, (const float*)gu, n, I, tiled);
   else

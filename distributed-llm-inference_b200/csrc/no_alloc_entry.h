@@ -15,8 +15,16 @@
 //
 // What it costs.  The array is DLI_NOALLOC_SCRATCH_FLOATS floats (4 MiB); every GPU on which a
 // process uses the library holds that much until the process exits.  A call needs
-// num_seqs * nh * splits * (head_dim + 2) floats and is refused with DLI_ERR_SCRATCH_TOO_SMALL,
-// before anything is launched, if that is more than the array holds.
+// (first_row + num_seqs) * nh * splits * (head_dim + 2) floats and is refused with
+// DLI_ERR_SCRATCH_TOO_SMALL, before anything is launched, if that is more than the array holds.
+//
+// first_row and q_start.  The sequences of a call bring one token each, and those tokens are
+// consecutive rows of q and out: sequence seq0 + i owns row first_row + i, and q_start must say
+// so (q_start[seq0 + i] == first_row + i).  The kernels place a row's partial results in the
+// array by that row number, counted from row 0 of the batch, which is why the need above counts
+// the first_row rows in front as well.  A q_start that breaks this contract sends partial
+// results to other rows' places, or past the end of the array; the entry point cannot check it,
+// because q_start lives on the device.
 //
 // Sharing.  All calls on a device use the same array, and it keeps whatever the last call
 // left.  Nothing in it has to start at zero: the first kernel of a call writes every slot that
@@ -26,7 +34,9 @@
 //
 // First call on a device.  The array's device address is looked up once per device
 // (cudaGetSymbolAddress, with the caller's current device current) the first time the entry
-// point is called on that device.  Make that first call outside any stream capture.
+// point is called on that device.  Make that first call outside any stream capture.  The table of
+// addresses is filled without a lock: two threads that make the first call on a device at the
+// same moment both look the address up and both store the same value.
 #pragma once
 #include <cuda_runtime.h>
 

@@ -53,9 +53,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// true when the phase with this parity has completed; false after WAIT_LIMIT polls
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+// true when the phase with this parity has completed; false after `limit` polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned limit) {
+  for (unsigned i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -203,7 +203,8 @@ __device__ __forceinline__ void st_peer_shared(uint32_t local_addr, uint32_t cta
 __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
                                                           int out_f32, int tokens, int features, int k_tiles, int tiles_per_slice,
-                                                          int npad, int stages, int tmem_cols, int* error_flag, const Epilogue ep) {
+                                                          int npad, int stages, int tmem_cols, int* error_flag, const Epilogue ep,
+                                                          unsigned wait_limit, int skip_tile) {
   pdl_launch_dependents();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -249,22 +250,26 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
     // kernel that runs before this one, so the first stages' weight tiles are requested before
     // the wait on that kernel; the activations only after it.
     if (lane == 0) {
+    // (skip_tile, -1 in every launch of the engine: the k tile whose copies a test leaves out, so that the wait
+    // for them runs out; see dli_skinny_gemm_wait_test)
     const int pre = min(nkt, stages);
     for (int i = 0; i < pre; ++i) {
+      if (kt0 + i == skip_tile) continue;
       mbar_expect_tx(full0 + 8 * i, (uint32_t)stage_bytes);
       tma_load_2d(smem_u32(smem + (size_t)i * stage_bytes), &map_w, (kt0 + i) * BK, tile * BM, full0 + 8 * i);
     }
     pdl_wait();
     for (int i = 0; i < pre; ++i)
-      tma_load_2d(smem_u32(smem + (size_t)i * stage_bytes) + A_BYTES, &map_x, (kt0 + i) * BK, 0, full0 + 8 * i);
+      if (kt0 + i != skip_tile) tma_load_2d(smem_u32(smem + (size_t)i * stage_bytes) + A_BYTES, &map_x, (kt0 + i) * BK, 0, full0 + 8 * i);
     for (int i = pre; i < nkt; ++i) {
       const int s = i % stages;
-      if (!mbar_wait(empty0 + 8 * s, ((i / stages) - 1) & 1)) {
+      if (!mbar_wait(empty0 + 8 * s, ((i / stages) - 1) & 1, wait_limit)) {
         *failed = 1;
         atomicExch(error_flag, 1);
         break;
       }
       if (*failed) break;
+      if (kt0 + i == skip_tile) continue;
       const uint32_t a = smem_u32(smem + (size_t)s * stage_bytes);
       mbar_expect_tx(full0 + 8 * s, (uint32_t)stage_bytes);
       tma_load_2d(a, &map_w, (kt0 + i) * BK, tile * BM, full0 + 8 * s);
@@ -278,7 +283,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
     if (lane == 0) {
     for (int i = 0; i < nkt; ++i) {
       const int s = i % stages;
-      if (!mbar_wait(full0 + 8 * s, (i / stages) & 1)) {
+      if (!mbar_wait(full0 + 8 * s, (i / stages) & 1, wait_limit)) {
         *failed = 2;
         atomicExch(error_flag, 2);
         break;
@@ -313,7 +318,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   const float gain_pre = (ep.mode == EP_RESIDUAL && f_own < features) ? ep.gain[f_own] : 0.f;
   bool ok = true;
   if (nkt > 0) {
-    ok = mbar_wait(accum, 0);
+    ok = mbar_wait(accum, 0, wait_limit);
     if (!ok) atomicExch(error_flag, 3);
   }
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -427,7 +432,7 @@ int* error_flag_host = nullptr;
 DLI_EXPORT int dli_skinny_gemm_slices(int tokens, int features, int K) {
   const int tiles = (features + BM - 1) / BM;
   const int k_tiles = (K + BK - 1) / BK;
-  int want = (148 * 2 + tiles - 1) / tiles;
+  int want = (sm_count() * 2 + tiles - 1) / tiles;
   int most = k_tiles / 4;
   if (most < 1) most = 1;
   if (most > MAX_SLICES) most = MAX_SLICES;
@@ -438,7 +443,7 @@ DLI_EXPORT int dli_skinny_gemm_slices(int tokens, int features, int K) {
 }
 
 static int launch_skinny(void* out, int out_f32, const void* x, const void* w, int tokens, int features, int K, int slices,
-                         int max_stages, const Epilogue& ep, cudaStream_t stream) {
+                         int max_stages, const Epilogue& ep, cudaStream_t stream, unsigned wait_limit = WAIT_LIMIT, int skip_tile = -1) {
   if (tokens < 1 || tokens > 256 || features < 1 || K < 8 || K % 8 || slices < 1 || slices > MAX_SLICES) return DLI_ERR_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return DLI_ERR_UNSUPPORTED;
   if (!error_flag_host) {
@@ -461,7 +466,7 @@ static int launch_skinny(void* out, int out_f32, const void* x, const void* w, i
   // beside its scratch (two per SM, this kernel's and the next one's; measured: deeper pipelines were
   // slower in a chain of such kernels).  A caller that launches one CTA per SM and nothing behind it may ask for more.
   const int ctas = ((features + BM - 1) / BM) * slices;
-  const int budget = max_stages > 0 ? 200 * 1024 : ctas > 148 ? 73 * 1024 - scratch : 72 * 1024;
+  const int budget = max_stages > 0 ? 200 * 1024 : ctas > sm_count() ? 73 * 1024 - scratch : 72 * 1024;
   if (max_stages > 0 && stages > max_stages) stages = max_stages;
   const int fixed = BARRIER_BYTES + scratch + 1024;
   while (stages > 1 && (stages * stage_bytes > budget || stages * stage_bytes + fixed > 227 * 1024)) --stages;
@@ -470,20 +475,20 @@ static int launch_skinny(void* out, int out_f32, const void* x, const void* w, i
   if (smem > 227 * 1024) return DLI_ERR_UNSUPPORTED;
   int tmem_cols = 32;
   while (tmem_cols < npad) tmem_cols <<= 1;
-  static bool big_clusters = false;
-  if (slices > 8 && !big_clusters) {
+  static OncePerDevice big_clusters;
+  if (slices > 8 && !big_clusters.here()) {
     cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
-    big_clusters = true;
+    big_clusters.here() = true;
   }
-  static int configured = 0;
-  if (smem > configured) {
+  static MaxPerDevice configured;
+  if (smem > configured.here()) {
     cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = smem;
+    configured.here() = smem;
   }
   cudaError_t e = launch_pdl(skinny_gemm_kernel, dim3((features + BM - 1) / BM, slices), dim3(128), (size_t)smem, stream, slices, map_w,
-                             map_x, out, out_f32, tokens, features, k_tiles, per, npad, stages, tmem_cols, error_flag_device, ep);
+                             map_x, out, out_f32, tokens, features, k_tiles, per, npad, stages, tmem_cols, error_flag_device, ep, wait_limit, skip_tile);
   return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
@@ -551,3 +556,18 @@ DLI_EXPORT int dli_skinny_gemm_residual(void* x_out, float* h, const float* gain
 DLI_EXPORT int dli_skinny_gemm_error() { return error_flag_host ? *error_flag_host : 0; }
 // Forget a recorded code (the host has read it); call with no launch of this library in flight.
 DLI_EXPORT int dli_skinny_gemm_clear_error() { if (error_flag_host) *error_flag_host = 0; return 0; }
+
+// For the test of the bounded waits only.  The plain product (float32 out, `slices` K slices), but the copies of
+// k tile `skip_tile` are never issued and every wait gives up after `wait_limit` polls: the tensor-core warp's wait
+// for that tile runs out, the kernel records code 2, stores whatever it has, completes its cluster barriers, frees
+// its tensor memory and returns.  With skip_tile the last tile of a slice, and no more tiles in a slice than the
+// pipeline has stages, no copy is in flight when the CTA leaves.  The engine never calls this.
+DLI_EXPORT int dli_skinny_gemm_wait_test(void* out, const void* x, const void* w, int tokens, int features, int K, int slices,
+                                         unsigned wait_limit, int skip_tile, cudaStream_t stream) {
+  if (wait_limit < 1 || wait_limit > WAIT_LIMIT) return DLI_ERR_UNSUPPORTED;
+  const int k_tiles = (K + BK - 1) / BK, per = (k_tiles + slices - 1) / (slices > 0 ? slices : 1);
+  if (per > 8) return DLI_ERR_UNSUPPORTED;  // every tile of a slice has a stage of its own
+  Epilogue ep = {};
+  ep.mode = EP_STORE;
+  return launch_skinny(out, 1, x, w, tokens, features, K, slices, 0, ep, stream, wait_limit, skip_tile);
+}

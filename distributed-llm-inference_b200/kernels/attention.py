@@ -13,8 +13,23 @@ import torch
 
 from . import ops
 
-ONE_WAVE = 148 * 2  # CTAs of the mma.sync decode kernel resident at once (two per SM in its few-sequences shape)
-ONE_WAVE_TMA = 148 * 4  # ... of the TMA-fed decode kernel (four per SM at head size 64; two at head size 128)
+import functools
+
+
+@functools.lru_cache(maxsize=None)
+def sm_count() -> int:
+    """SMs of the current CUDA device; without one (host-side tests) the B200's 148."""
+    if torch.cuda.is_available():
+        return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+    return 148
+
+
+def one_wave(ctas_per_sm: int) -> int:
+    """CTAs resident at once: the mma.sync decode kernel holds two per SM in its few-sequences shape, the
+    TMA-fed decode kernel four at head size 64 and two at head size 128."""
+    return sm_count() * ctas_per_sm
+
+
 MIN_TILES_PER_SPLIT = 2  # key tiles (of 64) a split should at least cover
 
 
@@ -22,10 +37,11 @@ CLUSTER_SPLITS_MAX = ops.DECODE_TMA_CLUSTER_SPLITS  # splits that the TMA decode
 CLUSTER_SPLITS_KV_LIMIT = 3072  # beyond this context more splits and a merge kernel win (16 K keys, 4 sequences: 28 us against 41)
 
 
-def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int = ONE_WAVE, fill_last_wave: bool = True) -> int:
+def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int | None = None, fill_last_wave: bool = True) -> int:
     """Key splits for single-token sequences: as many as still fit the GPU in one wave (a second,
     partly filled wave costs more than the extra parallelism brings), none shorter than
     MIN_TILES_PER_SPLIT key tiles (the role of src/dli/model/paged_attention.py:63-74)."""
+    wave = one_wave(2) if wave is None else wave
     pairs = max(1, num_seqs * ctas_per_seq)
     tiles = -(-max_kv_len // 64)
     most = max(1, tiles // MIN_TILES_PER_SPLIT)
@@ -48,7 +64,7 @@ def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_s
     """Key splits of the decode kernel that will serve these sizes."""
     ctas_per_seq = nkv * -(-(num_heads // nkv) // 16)
     tma = ops.decode_tma_supported(head_dim, page_size)
-    wave = (ONE_WAVE_TMA if head_dim <= 64 else ONE_WAVE_TMA // 2) if tma else ONE_WAVE
+    wave = one_wave(4 if head_dim <= 64 else 2) if tma else one_wave(2)
     splits = choose_splits(num_seqs, ctas_per_seq, max_kv_len, wave, fill_last_wave=not tma)
     if tma and max_kv_len <= CLUSTER_SPLITS_KV_LIMIT:
         # short contexts: a split count that one cluster merges on the chip (up to 8 CTAs, or 16) is faster than

@@ -577,6 +577,23 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
     return out
 
 
+def skinny_gemm_wait_test(x: torch.Tensor, weight: torch.Tensor, slices: int, wait_limit: int, skip_tile: int) -> torch.Tensor:
+    """For the test of the kernel's bounded waits: the plain product in float32, except that the copies of k tile
+    ``skip_tile`` (64 columns of K each) are left out and every wait gives up after ``wait_limit`` polls.  The
+    kernel then records code 2 (``skinny_gemm_error``), stores what it has and returns; nothing hangs or
+    faults.  ``skip_tile`` must be the last tile of its slice and K / 64 / slices at most 8.  Not used by the engine."""
+    _need(x, "x", torch.bfloat16), _need(weight, "weight", torch.bfloat16)
+    tokens, K = x.shape
+    features = weight.shape[0]
+    per = -(-(-(-K // 64)) // slices)
+    if weight.shape[1] != K or not 1 <= slices <= 16 or per > 8 or skip_tile < 0 or (skip_tile + 1) % per:
+        raise KernelError("skinny_gemm_wait_test: the tile left out must be the last one of a slice of at most 8 tiles")
+    out = torch.zeros((tokens, features), dtype=torch.float32, device=x.device)
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_wait_test", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.c_uint, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(weight), tokens, features, K, slices, wait_limit, skip_tile, _stream()), "skinny_gemm_wait_test")
+    return out
+
+
 def skinny_gemm_residual(x, weight: torch.Tensor, h: torch.Tensor, gain: torch.Tensor, eps: float, slices: int | None = None) -> ScaledRows:
     """h += x W^T (float32, in place) and the first half of the RMS norm that follows, in the
     product's epilogue: returns ScaledRows(bfloat16(h * gain), sums of h^2 per 128 features, eps).

@@ -88,9 +88,15 @@ def read_safetensors(path: str | Path) -> dict[str, np.ndarray]:
 
 def round_to_bfloat16(x: np.ndarray) -> np.ndarray:
     """Round float32 to the nearest bfloat16 (ties to even), returned as float32."""
-    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
-    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
-    return bits.astype(np.uint32).view(np.float32).reshape(x.shape)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    bits = x.view(np.uint32)
+    # 32-bit arithmetic: the sum wraps only for bit patterns above 0xFFFF8000, which are NaNs (put back below)
+    out = (bits + (np.uint32(0x7FFF) + ((bits >> np.uint32(16)) & np.uint32(1)))) & np.uint32(0xFFFF0000)
+    out = out.view(np.float32).reshape(x.shape)
+    nan = np.isnan(x)
+    if nan.any():
+        out[nan] = np.nan
+    return out
 
 
 # --------------------------------------------------------------------------- parts
@@ -151,19 +157,20 @@ def causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, window: int | 
     """
     heads, n, d = q.shape
     fan = heads // k.shape[0]
-    k = np.repeat(k, fan, axis=0)
-    v = np.repeat(v, fan, axis=0)
-    s = np.einsum("hqd,hkd->hqk", q, k) / q.dtype.type(math.sqrt(d))
     qi = np.arange(n)[:, None]
     ki = np.arange(n)[None, :]
     mask = ki <= qi
     if window is not None:
         mask &= (qi - ki) < window
-    s = np.where(mask[None], s, -np.inf)
-    s = s - s.max(axis=-1, keepdims=True)
-    p = np.exp(s)
-    p = p / p.sum(axis=-1, keepdims=True)
-    return np.einsum("hqk,hkd->hqd", p, v)
+    out = np.empty_like(q)
+    for h in range(heads):  # head by head: a square of scores at a time, however long the sequence
+        s = (q[h] @ k[h // fan].T) / q.dtype.type(math.sqrt(d))
+        s = np.where(mask, s, -np.inf)
+        s = s - s.max(axis=-1, keepdims=True)
+        p = np.exp(s)
+        p = p / p.sum(axis=-1, keepdims=True)
+        out[h] = p @ v[h // fan]
+    return out
 
 
 def attention_block(x, w, prefix, c, cos, sin):
@@ -201,8 +208,9 @@ def decoder_layer(x, w, i, c, cos, sin):
     return x + swiglu_mlp(rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"]), w, p + "mlp.")
 
 
-def forward(config: dict, weights: dict[str, np.ndarray], token_ids, dtype=np.float32) -> np.ndarray:
-    """Logits [n, vocab] of one whole sequence at positions 0..n-1.
+def forward(config: dict, weights: dict[str, np.ndarray], token_ids, dtype=np.float32, rows=None) -> np.ndarray:
+    """Logits [n, vocab] of one whole sequence at positions 0..n-1 (with ``rows``: only at those positions,
+    [len(rows), vocab]; every position still goes through the layers).
 
     src/dli/model/llama.py:291-305: embed, rope tables, layers, final norm, head
     (tied head uses the embedding matrix, :304).
@@ -215,6 +223,8 @@ def forward(config: dict, weights: dict[str, np.ndarray], token_ids, dtype=np.fl
     cos, sin = cos.astype(dtype), sin.astype(dtype)
     for i in range(c["layers"]):
         h = decoder_layer(h, w, i, c, cos, sin)
+    if rows is not None:
+        h = h[np.asarray(rows, dtype=np.int64)]
     h = rms_norm(h, w["model.norm.weight"], c["eps"])
     head = w["model.embed_tokens.weight"] if c["tied"] else w["lm_head.weight"]
     return (h @ head.T).astype(np.float32)

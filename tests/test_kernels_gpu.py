@@ -276,6 +276,44 @@ def test_paged_decode_tma(nh, nkv, page, window, splits, d):
     assert ops.paged_prefill_tc_error() == 0
 
 
+def plain_decode_rows(t, seqs, nh):
+    """Attention of each sequence's one query over all its keys, in float64, row by row (the whole-sequence
+    restatement above would build a square of scores per head, which thousands of keys make too large)."""
+    outs = []
+    for i in range(len(seqs)):
+        q = t["Q"][i].double().numpy()[0]  # [nh, d]
+        K, V = t["K"][i].double().numpy(), t["V"][i].double().numpy()  # [keys, nkv, d]
+        fan = nh // K.shape[1]
+        row = []
+        for h in range(nh):
+            sc = K[:, h // fan] @ q[h] / math.sqrt(q.shape[-1])
+            w = np.exp(sc - sc.max())
+            row.append((w / w.sum()) @ V[:, h // fan])
+        outs.append(np.concatenate(row))
+    return np.stack(outs)
+
+
+@pytest.mark.parametrize("d,nh,nkv,page,splits,lens", [
+    (64, 32, 8, 16, 16, [2048, 2049, 2500, 3071]),  # one cluster of 16 CTAs merges the splits (what one sequence at 2 K..3 K keys gets)
+    (64, 32, 8, 16, 24, [4096, 5003]),  # beyond a cluster: partial results in scratch, merged by the merge kernel
+    (64, 32, 8, 16, 32, [4100, 6001, 33]),
+    (64, 3, 1, 8, 16, [2300]),
+    (128, 24, 8, 16, 16, [2048, 3000]),
+    (128, 24, 8, 16, 32, [4200, 8100]),
+])
+def test_paged_decode_tma_many_splits_over_long_contexts(d, nh, nkv, page, splits, lens):
+    """The split counts the engine picks for few sequences with thousands of keys: 16 (merged on the chip by a
+    cluster of the non-portable size 16) and 24 / 32 (merge kernel), contexts that end on and off tile edges,
+    one sequence far shorter than a split's share."""
+    seqs = [(n - 1, 1) for n in lens]
+    t = attention_case(nh, nkv, d, page, seqs, torch.bfloat16, seed=splits + len(lens), sharp=(0, 0, lens[0] // 3))
+    out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scratch = (torch.full((len(seqs) * nh * splits * d,), float("nan"), device=DEV), torch.full((len(seqs) * nh * splits * 2,), float("nan"), device=DEV))
+    ops.paged_decode_tma(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(seqs), 0, nh, d**-0.5, None, splits, scratch)
+    np.testing.assert_allclose(out.float().cpu().numpy(), plain_decode_rows(t, seqs, nh), atol=tol(torch.bfloat16, 2))
+    assert ops.paged_prefill_tc_error() == 0
+
+
 @pytest.mark.parametrize("nh,nkv,page,window", [(6, 2, 16, None), (3, 1, 8, 70), (4, 4, 128, None), (24, 8, 32, 200), (9, 1, 16, None)])
 def test_paged_prefill_tc_head_size_128(nh, nkv, page, window):
     """Head size 128 goes to the kernel with a thread per row: two 128-byte slabs per row of keys and values."""
@@ -539,4 +577,23 @@ def test_skinny_gemm_with_residual_epilogue_and_row_scaling(tokens, H, K, slices
     want_h2 = h.double() + y @ w3.double().T
     np.testing.assert_allclose(h2.double().cpu().numpy(), want_h2.cpu().numpy(), atol=2e-2 * max(1.0, float(want_h2.abs().max())))
     np.testing.assert_allclose(nxt.ssq.double().sum(1).cpu().numpy(), (h2.double() ** 2).sum(1).cpu().numpy(), rtol=1e-4)
+    assert ops.skinny_gemm_error() == 0
+
+
+def test_a_wait_inside_the_decode_product_runs_out_and_the_kernel_gives_up_in_order():
+    """The copies of one k tile are never issued (a test-only entry; a flag that nothing sets) and the waits are
+    limited to a few thousand polls: the kernel gives the wait up, records which one it was, completes its cluster
+    barriers, frees its tensor memory and returns.  The host reads the code, nothing hangs, and the next
+    ordinary product — same shapes, same cluster size, tensor memory allocated afresh — is right."""
+    tokens, features, K, slices = 5, 384, 512, 2  # 8 k tiles: 4 per slice, each in a stage of its own
+    x, w = rnd(tokens, K, dtype=torch.bfloat16, seed=1), rnd(features, K, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = x.float() @ w.float().T
+    assert ops.device_wait_errors() == {}
+    ops.skinny_gemm_wait_test(x, w, slices, wait_limit=4000, skip_tile=7)  # the last tile of the second slice never arrives
+    torch.cuda.synchronize()  # returns: the kernel ended by itself
+    assert ops.skinny_gemm_error() == 2  # the tensor-core warp's wait for a stage's copies
+    assert ops.device_wait_errors() == {"skinny_gemm.cu": 2} and ops.device_wait_errors() == {}  # read once, then forgotten
+    for _ in range(3):
+        got = ops.skinny_gemm(x, w, out_dtype=torch.float32, slices=slices)
+        np.testing.assert_allclose(got.cpu().numpy(), want.cpu().numpy(), atol=2e-2)
     assert ops.skinny_gemm_error() == 0
