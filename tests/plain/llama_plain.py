@@ -147,13 +147,20 @@ def rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
     return w * (x / np.sqrt(var + w.dtype.type(eps)))
 
 
-def causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, window: int | None = None) -> np.ndarray:
+def _same(x):
+    return x
+
+
+def causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, window: int | None = None, rnd=_same) -> np.ndarray:
     """softmax(q k^T / sqrt(d) + causal mask) v for one whole sequence.
 
     q [heads, n, d]; k, v [kv_heads, n, d]; query head h reads kv head h // (heads/kv_heads).
     src/dli/model/llama.py:147-177 (expansion :158-163, causal case :169).
     ``window`` (keys u with p - u < window) is not part of the reference's architecture;
     it exists so that the engine's generic attention part can be checked with one.
+    ``rnd`` (identity, or round_to_bfloat16): applied to the unnormalised probabilities before the product
+    with v, as a bfloat16 tensor-core kernel must (src/dli/model/paged_attention.py:167 does the same);
+    the row sums stay float32.
     """
     heads, n, d = q.shape
     fan = heads // k.shape[0]
@@ -168,49 +175,55 @@ def causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, window: int | 
         s = np.where(mask, s, -np.inf)
         s = s - s.max(axis=-1, keepdims=True)
         p = np.exp(s)
-        p = p / p.sum(axis=-1, keepdims=True)
-        out[h] = p @ v[h // fan]
+        out[h] = (rnd(p) @ v[h // fan]) / p.sum(axis=-1, keepdims=True)
     return out
 
 
-def attention_block(x, w, prefix, c, cos, sin):
+def attention_block(x, w, prefix, c, cos, sin, rnd=_same):
     """q/k/v projections, RoPE on q and k, attention, output projection.
 
     src/dli/model/llama.py:72-76 (projections, rope), :94-95 (merge heads, o_proj).
+    ``rnd``: rounding of every tensor that a bfloat16 model holds in bfloat16 (identity for float32).
     """
     n = x.shape[0]
     d = c["head_dim"]
-    q = (x @ w[prefix + "q_proj.weight"].T).reshape(n, c["heads"], d).transpose(1, 0, 2)
-    k = (x @ w[prefix + "k_proj.weight"].T).reshape(n, c["kv_heads"], d).transpose(1, 0, 2)
-    v = (x @ w[prefix + "v_proj.weight"].T).reshape(n, c["kv_heads"], d).transpose(1, 0, 2)
-    q = apply_rope(q, cos, sin)
-    k = apply_rope(k, cos, sin)
-    o = causal_attention(q, k, v)
+    q = rnd(x @ w[prefix + "q_proj.weight"].T).reshape(n, c["heads"], d).transpose(1, 0, 2)
+    k = rnd(x @ w[prefix + "k_proj.weight"].T).reshape(n, c["kv_heads"], d).transpose(1, 0, 2)
+    v = rnd(x @ w[prefix + "v_proj.weight"].T).reshape(n, c["kv_heads"], d).transpose(1, 0, 2)
+    q = rnd(apply_rope(q, cos, sin))
+    k = rnd(apply_rope(k, cos, sin))
+    o = rnd(causal_attention(q, k, v, rnd=rnd))
     merged = o.transpose(1, 0, 2).reshape(n, c["heads"] * d)
-    return merged @ w[prefix + "o_proj.weight"].T
+    return rnd(merged @ w[prefix + "o_proj.weight"].T)
 
 
 def silu(z: np.ndarray) -> np.ndarray:
     return z / (1 + np.exp(-z))
 
 
-def swiglu_mlp(x, w, prefix):
+def swiglu_mlp(x, w, prefix, rnd=_same):
     """down(silu(gate(x)) * up(x)).  src/dli/model/llama.py:189-191."""
-    g = x @ w[prefix + "gate_proj.weight"].T
-    u = x @ w[prefix + "up_proj.weight"].T
-    return (silu(g) * u) @ w[prefix + "down_proj.weight"].T
+    g = rnd(x @ w[prefix + "gate_proj.weight"].T)
+    u = rnd(x @ w[prefix + "up_proj.weight"].T)
+    return rnd(rnd(silu(g) * u) @ w[prefix + "down_proj.weight"].T)
 
 
-def decoder_layer(x, w, i, c, cos, sin):
+def decoder_layer(x, w, i, c, cos, sin, rnd=_same):
     """x + attn(norm(x)), then x + mlp(norm(x)).  src/dli/model/llama.py:211-212."""
     p = f"model.layers.{i}."
-    x = x + attention_block(rms_norm(x, w[p + "input_layernorm.weight"], c["eps"]), w, p + "self_attn.", c, cos, sin)
-    return x + swiglu_mlp(rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"]), w, p + "mlp.")
+    x = x + attention_block(rnd(rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])), w, p + "self_attn.", c, cos, sin, rnd)
+    return x + swiglu_mlp(rnd(rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])), w, p + "mlp.", rnd)
 
 
-def forward(config: dict, weights: dict[str, np.ndarray], token_ids, dtype=np.float32, rows=None) -> np.ndarray:
+def forward(config: dict, weights: dict[str, np.ndarray], token_ids, dtype=np.float32, rows=None, bf16_activations=False) -> np.ndarray:
     """Logits [n, vocab] of one whole sequence at positions 0..n-1 (with ``rows``: only at those positions,
     [len(rows), vocab]; every position still goes through the layers).
+
+    ``bf16_activations``: a bfloat16 model as the reference runs one (src/dli/model/loader.py:46 casts the
+    weights; every module output is then bfloat16): the outputs of the products, of the norms, of rope, of the
+    attention (and its probabilities) and of SiLU * up are rounded to bfloat16; the arithmetic between
+    roundings, the residual sum and the logits stay float32.  With it off (and weights rounded by the
+    caller) only the weights are bfloat16.
 
     src/dli/model/llama.py:291-305: embed, rope tables, layers, final norm, head
     (tied head uses the embedding matrix, :304).
@@ -221,11 +234,12 @@ def forward(config: dict, weights: dict[str, np.ndarray], token_ids, dtype=np.fl
     h = w["model.embed_tokens.weight"][ids]
     cos, sin = rope_cos_sin(inverse_frequencies(c), np.arange(len(ids)))
     cos, sin = cos.astype(dtype), sin.astype(dtype)
+    rnd = round_to_bfloat16 if bf16_activations else _same
     for i in range(c["layers"]):
-        h = decoder_layer(h, w, i, c, cos, sin)
+        h = decoder_layer(h, w, i, c, cos, sin, rnd)
     if rows is not None:
         h = h[np.asarray(rows, dtype=np.int64)]
-    h = rms_norm(h, w["model.norm.weight"], c["eps"])
+    h = rnd(rms_norm(h, w["model.norm.weight"], c["eps"]))
     head = w["model.embed_tokens.weight"] if c["tied"] else w["lm_head.weight"]
     return (h @ head.T).astype(np.float32)
 

@@ -113,6 +113,12 @@ def test_portions_decode_and_batch_at_real_sizes(case, dtype):
 
 
 # ---- what the benchmark runs: contexts of 2,048 and more, 1 / 8 / 64 sequences decoding, 8,000 tokens at head size 128
+#
+# Over thousands of keys the plain implementation rounds where a bfloat16 model rounds (``bf16_activations``: the
+# outputs of products, norms, rope and attention, and the attention's probabilities).  With float32 activations and
+# only the weights rounded it lies as far from a bfloat16 run (0.28 at 2,048 tokens, logits up to 5) as the
+# tolerance allows in all, which would leave a fault nothing to show itself in; rounded alike, the engine is
+# within 0.10.
 
 
 def worst(got, want):
@@ -173,7 +179,7 @@ def long_1b(tmp_path_factory):
     cfg, path, weights = model_folder("llama_1b", tmp_path_factory)
     tokens = random_tokens(cfg["vocab_size"], 2048 + 24, seed=11)
     rows = sorted(set(range(0, 2048, 9)) | set(range(1960, 2048 + 24)))
-    want = dict(zip(rows, plain.forward(cfg, plain_weights_for(weights, "bfloat16"), tokens, rows=rows)))
+    want = dict(zip(rows, plain.forward(cfg, plain_weights_for(weights, "bfloat16"), tokens, rows=rows, bf16_activations=True)))
     tol = 5e-2 * max(1.0, max(float(np.abs(v).max()) for v in want.values()))
     return cfg, path, tokens, want, tol
 
@@ -250,7 +256,7 @@ def test_a_context_of_8000_tokens_at_head_size_128_in_portions_of_2048(tmp_path_
     cfg, path, weights = model_folder("llama_3b", tmp_path_factory)
     tokens = random_tokens(cfg["vocab_size"], 8000 + 4, seed=12)
     rows = sorted(set(range(5, 8000, 41)) | set(range(7990, 8004)))
-    want = dict(zip(rows, plain.forward(cfg, plain_weights_for(weights, "bfloat16"), tokens, rows=rows)))
+    want = dict(zip(rows, plain.forward(cfg, plain_weights_for(weights, "bfloat16"), tokens, rows=rows, bf16_activations=True)))
     tol = 5e-2 * max(1.0, max(float(np.abs(v).max()) for v in want.values()))
     model = dli_b200.load_model(path, "bfloat16")
     r = runner_with_used_pages(model, num_pages=8064 // 16 + 2, page_size=16, max_requests=2)
@@ -289,7 +295,7 @@ def test_a_prefix_hit_in_bfloat16_leaves_the_logits_as_they_are(long_1b):
     _, _, weights = _FOLDERS["llama_1b"]
     other = tokens[:1000] + random_tokens(cfg["vocab_size"], 240, seed=13)
     rows = list(range(1000, 1240, 7)) + [1239]
-    ref = dict(zip(rows, plain.forward(cfg, plain_weights_for(weights, "bfloat16"), other, rows=rows)))
+    ref = dict(zip(rows, plain.forward(cfg, plain_weights_for(weights, "bfloat16"), other, rows=rows, bf16_activations=True)))
     model = dli_b200.load_model(path, "bfloat16")
     r = runner_with_used_pages(model, num_pages=2 * (2048 // 16) + 8, page_size=16, max_requests=2, enable_prefix_caching=True)
     r.manager.allocate("first", tokens[:2048])
@@ -307,7 +313,12 @@ def test_a_prefix_hit_in_bfloat16_leaves_the_logits_as_they_are(long_1b):
             assert worst(out[0], ref[pos]) <= tol
     # teeth: the same request once more; in the second layer its first (shared) page and its last one, which holds
     # four of its tokens and junk behind them, change places
+    # (from an index that knows the first request only: everything is given back and forgotten, the first runs again)
     r.manager.free("second")
+    r.manager.free("first")
+    r.manager.reset_prefix_cache()
+    r.manager.allocate("first", tokens[:2048])
+    r.step([StepEntry("first", tokens[:2048], [])])
     assert r.manager.allocate("again", other[:1236]).num_cached_tokens == 992
     with pages_swapped_in_one_layer(r.pools.layer_caches[1], 0, 0, 77):
         got = r.step([StepEntry("again", other[992:1236], [i - 992 for i in here])]).cpu().numpy()
