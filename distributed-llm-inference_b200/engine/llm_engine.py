@@ -22,7 +22,6 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Collection, Iterable, Protocol, Sequence
 
-from ..cache import UNKNOWN_TOKEN, OutOfPages
 from ..sampling import SamplingParams
 from .request import FinishReason, Priority, Request
 from .scheduler import ScheduledChunk, Scheduler, SchedulerConfig
@@ -264,31 +263,18 @@ class LLMEngine:
         return self._run(sched.chunks, len(sched.preempted))
 
     def _launch_ahead(self, flight: _InFlight) -> _InFlight | None:
-        """The decode step that follows ``flight``, launched on the ids it leaves on the device;
-        None whenever the scheduler has something to decide first."""
-        sch = self.scheduler
-        if sch.waiting or not flight.sampling or len(flight.sampling) != len(sch.running):
-            return None  # an admission is due, a prompt is still in portions, or someone was aborted
+        """The decode step that follows ``flight``, launched on the ids it leaves on the device; None
+        whenever the scheduler has something to decide first (``Scheduler.schedule_ahead``)."""
         if flight.tokens.device_ids is None:
             return None
-        chosen = [(i, r) for i, r in enumerate(flight.sampling)
-                  if not r.is_finished and len(r.output_ids) + 1 < r.params.max_tokens]  # the others end with the token in flight
-        if not chosen or len(chosen) > sch.config.max_num_batched_tokens:
+        plan = self.scheduler.schedule_ahead(flight.sampling)
+        self._unknown.update(plan.unknown)
+        if plan.copies:
+            self.runner.copy_pages(plan.copies)
+        if not plan.chunks:
             return None
-        try:
-            for _, r in chosen:
-                position = r.num_tokens  # of the token in flight
-                if self.manager.num_tokens(r.request_id) <= position:
-                    copies = self.manager.append_slots(r.request_id, [UNKNOWN_TOKEN])
-                    self._unknown[r.request_id] = position
-                    if copies:
-                        self.runner.copy_pages(copies)
-        except OutOfPages:
-            return None  # the scheduler will decide who yields; slots taken so far are kept and named when the ids arrive
-        chunks = [ScheduledChunk(r, r.num_computed_tokens, 1, True) for _, r in chosen]
-        sch.step_launched_ahead([r for _, r in chosen])
         self.steps_ahead += 1
-        return self._run(chunks, 0, flight.tokens, [i for i, _ in chosen], ahead=1)
+        return self._run(plan.chunks, 0, flight.tokens, plan.token_rows, ahead=1)
 
     def _resolve(self, flight: _InFlight, tokens: list[int]) -> list[RequestOutput]:
         outputs = []

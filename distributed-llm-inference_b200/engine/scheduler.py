@@ -20,6 +20,11 @@ keep it waiting for ever).
 
 Who is served first among equals in need (classes of service with aging, tenants'
 weighted shares) is decided by ``ordering.ServiceOrder``.
+
+The scheduler is the only place that decides what a step holds.  That includes the step the
+engine launches *ahead* (``schedule_ahead``): the decode step behind one whose sampled ids are
+still on the device.  It is offered only when there is nothing to decide — every running request
+decodes, nobody waits, pages are there — and is counted and charged like any other step.
 """
 
 from __future__ import annotations
@@ -28,7 +33,7 @@ from collections import deque
 from collections.abc import Mapping
 from dataclasses import dataclass, field
 
-from ..cache import CacheManager, OutOfPages
+from ..cache import UNKNOWN_TOKEN, CacheManager, OutOfPages
 from .ordering import ServiceOrder
 from .request import FinishReason, Request, RequestStatus
 
@@ -67,10 +72,30 @@ class SchedulerOutput:
     preempted: list[Request] = field(default_factory=list)
     admitted: list[Request] = field(default_factory=list)
     copies: list = field(default_factory=list)  # cache.PageCopy: to carry out before the step runs
+    # of a step planned ahead only: for each chunk the row of the step in flight whose sampled id is its token,
+    # and request -> position that was given a slot without an id (the engine names it once the id is read)
+    token_rows: list[int] | None = None
+    unknown: dict[str, int] = field(default_factory=dict)
 
     @property
     def num_batched_tokens(self) -> int:
         return sum(c.num_tokens for c in self.chunks)
+
+
+@dataclass
+class _Step:
+    """A step while it is put together: what has been decided, the tokens still to give out, who is in."""
+
+    out: SchedulerOutput
+    budget: int
+    served: set[str] = field(default_factory=set)
+
+    def give(self, req: Request, n: int) -> None:
+        """``req`` runs its next ``n`` tokens in this step."""
+        start = req.num_computed_tokens
+        self.out.chunks.append(ScheduledChunk(req, start, n, start + n == req.num_tokens))
+        self.served.add(req.request_id)
+        self.budget -= n
 
 
 class Scheduler:
@@ -79,7 +104,7 @@ class Scheduler:
         self.manager = manager
         self.order = ServiceOrder(config.tenant_weights, config.aging_steps)
         self.waiting: deque[Request] = deque()
-        self.running: list[Request] = []
+        self.running: list[Request] = []  # kept in service order by every schedule()
         self._known: dict[str, Request] = {}
 
     # ------------------------------------------------------------ life of a request
@@ -127,53 +152,76 @@ class Scheduler:
     # ------------------------------------------------------------ one step's batch
 
     def schedule(self) -> SchedulerOutput:
-        out = SchedulerOutput()
-        left = self._serve_running(out, self.config.max_num_batched_tokens)
-        if not out.preempted:  # a step that had to take pages away gives none out
-            self._admit_waiting(out, left)
+        """Decide the next step from what the host knows (every sampled id has been read)."""
+        step = _Step(SchedulerOutput(), self.config.max_num_batched_tokens)
+        self.running.sort(key=self.order.running_key)
+        for req in tuple(self.running):
+            if step.budget == 0:
+                break
+            # (a request earlier in this loop may have taken this one's pages: it waits again)
+            if req.status is RequestStatus.RUNNING and req.num_tokens > req.num_computed_tokens:
+                self._continue(req, step)
+        if not step.out.preempted:  # a step that had to take pages away gives none out
+            self._admit(step)
         self.order.tick()
-        return out
+        return step.out
 
-    def step_launched_ahead(self, reqs) -> None:
-        """A decode step of ``reqs`` that the engine launched without asking ``schedule``: it
-        counts as a step and its tokens are charged, as if it had been scheduled."""
-        for req in reqs:
+    def schedule_ahead(self, in_flight: list[Request]) -> SchedulerOutput:
+        """The decode step behind a step that is still running.  ``in_flight``: the requests that step samples
+        a token for, in the order of its sampled rows; their ids are on the device, so each request's next
+        token is named by its row.  The plan has chunks only if there is nothing to decide first: nobody
+        waits, every running request is among those sampling (no prompt in portions, nobody aborted), and
+        every request that goes on gets its slot.  A request that ends by length with the token in flight is
+        left out.  Slots taken for tokens without an id are reported in ``unknown`` whether or not the step
+        comes about (they are kept, and named when the ids arrive); so are page copies."""
+        plan = SchedulerOutput(token_rows=[])
+        if self.waiting or not in_flight or len(in_flight) != len(self.running):
+            return plan
+        going_on = [(row, r) for row, r in enumerate(in_flight)
+                    if not r.is_finished and len(r.output_ids) + 1 < r.params.max_tokens]  # the others end with the token in flight
+        if not going_on or len(going_on) > self.config.max_num_batched_tokens:
+            return plan
+        try:
+            for _, req in going_on:
+                position = req.num_tokens  # of the token in flight
+                if self.manager.num_tokens(req.request_id) <= position:
+                    plan.copies.extend(self.manager.append_slots(req.request_id, [UNKNOWN_TOKEN]) or ())
+                    plan.unknown[req.request_id] = position
+        except OutOfPages:
+            return plan  # schedule() will decide who yields
+        for row, req in going_on:
+            plan.chunks.append(ScheduledChunk(req, req.num_computed_tokens, 1, True))
+            plan.token_rows.append(row)
             self.order.charge(req.tenant, 1)
         self.order.tick()
+        return plan
 
-    def _serve_running(self, out: SchedulerOutput, budget: int) -> int:
-        """Every running request's next token or next portion, in service order; returns the budget left."""
-        in_batch: set[str] = set()
-        self.running.sort(key=self.order.running_key)
-        for req in list(self.running):
-            if budget == 0:
-                break
-            if req.status is not RequestStatus.RUNNING:
-                continue  # taken as a victim earlier in this loop
-            total = len(req.prompt_ids) + len(req.output_ids)
-            n = min(total - req.num_computed_tokens, budget)
-            if n <= 0:
-                continue
-            while not self._reserve(req, total, out):
-                victim = next((c for c in reversed(self.running) if c.request_id not in in_batch and c is not req), None)
-                if victim is None:
-                    victim = req  # nobody else can yield
-                self._preempt(victim)
-                out.preempted.append(victim)
-                if victim is req:
-                    break
-            if req.status is not RequestStatus.RUNNING:
-                continue
-            start = req.num_computed_tokens
-            out.chunks.append(ScheduledChunk(req, start, n, start + n == total))
-            in_batch.add(req.request_id)
-            self.order.charge(req.tenant, n)
-            budget -= n
-        return budget
+    # ------------------------------------------------------------ internals
 
-    def _admit_waiting(self, out: SchedulerOutput, budget: int) -> None:
+    def _continue(self, req: Request, step: _Step) -> None:
+        """A running request's next token, or the next portion of its prompt cut to the budget.  Pages it lacks
+        are taken from whoever ``_who_yields`` names, one request at a time, until its slots are there (or it
+        has given up its own)."""
+        while not self._has_slots(req, step.out):
+            victim = self._who_yields(req, step.served)
+            self._send_back(victim)
+            step.out.preempted.append(victim)
+            if victim is req:
+                return
+        n = min(req.num_tokens - req.num_computed_tokens, step.budget)
+        step.give(req, n)
+        self.order.charge(req.tenant, n)
+
+    def _who_yields(self, needy: Request, served: set[str]) -> Request:
+        """The last request in service order that is not yet in the step's batch; the needy one itself if there is none."""
+        for c in reversed(self.running):
+            if c is not needy and c.request_id not in served:
+                return c
+        return needy
+
+    def _admit(self, step: _Step) -> None:
         """Waiting requests, the most deserving first, while budget, request cap and pages allow."""
-        while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
+        while self.waiting and step.budget > 0 and len(self.running) < self.config.max_num_seqs:
             req = min(self.waiting, key=self.order.admission_key)
             tokens = req.all_token_ids
             # The pages held back by the watermark are room for running requests to grow into.
@@ -181,35 +229,31 @@ class Scheduler:
             # them would otherwise wait for ever (it passed the capacity check, so it fits alone).
             hold_back = bool(self.running)
             if not self.manager.can_allocate(tokens, self.config.namespace, hold_back):
-                break  # the head of the queue waits for memory; nobody jumps past it
-            alloc = self.manager.allocate(req.request_id, tokens, namespace=self.config.namespace, respect_watermark=hold_back)
+                return  # the head of the queue waits for memory; nobody jumps past it
+            found = self.manager.allocate(req.request_id, tokens, namespace=self.config.namespace, respect_watermark=hold_back)
             self.waiting.remove(req)
-            req.status = RequestStatus.RUNNING
-            req.num_computed_tokens = alloc.num_cached_tokens
             self.running.append(req)
-            out.admitted.append(req)
-            n = min(len(tokens) - alloc.num_cached_tokens, budget)
-            out.chunks.append(ScheduledChunk(req, req.num_computed_tokens, n, req.num_computed_tokens + n == len(tokens)))
+            req.status, req.num_computed_tokens = RequestStatus.RUNNING, found.num_cached_tokens
+            step.out.admitted.append(req)
+            n = min(len(tokens) - found.num_cached_tokens, step.budget)
+            step.give(req, n)
             self.order.charge(req.tenant, n)
-            budget -= n
 
-    # ------------------------------------------------------------ internals
-
-    def _reserve(self, req: Request, total: int, out: SchedulerOutput) -> bool:
-        """Slots for tokens the cache manager has not seen yet (the newly sampled one)."""
-        missing = total - self.manager.num_tokens(req.request_id)
-        if missing <= 0:
+    def _has_slots(self, req: Request, out: SchedulerOutput) -> bool:
+        """Make sure every token the request knows has a slot (the newly sampled one may not); False if pages ran out."""
+        have = self.manager.num_tokens(req.request_id)
+        if have >= req.num_tokens:
             return True
         try:
-            out.copies.extend(self.manager.append_slots(req.request_id, req.token_slice(total - missing, total)) or ())
-            return True
+            out.copies.extend(self.manager.append_slots(req.request_id, req.token_slice(have, req.num_tokens)) or ())
         except OutOfPages:
             return False
+        return True
 
-    def _preempt(self, req: Request) -> None:
+    def _send_back(self, req: Request) -> None:
+        """Preemption by recompute: the pages go, the tokens stay, the request is first in the queue again."""
         self.manager.free(req.request_id)
         self.running.remove(req)
-        req.status = RequestStatus.WAITING
-        req.num_computed_tokens = 0
-        req.num_preemptions += 1
         self.waiting.appendleft(req)
+        req.status, req.num_computed_tokens = RequestStatus.WAITING, 0
+        req.num_preemptions += 1

@@ -25,12 +25,27 @@ GPU_FIELDS = ("name", "uuid", "memory.total", "compute_cap", "driver_version", "
 
 
 def _run(cmd: list[str], timeout: float = 20.0) -> str | None:
-    if shutil.which(cmd[0]) is None:
+    """What ``cmd`` prints, or None if the tool is not there, fails, or takes longer than ``timeout``."""
+    tool = shutil.which(cmd[0])
+    if tool is None:
         return None
     try:
-        return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, check=True).stdout.strip()
-    except (subprocess.SubprocessError, OSError):
+        done = subprocess.run([tool, *cmd[1:]], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, timeout=timeout)
+    except (subprocess.TimeoutExpired, OSError):
         return None
+    return done.stdout.strip() if done.returncode == 0 else None
+
+
+def _proc_field(path: str, key: str) -> str | None:
+    """The value behind ``key`` in a /proc file of ``key : value`` lines."""
+    try:
+        with open(path) as lines:
+            for line in lines:
+                if line.startswith(key):
+                    return line.partition(":")[2].strip()
+    except OSError:
+        pass
+    return None
 
 
 def gpus() -> list[dict[str, str]] | None:
@@ -41,23 +56,12 @@ def gpus() -> list[dict[str, str]] | None:
 
 
 def cpu() -> dict[str, Any]:
-    model = None
+    total = _proc_field("/proc/meminfo", "MemTotal")  # "<n> kB"
     try:
-        for line in Path("/proc/cpuinfo").read_text().splitlines():
-            if line.startswith("model name"):
-                model = line.split(":", 1)[1].strip()
-                break
-    except OSError:
-        pass
-    mem = None
-    try:
-        for line in Path("/proc/meminfo").read_text().splitlines():
-            if line.startswith("MemTotal"):
-                mem = round(int(line.split()[1]) / 2**20, 1)
-                break
-    except (OSError, ValueError, IndexError):
-        pass
-    return {"model": model, "logical_cores": os.cpu_count(), "memory_gib": mem}
+        mem = round(int(total.split()[0]) / 2**20, 1) if total else None
+    except (ValueError, IndexError):
+        mem = None
+    return {"model": _proc_field("/proc/cpuinfo", "model name"), "logical_cores": os.cpu_count(), "memory_gib": mem}
 
 
 def torch_info() -> dict[str, Any] | None:

@@ -1,5 +1,10 @@
-"""Per-request generation settings, with the reference's names, defaults and checks
-(src/dli/sampling.py:22-56)."""
+"""Per-request generation settings.
+
+This class is the reference's API schema restated: the same seven fields with the same defaults, the same
+four checks with the same messages, and the same ``greedy`` property as ``SamplingParams`` in
+src/dli/sampling.py:22-56, so that code written against the reference's engine passes its parameters
+unchanged.  Nothing here is this engine's own design; what the engine does with the fields is
+(``sampling/sampler.py``, ``csrc/sampling.cu``)."""
 
 from __future__ import annotations
 

@@ -20,6 +20,7 @@ from dli_b200.cache.page_pool import PagePool
 from dli_b200.engine import batch as batch_mod
 from dli_b200.engine.llm_engine import LLMEngine
 from dli_b200.engine.ordering import ServiceOrder
+from dli_b200.engine import scheduler as scheduler_mod
 from dli_b200.engine.scheduler import Scheduler
 
 
@@ -119,19 +120,21 @@ MUTANTS = {
     "eviction does not unlink the parent": (PagePool, "_evict", "parent.children -= 1", "pass", [reference_traces, shadow_store]),
     "a fork counts as a hit": (CacheManager, "fork", "found_by_hash=False", "found_by_hash=True", [reference_traces]),
     # scheduler and order
-    "the oldest running request is the victim": (Scheduler, "_serve_running", "for c in reversed(self.running)", "for c in self.running", [reference_schedules, scheduler_rules]),
-    "a step that preempted still admits": (Scheduler, "schedule", "if not out.preempted:", "if True:", [scheduler_rules, reference_schedules]),
-    "the shortest waiting prompt is admitted first": (Scheduler, "_admit_waiting", "req = min(self.waiting, key=self.order.admission_key)",
+    "the oldest running request is the victim": (Scheduler, "_who_yields", "for c in reversed(self.running)", "for c in self.running", [reference_schedules, scheduler_rules]),
+    "a step that preempted still admits": (Scheduler, "schedule", "if not step.out.preempted:", "if True:", [scheduler_rules, reference_schedules]),
+    "the shortest waiting prompt is admitted first": (Scheduler, "_admit", "req = min(self.waiting, key=self.order.admission_key)",
                                                       "req = min(self.waiting, key=lambda r: len(r.prompt_ids))", [scheduler_rules, reference_schedules]),
-    "the budget is not charged for admitted prompts": (Scheduler, "_admit_waiting", "        budget -= n", "        budget -= 0", [scheduler_rules, reference_schedules]),
+    "the budget is not charged for the tokens given out": (scheduler_mod._Step, "give", "self.budget -= n", "self.budget -= 0", [scheduler_rules, reference_schedules]),
+    "a request that lost its pages to an earlier one is served all the same": (Scheduler, "schedule", "if req.status is RequestStatus.RUNNING and", "if", [scheduler_rules, reference_schedules, engine_loop]),
     "new requests go before preempted ones": (ServiceOrder, "admission_key", "never_ran = 0 if req.num_preemptions else 1", "never_ran = 1 if req.num_preemptions else 0", [scheduler_rules, reference_schedules]),
     "aging never happens": (ServiceOrder, "service_class", "aged = self.steps - req.arrival_step >= self.aging_steps", "aged = False", [scheduler_rules, reference_schedules]),
     "weights are ignored": (ServiceOrder, "charge", "tokens / self.weights.get(tenant, 1.0)", "tokens", [scheduler_rules, reference_schedules]),
     "an idle tenant keeps its old clock": (ServiceOrder, "arrive", "max(self.clock(tenant), floor)", "self.clock(tenant)", [scheduler_rules, reference_schedules]),
     # the engine loop and the step launched ahead
-    "a request that ends by length still gets a step ahead": (LLMEngine, "_launch_ahead", "len(r.output_ids) + 1 < r.params.max_tokens", "len(r.output_ids) < r.params.max_tokens + 1", [engine_loop]),
+    "a request that ends by length still gets a step ahead": (Scheduler, "schedule_ahead", "len(r.output_ids) + 1 < r.params.max_tokens", "len(r.output_ids) < r.params.max_tokens + 1", [engine_loop]),
     "the surplus token of a finished request is kept": (LLMEngine, "_resolve", "if req.is_finished:\n            continue", "if False:\n            continue", [engine_loop]),
-    "a step is launched ahead although a request waits": (LLMEngine, "_launch_ahead", "if sch.waiting or not flight.sampling", "if not flight.sampling", [engine_loop, reference_schedules_ahead]),
+    "a step is launched ahead although a request waits": (Scheduler, "schedule_ahead", "if self.waiting or not in_flight", "if not in_flight", [engine_loop, reference_schedules_ahead]),
+    "slots taken for a step ahead that does not come about are forgotten": (LLMEngine, "_launch_ahead", "self._unknown.update(plan.unknown)", "pass", [engine_loop]),
     "an unknown token is never named": (LLMEngine, "_resolve", "self.manager.set_token(req.request_id, position, int(tok))", "pass", [engine_loop]),
     "the stop token is dropped from the output": (LLMEngine, "_append_token", "req.output_ids.append(tok)\n", "req.output_ids.append(tok)\n    if tok in req.params.stop_token_ids: req.output_ids.pop()\n", [engine_loop, reference_schedules]),
     # batch gathering
