@@ -128,9 +128,10 @@ def weight_bytes(model):
 
 
 def cache_bytes_per_token(model):
-    from dli_b200.cache import PagedKVNeed
+    from dli_b200.cache.needs import paged_need_of
 
-    return sum(2 * n.num_kv_heads * n.head_dim * model.dtype.itemsize for n in model.cache_needs() if isinstance(n, PagedKVNeed))
+    paged = [paged_need_of(n) for n in model.cache_needs()]
+    return sum(2 * n.num_kv_heads * n.head_dim * model.dtype.itemsize for n in paged if n is not None)
 
 
 def prefill_flops(cfg, layers, tokens):

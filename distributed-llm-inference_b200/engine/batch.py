@@ -53,7 +53,9 @@ class StepBatch:
     max_q_len: int = 0
     max_kv_len: int = 0
     max_kv_len_single: int = 0  # longest context among the single-token sequences
-    forced_splits: int = 0  # key splits of decode attention fixed by the caller (0: chosen per step)
+    # id(part) -> what that part answered to ``decode_launch_key`` when this step's shape was fixed ahead of its
+    # data (a captured graph); a part not named here decides its launches from the step itself
+    launch_keys: dict = field(default_factory=dict)
     token_src: torch.Tensor | None = None  # [n] int32: row of the token source per token, -1 where token_ids holds the id
     logits_all_rows: bool = False  # logit_rows is 0, 1, .., n - 1: the final norm's output needs no gather
     scratch: dict = field(default_factory=dict)  # per-step results that parts share across layers; cleared by each forward

@@ -2,7 +2,7 @@
 
 A step in which every sequence brings one token has the same kernels whatever the tokens
 are, so its launches are captured once per shape and replayed: shapes are buckets of
-(sequences, block-table width, key splits).  The step's integers are copied into a static
+(sequences, block-table width, what the model's parts say changes their launches).  The step's integers are copied into a static
 device buffer before the replay; rows beyond the real sequences are padding that reads and
 writes a scratch page no request owns.  (The reference replays its decode forward the same
 way, src/dli/engine/cuda_graph.py:83-237, to hide the launch cost of its eager kernels; here
@@ -15,7 +15,6 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from ..kernels.attention import decode_splits
 from .batch import GroupView, StepBatch
 
 SEQ_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
@@ -30,7 +29,7 @@ class DecodeGraph:
     """One captured shape: ``seqs`` rows, tables ``width`` pages wide."""
 
     def __init__(self, model, caches, num_groups: int, scratch_pages: list[int], page_size: int, seqs: int, width: int,
-                 splits: int) -> None:
+                 launch_keys: dict) -> None:
         self.seqs, self.width, self.num_groups = seqs, width, num_groups
         dev = model.device
         per_group = seqs + seqs * width
@@ -48,7 +47,7 @@ class DecodeGraph:
             n=seqs, num_seqs=seqs, num_single=seqs, token_ids=self.ints[0:seqs], positions=self.ints[seqs : 2 * seqs],
             seq_of_token=arange[:seqs], q_start=arange, kv_len=self.ints[2 * seqs : 3 * seqs], state_slot=self.ints[3 * seqs : 4 * seqs],
             logit_rows=arange[:seqs], groups=views, q_lens=[1] * seqs, starts=[0] * seqs, state_slots=[0] * seqs, max_q_len=1,
-            max_kv_len=width * page_size, max_kv_len_single=width * page_size, forced_splits=splits,
+            max_kv_len=width * page_size, max_kv_len_single=width * page_size, launch_keys=launch_keys,
             logits_all_rows=True,
         )
         self._pad = pad
@@ -113,30 +112,41 @@ class DecodeGraphs:
 
     def __init__(self, model, pools, page_size: int) -> None:
         self.model, self.pools, self.page_size = model, pools, page_size
-        self.graphs: dict[tuple[int, int, int], DecodeGraph] = {}
-        self.max_graphs = 32
+        self.graphs: dict[tuple, DecodeGraph] = {}  # (sequences, width, the parts' launch keys) -> graph, oldest use first
+        self.max_graphs = 32  # at the cap the graph that was used least recently makes room
         self.failure: str | None = None
+        self._asked: dict[tuple[int, int], dict] = {}  # (sequences, width) -> the parts' answers (they depend on nothing else)
 
-    def splits_for(self, seqs: int, max_kv_len: int) -> int:
-        """One split count per graph: the smallest any attention mixer of the model would choose."""
-        counts = [decode_splits(seqs, m.nh, m.nkv, m.d, self.page_size, max_kv_len)
-                  for layer in self.model.layers for m in [getattr(layer, "mixer", None)] if hasattr(m, "nkv")]
-        return min(counts, default=1)
+    def launch_keys(self, seqs: int, max_kv_len: int) -> dict:
+        """id(part) -> the part's answer, for every part of the model that has one (``Part.decode_launch_key``)."""
+        keys = {}
+        for part in self.model.parts():
+            ask = getattr(part, "decode_launch_key", None)
+            key = ask(seqs, max_kv_len, self.page_size) if ask is not None else None
+            if key is not None:
+                keys[id(part)] = key
+        return keys
 
     def lookup(self, num_seqs: int, width: int, max_kv_len: int) -> DecodeGraph | None:
         seqs = bucket_seqs(num_seqs)
         if seqs is None:
             return None
         width = -(-width // WIDTH_STEP) * WIDTH_STEP
-        splits = self.splits_for(seqs, width * self.page_size)
-        key = (seqs, width, splits)
-        graph = self.graphs.get(key)
-        if graph is None:
-            if len(self.graphs) >= self.max_graphs:
+        launch = self._asked.get((seqs, width))
+        if launch is None:
+            launch = self._asked[(seqs, width)] = self.launch_keys(seqs, width * self.page_size)
+        key = (seqs, width, tuple(launch.values()))  # (parts are walked in a fixed order)
+        graph = self.graphs.pop(key, None)
+        if graph is not None:
+            self.graphs[key] = graph  # most recently used: last
+        else:
+            if self.max_graphs == 0:
                 return None
+            while len(self.graphs) >= self.max_graphs:
+                del self.graphs[next(iter(self.graphs))]  # shapes drift in a long run: the stalest graph goes
             try:
                 graph = self.graphs[key] = DecodeGraph(self.model, self.pools.layer_caches, len(self.pools.group_needs),
-                                                       self.pools.scratch_pages, self.page_size, seqs, width, splits)
+                                                       self.pools.scratch_pages, self.page_size, seqs, width, launch)
             except RuntimeError as exc:  # a part turned out not to be capturable after all: run step by step from now on
                 self.max_graphs = 0
                 self.failure = str(exc)

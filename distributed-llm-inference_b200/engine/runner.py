@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheManager, CachePools, GroupSpec
-from ..cache.needs import PagedKVNeed, StateNeed
+from ..cache.needs import paged_need_of, state_needs_of
 from ..config.registry import load_config, resolve_architecture
 from ..kernels import ops
 from ..parts import DecoderModel
@@ -78,13 +78,13 @@ class ModelRunner:
         self.model = model
         needs = model.cache_needs()
         order = model.spec.run_order
-        n_groups = len({n for n in needs if isinstance(n, PagedKVNeed)})
+        n_groups = len({paged_need_of(n) for n in needs} - {None})
         pages = [num_pages] * n_groups if isinstance(num_pages, int) else list(num_pages)
         self.pools = CachePools(needs, order, pages, page_size, max_requests, model.dtype, model.device)
         self.manager = CacheManager(
             [GroupSpec(p, need.window) for p, need in zip(pages, self.pools.group_needs)],
             page_size, max_requests, enable_prefix_caching=enable_prefix_caching,
-            has_state=any(isinstance(n, StateNeed) for n in needs), watermark=watermark, eviction_policy=eviction_policy,
+            has_state=any(state_needs_of(n) for n in needs), watermark=watermark, eviction_policy=eviction_policy,
         )
         self.page_size = page_size
         self.uploader = Uploader(model.device)

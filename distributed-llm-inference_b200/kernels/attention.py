@@ -76,7 +76,10 @@ def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_s
     return splits
 
 
-def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_heads: int, scale: float, window: int | None) -> None:
+def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_heads: int, scale: float, window: int | None,
+                    splits: int | None = None) -> None:
+    """Attention of every token of the step over its sequence's pages.  ``splits``: key runs per single-token
+    sequence, if the caller fixed them (a recorded graph); otherwise chosen from this step's shape."""
     group = batch.group(cache.group)
     _, nkv, _, d = cache.k.shape
     if out.dtype != torch.bfloat16 or not ops.mma_head_dim_supported(d):
@@ -86,7 +89,7 @@ def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_head
     singles, total = batch.num_single, batch.num_seqs
     if singles:
         tma = ops.decode_tma_supported(d, cache.page_size)
-        splits = batch.forced_splits or decode_splits(singles, num_heads, nkv, d, cache.page_size, batch.max_kv_len_single)
+        splits = splits or decode_splits(singles, num_heads, nkv, d, cache.page_size, batch.max_kv_len_single)
         scratch = None
         if splits > 1:
             rows = singles * num_heads

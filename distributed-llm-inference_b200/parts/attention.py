@@ -59,6 +59,10 @@ class GQAttention(Part):
     def cache_need(self):
         return PagedKVNeed(self.nkv, self.d, self.window)
 
+    def decode_launch_key(self, num_seqs: int, max_kv_len: int, page_size: int):
+        """Into how many runs the decode kernel cuts each sequence's keys (1: not at all)."""
+        return attn_kernels.decode_splits(num_seqs, self.nh, self.nkv, self.d, page_size, max_kv_len)
+
     def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
         encode = getattr(self.position, "project_and_encode", None)
         if encode is not None:  # the position part may fuse the projection with its encoding
@@ -66,5 +70,5 @@ class GQAttention(Part):
         else:
             q = self.position.rotate_and_store(project(x, self.wqkv), batch, cache, self.nh, self.nkv, cache.writes)
         out = torch.empty((x.shape[0], self.nh * self.d), dtype=x.dtype, device=x.device)
-        attn_kernels.paged_attention(out, q, cache, batch, self.nh, self.scale, self.window)
+        attn_kernels.paged_attention(out, q, cache, batch, self.nh, self.scale, self.window, splits=batch.launch_keys.get(id(self)))
         return last_product(out, self.wo, self.defer_output)

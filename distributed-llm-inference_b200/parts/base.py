@@ -15,13 +15,17 @@ Interfaces by category (what a new part of that category must provide):
                   encodes position into the q and k heads of qkv [n, cols], writes
                   k, v into the cache's pages at ``batch.group(cache.group).slots`` and returns the
                   tensor whose leading columns are the encoded queries.
-``mixer``         ``cache_need() -> PagedKVNeed | StateNeed | None`` and
+``mixer``         ``cache_need() -> PagedKVNeed | StateNeed | a sequence of them | None`` and
                   ``forward(x, batch, cache) -> [n, H]``; x is the normed input (activation dtype).
-                  ``cache`` is the ``LayerCache`` of its run step (pools or state slots; ``writes``
+                  ``cache`` is the ``LayerCache`` of its run step: pages (``k, v``) for a PagedKVNeed,
+                  ``state`` / ``states`` for StateNeeds, both for a mixer that asks for both (``writes``
                   is False when the step reads another step's cache).
 ``feed_forward``  ``forward(x) -> [n, H]``.
 ``arrangement``   built from a ``LayerSpec``; ``forward(stream, batch, cache)`` wires norms, mixer
-                  and feed-forward around the residual ``stream`` (h plus a pending delta).
+                  and feed-forward around the residual ``stream`` (h plus a pending delta);
+                  ``cache_need()`` says what its run step needs of the cache manager (usually its
+                  mixer's answer; an arrangement with several mixers side by side returns all their
+                  needs, and hands each mixer the same ``LayerCache``).
 ``embedding``     ``forward(token_ids) -> h`` float32 [n, H].
 ``head``          ``forward(y) -> logits`` float32 [k, V].
 
@@ -69,6 +73,15 @@ class Part:
     def __init__(self, spec: PartSpec, env: BuildEnv) -> None:
         self.spec = spec
         self.env = env
+
+    def decode_launch_key(self, num_seqs: int, max_kv_len: int, page_size: int):
+        """What, besides the number of sequences and the width of the block tables, changes this part's
+        launches in a step where every sequence brings one token (for attention: into how many runs the
+        keys are cut).  The step function records one graph per distinct answer and hands the answer back
+        in ``batch.launch_keys[id(part)]`` when it runs the part for that graph, so that the part launches
+        what it said it would.  None (the default): nothing does.  ``max_kv_len`` is the longest context
+        the graph's tables can hold."""
+        return None
 
     def declare(self) -> dict[str, TensorDecl]:
         return {}

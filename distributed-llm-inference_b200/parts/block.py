@@ -26,6 +26,10 @@ class PreNormBlock(Part):
     def children(self):
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
 
+    def cache_need(self):
+        """What this layer's run step keeps between steps: whatever its one mixer needs."""
+        return self.mixer.cache_need()
+
     def first_consumer(self):
         """The norm that takes the stream's pending delta, and the part that reads its output."""
         return self.mixer_norm, self.mixer

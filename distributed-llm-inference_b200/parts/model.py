@@ -126,11 +126,14 @@ class DecoderModel:
             part.load(tensors)
 
     def cache_needs(self) -> list:
-        """The need of each run step's mixer (None for a step that reads another step's cache)."""
+        """What each run step asks of the cache manager, as its arrangement answers ``cache_need()``: None, one
+        need, or several (pages and a fixed-size state side by side).  None for a step that reads another
+        step's cache.  An arrangement without that method is asked through its attribute ``mixer``."""
         needs = []
         for step in self.spec.run_order:
-            mixer = getattr(self.layers[step.layer], "mixer", None)
-            needs.append(mixer.cache_need() if mixer is not None and step.cache_of is None else None)
+            layer = self.layers[step.layer]
+            ask = getattr(layer, "cache_need", None) or getattr(getattr(layer, "mixer", None), "cache_need", None)
+            needs.append(ask() if ask is not None and step.cache_of is None else None)
         return needs
 
     def forward(self, batch, caches) -> torch.Tensor:

@@ -6,7 +6,10 @@ import numpy as np
 from dli_b200.cache import CacheManager, GroupSpec
 from dli_b200.engine import StepEntry
 from dli_b200.engine.batch import gather_single_tokens
-from dli_b200.engine.graphs import SEQ_BUCKETS, WIDTH_STEP, DecodeGraph, bucket_seqs
+from types import SimpleNamespace
+
+from dli_b200.engine import graphs as graphs_mod
+from dli_b200.engine.graphs import SEQ_BUCKETS, WIDTH_STEP, DecodeGraph, DecodeGraphs, bucket_seqs
 
 
 def bare_graph(seqs, width, num_groups, scratch_pages, page_size):
@@ -61,3 +64,43 @@ def test_fill_puts_a_gathered_step_in_front_of_the_padding():
         assert set(tables[3].tolist()) == {64}
     assert flat[g.src_base : g.src_base + 4].tolist() == [-1, 5, -1, -1]
     assert np.array_equal(g._pad, bare_graph(4, WIDTH_STEP, 2, [64, 64], 16)._pad), "fill must not write into the padding it starts from"
+
+
+def test_graphs_are_keyed_by_what_the_parts_answer_and_the_stalest_one_makes_room(monkeypatch):
+    """The graph layer imports no kernel policy: it asks every part of the model what changes its launches, keys
+    a shape's graph by the answers, and hands them to the graph (which puts them in its batch).  At the cap the
+    least recently used graph goes, so a long run whose shapes drift keeps recording."""
+    made = []
+
+    class Recorded:
+        def __init__(self, model, caches, num_groups, scratch_pages, page_size, seqs, width, launch_keys):
+            self.shape, self.launch_keys = (seqs, width), dict(launch_keys)
+            made.append(self)
+
+    monkeypatch.setattr(graphs_mod, "DecodeGraph", Recorded)
+
+    class Splitter:
+        def decode_launch_key(self, num_seqs, max_kv_len, page_size):
+            return max(1, min(8, max_kv_len // (1024 * num_seqs)))
+
+    class Indifferent:  # has the method's default answer
+        def decode_launch_key(self, num_seqs, max_kv_len, page_size):
+            return None
+
+    class Unaware:  # a part from before the method existed
+        pass
+
+    a, b = Splitter(), Splitter()
+    model = SimpleNamespace(parts=lambda: [a, Indifferent(), Unaware(), b], device="cpu")
+    pools = SimpleNamespace(layer_caches=[], group_needs=[None], scratch_pages=[7])
+    graphs = DecodeGraphs(model, pools, page_size=16)
+    g1 = graphs.lookup(3, 10, 150)  # 4 rows, 64 pages = 1,024 keys
+    assert g1.shape == (4, 64) and g1.launch_keys == {id(a): 1, id(b): 1} and list(graphs.graphs) == [(4, 64, (1, 1))]
+    assert graphs.lookup(4, 60, 900) is g1 and len(made) == 1
+    g2 = graphs.lookup(1, 200, 3100)  # 1 row, 256 pages = 4,096 keys: four runs
+    assert g2.launch_keys == {id(a): 4, id(b): 4} and (1, 256, (4, 4)) in graphs.graphs
+    graphs.max_graphs = 2
+    assert graphs.lookup(3, 12, 100) is g1  # used again: g2 is now the stalest
+    g3 = graphs.lookup(8, 10, 100)
+    assert g3 is not None and list(graphs.graphs) == [(4, 64, (1, 1)), (8, 64, (1, 1))], "the least recently used graph makes room"
+    assert graphs.lookup(300, 10, 100) is None  # more rows than the largest bucket: step by step

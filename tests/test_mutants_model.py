@@ -65,7 +65,7 @@ MUTANTS = {
     "the last layer's output misses the final norm": (model_mod.DecoderModel, "forward", "stream.take_pending(), self.head, rows=rows)", "None, self.head, rows=rows)"),
     "gate and up change places": (mlp_mod.SwiGLU, "load", 'gate, up = tensors[px + "gate_proj.weight"], tensors[px + "up_proj.weight"]', 'up, gate = tensors[px + "gate_proj.weight"], tensors[px + "up_proj.weight"]'),
     "keys and values change places at load": (GQAttention, "load", 'tensors[px + "k_proj.weight"], tensors[px + "v_proj.weight"]], 0)', 'tensors[px + "v_proj.weight"], tensors[px + "k_proj.weight"]], 0)'),
-    "the scale of the scores is lost": (GQAttention, "forward", "self.nh, self.scale, self.window)", "self.nh, 1.0, self.window)"),
+    "the scale of the scores is lost": (GQAttention, "forward", "self.nh, self.scale, self.window,", "self.nh, 1.0, self.window,"),
     "a pending product is dropped instead of computed": (ResidualStream, "take_pending", "return self._pending", "return None if type(self._pending).__name__ == 'PendingProduct' else self._pending"),
 }
 

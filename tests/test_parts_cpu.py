@@ -67,3 +67,8 @@ def toy_architecture():
 def test_toy_parts(toy_architecture):
     g.test_toy_mixer_with_state_is_registered_built_and_stepped(toy_architecture)
     g.test_toy_routed_feed_forward_is_registered_and_stepped()
+
+
+def test_toy_layer_with_pages_and_state_and_toy_mixer_with_a_launch_key():
+    g.test_a_layer_may_keep_pages_and_a_state_slot()
+    g.test_a_toy_mixer_with_its_own_launch_key_decodes_through_graphs()

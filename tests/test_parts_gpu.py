@@ -357,6 +357,200 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(toy_architecture):
         np.testing.assert_allclose(np32(torch.cat(got[rid])), want[rid], atol=1e-4, err_msg=rid)
 
 
+# ------------------------------------------------------------------ a toy layer that keeps pages AND a state slot
+
+
+class HybridBlock(Part):
+    """x = x + attention(norm(x)) + running_mean(norm(x)); x = x + ffn(norm(x)): two mixers side by side in one
+    layer, one with keys and values in pages, one with state of fixed size.  The arrangement declares both
+    needs; both mixers get the run step's one LayerCache.  Defined here only."""
+
+    def __init__(self, spec, env):
+        self.spec, self.env = spec, env
+        self.mixer_norm = build_part("norm", spec.parts["mixer_norm"], env)
+        self.attention = build_part("mixer", spec.parts["mixer"], env)
+        self.mean = build_part("mixer", spec.parts["second_mixer"], env)
+        self.ffn_norm = build_part("norm", spec.parts["ffn_norm"], env)
+        self.ffn = build_part("feed_forward", spec.parts["ffn"], env)
+
+    def children(self):
+        return [self.mixer_norm, self.attention, self.mean, self.ffn_norm, self.ffn]
+
+    def cache_need(self):
+        return (self.attention.cache_need(), self.mean.cache_need())
+
+    def forward(self, stream, batch, cache):
+        y = self.mixer_norm.add_norm(stream.h, stream.pending)
+        delta = self.attention.forward(y, batch, cache) + self.mean.forward(y, batch, cache)
+        y = self.ffn_norm.add_norm(stream.h, delta)
+        stream.pending = self.ffn.forward(y)
+
+
+def test_a_layer_may_keep_pages_and_a_state_slot():
+    """Layer 1 of tiny-B becomes the hybrid arrangement: the cache manager gives its run step pages and a slot,
+    requests are cut into portions beside one another, a slot is used again, and the logits are those of a
+    numpy restatement."""
+    register_part("mixer", "toy_running_mean")(RunningMean)
+    register_part("arrangement", "toy_hybrid")(HybridBlock)
+    try:
+        base = llama_model_spec(LlamaConfig.from_hf_dict(TINY_B))
+        layers = list(base.layers)
+        mean = PartSpec("toy_running_mean", {"hidden_size": base.hidden_size}, "model.layers.1.toy.")
+        layers[1] = LayerSpec("toy_hybrid", {**layers[1].parts, "second_mixer": mean})
+        spec = dataclasses.replace(base, layers=tuple(layers))
+        model, w = build(spec, torch.float32, seed=21)
+        needs = model.cache_needs()
+        assert [type(n).__name__ for n in needs] == ["PagedKVNeed", "tuple", "PagedKVNeed"]
+        assert [type(n).__name__ for n in needs[1]] == ["PagedKVNeed", "StateNeed"]
+
+        def want_for(tokens):
+            c = plain.read_config(TINY_B)
+            x = w["model.embed_tokens.weight"][np.asarray(tokens)]
+            cos, sin = plain.rope_cos_sin(plain.inverse_frequencies(c), np.arange(len(tokens)))
+            for i in range(c["layers"]):
+                if i != 1:
+                    x, _ = plain_layer(x, w, i, c, cos, sin)
+                    continue
+                p = "model.layers.1."
+                y = plain.rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
+                mean_y = np.cumsum(y, axis=0) / np.arange(1, len(tokens) + 1)[:, None]
+                x = x + plain.attention_block(y, w, p + "self_attn.", c, cos, sin) + mean_y @ w[p + "toy.mix.weight"].T
+                x = x + plain.swiglu_mlp(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"]), w, p + "mlp.")
+            return plain.rms_norm(x, w["model.norm.weight"], c["eps"]) @ w["lm_head.weight"].T
+
+        reqs = {rid: np.random.default_rng(30 + k).integers(0, 1000, n).tolist() for k, (rid, n) in enumerate([("p", 41), ("q", 30), ("r", 37)])}
+        r = ModelRunner(model, num_pages=8, page_size=16, max_requests=2, watermark=0.0)
+        assert r.pools.layer_caches[1].k is not None and len(r.pools.layer_caches[1].states) == 1 and r.graphs is None
+        assert not r.manager.prefix_caching  # pages alone would not bring a request's state back
+        got = {rid: [] for rid in reqs}
+
+        def feed(entries):
+            batch = []
+            for rid, lo, hi in entries:
+                toks = reqs[rid][lo:hi]
+                if r.manager.has_request(rid):
+                    r.manager.append_slots(rid, toks)
+                else:
+                    r.start_request(rid, r.manager.allocate(rid, toks).state_slot)
+                batch.append(StepEntry(rid, toks, range(hi - lo)))
+            out = r.step(batch)
+            row = 0
+            for rid, lo, hi in entries:
+                got[rid].append(out[row : row + hi - lo])
+                row += hi - lo
+
+        feed([("p", 0, 18)])
+        feed([("p", 18, 19), ("q", 0, 28)])
+        feed([("q", 28, 30), ("p", 19, 41)])
+        r.manager.free("p")
+        feed([("r", 0, 3)])  # p's slot and pages, used again
+        feed([("r", 3, 37)])
+        r.manager.free("q"), r.manager.free("r")
+        r.manager.check_invariants()
+        for rid, tokens in reqs.items():
+            np.testing.assert_allclose(np32(torch.cat(got[rid])), want_for(tokens), atol=1e-4, err_msg=rid)
+    finally:
+        unregister_part("arrangement", "toy_hybrid")
+        unregister_part("mixer", "toy_running_mean")
+
+
+# ------------------------------------------------------------------ a toy mixer whose launches depend on the step's shape
+
+
+class ChunkedLinearMixer(Part):
+    """out = x W^T, computed in one product or in two halves of the width added up, as it sees fit from the number
+    of sequences: a stand-in for a mixer with a launch policy of its own.  It tells the step function what its
+    policy depends on (``decode_launch_key``) and is handed its answer back for steps replayed from a graph."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = spec.params["hidden_size"]
+        self.w = None
+        self.keys_seen = []  # what forward was handed, call by call (graph captures included)
+
+    def declare(self):
+        return {self.spec.prefix + "mix.weight": TensorDecl((self.hidden, self.hidden))}
+
+    def load(self, tensors):
+        self.w = tensors[self.spec.prefix + "mix.weight"]
+
+    def cache_need(self):
+        return None
+
+    def decode_launch_key(self, num_seqs, max_kv_len, page_size):
+        return ("halves", 2 if num_seqs <= 2 else 1)
+
+    def forward(self, x, batch, cache):
+        key = batch.launch_keys.get(id(self))
+        self.keys_seen.append(key)
+        halves = key[1] if key is not None else 1
+        if halves == 1:
+            return x @ self.w.t()
+        mid = self.hidden // 2
+        return x[:, :mid] @ self.w[:, :mid].t() + x[:, mid:] @ self.w[:, mid:].t()
+
+
+def test_a_toy_mixer_with_its_own_launch_key_decodes_through_graphs():
+    """The graph layer knows nothing of the toy: it asks every part, keys its graphs by the answers and hands each
+    part its own answer back.  One and two sequences decode through a graph recorded with two halves, four
+    sequences through one recorded with one product; the logits are right either way."""
+    register_part("mixer", "toy_chunked_linear")(ChunkedLinearMixer)
+    try:
+        base = llama_model_spec(LlamaConfig.from_hf_dict(TINY_B))
+        layers = list(base.layers)
+        toy = PartSpec("toy_chunked_linear", {"hidden_size": base.hidden_size}, "model.layers.1.toy.")
+        layers[1] = LayerSpec("prenorm", {**layers[1].parts, "mixer": toy})
+        spec = dataclasses.replace(base, layers=tuple(layers))
+        model, w = build(spec, torch.float32, seed=22)
+        mixer = model.layers[1].mixer
+
+        def want_for(tokens):
+            c = plain.read_config(TINY_B)
+            x = w["model.embed_tokens.weight"][np.asarray(tokens)]
+            cos, sin = plain.rope_cos_sin(plain.inverse_frequencies(c), np.arange(len(tokens)))
+            for i in range(c["layers"]):
+                if i != 1:
+                    x, _ = plain_layer(x, w, i, c, cos, sin)
+                    continue
+                p = "model.layers.1."
+                x = x + plain.rms_norm(x, w[p + "input_layernorm.weight"], c["eps"]) @ w[p + "toy.mix.weight"].T
+                x = x + plain.swiglu_mlp(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"]), w, p + "mlp.")
+            return plain.rms_norm(x, w["model.norm.weight"], c["eps"]) @ w["lm_head.weight"].T
+
+        reqs = {f"s{i}": np.random.default_rng(50 + i).integers(0, 1000, 20 + 3 * i).tolist() for i in range(4)}
+        want = {rid: want_for(t) for rid, t in reqs.items()}
+        r = ModelRunner(model, num_pages=16, page_size=16, max_requests=4, watermark=0.0, enable_prefix_caching=False)
+        assert r.graphs is not None
+        for rid, toks in reqs.items():
+            r.manager.allocate(rid, toks[:-6])
+            r.step([StepEntry(rid, toks[:-6], [])])
+
+        def decode(ids, back):
+            for rid in ids:
+                r.manager.append_slots(rid, [reqs[rid][-back]])
+            out = np32(r.step([StepEntry(rid, [reqs[rid][-back]], [0]) for rid in ids]))
+            for j, rid in enumerate(ids):
+                np.testing.assert_allclose(out[j], want[rid][len(reqs[rid]) - back], atol=1e-4, err_msg=f"{rid} at -{back}")
+
+        if DEV.type != "cuda":  # (on the stand-ins there is nothing to record; the toy still runs step by step)
+            decode(list(reqs), 6)
+            return
+        decode(["s0"], 6)
+        decode(["s0", "s1"], 5)
+        assert r.graph_steps == 2 and ("halves", 2) in mixer.keys_seen
+        decode(list(reqs), 4)
+        assert r.graph_steps == 3 and ("halves", 1) in mixer.keys_seen
+        shapes = {(key[0], key[2][-1] if key[2] and key[2][-1][0] == "halves" else None) for key in r.graphs.graphs}
+        assert any(("halves", 2) in key[2] for key in r.graphs.graphs) and any(("halves", 1) in key[2] for key in r.graphs.graphs), shapes
+        calls = len(mixer.keys_seen)
+        decode(list(reqs), 3)  # replayed: the toy's Python does not run again
+        assert r.graph_steps == 4 and len(mixer.keys_seen) == calls
+    finally:
+        unregister_part("mixer", "toy_chunked_linear")
+
+
 def test_unknown_part_kind_is_named():
     with pytest.raises(ValueError, match="no mixer part of kind 'nonesuch'"):
         build_part("mixer", PartSpec("nonesuch"), env(torch.float32))

@@ -200,7 +200,7 @@ def test_a_prompt_of_2048_tokens_whole_then_one_sequence_decoding(long_1b):
         r.manager.append_slots("w", tokens[pos : pos + 1])
         out = r.step([StepEntry("w", tokens[pos : pos + 1], [0])]).cpu().numpy()
         assert worst(out[0], want[pos]) <= tol, f"decoding at position {pos}: error {worst(out[0], want[pos]):.3g}"
-    assert r.graph_steps == 6 and any(key[0] == 1 and key[2] == 16 for key in r.graphs.graphs), sorted(r.graphs.graphs)
+    assert r.graph_steps == 6 and any(key[0] == 1 and set(key[2]) == {16} for key in r.graphs.graphs), sorted(r.graphs.graphs)
     # teeth: the first and the last (half-filled) page of the table change places
     with pages_swapped_in_table(r.manager, "w", 0, (2048 + 6) // 16):
         r.manager.append_slots("w", tokens[2054:2055])
@@ -237,7 +237,7 @@ def test_many_sequences_decode_behind_prompts_of_about_2048_tokens(long_1b, num_
         err = np.array([worst(out[j], want[lens[rid] + step]) for j, rid in enumerate(ids)])
         assert err.max() <= tol, f"step {step}: sequence {ids[int(np.argmax(err))]} is wrong (error {err.max():.3g}, tolerance {tol:.3g})"
     splits = 8 if num_seqs == 8 else 1
-    assert r.graph_steps == 3 and any(key[0] == num_seqs and key[2] == splits for key in r.graphs.graphs), sorted(r.graphs.graphs)
+    assert r.graph_steps == 3 and any(key[0] == num_seqs and set(key[2]) == {splits} for key in r.graphs.graphs), sorted(r.graphs.graphs)
     # teeth: in one sequence's table the second page and the last one (half filled: junk behind its tokens) change places
     v = next(j for j, rid in enumerate(ids) if 2 <= (lens[rid] + 4) % 16 <= 12)
     with pages_swapped_in_table(r.manager, ids[v], 1, (lens[ids[v]] + 3) // 16):
@@ -271,7 +271,7 @@ def test_a_context_of_8000_tokens_at_head_size_128_in_portions_of_2048(tmp_path_
         r.manager.append_slots("p", tokens[pos : pos + 1])
         out = r.step([StepEntry("p", tokens[pos : pos + 1], [0])]).cpu().numpy()
         assert worst(out[0], want[pos]) <= tol, f"decoding at position {pos}: error {worst(out[0], want[pos]):.3g}"
-    assert any(key[0] == 1 and key[2] > 16 for key in r.graphs.graphs), sorted(r.graphs.graphs)
+    assert any(key[0] == 1 and min(key[2]) > 16 for key in r.graphs.graphs), sorted(r.graphs.graphs)
     # teeth, decoding: the first page and the last one (four tokens, junk behind them) change places in the table
     with pages_swapped_in_table(r.manager, "p", 0, 500):
         r.manager.append_slots("p", tokens[8003:8004])
