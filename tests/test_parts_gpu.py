@@ -527,25 +527,27 @@ def test_a_toy_mixer_with_its_own_launch_key_decodes_through_graphs():
             r.manager.allocate(rid, toks[:-6])
             r.step([StepEntry(rid, toks[:-6], [])])
 
-        def decode(ids, back):
+        at = {rid: len(toks) - 6 for rid, toks in reqs.items()}  # each request's next position
+
+        def decode(ids):
             for rid in ids:
-                r.manager.append_slots(rid, [reqs[rid][-back]])
-            out = np32(r.step([StepEntry(rid, [reqs[rid][-back]], [0]) for rid in ids]))
+                r.manager.append_slots(rid, [reqs[rid][at[rid]]])
+            out = np32(r.step([StepEntry(rid, [reqs[rid][at[rid]]], [0]) for rid in ids]))
             for j, rid in enumerate(ids):
-                np.testing.assert_allclose(out[j], want[rid][len(reqs[rid]) - back], atol=1e-4, err_msg=f"{rid} at -{back}")
+                np.testing.assert_allclose(out[j], want[rid][at[rid]], atol=1e-4, err_msg=f"{rid} at {at[rid]}")
+                at[rid] += 1
 
         if DEV.type != "cuda":  # (on the stand-ins there is nothing to record; the toy still runs step by step)
-            decode(list(reqs), 6)
+            decode(list(reqs))
             return
-        decode(["s0"], 6)
-        decode(["s0", "s1"], 5)
+        decode(["s0"])
+        decode(["s0", "s1"])
         assert r.graph_steps == 2 and ("halves", 2) in mixer.keys_seen
-        decode(list(reqs), 4)
+        decode(list(reqs))
         assert r.graph_steps == 3 and ("halves", 1) in mixer.keys_seen
-        shapes = {(key[0], key[2][-1] if key[2] and key[2][-1][0] == "halves" else None) for key in r.graphs.graphs}
-        assert any(("halves", 2) in key[2] for key in r.graphs.graphs) and any(("halves", 1) in key[2] for key in r.graphs.graphs), shapes
+        assert any(("halves", 2) in key[2] for key in r.graphs.graphs) and any(("halves", 1) in key[2] for key in r.graphs.graphs), sorted(r.graphs.graphs)
         calls = len(mixer.keys_seen)
-        decode(list(reqs), 3)  # replayed: the toy's Python does not run again
+        decode(list(reqs))  # replayed: the toy's Python does not run again
         assert r.graph_steps == 4 and len(mixer.keys_seen) == calls
     finally:
         unregister_part("mixer", "toy_chunked_linear")
