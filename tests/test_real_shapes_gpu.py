@@ -144,7 +144,7 @@ def pages_swapped_in_one_layer(layer_cache, row: int, a: int, b: int):
     and the half-filled last page go wrong.  A comparison that still passes has no teeth."""
     real = attn_kernels.paged_attention
 
-    def mutated(out, qkv, cache, batch, *rest):
+    def mutated(out, qkv, cache, batch, *rest, **named):
         if cache.k is not None and cache.k.data_ptr() == layer_cache.k.data_ptr():
             view = batch.group(cache.group)
             tables = view.block_tables.clone()
@@ -152,7 +152,7 @@ def pages_swapped_in_one_layer(layer_cache, row: int, a: int, b: int):
             batch = copy.copy(batch)
             batch.groups = list(batch.groups)
             batch.groups[cache.group] = GroupView(tables, view.slots)
-        return real(out, qkv, cache, batch, *rest)
+        return real(out, qkv, cache, batch, *rest, **named)
 
     attn_kernels.paged_attention = mutated
     try:
