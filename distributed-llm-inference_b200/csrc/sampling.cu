@@ -55,7 +55,9 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, 
                                                          long long row_stride, int V, const float* __restrict__ temperature,
                                                          const int* __restrict__ top_k, const float* __restrict__ top_p,
                                                          const unsigned long long* __restrict__ seed,
-                                                         const unsigned long long* __restrict__ draw) {
+                                                         unsigned long long* __restrict__ draw, const int* __restrict__ slots) {
+  // With ``slots`` the five parameter arrays are tables indexed by the request's state slot (slots[row]) and a
+  // stochastic row's draw count is advanced by one on the device; without it they are indexed by the row.
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float redf[33];
@@ -98,13 +100,14 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, 
   const float xmax = wmax[0];
   const int arg = widx[0];
 
-  const float T = temperature ? temperature[row] : 0.f;
-  const int k = top_k ? top_k[row] : -1;
+  const int at = slots ? slots[row] : row;
+  const float T = temperature ? temperature[at] : 0.f;
+  const int k = top_k ? top_k[at] : -1;
   if (T == 0.f || k == 1) {
     if (tid == 0) out[row] = arg;
     return;
   }
-  const float P = top_p ? top_p[row] : 1.f;
+  const float P = top_p ? top_p[at] : 1.f;
   const float zmax = xmax / T;
 
   // ---- top-k: largest key K with count(key >= K) >= k
@@ -170,8 +173,9 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, 
   }
   __syncthreads();
   const float total = redf[0];
-  uint32_t c[4] = {(uint32_t)draw[row], (uint32_t)(draw[row] >> 32), 0u, 0u};
-  philox4x32_10(c, (uint32_t)seed[row], (uint32_t)(seed[row] >> 32));
+  const unsigned long long this_draw = draw[at];
+  uint32_t c[4] = {(uint32_t)this_draw, (uint32_t)(this_draw >> 32), 0u, 0u};
+  philox4x32_10(c, (uint32_t)seed[at], (uint32_t)(seed[at] >> 32));
   const float u = (float)(c[0] >> 8) * (1.0f / 16777216.0f);
   const float target = u * total;
   const float before = chunk_prefix[tid];
@@ -186,6 +190,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, 
     }
   }
   __syncthreads();
+  if (slots && tid == 0) draw[at] = this_draw + 1;  // every thread has read it; the request's next token is its next draw
   int result = found;
   if (result == 0x7fffffff) {  // rounding left the target at or past the end: last kept token
     if (tid == 0) widx[0] = -1;
@@ -202,9 +207,10 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, 
 
 DLI_EXPORT int dli_sample(int* out, const float* logits, long long row_stride, int rows, int V, const float* temperature,
                           const int* top_k, const float* top_p, const unsigned long long* seed,
-                          const unsigned long long* draw, cudaStream_t stream) {
+                          unsigned long long* draw, const int* slots, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (V < 1) return DLI_ERR_UNSUPPORTED;
-  launch_pdl((sample_kernel), dim3(rows), dim3(THREADS), 0, stream, 1, out, logits, row_stride, V, temperature, top_k, top_p, seed, draw);
+  if (slots && !(temperature && top_k && top_p && seed && draw)) return DLI_ERR_UNSUPPORTED;
+  launch_pdl((sample_kernel), dim3(rows), dim3(THREADS), 0, stream, 1, out, logits, row_stride, V, temperature, top_k, top_p, seed, draw, slots);
   return (int)cudaGetLastError();
 }

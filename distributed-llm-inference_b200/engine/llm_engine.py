@@ -107,6 +107,8 @@ class LLMEngine:
         # one step ahead needs a runner that takes token ids from the device and a sampler that leaves them there
         self.lookahead = bool(lookahead and getattr(runner, "takes_token_source", False) and hasattr(sampler, "sample_async"))
         self.steps_ahead = 0  # steps that were launched before the ids they run on were read
+        # a sampler with a table of state slots keeps each request's parameters, seed and draw count on the device
+        self._by_slot = getattr(sampler, "state", None) is not None and hasattr(sampler, "sample_slots_async")
         self._inflight: _InFlight | None = None
         self._unknown: dict[str, int] = {}  # request -> position whose id the cache manager does not know yet
         self._preempted_for_nothing = 0  # requests preempted by a scheduling round that produced no batch
@@ -132,7 +134,8 @@ class LLMEngine:
             num_blocks = ModelRunner.pages_for_budget(model, (kv_cache_gb or 1.0) * 2**30, block_size)
         runner = ModelRunner(model, num_pages=num_blocks, page_size=block_size, max_requests=config.max_num_seqs,
                              enable_prefix_caching=enable_prefix_caching, watermark=watermark, eviction_policy=eviction_policy)
-        return cls(runner, config, sampler=Sampler(model.device), eos_token_ids=eos_token_ids, seed=seed, lookahead=lookahead)
+        sampler = Sampler(model.device, max_requests=config.max_num_seqs)  # a slot of sampler state beside each request's cache state
+        return cls(runner, config, sampler=sampler, eos_token_ids=eos_token_ids, seed=seed, lookahead=lookahead)
 
     @classmethod
     def from_model_dir(cls, model_dir: str | Path, *, dtype: str = "auto", device: str = "cuda:0", **kwargs) -> "LLMEngine":
@@ -232,6 +235,9 @@ class LLMEngine:
 
     def _sample(self, logits, reqs: list[Request], ahead: int):
         """Ids for ``reqs`` (row order); ``ahead``: tokens of each request that are sampled but not read."""
+        if self._by_slot:  # the device knows every request's seed and draw count by its state slot
+            return self.sampler.sample_slots_async(logits, [self.manager.state_slot(r.request_id) for r in reqs],
+                                                   all_greedy=all(r.params.greedy for r in reqs))
         args = ([r.params for r in reqs], [r.seed for r in reqs], [len(r.output_ids) + ahead for r in reqs])
         if hasattr(self.sampler, "sample_async"):
             return self.sampler.sample_async(logits, *args)
@@ -257,7 +263,10 @@ class LLMEngine:
             self._preempted_for_nothing = len(sched.preempted)  # (a lone request that gave up its own pages)
             return None
         for req in sched.admitted:
-            self.runner.start_request(req.request_id, self.manager.state_slot(req.request_id))
+            slot = self.manager.state_slot(req.request_id)
+            self.runner.start_request(req.request_id, slot)
+            if self._by_slot:  # (again after a preemption: the draws made so far are the tokens generated so far)
+                self.sampler.bind(slot, req.params, req.seed, len(req.output_ids))
         if sched.copies:
             self.runner.copy_pages(sched.copies)
         return self._run(sched.chunks, len(sched.preempted))

@@ -405,9 +405,12 @@ def sample(
     top_p: torch.Tensor | None = None,
     seed: torch.Tensor | None = None,
     draw: torch.Tensor | None = None,
+    slots: torch.Tensor | None = None,
 ) -> None:
     """out[r] = token of row r of float32 logits [rows, V]; all-greedy when temperature is None.
-    seed and draw are int64 tensors read as unsigned 64-bit."""
+    seed and draw are int64 tensors read as unsigned 64-bit.  With ``slots`` (int32, one per row) the five
+    parameter tensors are tables indexed by slots[r] instead of r (the requests' state slots), and the draw
+    count of every stochastic row's slot is advanced by one on the device."""
     _need(out, "out", torch.int32), _need(logits, "logits", torch.float32)
     rows, V = logits.shape
     if out.numel() != rows:
@@ -417,14 +420,20 @@ def sample(
             raise KernelError("sample: stochastic rows need top_k, top_p, seed and draw")
         _need(temperature, "temperature", torch.float32), _need(top_k, "top_k", torch.int32), _need(top_p, "top_p", torch.float32)
         _need(seed, "seed", torch.int64), _need(draw, "draw", torch.int64)
-        if not (temperature.numel() == top_k.numel() == top_p.numel() == seed.numel() == draw.numel() == rows):
-            raise KernelError("sample: one parameter per row")
+        entries = rows if slots is None else temperature.numel()
+        if not (temperature.numel() == top_k.numel() == top_p.numel() == seed.numel() == draw.numel() == entries):
+            raise KernelError("sample: one parameter per row (or, with slots, tables of one length)")
+    if slots is not None:
+        _need(slots, "slots", torch.int32)
+        if temperature is None or slots.numel() != rows:
+            raise KernelError("sample: slots go with parameter tables and name one slot per row")
     f = _fn(
         "sampling.cu", "dli_sample",
-        [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     )
     _check(
-        f(_ptr(out), _ptr(logits), logits.stride(0), rows, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(draw), _stream()),
+        f(_ptr(out), _ptr(logits), logits.stride(0), rows, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(draw), _ptr(slots),
+          _stream()),
         "sample",
     )
 

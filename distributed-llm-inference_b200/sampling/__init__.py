@@ -1,4 +1,4 @@
 from .params import SamplingParams
-from .sampler import PendingTokens, Sampler
+from .sampler import PendingTokens, Sampler, SamplerState
 
-__all__ = ["PendingTokens", "Sampler", "SamplingParams"]
+__all__ = ["PendingTokens", "Sampler", "SamplerState", "SamplingParams"]

@@ -463,6 +463,36 @@ def test_sampled_frequencies_follow_the_distribution():
     assert set(toks) == {0}
 
 
+def test_sampling_by_state_slot_reads_the_table_and_advances_the_draws():
+    """The engine's way of sampling: the five parameter arrays are tables indexed by each row's state slot, and the
+    kernel itself counts a stochastic row's draw.  Rows in an order that is not the slots', one greedy row, one
+    row with top_k = 1; against the same rows sampled with explicit values, three steps in a row."""
+    from dli_b200.sampling import Sampler, SamplingParams
+
+    V, slots = 700, [5, 0, 3, 6, 2]
+    g = torch.Generator().manual_seed(3)
+    sampler = Sampler(DEV, max_requests=8)
+    params = [SamplingParams(temperature=0.9, seed=11), SamplingParams(temperature=0.0), SamplingParams(temperature=1.4, top_k=20, seed=12),
+              SamplingParams(temperature=0.7, top_k=1, seed=13), SamplingParams(temperature=1.1, top_p=0.8, seed=14)]
+    start = [0, 0, 7, 3, 100]  # draws made so far (a request that comes back after a preemption starts where it was)
+    for slot, p, d in zip(slots, params, start):
+        sampler.bind(slot, p, p.seed or 0, d)
+    stochastic = [not p.greedy for p in params]
+    for step in range(3):
+        logits = (torch.randn(len(slots), V, generator=g) * 2.0).to(DEV)
+        got = sampler.sample_slots_async(logits, slots, all_greedy=False).result()
+        want = sample_rows(logits, [0.0 if p.greedy else p.temperature for p in params], [p.top_k for p in params], [p.top_p for p in params],
+                           [p.seed or 0 for p in params], [d + step for d in start])
+        assert got == want, f"step {step}"
+    draws = sampler.state.draws.tolist()
+    assert [draws[s] for s in slots] == [d + 3 * st for d, st in zip(start, stochastic)]  # greedy rows draw nothing
+    assert draws[1] == draws[4] == draws[7] == 0  # slots nobody was bound to
+    # a slot given to another request takes that request's values, not its predecessor's
+    sampler.bind(5, SamplingParams(temperature=0.0), 0, 0)
+    logits = (torch.randn(1, V, generator=g) * 2.0).to(DEV)
+    assert sampler.sample_slots_async(logits, [5], all_greedy=False).result() == [int(logits[0].argmax())]
+
+
 # ------------------------------------------------------------------ decode matrix product
 
 

@@ -5,7 +5,7 @@ import random
 import pytest
 
 from dli_b200 import SamplingParams
-from dli_b200.engine import FinishReason, Priority, SchedulerConfig
+from dli_b200.engine import FinishReason, LLMEngine, Priority, SchedulerConfig
 from tests.fake_runner import fake_engine, sequential
 
 
@@ -441,3 +441,54 @@ def test_a_device_wait_that_ran_out_fails_the_steps_requests_and_leaves_the_engi
     steps_before = len(runner.steps)
     assert eng.generate([prompts[0]], SamplingParams(max_tokens=6)) == [sequential(prompts[0], 6)]
     assert runner.steps[steps_before][0][1:3] == (0, len(prompts[0])), "the prompt was served from pages of the failed step"
+
+
+def test_a_sampler_with_state_slots_is_told_each_requests_seed_and_draws_and_counts_on_by_itself():
+    """The engine's side of sampling by state slot: every admitted request is bound to its slot with its parameters, its
+    seed and the draws it has made (none at first; after a preemption as many as it has tokens), every step passes the
+    slots of its rows, and the sampler counts the draws itself.  The fake below keeps the table on the host and records,
+    per request seed, which draw produced which token: every request must have used draws 0, 1, 2, ... exactly once each,
+    in a pool so small that requests are preempted, with steps launched ahead."""
+    from tests.fake_runner import AheadRunner, FakeTokens
+
+    class SlotSampler:
+        def __init__(self):
+            self.state = {}  # slot -> [seed, draws, greedy]
+            self.used = {}  # seed -> draw indices, in the order they were made
+
+        def bind(self, slot, params, seed, draws):
+            self.state[slot] = [seed, draws, params.greedy]
+
+        def sample_slots_async(self, logits, slots, all_greedy):
+            assert len(slots) == len(logits)
+            for slot in slots:
+                seed, draws, greedy = self.state[slot]
+                if not greedy:
+                    assert not all_greedy
+                    self.used.setdefault(seed, []).append(draws)
+                    self.state[slot][1] = draws + 1
+            return FakeTokens(logits)
+
+        sample_async = None  # (present, so the engine may launch a step ahead)
+
+    runner = AheadRunner(10, 4, max_requests=4, prefix_caching=True, watermark=0.0)
+    sampler = SlotSampler()
+    eng = LLMEngine(runner, SchedulerConfig(4, 16), sampler=sampler)
+    assert eng.lookahead
+    rng = random.Random(5)
+    reqs = []
+    for i in range(6):
+        greedy = i == 2
+        reqs.append(eng.add_request(f"r{i}", [rng.randrange(50) for _ in range(rng.randrange(3, 11))],
+                                    SamplingParams(max_tokens=rng.randrange(4, 9), temperature=0.0 if greedy else 0.8, seed=1000 + i)))
+    while eng.has_unfinished():
+        eng.step()
+        assert not eng.is_stalled()
+    assert sum(s.num_preempted for s in eng.stats.steps) > 0 and eng.steps_ahead > 0
+    for i, r in enumerate(reqs):
+        assert r.output_ids == sequential(r.prompt_ids, r.params.max_tokens)
+        if i == 2:
+            assert 1002 not in sampler.used
+        else:  # a step launched ahead may have drawn once more than the request kept
+            draws = sampler.used[1000 + i]
+            assert draws[: len(r.output_ids)] == list(range(len(r.output_ids))) and len(draws) <= len(r.output_ids) + 1, (i, draws)
