@@ -250,6 +250,35 @@ def test_many_sequences_decode_behind_prompts_of_about_2048_tokens(long_1b, num_
     assert ops.device_wait_errors() == {}
 
 
+def test_one_sequence_decodes_beyond_3072_keys_through_the_merge_kernel(tmp_path_factory):
+    """Head size 64 with more keys than one cluster's splits are chosen for (3,072): the engine's policy asks for more
+    than 16 splits, partial results go to scratch and the merge kernel finishes them; the graph's tables are 256 pages
+    wide.  A prompt of 3,100 tokens in two portions, then three tokens decoded."""
+    cfg, path, weights = model_folder("llama_1b", tmp_path_factory)
+    tokens = random_tokens(cfg["vocab_size"], 3100 + 4, seed=14)
+    rows = sorted(set(range(2040, 3100, 53)) | set(range(3096, 3104)))
+    want = dict(zip(rows, plain.forward(cfg, plain_weights_for(weights, "bfloat16"), tokens, rows=rows, bf16_activations=True)))
+    tol = 5e-2 * max(1.0, max(float(np.abs(v).max()) for v in want.values()))
+    model = dli_b200.load_model(path, "bfloat16")
+    r = runner_with_used_pages(model, num_pages=3200 // 16 + 2, page_size=16, max_requests=2)
+    r.manager.allocate("p", tokens[:3100])
+    r.step([StepEntry("p", tokens[:2048], [])])
+    here = [i for i in rows if 2048 <= i < 3100]
+    got = r.step([StepEntry("p", tokens[2048:3100], [i - 2048 for i in here])]).cpu().numpy()
+    err = np.array([worst(got[j], want[i]) for j, i in enumerate(here)])
+    assert err.max() <= tol, f"second portion: first wrong position {here[int(np.argmax(err > tol))]} (error {err.max():.3g}, tolerance {tol:.3g})"
+    for pos in range(3100, 3103):
+        r.manager.append_slots("p", tokens[pos : pos + 1])
+        out = r.step([StepEntry("p", tokens[pos : pos + 1], [0])]).cpu().numpy()
+        assert worst(out[0], want[pos]) <= tol, f"decoding at position {pos}: error {worst(out[0], want[pos]):.3g}"
+    assert any(key[0] == 1 and key[1] == 256 and min(key[2]) > 16 for key in r.graphs.graphs), sorted(r.graphs.graphs)
+    with pages_swapped_in_table(r.manager, "p", 2, 3103 // 16):  # teeth: the third page and the last, half-filled one
+        r.manager.append_slots("p", tokens[3103:3104])
+        out = r.step([StepEntry("p", tokens[3103:3104], [0])]).cpu().numpy()
+    assert worst(out[0], want[3103]) > tol, "two pages of the table changed places and the logits did not notice"
+    assert ops.device_wait_errors() == {}
+
+
 def test_a_context_of_8000_tokens_at_head_size_128_in_portions_of_2048(tmp_path_factory):
     """The Llama-3.2-3B layer sizes (24 heads on 8, head size 128): a prompt of 8,000 tokens prefilled in portions
     of 2,048, then decoded on from 8,000 (more key splits than a cluster holds: the merge kernel)."""
