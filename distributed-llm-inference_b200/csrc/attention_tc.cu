@@ -464,9 +464,11 @@ struct T2Cfg {
   static constexpr int TMEM = QT * KEYS + QT * HD <= 256 ? 256 : 512;
 };
 
+// Has the phase with this parity completed?  Never waits (test_wait, not try_wait, which may suspend the thread for a
+// while before it answers no): the thread that issues the products asks about many barriers in turn.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t done;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done != 0;
 }
@@ -517,7 +519,7 @@ __global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kerne
   const int num_tiles = t_end - t_begin;  // both query tiles walk all of them (the later tile sees at most one more)
 
   if (tid == 0) {
-    for (int i = 0; i < 10; ++i) mbar_init(k_full + 8 * i, 1);  // k_full, v_full, k_free, v_free, s_done
+    for (int i = 0; i < 10; ++i) mbar_init(k_full + 8 * i, (i >= 4 && i < 8) ? QT : 1);  // k_full, v_full, k_free, v_free (one arrival per issuing thread), s_done
     for (int i = 10; i < 14; ++i) mbar_init(k_full + 8 * i, ROWS);  // s_read, p_ready
     for (int i = 14; i < 16; ++i) mbar_init(k_full + 8 * i, 1);  // o_done
     *failed = 0;
@@ -592,18 +594,22 @@ __global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kerne
       }
       if (lane >= 16) issue(false, st, cur);
     }
-  } else if (warp == QT * ROWS / 32) {
-    // ================================================================ the warp that issues the matrix products (its first lane)
+  } else if (warp == QT * ROWS / 32 || (QT == 2 && warp == QT * ROWS / 32 + 2)) {
+    // ================================================================ the warps that issue the matrix products (their first lanes):
+    // one per query tile.  A single thread that serves both tiles spends its time on issuing (descriptors, polls) and
+    // becomes what every softmax group waits for; two threads halve that.  A stage of keys or values is handed back
+    // to the copies when both have committed their products with it (the barriers count QT arrivals).
+    const int my_q = warp == QT * ROWS / 32 ? 0 : 1;
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc(ROWS, KEYS, 0), idesc_o = instr_desc(ROWS, 64, 1);
-      int next_qk[2] = {0, QT == 2 ? 0 : num_tiles}, next_pv[2] = {0, QT == 2 ? 0 : num_tiles};  // a tile that does not exist is finished
+      int next_qk = 0, next_pv = 0;
       unsigned spins = 0;
-      while ((next_pv[0] < num_tiles || next_pv[1] < num_tiles) && !*failed) {
+      while (next_pv < num_tiles && !*failed) {
         bool progress = false;
-#pragma unroll
-        for (int q = 0; q < QT; ++q) {
+        {
+          const int q = my_q;  // this thread's query tile
           // S_q(t) = Q_q K(t)^T: the keys are there and the thread of every row has S_q(t - 1) in registers
-          int t = next_qk[q];
+          int t = next_qk;
           if (t < num_tiles && mbar_test(k_full + 8 * (t & 1), (t >> 1) & 1) && (t == 0 || mbar_test(s_read + 8 * q, (t - 1) & 1))) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a = smem_u32(sQ + q * KV_BYTES), k = smem_u32(sK + (t & 1) * KV_BYTES);
@@ -611,12 +617,12 @@ __global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kerne
             for (int kk = 0; kk < D / 16; ++kk)
               umma(tmem_s + q * KEYS, smem_desc_sw128(a + (kk >> 2) * TILE_BYTES + (kk & 3) * 32), smem_desc_sw128(k + (kk >> 2) * TILE_BYTES + (kk & 3) * 32), idesc_s, kk != 0);
             umma_commit(s_done + 8 * q);
-            next_qk[q] = t + 1;
-            if (next_qk[q ^ 1] > t) umma_commit(k_free + 8 * (t & 1));  // every tile's product with K(t) is issued
+            next_qk = t + 1;
+            umma_commit(k_free + 8 * (t & 1));  // this tile's product with K(t) is issued
             progress = true;
           }
           // O_q += P_q(t) V(t)
-          t = next_pv[q];
+          t = next_pv;
           if (t < num_tiles && mbar_test(p_ready + 8 * q, t & 1) && mbar_test(v_full + 8 * (t & 1), (t >> 1) & 1)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a = smem_u32(sP + q * 2 * TILE_BYTES), v = smem_u32(sV + (t & 1) * KV_BYTES);
@@ -626,8 +632,8 @@ __global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kerne
               for (int k = 0; k < KEYS / 16; ++k)
                 umma(tmem_o + q * D + sl * 64, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(v + sl * TILE_BYTES + k * 2048), idesc_o, (t | k) != 0);
             umma_commit(o_done + 8 * q);
-            next_pv[q] = t + 1;
-            if (next_pv[q ^ 1] > t) umma_commit(v_free + 8 * (t & 1));  // every tile's product with V(t) is issued
+            next_pv = t + 1;
+            umma_commit(v_free + 8 * (t & 1));  // this tile's product with V(t) is issued
             progress = true;
           }
         }

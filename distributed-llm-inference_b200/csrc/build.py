@@ -108,6 +108,12 @@ def compile_library(source: str, defines: dict[str, object] | None = None, extra
         raise ExtensionError(f"nvcc failed for {source}:\n{log}")
     os.replace(tmp, out)  # atomic: a concurrent process sees the whole file or none
     _say(f"built {out.name} in {time.time() - t0:.1f} s")
+    for old in out.parent.glob(out.name[: -len("0123456789abcdef.so")] + "*.so"):  # libraries of earlier versions of this source
+        if old != out and len(old.name) == len(out.name) and ".tmp" not in old.name:
+            try:
+                old.unlink()  # a process that has one loaded keeps its mapping
+            except OSError:
+                pass
     return out
 
 
