@@ -458,19 +458,35 @@ struct T2Cfg {
   static_assert(HD == 64 || HD == 128, "head sizes with whole 128-byte slabs");
   static constexpr int QT = HD == 64 ? 2 : 1;             // query tiles per CTA
   static constexpr int SLABS = HD / 64;
-  static constexpr int THREADS = QT * ROWS + 128;         // softmax warpgroups and one of which two warps work (products, copies)
+  static constexpr int THREADS = QT * ROWS + 128;         // softmax warpgroups and one whose warps issue the products (one per query tile) and the copies (keys, values)
   static constexpr int KV_BYTES = SLABS * TILE_BYTES;     // one stage of keys or of values; also one Q tile
   static constexpr int SMEM = QT * KV_BYTES + 4 * KV_BYTES + QT * 2 * TILE_BYTES + 256 + 1024;  // Q, K x2, V x2, P per query tile, barriers, alignment
   static constexpr int TMEM = QT * KEYS + QT * HD <= 256 ? 256 : 512;
 };
 
-// Has the phase with this parity completed?  Never waits (test_wait, not try_wait, which may suspend the thread for a
-// while before it answers no): the thread that issues the products asks about many barriers in turn.
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-  return done != 0;
+// Pairs of float32 in a 64-bit register, for the instructions that work on both at once (sm_100).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// the largest of three (one instruction on sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 template <int HD>
@@ -552,29 +568,23 @@ __global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kerne
   // The softmax threads hold a row of 128 scores in registers; the third warpgroup needs few and gives its
   // share away (a scheduler then holds two warps of 224 registers and one of 40).
   if (warp >= QT * ROWS / 32) {
-    if (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-  if (warp == QT * ROWS / 32 + 1) {
-    // ================================================================ the warp that copies
-    // a lane copies one page (lanes 0..15 keys, lanes 16..31 values), all its slabs of 64 columns
+    // 384 threads start with 168 registers each; the two softmax warpgroups take 224, which leaves 56 for this one
+    if (QT == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if (warp == QT * ROWS / 32 + 1 || warp == QT * ROWS / 32 + 3) {
+    // ================================================================ the warps that copy: one the keys, one the values
+    // (a copy of a small page costs its issuing thread a few hundred clocks whatever its size; with one warp for both,
+    // the keys of the next tile stood in line behind the values of this one, which wait for an older product)
+    // a lane copies one page, all its slabs of 64 columns
+    const bool keys = warp == QT * ROWS / 32 + 1;
     const int pages = KEYS / p.page_size;
     const int page_i = lane & 15;
+    const uint32_t full = keys ? k_full : v_full, freed = keys ? k_free : v_free;
+    unsigned char* stage0 = keys ? sK : sV;
+    const CUtensorMap* map = keys ? &map_k : &map_v;
     auto lookup = [&](int t) -> int {
       const int first = t * KEYS + page_i * p.page_size;
-      const bool need = t < t_end && page_i < pages && first < hi && first + p.page_size > lo;
+      const bool need = lane < 16 && t < t_end && page_i < pages && first < hi && first + p.page_size > lo;
       return need ? table[first / p.page_size] : -1;
-    };
-    auto issue = [&](bool keys, int stage, int page) {
-      const uint32_t bar = (keys ? k_full : v_full) + 8 * stage;
-      unsigned char* dst = (keys ? sK : sV) + stage * KV_BYTES;
-      const unsigned side = keys ? 0x0000ffffu : 0xffff0000u;
-      const int count = __popc(__ballot_sync(side, page >= 0));
-      if (page_i == 0) mbar_expect_tx(bar, (uint32_t)(count * p.page_size * 128 * SLABS));
-      __syncwarp(side);
-      if (page >= 0) {
-#pragma unroll
-        for (int sl = 0; sl < SLABS; ++sl)
-          tma_load_2d(smem_u32(dst + sl * TILE_BYTES + page_i * p.page_size * 128), keys ? &map_k : &map_v, sl * 64, (page * p.nkv + kvh) * p.page_size, bar);
-      }
     };
     int page = lookup(t_begin);
     for (int t = 0; t < num_tiles && !*failed; ++t) {
@@ -582,66 +592,60 @@ __global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kerne
       const int cur = page;
       page = lookup(t_begin + t + 1);
       if (t >= 2) {
-        if (lane == 0) wait_or_fail(k_free + 8 * st, par, failed, 12, p.error_flag);
+        if (lane == 0) wait_or_fail(freed + 8 * st, par, failed, keys ? 12 : 13, p.error_flag);
         __syncwarp();
         if (*failed) break;
       }
-      if (lane < 16) issue(true, st, cur);
-      if (t >= 2) {
-        if (lane == 0) wait_or_fail(v_free + 8 * st, par, failed, 13, p.error_flag);
-        __syncwarp();
-        if (*failed) break;
+      const int count = __popc(__ballot_sync(0xffffffffu, cur >= 0));
+      if (lane == 0) mbar_expect_tx(full + 8 * st, (uint32_t)(count * p.page_size * 128 * SLABS));
+      __syncwarp();
+      if (cur >= 0) {
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl)
+          tma_load_2d(smem_u32(stage0 + st * KV_BYTES + sl * TILE_BYTES + page_i * p.page_size * 128), map, sl * 64, (cur * p.nkv + kvh) * p.page_size, full + 8 * st);
       }
-      if (lane >= 16) issue(false, st, cur);
     }
   } else if (warp == QT * ROWS / 32 || (QT == 2 && warp == QT * ROWS / 32 + 2)) {
     // ================================================================ the warps that issue the matrix products (their first lanes):
-    // one per query tile.  A single thread that serves both tiles spends its time on issuing (descriptors, polls) and
-    // becomes what every softmax group waits for; two threads halve that.  A stage of keys or values is handed back
-    // to the copies when both have committed their products with it (the barriers count QT arrivals).
-    const int my_q = warp == QT * ROWS / 32 ? 0 : 1;
+    // one per query tile.  A single thread that served both tiles spent its time on issuing and became what every
+    // softmax group waited for.  A tile's products become possible in a fixed order, S(t + 1) (its threads have S(t) in
+    // registers) before O += P(t) V(t) (the same threads have written P(t)), so the thread waits for each in turn and
+    // sleeps in the barrier meanwhile: a polling loop takes issue slots from the softmax warps of its scheduler.  A stage
+    // of keys or values is handed back to the copies when both threads have committed their products with it (those
+    // barriers count QT arrivals).
+    const int q = warp == QT * ROWS / 32 ? 0 : 1;  // this thread's query tile
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc(ROWS, KEYS, 0), idesc_o = instr_desc(ROWS, 64, 1);
-      int next_qk = 0, next_pv = 0;
-      unsigned spins = 0;
-      while (next_pv < num_tiles && !*failed) {
-        bool progress = false;
-        {
-          const int q = my_q;  // this thread's query tile
-          // S_q(t) = Q_q K(t)^T: the keys are there and the thread of every row has S_q(t - 1) in registers
-          int t = next_qk;
-          if (t < num_tiles && mbar_test(k_full + 8 * (t & 1), (t >> 1) & 1) && (t == 0 || mbar_test(s_read + 8 * q, (t - 1) & 1))) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a = smem_u32(sQ + q * KV_BYTES), k = smem_u32(sK + (t & 1) * KV_BYTES);
+      const uint32_t qa = smem_u32(sQ + q * KV_BYTES), pa = smem_u32(sP + q * 2 * TILE_BYTES);
+      auto scores = [&](int t) {  // S_q(t) = Q_q K(t)^T
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t k = smem_u32(sK + (t & 1) * KV_BYTES);
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk)
-              umma(tmem_s + q * KEYS, smem_desc_sw128(a + (kk >> 2) * TILE_BYTES + (kk & 3) * 32), smem_desc_sw128(k + (kk >> 2) * TILE_BYTES + (kk & 3) * 32), idesc_s, kk != 0);
-            umma_commit(s_done + 8 * q);
-            next_qk = t + 1;
-            umma_commit(k_free + 8 * (t & 1));  // this tile's product with K(t) is issued
-            progress = true;
-          }
-          // O_q += P_q(t) V(t)
-          t = next_pv;
-          if (t < num_tiles && mbar_test(p_ready + 8 * q, t & 1) && mbar_test(v_full + 8 * (t & 1), (t >> 1) & 1)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a = smem_u32(sP + q * 2 * TILE_BYTES), v = smem_u32(sV + (t & 1) * KV_BYTES);
-#pragma unroll
-            for (int sl = 0; sl < SLABS; ++sl)  // 64 output columns at a time: the values' slab is the MN-major operand
-#pragma unroll
-              for (int k = 0; k < KEYS / 16; ++k)
-                umma(tmem_o + q * D + sl * 64, smem_desc_sw128(a + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(v + sl * TILE_BYTES + k * 2048), idesc_o, (t | k) != 0);
-            umma_commit(o_done + 8 * q);
-            next_pv = t + 1;
-            umma_commit(v_free + 8 * (t & 1));  // this tile's product with V(t) is issued
-            progress = true;
-          }
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma(tmem_s + q * KEYS, smem_desc_sw128(qa + (kk >> 2) * TILE_BYTES + (kk & 3) * 32), smem_desc_sw128(k + (kk >> 2) * TILE_BYTES + (kk & 3) * 32), idesc_s, kk != 0);
+        umma_commit(s_done + 8 * q);
+        umma_commit(k_free + 8 * (t & 1));  // this tile's product with K(t) is issued
+      };
+      bool ok = num_tiles > 0 && wait_or_fail(k_full, 0, failed, 17, p.error_flag);
+      if (ok) scores(0);
+      for (int t = 0; t < num_tiles && ok; ++t) {
+        if (t + 1 < num_tiles) {  // the keys are there and the thread of every row has S_q(t) in registers
+          ok = wait_or_fail(k_full + 8 * ((t + 1) & 1), ((t + 1) >> 1) & 1, failed, 17, p.error_flag) && wait_or_fail(s_read + 8 * q, t & 1, failed, 18, p.error_flag);
+          if (!ok) break;
+          scores(t + 1);
         }
-        if (progress) spins = 0;
-        else if (++spins > WAIT_LIMIT) {
-          *failed = 17;
-          atomicExch(p.error_flag, 17);
-        }
+        // O_q += P_q(t) V(t)
+        ok = wait_or_fail(p_ready + 8 * q, t & 1, failed, 19, p.error_flag) && wait_or_fail(v_full + 8 * (t & 1), (t >> 1) & 1, failed, 20, p.error_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t v = smem_u32(sV + (t & 1) * KV_BYTES);
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl)  // 64 output columns at a time: the values' slab is the MN-major operand
+#pragma unroll
+          for (int k = 0; k < KEYS / 16; ++k)
+            umma(tmem_o + q * D + sl * 64, smem_desc_sw128(pa + (k >> 2) * TILE_BYTES + (k & 3) * 32), smem_desc_sw128(v + sl * TILE_BYTES + k * 2048), idesc_o, (t | k) != 0);
+        umma_commit(o_done + 8 * q);
+        umma_commit(v_free + 8 * (t & 1));  // this tile's product with V(t) is issued
       }
     }
     __syncwarp();
@@ -694,10 +698,14 @@ __global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kerne
       }
       float mx[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) mx[j] = sc[j];
+      for (int j = 0; j < 8; ++j) mx[j] = max3(sc[j], sc[j + 8], sc[j + 16]);
 #pragma unroll
-      for (int j = 8; j < 128; ++j) mx[j & 7] = fmaxf(mx[j & 7], sc[j]);
-      m = fmaxf(m, fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))));
+      for (int j = 24; j < 120; j += 16)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx[i] = max3(mx[i], sc[j + i], sc[j + 8 + i]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx[i] = fmaxf(mx[i], sc[120 + i]);
+      m = max3(m, max3(mx[0], mx[1], mx[2]), max3(max3(mx[3], mx[4], mx[5]), mx[6], mx[7]));
       float corr = 1.f;
       const bool grown = (m - m_ref) * p.scale_log2 > RESCALE_STEP;  // also the first finite maximum (m_ref = -inf)
       if (grown) {
@@ -730,20 +738,31 @@ __global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kerne
         if (q == 0) asm volatile("bar.sync 1, %0;" ::"n"(2 * ROWS) : "memory");
         else asm volatile("bar.sync 2, %0;" ::"n"(2 * ROWS) : "memory");
       }
-      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      // two elements per instruction where there is one for it (fma and add on pairs of float32): the loop is
+      // bound by the number of instructions that one warp gets issued, not by the special-function units alone
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
+      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), neg2 = pack_f32x2(neg, neg);
       unsigned char* prow = sP + q * 2 * TILE_BYTES + r * 128;
 #pragma unroll
       for (int j = 0; j < 128; j += 8) {
         uint32_t packed[4];
 #pragma unroll
         for (int e = 0; e < 8; e += 2) {
-          const float p0 = ex2(fmaf(sc[j + e], p.scale_log2, neg));  // masked: ex2(-inf) = 0
-          const float p1 = ex2(fmaf(sc[j + e + 1], p.scale_log2, neg));
-          sum[(e >> 1) & 3] += p0 + p1;
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(sc[j + e], sc[j + e + 1]), scale2, neg2), x0, x1);
+          const float p0 = ex2(x0), p1 = ex2(x1);  // masked: ex2(-inf) = 0
+          sum2[(e >> 1) & 3] = add_f32x2(sum2[(e >> 1) & 3], pack_f32x2(p0, p1));
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           packed[e >> 1] = *reinterpret_cast<uint32_t*>(&b2);
         }
         *reinterpret_cast<uint4*>(prow + (j >> 6) * TILE_BYTES + ((((j >> 3) & 7) ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+      float sum[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float lo_, hi_;
+        unpack_f32x2(sum2[i], lo_, hi_);
+        sum[i] = lo_ + hi_;
       }
       if (QT == 2) {
         if (q == 0) asm volatile("bar.arrive 2, %0;" ::"n"(2 * ROWS) : "memory");

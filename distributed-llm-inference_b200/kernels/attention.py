@@ -34,7 +34,15 @@ MIN_TILES_PER_SPLIT = 2  # key tiles (of 64) a split should at least cover
 
 
 CLUSTER_SPLITS_MAX = ops.DECODE_TMA_CLUSTER_SPLITS  # splits that the TMA decode kernel merges inside one thread-block cluster
-CLUSTER_SPLITS_KV_LIMIT = 3072  # beyond this context more splits and a merge kernel win (16 K keys, 4 sequences: 28 us against 41)
+# Splits of the TMA-fed kernel, measured on a B200 with the keys and values not in L2 (head size 64, 8 KV heads;
+# us at 1 / 2 / 4 sequences):  8 K keys: 16 splits 17 / 21 / 35, 8 splits 23 / 25 / 27, 64 splits 30 / 36 / 48;
+# 32 K keys: 16 splits 40 / 45 / 89, 8 splits 60 / 66 / 68, 32 splits 34 / 48 / 79.  A cluster's merge on the chip beats
+# more splits with a merge kernel at every length up to about 24 K keys; a cluster of 16 is worth its narrower
+# placement only while the grid is small (one or two sequences' head groups); one sequence alone beyond 24 K keys
+# is the case for 32 splits and the merge kernel.
+CLUSTER_16_MAX_CTAS_PER_SPLIT = 16
+MERGE_KERNEL_MIN_KV = 24576
+MERGE_KERNEL_SPLITS = 32
 
 
 def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int | None = None, fill_last_wave: bool = True) -> int:
@@ -66,12 +74,14 @@ def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_s
     tma = ops.decode_tma_supported(head_dim, page_size)
     wave = one_wave(4 if head_dim <= 64 else 2) if tma else one_wave(2)
     splits = choose_splits(num_seqs, ctas_per_seq, max_kv_len, wave, fill_last_wave=not tma)
-    if tma and max_kv_len <= CLUSTER_SPLITS_KV_LIMIT:
-        # short contexts: a split count that one cluster merges on the chip (up to 8 CTAs, or 16) is faster than
-        # a few more splits and a merge kernel
-        if splits > CLUSTER_SPLITS_MAX:
+    if tma and splits > 8:
+        pairs = num_seqs * ctas_per_seq
+        most = max(1, -(-max_kv_len // 64) // MIN_TILES_PER_SPLIT)
+        if head_dim <= 64 and pairs * 2 <= CLUSTER_16_MAX_CTAS_PER_SPLIT and max_kv_len >= MERGE_KERNEL_MIN_KV and most >= MERGE_KERNEL_SPLITS:
+            splits = MERGE_KERNEL_SPLITS
+        elif splits >= CLUSTER_SPLITS_MAX and pairs <= CLUSTER_16_MAX_CTAS_PER_SPLIT:
             splits = CLUSTER_SPLITS_MAX
-        elif 8 < splits < CLUSTER_SPLITS_MAX:
+        else:
             splits = 8
     return splits
 

@@ -1,0 +1,27 @@
+"""The host-side choice of key splits for single-token sequences (kernels/attention.py): no GPU needed."""
+
+from dli_b200.kernels.attention import CLUSTER_SPLITS_MAX, decode_splits
+
+
+def splits(seqs, ctx, heads=32, nkv=8, d=64, page=16):
+    return decode_splits(seqs, heads, nkv, d, page, ctx)
+
+
+def test_short_contexts_are_not_cut_below_two_key_tiles():
+    assert splits(1, 100) == 1
+    assert splits(1, 300) == 2
+    assert splits(64, 2048) == 1  # the grid is full without splits
+
+
+def test_few_sequences_merge_in_a_cluster():
+    assert [splits(1, c) for c in (2048, 8192, 16384)] == [CLUSTER_SPLITS_MAX] * 3
+    assert [splits(2, c) for c in (2048, 8192, 65536)] == [CLUSTER_SPLITS_MAX] * 3
+    assert [splits(4, c) for c in (2048, 8192, 65536)] == [8] * 3  # a cluster of 16 only while the grid is small
+    assert splits(8, 2048) == 8
+    assert splits(16, 8192) == 4  # one wave of CTAs
+
+
+def test_one_long_sequence_takes_the_merge_kernel():
+    assert splits(1, 32768) == 32 and splits(1, 65536) == 32
+    assert splits(2, 32768) == CLUSTER_SPLITS_MAX
+    assert splits(1, 32768, heads=24, d=128) == CLUSTER_SPLITS_MAX  # head size 128: a cluster at every length measured

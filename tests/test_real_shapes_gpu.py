@@ -250,10 +250,11 @@ def test_many_sequences_decode_behind_prompts_of_about_2048_tokens(long_1b, num_
     assert ops.device_wait_errors() == {}
 
 
-def test_one_sequence_decodes_beyond_3072_keys_through_the_merge_kernel(tmp_path_factory):
-    """Head size 64 with more keys than one cluster's splits are chosen for (3,072): the engine's policy asks for more
-    than 16 splits, partial results go to scratch and the merge kernel finishes them; the graph's tables are 256 pages
-    wide.  A prompt of 3,100 tokens in two portions, then three tokens decoded."""
+def test_one_sequence_decodes_with_more_splits_than_a_cluster_through_the_merge_kernel(tmp_path_factory, monkeypatch):
+    """More key splits than one cluster merges (the engine's policy asks for them from about 24,000 keys of one
+    sequence on; here it is made to ask at 3,100): partial results go to scratch and the merge kernel finishes them; the
+    graph's tables are 256 pages wide.  A prompt of 3,100 tokens in two portions, then three tokens decoded."""
+    monkeypatch.setattr(attn_kernels, "decode_splits", lambda *sizes: 24)
     cfg, path, weights = model_folder("llama_1b", tmp_path_factory)
     tokens = random_tokens(cfg["vocab_size"], 3100 + 4, seed=14)
     rows = sorted(set(range(2040, 3100, 53)) | set(range(3096, 3104)))
@@ -281,7 +282,7 @@ def test_one_sequence_decodes_beyond_3072_keys_through_the_merge_kernel(tmp_path
 
 def test_a_context_of_8000_tokens_at_head_size_128_in_portions_of_2048(tmp_path_factory):
     """The Llama-3.2-3B layer sizes (24 heads on 8, head size 128): a prompt of 8,000 tokens prefilled in portions
-    of 2,048, then decoded on from 8,000 (more key splits than a cluster holds: the merge kernel)."""
+    of 2,048, then decoded on from 8,000 (sixteen key splits, merged in a cluster)."""
     cfg, path, weights = model_folder("llama_3b", tmp_path_factory)
     tokens = random_tokens(cfg["vocab_size"], 8000 + 4, seed=12)
     rows = sorted(set(range(5, 8000, 41)) | set(range(7990, 8004)))
@@ -300,7 +301,7 @@ def test_a_context_of_8000_tokens_at_head_size_128_in_portions_of_2048(tmp_path_
         r.manager.append_slots("p", tokens[pos : pos + 1])
         out = r.step([StepEntry("p", tokens[pos : pos + 1], [0])]).cpu().numpy()
         assert worst(out[0], want[pos]) <= tol, f"decoding at position {pos}: error {worst(out[0], want[pos]):.3g}"
-    assert any(key[0] == 1 and min(key[2]) > 16 for key in r.graphs.graphs), sorted(r.graphs.graphs)
+    assert any(key[0] == 1 and key[2] == (16,) for key in r.graphs.graphs), sorted(r.graphs.graphs)
     # teeth, decoding: the first page and the last one (four tokens, junk behind them) change places in the table
     with pages_swapped_in_table(r.manager, "p", 0, 500):
         r.manager.append_slots("p", tokens[8003:8004])
