@@ -1028,32 +1028,28 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
   const int box_rows = p.page_size < DN ? p.page_size : DN;  // a tile is one piece of a page, or two whole pages of 8
   const int boxes = DN / box_rows;
 
-  // Block-table entries are read 32 boxes at a time, one per lane, and handed to lane 0 by shuffle:
-  // lane 0 must never wait for a global load between two copies.
+  // Where the boxes lie is worked out 32 boxes at a time, one per lane (block-table entry, row in the pools), and
+  // handed to lane 0 by shuffle: lane 0 must never wait for a global load, or divide, between two copies.
   int cached_first = 0;
-  auto box_page = [&](int e) -> int {  // page of this warp's e-th box (box = tile piece of box_rows keys)
-    const int key = (t_begin + warp + (e / boxes) * DWARPS) * DN + (e % boxes) * box_rows;
-    if (key >= hi || key + box_rows <= lo) return -1;  // no key of the box is visible: it is filled with zeros
-    return table[key / p.page_size];
+  auto box_row = [&](int e) -> int {  // first pool row of this warp's e-th box (box = tile piece of box_rows keys)
+    const int key = (t_begin + warp + (boxes == 2 ? e >> 1 : e) * DWARPS) * DN + (boxes == 2 ? e & 1 : 0) * box_rows;
+    if (key >= hi || key + box_rows <= lo) return 0x3fffff00;  // no key of the box is visible: a row beyond the pool makes the copy fill the box with zeros
+    const int entry = key / p.page_size;
+    return (table[entry] * p.nkv + kvh) * p.page_size + (key - entry * p.page_size);
   };
-  int cached = box_page(lane);
-  // every lane calls this (the shuffles need them all); lane 0 issues the copies of the warp's i-th tile
-  auto issue = [&](int i) {
-    const int st = i % DSTAGES;
-    const int key0 = (t_begin + warp + i * DWARPS) * DN;
+  int cached = box_row(lane);
+  // every lane calls this (the shuffles need them all); lane 0 issues the copies of the warp's i-th tile into stage st
+  auto issue = [&](int i, int st) {
     const uint32_t bar = wbar + 8 * st;
     if (lane == 0) mbar_expect_tx(bar, 2 * DTILE);
     for (int b = 0; b < boxes; ++b) {
       const int e = i * boxes + b;
       if (e >= cached_first + 32) {
         cached_first = e;
-        cached = box_page(e + lane);
+        cached = box_row(e + lane);
       }
-      const int page = __shfl_sync(0xffffffffu, cached, e - cached_first);
+      const int row = __shfl_sync(0xffffffffu, cached, e - cached_first);
       if (lane == 0) {
-        const int key = key0 + b * box_rows;
-        // a row coordinate beyond the pool makes the copy fill the box with zeros
-        const int row = page < 0 ? 0x3fffff00 : (page * p.nkv + kvh) * p.page_size + (key % p.page_size);
 #pragma unroll
         for (int sl = 0; sl < Cfg::SLABS; ++sl) {
           tma_load_2d(smem_u32(wbuf + st * 2 * DTILE + sl * Cfg::SLAB + b * box_rows * 128), &map_k, sl * 64, row, bar);
@@ -1064,7 +1060,6 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
   };
 
   const int r0 = lane >> 2, r1 = r0 + 8;
-  const bool rv0 = r0 < nheads, rv1 = r1 < nheads;
   float m[2] = {-CUDART_INF_F, -CUDART_INF_F};
   float l[2] = {0.f, 0.f};
   float o[D / 8][4];
@@ -1078,10 +1073,10 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
   int deferred = -1;
   for (int i = 0; i < DSTAGES - 1 && i < my_tiles; ++i) {
     if (t_begin + warp + i * DWARPS == newest_tile) deferred = i;  // the last of this warp's tiles, if any
-    else issue(i);
+    else issue(i, i);
   }
   pdl_wait();
-  if (deferred >= 0) issue(deferred);
+  if (deferred >= 0) issue(deferred, deferred);
 
   for (int idx = tid; idx < 16 * (D / 8); idx += DWARPS * 32) {
     const int r = idx / (D / 8), c = idx - r * (D / 8);
@@ -1097,11 +1092,17 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
   for (int kk = 0; kk < D / 16; ++kk) ldsm_x4(qf[kk], smem_u32(sQ + (lane & 15) * QROW + (kk * 16 + (lane >> 4) * 8) * 2));
   if (p.cluster_merge) cluster_arrive();  // this thread is done with the query rows; waited for before the first push
 
+  // The running maximum m of a row is a reference, not the exact maximum: it moves only when a tile's maximum
+  // exceeds it by more than 2^RESCALE_STEP (or is the first finite one), and only then are the sums rescaled; the
+  // probabilities are 2^(s - m) <= 2^RESCALE_STEP meanwhile, which bfloat16 and float32 hold as well as values <= 1.
+  // Scores stay raw; the scale goes into the exponent's multiply-add.  Tiles that lie wholly inside the visible
+  // range, all but the last and a window's first, skip the mask.
+  constexpr float RESCALE_STEP = 8.f;
   bool ok = true;
+  int st = 0, phase = 0;
   for (int i = 0; i < my_tiles; ++i) {
-    const int st = i % DSTAGES;
-    if (i + DSTAGES - 1 < my_tiles) issue(i + DSTAGES - 1);  // into the stage finished an iteration ago
-    if (ok && !wait_or_fail(wbar + 8 * st, (i / DSTAGES) & 1, failed, 21, p.error_flag)) ok = false;
+    if (i + DSTAGES - 1 < my_tiles) issue(i + DSTAGES - 1, st == 0 ? DSTAGES - 1 : st - 1);  // into the stage finished an iteration ago
+    if (ok && !wait_or_fail(wbar + 8 * st, phase, failed, 21, p.error_flag)) ok = false;
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       const uint32_t tK = smem_u32(wbuf + st * 2 * DTILE), tV = tK + DTILE;
@@ -1117,42 +1118,46 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
         mma16816(sc[0], qf[kk], b[0], b[1]);
         mma16816(sc[1], qf[kk], b[2], b[3]);
       }
-      // ---- mask and online softmax
-      float tmax[2] = {-CUDART_INF_F, -CUDART_INF_F};
+      // ---- mask (only a tile that reaches beyond the visible keys) and online softmax
+      if (base < lo || base + DN - 1 > pos) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = base + j * 8 + (lane & 3) * 2 + (e & 1);
-          const bool vis = ((e >> 1) ? rv1 : rv0) && key <= pos && key >= lo;
-          const float t = vis ? sc[j][e] * p.scale_log2 : -CUDART_INF_F;
-          sc[j][e] = t;
-          tmax[e >> 1] = fmaxf(tmax[e >> 1], t);
-        }
-      float corr[2], msafe[2];
+          for (int e = 0; e < 4; ++e) {
+            const int key = base + j * 8 + (lane & 3) * 2 + (e & 1);
+            if (key > pos || key < lo) sc[j][e] = -CUDART_INF_F;
+          }
+      }
+      float tmax[2];
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
+        tmax[rr] = fmaxf(fmaxf(sc[0][2 * rr], sc[0][2 * rr + 1]), fmaxf(sc[1][2 * rr], sc[1][2 * rr + 1]));
         tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
-        tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
-        const float mnew = fmaxf(m[rr], tmax[rr]);
-        msafe[rr] = (mnew == -CUDART_INF_F) ? 0.f : mnew;
-        corr[rr] = ex2(m[rr] - msafe[rr]);
-        m[rr] = mnew;
-        l[rr] *= corr[rr];
+        tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2)) * p.scale_log2;  // the scale is positive
       }
+      const bool grown0 = tmax[0] - m[0] > RESCALE_STEP, grown1 = tmax[1] - m[1] > RESCALE_STEP;  // also the first finite maximum; never a NaN's turn
+      if (__any_sync(0xffffffffu, grown0 || grown1)) {
+        const float c0 = grown0 ? ((m[0] == -CUDART_INF_F) ? 0.f : ex2(m[0] - tmax[0])) : 1.f;
+        const float c1 = grown1 ? ((m[1] == -CUDART_INF_F) ? 0.f : ex2(m[1] - tmax[1])) : 1.f;
+        if (grown0) m[0] = tmax[0];
+        if (grown1) m[1] = tmax[1];
+        l[0] *= c0;
+        l[1] *= c1;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+          o[j][0] *= c0; o[j][1] *= c0;
+          o[j][2] *= c1; o[j][3] *= c1;
+        }
+      }
+      const float neg0 = (m[0] == -CUDART_INF_F) ? 0.f : -m[0], neg1 = (m[1] == -CUDART_INF_F) ? 0.f : -m[1];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float pv = ex2(sc[j][e] - msafe[e >> 1]);
+          const float pv = ex2(fmaf(sc[j][e], p.scale_log2, (e >> 1) ? neg1 : neg0));  // masked: ex2(-inf) = 0
           sc[j][e] = pv;
           l[e >> 1] += pv;
         }
-#pragma unroll
-      for (int j = 0; j < D / 8; ++j) {
-        o[j][0] *= corr[0]; o[j][1] *= corr[0];
-        o[j][2] *= corr[1]; o[j][3] *= corr[1];
-      }
       // ---- O += P V (16 keys = one k step)
       uint32_t a[4] = {pack2(sc[0][0], sc[0][1]), pack2(sc[0][2], sc[0][3]), pack2(sc[1][0], sc[1][1]), pack2(sc[1][2], sc[1][3])};
 #pragma unroll
@@ -1166,6 +1171,7 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
       }
     }
     __syncwarp();  // every lane has read the stage before lane 0 refills it
+    if (++st == DSTAGES) { st = 0; phase ^= 1; }
   }
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {

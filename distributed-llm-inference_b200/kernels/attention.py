@@ -35,13 +35,14 @@ MIN_TILES_PER_SPLIT = 2  # key tiles (of 64) a split should at least cover
 
 CLUSTER_SPLITS_MAX = ops.DECODE_TMA_CLUSTER_SPLITS  # splits that the TMA decode kernel merges inside one thread-block cluster
 # Splits of the TMA-fed kernel, measured on a B200 with the keys and values not in L2 (head size 64, 8 KV heads;
-# us at 1 / 2 / 4 sequences):  8 K keys: 16 splits 17 / 21 / 35, 8 splits 23 / 25 / 27, 64 splits 30 / 36 / 48;
-# 32 K keys: 16 splits 40 / 45 / 89, 8 splits 60 / 66 / 68, 32 splits 34 / 48 / 79.  A cluster's merge on the chip beats
-# more splits with a merge kernel at every length up to about 24 K keys; a cluster of 16 is worth its narrower
-# placement only while the grid is small (one or two sequences' head groups); one sequence alone beyond 24 K keys
-# is the case for 32 splits and the merge kernel.
+# us at 1 / 2 / 4 sequences):  8 K keys: 16 splits 15 / 21 / 35, 8 splits 23 / 25 / 27, 64 splits 30 / 36 / 48;
+# 32 K keys: 16 splits 33 / 39 / 89, 8 splits 60 / 66 / 68, 32 splits 32 / 48 / 79;  64 K keys, one sequence: 16 splits
+# 51, 32 splits 46;  128 K keys: 89 and 70.  A cluster's merge on the chip beats more splits with a merge kernel at every
+# length up to about 40 K keys; a cluster of 16 is worth its narrower placement only while the grid is small (one or
+# two sequences' head groups); one sequence alone beyond 40 K keys is the case for 32 splits and the merge kernel
+# (head size 128: a cluster at every length measured).
 CLUSTER_16_MAX_CTAS_PER_SPLIT = 16
-MERGE_KERNEL_MIN_KV = 24576
+MERGE_KERNEL_MIN_KV = 40960
 MERGE_KERNEL_SPLITS = 32
 
 
