@@ -526,6 +526,7 @@ def main() -> int:
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                     help="profiling runs: only the device-timed decode steps, or only the prefill step (prints a short line)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling runs: launch the decode step's kernels one by one")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="profiling runs of --phase decode: the context at which decoding starts")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -545,8 +546,9 @@ def main() -> int:
     model = dli_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     clocks = ClockSampler(device_id_for_smi())
     if args.phase == "decode":
-        run = decode_device_timed(model, args.batch, args.steps, args.warmup, graphs=not args.no_graphs, blocks=1)
-        print(json.dumps({"phase": "decode", "batch": args.batch, "layers": args.layers, **run}))
+        run = decode_device_timed(model, args.batch, args.steps, args.warmup, graphs=not args.no_graphs, blocks=1, prompt_len=args.prompt_len,
+                                  context=max(CONTEXT, args.prompt_len + 512))
+        print(json.dumps({"phase": "decode", "batch": args.batch, "layers": args.layers, "prompt_len": args.prompt_len, **run}))
         return 0
     if args.phase == "prefill":
         print(json.dumps({"phase": "prefill", "layers": args.layers, **prefill_timed(model, cfg, args.layers, pk["bf16_tflops"], reps=args.steps)}))
