@@ -909,16 +909,19 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
 namespace {
 
 constexpr int DN = 16;                 // keys per tile of one warp
-constexpr int DWARPS = 4;
 constexpr int CLUSTER_SPLITS_MAX = 16;  // the largest cluster of this GPU (more than 8 is the kernel's opt-in)
 constexpr int CLUSTER_ROWS_MAX = 23;    // rows of partial results that may arrive at one CTA
 
 // Sizes that depend on the head size HD (64 or 128).  A row of keys or values is HD * 2 bytes; the
 // 128-byte swizzle covers 64 elements, so a tile of 16 rows lies in shared memory as HD / 64 slabs of
 // [16 rows x 128 bytes], each filled by its own TMA box (the columns 64 s .. 64 s + 63 of the rows).
-template <int HD>
+// DWARPS: warps of a CTA, each with its own tiles and stages.  Four, so that four CTAs (two at head size 128) share an
+// SM when the grid is large; eight when the grid has fewer CTAs than two per SM (one or two long sequences), where
+// nothing else would hide a warp's latencies.
+template <int HD, int DWARPS>
 struct DecodeCfg {
   static_assert(HD == 64 || HD == 128, "head sizes with whole 128-byte slabs");
+  static_assert(DWARPS == 4 || DWARPS == 8, "four or eight warps");
   static constexpr int SLABS = HD / 64;
   static constexpr int SLAB = DN * 128;                 // bytes of one slab
   static constexpr int TILE = SLABS * SLAB;             // one K or V tile
@@ -933,7 +936,7 @@ struct DecodeCfg {
   static constexpr int SMEM = 1024 + DWARPS * STAGES * 2 * TILE + RECV_BYTES + DWARPS * STAGES * 8 + 64;
   static_assert(RECV_BYTES >= 16 * QROW, "the received partial results lie over the query rows");
   static_assert(DWARPS * 16 * (HD + 2) * 4 <= DWARPS * STAGES * 2 * TILE, "the merge buffer reuses the key/value stages");
-  static_assert((HD == 64 ? 4 : 2) * (SMEM + 1024) <= 227 * 1024, "four CTAs per SM at head size 64, two at 128");
+  static_assert((DWARPS == 8 ? 1 : HD == 64 ? 4 : 2) * (SMEM + 1024) <= 227 * 1024, "four CTAs per SM at head size 64, two at 128 (four warps)");
 };
 
 struct DecodeParams {
@@ -980,10 +983,10 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // are the query heads of one KV head; each warp walks its own share of the 16-key tiles.  A tile's
 // keys and values arrive by TMA (one box per page piece, 128-byte swizzle), four tiles ahead, on the
 // warp's own mbarriers: no thread spends instructions on addresses of individual 16-byte copies.
-template <int HD>
+template <int HD, int DWARPS>
 __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
-  using Cfg = DecodeCfg<HD>;
+  using Cfg = DecodeCfg<HD, DWARPS>;
   constexpr int DSTAGES = Cfg::STAGES, DTILE = Cfg::TILE, QROW = Cfg::QROW, RECV_BYTES = Cfg::RECV_BYTES, RECV_ROW = Cfg::RECV_ROW;
   constexpr int D = HD;  // shadows the prefill kernel's head size within this kernel
   pdl_launch_dependents();
@@ -1302,18 +1305,18 @@ bool merges_in_cluster(int nh, int nkv, int splits) {
   return splits > 1 && (splits <= 8 || splits == CLUSTER_SPLITS_MAX) && splits * ((rows + splits - 1) / splits) <= CLUSTER_ROWS_MAX;
 }
 
-template <int HD>
-int launch_decode(const CUtensorMap& map_k, const CUtensorMap& map_v, const DecodeParams& p, int num_seqs, int first_row, cudaStream_t stream) {
+template <int HD, int DWARPS>
+int launch_decode_warps(const CUtensorMap& map_k, const CUtensorMap& map_v, const DecodeParams& p, int num_seqs, int first_row, cudaStream_t stream) {
   static OncePerDevice configured;
   if (!configured.here()) {
-    cudaError_t e = cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<HD>::SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    cudaError_t e = cudaFuncSetAttribute(paged_decode_tma_kernel<HD, DWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<HD, DWARPS>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(paged_decode_tma_kernel<HD, DWARPS>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
     configured.here() = true;
   }
   const int G = p.nh / p.nkv;
-  cudaError_t e = launch_pdl(paged_decode_tma_kernel<HD>, dim3(num_seqs, p.splits, p.nkv * ((G + 15) / 16)), dim3(DWARPS * 32),
-                             (size_t)DecodeCfg<HD>::SMEM, stream, p.cluster_merge ? p.splits : 1, map_k, map_v, p);
+  cudaError_t e = launch_pdl(paged_decode_tma_kernel<HD, DWARPS>, dim3(num_seqs, p.splits, p.nkv * ((G + 15) / 16)), dim3(DWARPS * 32),
+                             (size_t)DecodeCfg<HD, DWARPS>::SMEM, stream, p.cluster_merge ? p.splits : 1, map_k, map_v, p);
   if (e != cudaSuccess) return (int)e;
   if (p.splits > 1 && !p.cluster_merge)
     e = launch_pdl(merge_decode_splits_kernel, dim3(num_seqs * p.nh), dim3(64), 0, stream, 1, p.out, (const float*)p.part_acc,
@@ -1321,6 +1324,19 @@ int launch_decode(const CUtensorMap& map_k, const CUtensorMap& map_v, const Deco
   return (int)e;
 }
 
+
+// Eight warps a CTA at head size 64 when the grid leaves SMs with one CTA at most and every warp still gets four tiles
+// or more: one sequence of 32 K keys in 16 splits takes 33 us with four warps and 27 with eight.  (Measured slower
+// with eight: two CTAs on an SM, 39 -> 48 us for two such sequences, and head size 128, 44 -> 58 us.)
+template <int HD>
+int launch_decode(const CUtensorMap& map_k, const CUtensorMap& map_v, const DecodeParams& p, int num_seqs, int first_row, int max_kv_len,
+                  cudaStream_t stream) {
+  const int G = p.nh / p.nkv;
+  const long long ctas = (long long)num_seqs * p.splits * p.nkv * ((G + 15) / 16);
+  const int tiles_per_split = (max_kv_len + DN - 1) / DN / p.splits;
+  if (HD == 64 && ctas <= sm_count() && tiles_per_split >= 32) return launch_decode_warps<HD, 8>(map_k, map_v, p, num_seqs, first_row, stream);
+  return launch_decode_warps<HD, 4>(map_k, map_v, p, num_seqs, first_row, stream);
+}
 }  // namespace
 
 // Attention of num_seqs single-token sequences (head size 64 or 128; page size a multiple of 8, and
@@ -1330,7 +1346,7 @@ DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride
                                     long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
                                     const int* kv_len, int seq0, int num_seqs, int first_row, int nh, int nkv, int head_dim,
                                     int page_size, int window, float scale, int splits, float* part_acc, float* part_ml,
-                                    cudaStream_t stream) {
+                                    int max_kv_len, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (head_dim != 64 && head_dim != 128) return DLI_ERR_UNSUPPORTED;
   if (nkv < 1 || nh % nkv || splits < 1 || (splits > 1 && (!part_acc || !part_ml))) return DLI_ERR_UNSUPPORTED;
@@ -1353,8 +1369,8 @@ DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride
   p.scale_log2 = scale * 1.4426950408889634f;
   p.part_acc = part_acc; p.part_ml = part_ml; p.error_flag = error_flag_device;
   p.cluster_merge = merges_in_cluster(nh, nkv, splits);
-  return head_dim == 64 ? launch_decode<64>(map_k, map_v, p, num_seqs, first_row, stream)
-                        : launch_decode<128>(map_k, map_v, p, num_seqs, first_row, stream);
+  return head_dim == 64 ? launch_decode<64>(map_k, map_v, p, num_seqs, first_row, max_kv_len, stream)
+                        : launch_decode<128>(map_k, map_v, p, num_seqs, first_row, max_kv_len, stream);
 }
 
 DLI_EXPORT int dli_decode_tma_merges_in_cluster(int nh, int nkv, int splits) { return merges_in_cluster(nh, nkv, splits) ? 1 : 0; }

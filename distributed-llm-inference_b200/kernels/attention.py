@@ -36,14 +36,11 @@ MIN_TILES_PER_SPLIT = 2  # key tiles (of 64) a split should at least cover
 CLUSTER_SPLITS_MAX = ops.DECODE_TMA_CLUSTER_SPLITS  # splits that the TMA decode kernel merges inside one thread-block cluster
 # Splits of the TMA-fed kernel, measured on a B200 with the keys and values not in L2 (head size 64, 8 KV heads;
 # us at 1 / 2 / 4 sequences):  8 K keys: 16 splits 15 / 21 / 35, 8 splits 23 / 25 / 27, 64 splits 30 / 36 / 48;
-# 32 K keys: 16 splits 33 / 39 / 89, 8 splits 60 / 66 / 68, 32 splits 32 / 48 / 79;  64 K keys, one sequence: 16 splits
-# 51, 32 splits 46;  128 K keys: 89 and 70.  A cluster's merge on the chip beats more splits with a merge kernel at every
-# length up to about 40 K keys; a cluster of 16 is worth its narrower placement only while the grid is small (one or
-# two sequences' head groups); one sequence alone beyond 40 K keys is the case for 32 splits and the merge kernel
-# (head size 128: a cluster at every length measured).
+# 32 K keys: 16 splits 27 / 39 / 89, 8 splits 60 / 66 / 68, 32 splits 32 / 48 / 79;  one sequence of 128 K keys: 16
+# splits 68, 32 splits 70.  A cluster's merge on the chip beats more splits with a merge kernel at every length a
+# model here reaches; a cluster of 16 is worth its narrower placement only while the grid is small (one or two
+# sequences' head groups).  (More than 16 splits, merged by a second kernel, remain for callers that ask for them.)
 CLUSTER_16_MAX_CTAS_PER_SPLIT = 16
-MERGE_KERNEL_MIN_KV = 40960
-MERGE_KERNEL_SPLITS = 32
 
 
 def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int | None = None, fill_last_wave: bool = True) -> int:
@@ -75,15 +72,9 @@ def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_s
     tma = ops.decode_tma_supported(head_dim, page_size)
     wave = one_wave(4 if head_dim <= 64 else 2) if tma else one_wave(2)
     splits = choose_splits(num_seqs, ctas_per_seq, max_kv_len, wave, fill_last_wave=not tma)
-    if tma and splits > 8:
+    if tma and splits > 8:  # a cluster merges its splits on the chip: 16 of them for one or two sequences' head groups, else 8
         pairs = num_seqs * ctas_per_seq
-        most = max(1, -(-max_kv_len // 64) // MIN_TILES_PER_SPLIT)
-        if head_dim <= 64 and pairs * 2 <= CLUSTER_16_MAX_CTAS_PER_SPLIT and max_kv_len >= MERGE_KERNEL_MIN_KV and most >= MERGE_KERNEL_SPLITS:
-            splits = MERGE_KERNEL_SPLITS
-        elif splits >= CLUSTER_SPLITS_MAX and pairs <= CLUSTER_16_MAX_CTAS_PER_SPLIT:
-            splits = CLUSTER_SPLITS_MAX
-        else:
-            splits = 8
+        splits = CLUSTER_SPLITS_MAX if splits >= CLUSTER_SPLITS_MAX and pairs <= CLUSTER_16_MAX_CTAS_PER_SPLIT else 8
     return splits
 
 
@@ -108,7 +99,7 @@ def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_head
                        torch.empty(rows * splits * 2, dtype=torch.float32, device=out.device))
         kernel = ops.paged_decode_tma if tma else ops.paged_attention_mma
         args = (out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, 0, singles) + (() if tma else (1,))
-        kernel(*args, 0, num_heads, scale, window, splits, scratch)
+        kernel(*args, 0, num_heads, scale, window, splits, scratch, *((batch.max_kv_len_single,) if tma else ()))
     if total > singles and ops.prefill_tc_supported(d, cache.page_size):
         ops.paged_prefill_tc(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, singles, total - singles,
                              batch.max_q_len, num_heads, scale, window)

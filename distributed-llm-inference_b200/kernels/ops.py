@@ -328,9 +328,12 @@ def paged_decode_tma(
     window: int | None = None,
     splits: int = 1,
     scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
+    max_kv_len: int = 0,
 ) -> None:
     """bfloat16 attention of single-token sequences whose keys and values arrive by TMA (head size
-    64 or 128; page sizes 8, 16, 32, ...).  Arguments as paged_attention_mma with max_q_len = 1."""
+    64 or 128; page sizes 8, 16, 32, ...).  Arguments as paged_attention_mma with max_q_len = 1.
+    ``max_kv_len``: the longest sequence, if the host knows it (a hint: with few CTAs and long runs of keys
+    the launcher gives a CTA eight warps instead of four); 0 if not."""
     for t, name in ((out, "out"), (qkv, "qkv"), (k_pool, "k_pool"), (v_pool, "v_pool")):
         _need(t, name, torch.bfloat16)
     _need(block_tables, "block_tables", torch.int32), _need(q_start, "q_start", torch.int32), _need(kv_len, "kv_len", torch.int32)
@@ -353,12 +356,12 @@ def paged_decode_tma(
     f = _fn(
         "attention_tc.cu", "dli_paged_decode_tma",
         [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 8
-        + [c_float, c_int, c_void_p, c_void_p, c_void_p],
+        + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p],
     )
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_tables), block_tables.shape[1],
           _ptr(q_start), _ptr(kv_len), seq0, num_seqs, first_row, num_heads, nkv, d, page_size, int(window or 0), scale, splits,
-          _ptr(acc), _ptr(ml), _stream()),
+          _ptr(acc), _ptr(ml), int(max_kv_len), _stream()),
         "paged_decode_tma",
     )
     global launch_count

@@ -123,7 +123,7 @@ def paged_attention_mma(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len,
 
 
 def paged_decode_tma(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, first_row, num_heads, scale,
-                     window=None, splits=1, scratch=None):
+                     window=None, splits=1, scratch=None, max_kv_len=0):
     assert splits == 1 or scratch is not None
     _attend(out, qkv, k_pool, v_pool, block_tables, q_start, kv_len, seq0, num_seqs, num_heads, scale, window)
 

@@ -21,7 +21,7 @@ def test_few_sequences_merge_in_a_cluster():
     assert splits(16, 8192) == 4  # one wave of CTAs
 
 
-def test_one_long_sequence_takes_the_merge_kernel():
-    assert splits(1, 49152) == 32 and splits(1, 131072) == 32
-    assert splits(1, 32768) == CLUSTER_SPLITS_MAX and splits(2, 65536) == CLUSTER_SPLITS_MAX
-    assert splits(1, 65536, heads=24, d=128) == CLUSTER_SPLITS_MAX  # head size 128: a cluster at every length measured
+def test_long_sequences_stay_with_a_cluster():
+    assert splits(1, 49152) == CLUSTER_SPLITS_MAX and splits(1, 131072) == CLUSTER_SPLITS_MAX
+    assert splits(2, 65536) == CLUSTER_SPLITS_MAX and splits(4, 131072) == 8
+    assert splits(1, 65536, heads=24, d=128) == CLUSTER_SPLITS_MAX

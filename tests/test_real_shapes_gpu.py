@@ -251,8 +251,8 @@ def test_many_sequences_decode_behind_prompts_of_about_2048_tokens(long_1b, num_
 
 
 def test_one_sequence_decodes_with_more_splits_than_a_cluster_through_the_merge_kernel(tmp_path_factory, monkeypatch):
-    """More key splits than one cluster merges (the engine's policy asks for them from about 40,000 keys of one
-    sequence on; here it is made to ask at 3,100): partial results go to scratch and the merge kernel finishes them; the
+    """More key splits than one cluster merges (the engine's own policy stays with a cluster; here it is made to ask
+    for 24): partial results go to scratch and the merge kernel finishes them; the
     graph's tables are 256 pages wide.  A prompt of 3,100 tokens in two portions, then three tokens decoded."""
     monkeypatch.setattr(attn_kernels, "decode_splits", lambda *sizes: 24)
     cfg, path, weights = model_folder("llama_1b", tmp_path_factory)
