@@ -276,13 +276,15 @@ def test_paged_decode_tma(nh, nkv, page, window, splits, d):
     assert ops.paged_prefill_tc_error() == 0
 
 
-def plain_decode_rows(t, seqs, nh):
-    """Attention of each sequence's one query over all its keys, in float64, row by row (the whole-sequence
-    restatement above would build a square of scores per head, which thousands of keys make too large)."""
+def plain_decode_rows(t, seqs, nh, window=None):
+    """Attention of each sequence's one query over all its keys (the last ``window`` of them), in float64, row by row
+    (the whole-sequence restatement above would build a square of scores per head, which thousands of keys make too large)."""
     outs = []
     for i in range(len(seqs)):
         q = t["Q"][i].double().numpy()[0]  # [nh, d]
         K, V = t["K"][i].double().numpy(), t["V"][i].double().numpy()  # [keys, nkv, d]
+        if window:
+            K, V = K[-window:], V[-window:]
         fan = nh // K.shape[1]
         row = []
         for h in range(nh):
@@ -311,6 +313,44 @@ def test_paged_decode_tma_many_splits_over_long_contexts(d, nh, nkv, page, split
     scratch = (torch.full((len(seqs) * nh * splits * d,), float("nan"), device=DEV), torch.full((len(seqs) * nh * splits * 2,), float("nan"), device=DEV))
     ops.paged_decode_tma(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(seqs), 0, nh, d**-0.5, None, splits, scratch)
     np.testing.assert_allclose(out.float().cpu().numpy(), plain_decode_rows(t, seqs, nh), atol=tol(torch.bfloat16, 2))
+    assert ops.paged_prefill_tc_error() == 0
+
+
+@pytest.mark.parametrize("nh,nkv,page,window,keys", [(32, 8, 16, None, 8300), (32, 8, 16, 5000, 9001), (3, 1, 8, None, 8200), (8, 8, 64, None, 16400)])
+def test_paged_decode_tma_with_eight_warps_a_cta(nh, nkv, page, window, keys):
+    """One long sequence at head size 64: told the length, the launcher gives a CTA eight warps instead of four (the
+    grid is smaller than the GPU and every warp still has four tiles or more).  The result is that of four warps and
+    of the plain softmax."""
+    d, splits = 64, 16
+    seqs = [(keys - 1, 1)]
+    t = attention_case(nh, nkv, d, page, seqs, torch.bfloat16, seed=keys % 97, sharp=(0, 0, keys // 3))
+    want = plain_decode_rows(t, seqs, nh, window)
+    outs = []
+    for hint in (0, keys):
+        out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        scratch = (torch.full((nh * splits * d,), float("nan"), device=DEV), torch.full((nh * splits * 2,), float("nan"), device=DEV))
+        ops.paged_decode_tma(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, 1, 0, nh, d**-0.5, window, splits, scratch, hint)
+        np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2), err_msg=f"length hint {hint}")
+        outs.append(out.float().cpu().numpy())
+    np.testing.assert_allclose(outs[0], outs[1], atol=tol(torch.bfloat16, 1))
+    assert ops.paged_prefill_tc_error() == 0
+
+
+@pytest.mark.parametrize("ramp", [0.02, 0.3])
+@pytest.mark.parametrize("d", [64, 128])
+def test_decode_tma_when_row_maxima_keep_rising(ramp, d):
+    """Scores that grow with the key's position: the decode kernel's reference maximum stays where it is over many
+    tiles (0.02: a sixteenth of a power of two per 16-key tile, far below its step of 2^8) or moves at every tile
+    (0.3), with one, a few and sixteen splits."""
+    nh, nkv, page = 8, 2, 16
+    seqs = [(699, 1), (2999, 1), (15, 1)]
+    t = attention_case(nh, nkv, d, page, seqs, torch.bfloat16, seed=6, ramp=ramp)
+    want = plain_decode_rows(t, seqs, nh)
+    for splits in (1, 3, 16):
+        out = torch.full((t["n"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        scratch = (torch.full((len(seqs) * nh * splits * d,), float("nan"), device=DEV), torch.full((len(seqs) * nh * splits * 2,), float("nan"), device=DEV))
+        ops.paged_decode_tma(out, t["qkv"], t["kp"], t["vp"], t["tables"], t["q_start"], t["kv_len"], 0, len(seqs), 0, nh, d**-0.5, None, splits, scratch if splits > 1 else None)
+        np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=tol(torch.bfloat16, 2), err_msg=f"{splits} splits")
     assert ops.paged_prefill_tc_error() == 0
 
 
