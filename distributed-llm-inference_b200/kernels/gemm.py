@@ -41,6 +41,44 @@ def fused_epilogue(x: torch.Tensor) -> bool:
     return decode_product(x) and x.shape[0] <= FUSED_EPILOGUE_MAX_TOKENS
 
 
+# From this many tokens two of a layer's bfloat16 products go to the engine's tcgen05 product for many tokens, which
+# does the elementwise step behind the product in its epilogue.  Measured on B200 at Llama-3.2-1B sizes (us, this
+# product against the library's product plus the kernel it saves; 512 / 2,048 / 8,192 tokens): gate|up with SiLU * up
+# 39/42, 107/115, 397/424: always.  q|k|v with rotary and cache write 26/37, 41/38, 93/97: when its tiles fill their
+# waves (2,048 tokens are 192 tiles on 148 SMs).  The o and down products stay with the library: with the residual
+# addition and the norm's sums in the epilogue they took 31/34 and 68/58 us at 2,048 tokens and 98/81, 259/209 at
+# 8,192 (the epilogue reads and writes the float32 residual a row per thread, and at K = 8,192 the plain product is
+# 0.87 of the library's), so that epilogue was taken out again.
+DENSE_MIN_TOKENS = 512
+DENSE_TILE = (128, 256)  # tokens x features of the product's tiles
+WAVE_FILL_MIN = 0.8
+
+
+def _dense_tiles(tokens: int, features: int) -> int:
+    return -(-tokens // DENSE_TILE[0]) * -(-features // DENSE_TILE[1])
+
+
+def _dense_candidate(x, features: int) -> bool:
+    from . import ops
+
+    return x.dtype == torch.bfloat16 and x.shape[0] >= DENSE_MIN_TOKENS and ops.dense_gemm_supported(x.shape[1], features)
+
+
+def dense_product(x, features: int, epilogue: str) -> bool:
+    """Whether the product of these activations with a [features, K] weight, followed by ``epilogue`` ("swiglu",
+    "rotary" or "residual"), goes to the engine's product for many tokens."""
+    from .attention import sm_count
+
+    if not _dense_candidate(x, features):
+        return False
+    tiles, sms = _dense_tiles(x.shape[0], features), sm_count()
+    if epilogue == "swiglu":
+        return True
+    if epilogue == "rotary":
+        return tiles <= sms or tiles / (-(-tiles // sms) * sms) >= WAVE_FILL_MIN
+    raise ValueError(f"unknown epilogue {epilogue!r}")
+
+
 def project(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, max_tokens: int = SKINNY_MAX_TOKENS) -> torch.Tensor:
     """y = x W^T for a step's tokens, in x's dtype or in ``out_dtype`` (float32 for logits).  x may be
     ops.ScaledRows (rows that still lack their norm's factor): those only exist for token counts that

@@ -386,6 +386,7 @@ def device_wait_errors(clear: bool = True) -> dict[str, int]:
     reached the host.  With ``clear`` a code that was read is forgotten."""
     found = {}
     for source, read, forget in (("skinny_gemm.cu", "dli_skinny_gemm_error", "dli_skinny_gemm_clear_error"),
+                                 ("dense_gemm.cu", "dli_dense_gemm_error", "dli_dense_gemm_clear_error"),
                                  ("attention_tc.cu", "dli_paged_prefill_tc_error", "dli_paged_prefill_tc_clear_error")):
         if not _library_in_use(source):
             continue
@@ -675,6 +676,86 @@ def skinny_gemm_rotary(x, wqkv, positions, inv_freq, slots, k_pool, v_pool, num_
              _ptr(v_pool if write_kv else None), num_heads, num_kv_heads, head_dim, rotary_dim, page_size, int(write_kv), *scale, _stream()),
            "skinny_gemm_rotary")
     return q
+
+
+# ------------------------------------------------------------------ matrix product of many tokens
+# A portion of a prompt: tokens are the 128-row side of the tensor-core instruction, a thread of the epilogue holds
+# one token's row of a tile, and the elementwise step behind the product is done on the sums before they are stored.
+
+
+def dense_gemm_supported(in_features: int, features: int) -> bool:
+    return in_features >= 8 and in_features % 8 == 0 and features >= 8 and features % 8 == 0
+
+
+def dense_rotary_supported(head_dim: int, rotary_dim: int) -> bool:
+    return head_dim in (64, 128) and rotary_dim in (0, 64, 128) and rotary_dim <= head_dim
+
+
+def _dense_sizes(x: torch.Tensor, weight: torch.Tensor, name: str):
+    _need(x, "x", torch.bfloat16), _need(weight, "weight", torch.bfloat16)
+    tokens, K = x.shape
+    features = weight.shape[0]
+    if weight.shape[1] != K or tokens < 1 or not dense_gemm_supported(K, features):
+        raise KernelError(f"{name}: K {K} and features {features} must be multiples of 8 and the shapes agree")
+    return tokens, features, K
+
+
+def dense_gemm(x, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [tokens, K] times weight [features, K] transposed, bfloat16 in and out, float32 sums, on tcgen05 tensor
+    cores fed by TMA: persistent CTAs over tiles of 128 tokens x 256 features, two accumulators in tensor memory."""
+    tokens, features, K = _dense_sizes(x, weight, "dense_gemm")
+    if out is None:
+        out = torch.empty((tokens, features), dtype=torch.bfloat16, device=x.device)
+    else:
+        _need(out, "out", torch.bfloat16)
+        if tuple(out.shape) != (tokens, features):
+            raise KernelError("dense_gemm: out has the wrong shape")
+    f = _fn("dense_gemm.cu", "dli_dense_gemm", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(weight), tokens, features, K, _stream()), "dense_gemm")
+    return out
+
+
+def dense_gemm_swiglu(x, weight_tiled: torch.Tensor) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) in the product's epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate
+    rows, then the 64 up rows of the same features.  Returns bfloat16 [tokens, I]."""
+    tokens, features, K = _dense_sizes(x, weight_tiled, "dense_gemm_swiglu")
+    if features % 128:
+        raise KernelError("dense_gemm_swiglu: the interleaved layout needs an intermediate size that is a multiple of 64")
+    act = torch.empty((tokens, features // 2), dtype=torch.bfloat16, device=x.device)
+    f = _fn("dense_gemm.cu", "dli_dense_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(act), _ptr(x), _ptr(weight_tiled), tokens, features, K, _stream()), "dense_gemm_swiglu")
+    return act
+
+
+def dense_gemm_rotary(x, wqkv, table, slots, k_pool, v_pool, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
+                      page_size: int, write_kv: bool) -> torch.Tensor:
+    """q | k | v = x Wqkv^T with the rotary embedding (``table`` [tokens, rotary_dim]: cos | sin of every token's
+    angles, as ``rotary_table`` makes it) and the write of keys and values into the cache pages done in the
+    product's epilogue; returns the rotated queries [tokens, nh * d]."""
+    features = (num_heads + 2 * num_kv_heads) * head_dim
+    tokens, _, K = _dense_sizes(x, wqkv, "dense_gemm_rotary")
+    if wqkv.shape[0] != features or not dense_rotary_supported(head_dim, rotary_dim):
+        raise KernelError("dense_gemm_rotary: sizes not supported")
+    if rotary_dim:
+        _need(table, "table", torch.float32)
+        if tuple(table.shape) != (tokens, rotary_dim):
+            raise KernelError("dense_gemm_rotary: table must be [tokens, rotary_dim]")
+    if write_kv:
+        _need(slots, "slots", torch.int32), _need(k_pool, "k_pool", torch.bfloat16), _need(v_pool, "v_pool", torch.bfloat16)
+        if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, head_dim) or k_pool.shape != v_pool.shape or slots.numel() != tokens:
+            raise KernelError("dense_gemm_rotary: pool layout must be [pages, kv_heads, page_size, head_dim]")
+    q = torch.empty((tokens, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+    f = _fn("dense_gemm.cu", "dli_dense_gemm_rotary",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
+    _check(f(_ptr(q), _ptr(x), _ptr(wqkv), tokens, K, _ptr(table if rotary_dim else None), _ptr(slots if write_kv else None),
+             _ptr(k_pool if write_kv else None), _ptr(v_pool if write_kv else None), num_heads, num_kv_heads, head_dim, rotary_dim,
+             page_size, int(write_kv), _stream()), "dense_gemm_rotary")
+    return q
+
+
+def dense_gemm_error() -> int:
+    """0, or which bounded wait of the many-token product ran out (1 copies, 2 and 3 products, 4 epilogue)."""
+    return _fn("dense_gemm.cu", "dli_dense_gemm_error", [])()
 
 
 def skinny_gemm_error() -> int:

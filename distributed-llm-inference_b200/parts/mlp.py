@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from ..kernels.gemm import fused_epilogue, last_product, project
+from ..kernels.gemm import dense_product, fused_epilogue, last_product, project
 from ..weights.loader import TensorDecl
 from .base import Part, register_part
 
@@ -52,6 +52,8 @@ class SwiGLU(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.tiled and fused_epilogue(x):
             act = ops.skinny_gemm_swiglu(x, self.w_gate_up)
+        elif self.tiled and dense_product(x, 2 * self.inter, "swiglu"):
+            act = ops.dense_gemm_swiglu(x, self.w_gate_up)
         else:
             gate_up = project(x, self.w_gate_up)
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)

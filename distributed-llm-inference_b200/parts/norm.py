@@ -39,6 +39,6 @@ class RMSNorm(Part):
         """h += product (computed here, float32 sums added to float32 h) and the norm's first half
         in the product's epilogue; the factor rsqrt(mean(h^2) + eps) of each row travels with the
         result and is applied by the product that reads it, to its float32 sums."""
-        if not ops.skinny_gemm_supported(h.shape[0], self.size):
+        if not ops.skinny_gemm_supported(h.shape[0], self.size) or h.shape[0] > 64:
             return None  # the product that reads the result could not take rows of this size
         return ops.skinny_gemm_residual(product.x, product.weight, h, self.weight, self.eps)

@@ -7,7 +7,7 @@ import math
 import torch
 
 from ..kernels import ops
-from ..kernels.gemm import fused_epilogue, project
+from ..kernels.gemm import dense_product, fused_epilogue, project
 from .base import Part, register_part
 
 
@@ -37,6 +37,15 @@ def inverse_frequencies(params) -> torch.Tensor:
     return torch.where(medium, smoothed, scaled)
 
 
+def _step_table(batch, inv_freq, table_key):
+    """The sines and cosines of the step's tokens, computed once and shared by all layers with these frequencies."""
+    key = ("rotary_table", table_key)
+    table = batch.scratch.get(key)
+    if table is None:
+        table = batch.scratch[key] = ops.rotary_table(batch.positions, inv_freq)
+    return table
+
+
 def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq, table_key=None):
     """Runs the fused kernel and returns the tensor whose leading num_heads * head_dim columns
     are the encoded queries (qkv itself: queries are rotated in place)."""
@@ -44,24 +53,24 @@ def _rotate_and_store(qkv, batch, cache, num_heads, num_kv_heads, write_kv, head
     args = (batch.positions, inv_freq, group.slots if write_kv else None, cache.k if write_kv else None,
             cache.v if write_kv else None, num_heads, num_kv_heads, head_dim, rotary_dim, cache.page_size, write_kv)
     if rotary_dim or write_kv:
-        table = None
-        if rotary_dim and qkv.dtype == torch.bfloat16 and qkv.shape[0] > 64:
-            # many tokens: the sines and cosines of the step are computed once and shared by all layers
-            key = ("rotary_table", table_key)
-            table = batch.scratch.get(key)
-            if table is None:
-                table = batch.scratch[key] = ops.rotary_table(batch.positions, inv_freq)
-        ops.rotary_store(qkv, *args, table=table)
+        many = rotary_dim and qkv.dtype == torch.bfloat16 and qkv.shape[0] > 64
+        ops.rotary_store(qkv, *args, table=_step_table(batch, inv_freq, table_key) if many else None)
     return qkv
 
 
 def _project_and_encode(x, wqkv, batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq, table_key=None):
     """q | k | v projection followed by position encoding and cache write; for a decode step's few
-    tokens both happen in one kernel (the product's epilogue rotates and writes the cache)."""
+    tokens and for a long portion's many both happen in one kernel (the product's epilogue rotates and
+    writes the cache)."""
     if fused_epilogue(x) and ops.skinny_rotary_supported(head_dim):
         group = batch.group(cache.group)
         return ops.skinny_gemm_rotary(x, wqkv, batch.positions, inv_freq, group.slots, cache.k, cache.v, num_heads, num_kv_heads,
                                       head_dim, rotary_dim, cache.page_size, write_kv)
+    if ops.dense_rotary_supported(head_dim, rotary_dim) and dense_product(x, wqkv.shape[0], "rotary"):
+        group = batch.group(cache.group)
+        table = _step_table(batch, inv_freq, table_key) if rotary_dim else None
+        return ops.dense_gemm_rotary(x, wqkv, table, group.slots if write_kv else None, cache.k if write_kv else None,
+                                     cache.v if write_kv else None, num_heads, num_kv_heads, head_dim, rotary_dim, cache.page_size, write_kv)
     return _rotate_and_store(project(x, wqkv), batch, cache, num_heads, num_kv_heads, write_kv, head_dim, rotary_dim, inv_freq, table_key)
 
 

@@ -183,6 +183,35 @@ def skinny_gemm_rotary(x, wqkv, positions, inv_freq, slots, k_pool, v_pool, num_
     return qkv[:, : num_heads * head_dim].to(torch.bfloat16)
 
 
+# ---- the product of many tokens and its epilogues
+
+
+def dense_gemm(x, weight, out=None):
+    return skinny_gemm(x, weight, torch.bfloat16, out=out)
+
+
+def dense_gemm_swiglu(x, weight_tiled):
+    return skinny_gemm_swiglu(x, weight_tiled)
+
+
+def dense_gemm_rotary(x, wqkv, table, slots, k_pool, v_pool, num_heads, num_kv_heads, head_dim, rotary_dim, page_size, write_kv):
+    qkv = _sums(x, wqkv)
+    n = qkv.shape[0]
+    heads = qkv.view(n, num_heads + 2 * num_kv_heads, head_dim)
+    if rotary_dim:
+        half = rotary_dim // 2
+        cos, sin = table[:, None, :half], table[:, None, half:]
+        qk = heads[:, : num_heads + num_kv_heads, :rotary_dim]
+        lo, hi = qk[..., :half].clone(), qk[..., half:].clone()
+        heads[:, : num_heads + num_kv_heads, :half] = lo * cos - hi * sin
+        heads[:, : num_heads + num_kv_heads, half:rotary_dim] = hi * cos + lo * sin
+    if write_kv:
+        page, off = (slots // page_size).long(), (slots % page_size).long()
+        k_pool[page, :, off, :] = heads[:, num_heads : num_heads + num_kv_heads].to(k_pool.dtype)
+        v_pool[page, :, off, :] = heads[:, num_heads + num_kv_heads :].to(v_pool.dtype)
+    return qkv[:, : num_heads * head_dim].to(torch.bfloat16)
+
+
 def sample(out, logits, temperature=None, top_k=None, top_p=None, seed=None, draw=None):
     rows = logits.shape[0]
     for r in range(rows):
@@ -230,7 +259,9 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "rotary_table": rotary_table, "rotary_store": rotary_store, "silu_mul": silu_mul, "paged_attention_simt": paged_attention_simt,
        "paged_attention_mma": paged_attention_mma, "paged_decode_tma": paged_decode_tma, "paged_prefill_tc": paged_prefill_tc,
        "skinny_gemm_slices": skinny_gemm_slices, "skinny_gemm": skinny_gemm, "skinny_gemm_residual": skinny_gemm_residual,
-       "skinny_gemm_swiglu": skinny_gemm_swiglu, "skinny_gemm_rotary": skinny_gemm_rotary, "sample": sample}
+       "skinny_gemm_swiglu": skinny_gemm_swiglu, "skinny_gemm_rotary": skinny_gemm_rotary, "dense_gemm": dense_gemm,
+       "dense_gemm_swiglu": dense_gemm_swiglu, "dense_gemm_rotary": dense_gemm_rotary,
+       "sample": sample}
 
 
 calls: dict[str, int] = {}  # how often each stand-in ran since patched() was entered

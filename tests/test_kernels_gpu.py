@@ -650,6 +650,80 @@ def test_skinny_gemm_with_residual_epilogue_and_row_scaling(tokens, H, K, slices
     assert ops.skinny_gemm_error() == 0
 
 
+# ------------------------------------------------------------------ matrix product of many tokens
+
+
+@pytest.mark.parametrize("tokens,features,K", [(1, 8, 8), (128, 256, 64), (130, 264, 72), (517, 1000, 136), (2048, 3072, 2048), (300, 20000, 520), (5000, 384, 264)])
+def test_dense_gemm(tokens, features, K):
+    """Sizes on and off the 128 x 256 x 64 tile, fewer tiles than SMs and many per CTA (both accumulators in turn,
+    every stage reused), against a float64 product."""
+    x = rnd(tokens, K, dtype=torch.bfloat16, seed=tokens)
+    w = rnd(features, K, dtype=torch.bfloat16, seed=features, scale=0.1)
+    want = (x.double() @ w.double().T).cpu().numpy()
+    for _ in range(2):
+        got = ops.dense_gemm(x, w)
+        assert got.dtype == torch.bfloat16 and tuple(got.shape) == (tokens, features)
+        err = np.abs(got.double().cpu().numpy() - want).max()
+        assert err <= 8e-3 * max(1.0, np.abs(want).max()), err
+    assert ops.dense_gemm_error() == 0
+
+
+def test_dense_gemm_refuses_what_it_cannot_do():
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.dense_gemm(rnd(4, 36, dtype=torch.bfloat16), rnd(8, 36, dtype=torch.bfloat16))
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.dense_gemm(rnd(4, 64, dtype=torch.bfloat16), rnd(12, 64, dtype=torch.bfloat16))
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.dense_gemm_rotary(rnd(4, 64, dtype=torch.bfloat16), rnd(4 * 80, 64, dtype=torch.bfloat16), None, None, None, None, 2, 1, 80, 0, 16, False)
+
+
+@pytest.mark.parametrize("tokens,I,K", [(1, 64, 96), (129, 192, 200), (700, 1024, 2048), (2048, 8192, 264)])
+def test_dense_gemm_with_swiglu_epilogue(tokens, I, K):
+    x = rnd(tokens, K, dtype=torch.bfloat16, seed=I)
+    gate = rnd(I, K, dtype=torch.bfloat16, seed=I + 1, scale=0.1)
+    up = rnd(I, K, dtype=torch.bfloat16, seed=I + 2, scale=0.1)
+    tiled = torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], 1).reshape(2 * I, K).contiguous()
+    got = ops.dense_gemm_swiglu(x, tiled)
+    assert tuple(got.shape) == (tokens, I)
+    g = (x.double() @ gate.double().T).cpu().numpy()
+    u = (x.double() @ up.double().T).cpu().numpy()
+    want = plain.silu(g) * u
+    np.testing.assert_allclose(got.double().cpu().numpy(), want, atol=8e-3 * max(1.0, np.abs(want).max()))
+    assert ops.dense_gemm_error() == 0
+
+
+@pytest.mark.parametrize("nh,nkv,d,rot,page,tokens", [(5, 1, 64, 64, 8, 7), (2, 1, 128, 128, 16, 300), (3, 2, 128, 64, 16, 131), (6, 2, 64, 0, 32, 257), (32, 8, 64, 64, 16, 600)])
+def test_dense_gemm_with_rotary_epilogue(nh, nkv, d, rot, page, tokens):
+    """The fused projection + rotary + cache write against the separate kernels: heads of 64 and 128, whole, partial
+    and no rotation, tokens without a slot, more heads than a tile holds."""
+    K = 264
+    pages = tokens // page + 3
+    x = rnd(tokens, K, dtype=torch.bfloat16, seed=nh)
+    w = rnd((nh + 2 * nkv) * d, K, dtype=torch.bfloat16, seed=d, scale=0.1)
+    g = torch.Generator().manual_seed(tokens)
+    positions = torch.randint(0, 100000, (tokens,), generator=g).to(torch.int32).to(DEV)
+    slots = torch.randperm(pages * page, generator=g)[:tokens].to(torch.int32)
+    slots[3 % tokens] = -1
+    slots = slots.to(DEV)
+    inv = torch.from_numpy(plain.inverse_frequencies({"head_dim": rot, "theta": 10000.0, "rope_type": "default"})).to(DEV) if rot else None
+    table = ops.rotary_table(positions, inv) if rot else None
+    kp1, vp1 = (torch.full((pages, nkv, page, d), 9.0, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    kp2, vp2 = kp1.clone(), vp1.clone()
+    q = ops.dense_gemm_rotary(x, w, table, slots, kp1, vp1, nh, nkv, d, rot, page, True)
+    qkv = (x.float() @ w.float().T)  # float32 product, then the stand-alone kernel on its bfloat16 rounding
+    ref = qkv.to(torch.bfloat16).contiguous()
+    ops.rotary_store(ref, positions, inv, slots, kp2, vp2, nh, nkv, d, rot, page, True)
+    t2 = 2e-2 * max(1.0, float(qkv.abs().max()))
+    np.testing.assert_allclose(q.float().cpu().numpy(), ref[:, : nh * d].float().cpu().numpy(), atol=t2)
+    np.testing.assert_allclose(kp1.float().cpu().numpy(), kp2.float().cpu().numpy(), atol=t2)
+    np.testing.assert_allclose(vp1.float().cpu().numpy(), vp2.float().cpu().numpy(), atol=t2)
+    # without the cache write the pools stay as they are
+    kp3, vp3 = kp1.clone(), vp1.clone()
+    q2 = ops.dense_gemm_rotary(x, w, table, None, None, None, nh, nkv, d, rot, page, False)
+    assert torch.equal(q, q2) and torch.equal(kp3, kp1) and torch.equal(vp3, vp1)
+    assert ops.dense_gemm_error() == 0
+
+
 def test_a_wait_inside_the_decode_product_runs_out_and_the_kernel_gives_up_in_order():
     """The copies of one k tile are never issued (a test-only entry; a flag that nothing sets) and the waits are
     limited to a few thousand polls: the kernel gives the wait up, records which one it was, completes its cluster
