@@ -6,16 +6,31 @@
 // with the cache write) can be done on the sums before they are stored: the product's raw output is then never
 // written and re-read by a kernel of its own.
 //
-//   * A CTA is persistent: it walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ... of [128 tokens x 256 features].
-//   * One thread issues the TMA copies (cp.async.bulk.tensor, 128-byte swizzle) of a [128 x 64] tile of x and a
-//     [256 x 64] tile of W per k step, STAGES steps ahead; rows beyond the matrices arrive as zeros.
-//   * One thread issues tcgen05.mma (M = 128, N = 256, K = 16; four per k step) into one of TWO accumulators in
-//     tensor memory (2 x 256 columns), so the products of the next tile run while
-//   * four warps read the finished accumulator with tcgen05.ld (lane = token, column = feature), apply the
-//     epilogue and store.
+// Two CTAs, the two SMs of a cluster, work as one (tcgen05 cta_group::2): a pair owns a tile of 256 tokens x 256
+// features, each CTA its 128 tokens of it in its own tensor memory, and each CTA loads only HALF of the weight tile
+// (128 of its 256 rows); the instruction, issued by the pair's first CTA, reads both halves.
+//
+//   * A pair is persistent: it walks the tiles pair, pair + pairs, ... (token tile first: the pairs that run together
+//     share few weight tiles).
+//   * One thread of each CTA issues its TMA copies (cp.async.bulk.tensor, 128-byte swizzle) of a [128 x 64] tile of
+//     x and a [128 x 64] half tile of W per k step, six steps ahead; rows beyond the matrices arrive as zeros.
+//   * One thread of the first CTA issues tcgen05.mma (M = 2 x 128, N = 256, K = 16; four per k step) into one of TWO
+//     accumulators in tensor memory (2 x 256 columns in each CTA), so the products of the next tile run while
+//   * four warps of each CTA read the finished accumulator with tcgen05.ld (lane = token, column = feature), apply
+//     the epilogue and store.
+//
+// Measured with one CTA to a tile of 128 x 256 first (48 KB a k step, four stages, the copies 2,048 tensor-core clocks
+// ahead of the products): the tensor pipe stood idle a third of the time waiting for operands and the plain product
+// took 1.12 of the library's time at 2,048 x 16,384 x 2,048; with the pair (32 KB a k step and CTA, six stages, 3,072
+// clocks ahead) it takes 1.00.
+//
+//   full[s]      (first CTA)  both CTAs' copies of stage s have landed: their bytes are counted on the first CTA's barrier
+//   empty[s]     (each CTA)   the products have read stage s: the commit arrives in both CTAs
+//   acc_full[b]  (each CTA)   accumulator b is finished: the commit arrives in both CTAs
+//   acc_empty[b] (first CTA)  the epilogue threads of both CTAs (256) have read accumulator b
 //
 // Every wait on an mbarrier is bounded: after `wait_limit` polls the kernel records a code in *error_flag,
-// stops issuing work, frees its tensor memory and returns.
+// stops issuing work, frees its tensor memory and returns.  Neither CTA leaves before the other has reached the end.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -24,16 +39,11 @@ using namespace dli;
 
 namespace {
 
-constexpr int BM = 128;   // tokens per tile
+constexpr int BM = 128;   // tokens per CTA of a tile (a pair's tile has 256)
 constexpr int BN = 256;   // features per tile
 constexpr int BK = 64;    // k per stage: 128 bytes of bfloat16, one swizzle row
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int THREADS = 192;  // warp 0: copies; warp 1: products; warps 2..5: epilogue
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;  // stages, barriers, alignment
-static_assert(SMEM_BYTES <= 227 * 1024, "one CTA per SM");
+constexpr int THREADS = 192;  // warp 0: copies; warp 1: products (first CTA); warps 2..5: epilogue
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -43,7 +53,6 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 // true when the phase with this parity has completed; false after `limit` polls or once another thread has failed
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned limit, volatile int* failed) {
   for (unsigned i = 0; i < limit; ++i) {
@@ -55,10 +64,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     if ((i & 1023) == 1023 && *failed) return false;
   }
   return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in 128-byte mode:
 // start address, 1024 bytes between groups of eight rows, layout code 2.
@@ -73,15 +78,6 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 // Instruction descriptor of kind::f16: float32 accumulator, bfloat16 A and B, both K-major.
 __device__ __forceinline__ uint32_t instr_desc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
@@ -244,68 +240,108 @@ __device__ __forceinline__ void epilogue_row(const DenseParams& p, uint32_t acc,
   }
 }
 
-__global__ void __launch_bounds__(THREADS, 1) dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x,
-                                                                const __grid_constant__ CUtensorMap map_w, const DenseParams p) {
+constexpr int PAIR_STAGES = 6;  // of a [128 x 64] tile of x and a [128 x 64] half tile of W
+constexpr int PAIR_B_BYTES = (BN / 2) * BK * 2;
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 256 + 1024;
+static_assert(PAIR_SMEM_BYTES <= 227 * 1024, "one CTA per SM");
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;  // a shared-memory address with this bit cleared names the pair's first CTA
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// a copy whose bytes are counted on the barrier of the pair's first CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar & PEER_BIT_MASK), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives, once the products issued so far have finished, on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_at(uint32_t bar, uint32_t cta) {
+  asm volatile("{\n\t.reg .b32 remote;\n\tmapa.shared::cluster.u32 remote, %0, %1;\n\tmbarrier.arrive.shared::cluster.b64 _, [remote];\n\t}"
+               ::"r"(bar), "r"(cta) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1) dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                     const __grid_constant__ CUtensorMap map_w, const DenseParams p) {
   pdl_launch_dependents();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);  // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+  uint64_t* bars = (uint64_t*)(smem + PAIR_STAGES * PAIR_STAGE_BYTES);  // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * PAIR_STAGES + 4);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), acc_full0 = smem_u32(bars + 2 * STAGES),
-                 acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
+  const uint32_t rank = cluster_ctarank();  // 0: the CTA that issues the products
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + PAIR_STAGES), acc_full0 = smem_u32(bars + 2 * PAIR_STAGES),
+                 acc_empty0 = smem_u32(bars + 2 * PAIR_STAGES + 2);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full0 + 8 * b, 1);
-      mbar_init(acc_empty0 + 8 * b, 128);  // every epilogue thread has read its row
+      mbar_init(acc_empty0 + 8 * b, 256);  // every epilogue thread of both CTAs has read its row
     }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  cluster_sync_all();  // the other CTA's barriers are set up before anything is sent to them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  const int tiles = p.m_tiles * p.n_tiles;
+  const int m_pairs = (p.m_tiles + 1) / 2;  // tiles of 256 tokens
+  const int tiles = m_pairs * p.n_tiles;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
 
   if (warp == 0) {
-    // ---- copies.  Tiles are walked token tile first: the CTAs that run together share few weight tiles.
+    // ---- copies: this CTA's 128 tokens and its half of the weight tile's rows
     if (lane == 0) {
       pdl_wait();  // the activations are the work of the kernel before this one
       int it = 0;
-      for (int tile = blockIdx.x; tile < tiles && !*failed; tile += gridDim.x) {
-        const int m = tile % p.m_tiles, n = tile / p.m_tiles;
+      for (int tile = pair; tile < tiles && !*failed; tile += pairs) {
+        const int m = tile % m_pairs, n = tile / m_pairs;
         for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
-          const int s = it % STAGES;
-          if (it >= STAGES && !mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, p.wait_limit, failed)) {
+          const int s = it % PAIR_STAGES;
+          if (it >= PAIR_STAGES && !mbar_wait(empty0 + 8 * s, ((it / PAIR_STAGES) - 1) & 1, p.wait_limit, failed)) {
             if (!*failed) { *failed = 1; atomicExch(p.error_flag, 1); }
             break;
           }
-          const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
-          mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-          tma_load_2d(a, &map_x, kt * BK, m * BM, full0 + 8 * s);
-          tma_load_2d(a + A_BYTES, &map_w, kt * BK, n * BN, full0 + 8 * s);
+          const uint32_t a = smem_u32(smem + (size_t)s * PAIR_STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
+          tma_load_2d_pair(a, &map_x, kt * BK, m * 2 * BM + (int)rank * BM, full0 + 8 * s);
+          tma_load_2d_pair(a + A_BYTES, &map_w, kt * BK, n * BN + (int)rank * (BN / 2), full0 + 8 * s);
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ---- products
-    if (lane == 0) {
-      const uint32_t idesc = instr_desc(BM, BN);
+    // ---- products: the first CTA's thread issues them for both
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = instr_desc(2 * BM, BN);
       int it = 0, local = 0;
-      for (int tile = blockIdx.x; tile < tiles && !*failed; tile += gridDim.x, ++local) {
+      for (int tile = pair; tile < tiles && !*failed; tile += pairs, ++local) {
         const int buf = local & 1;
         if (local >= 2 && !mbar_wait(acc_empty0 + 8 * buf, ((local >> 1) - 1) & 1, p.wait_limit, failed)) {
           if (!*failed) { *failed = 2; atomicExch(p.error_flag, 2); }
@@ -314,48 +350,49 @@ __global__ void __launch_bounds__(THREADS, 1) dense_gemm_kernel(const __grid_con
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         bool ok = true;
         for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, p.wait_limit, failed)) {
+          const int s = it % PAIR_STAGES;
+          if (!mbar_wait(full0 + 8 * s, (it / PAIR_STAGES) & 1, p.wait_limit, failed)) {
             if (!*failed) { *failed = 3; atomicExch(p.error_flag, 3); }
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint32_t a = smem_u32(smem + (size_t)s * PAIR_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            umma(tmem + buf * BN, smem_desc_sw128(a + k * 32), smem_desc_sw128(a + A_BYTES + k * 32), idesc, (kt | k) != 0);
-          umma_commit(empty0 + 8 * s);  // arrives once these products have read the stage
+            umma_pair(tmem + buf * BN, smem_desc_sw128(a + k * 32), smem_desc_sw128(a + A_BYTES + k * 32), idesc, (kt | k) != 0);
+          umma_commit_pair(empty0 + 8 * s);  // arrives in both CTAs once these products have read the stage
         }
         if (!ok) break;
-        umma_commit(acc_full0 + 8 * buf);  // arrives once every product of the tile has finished
+        umma_commit_pair(acc_full0 + 8 * buf);  // arrives in both CTAs once every product of the tile has finished
       }
     }
     __syncwarp();
   } else {
-    // ---- epilogue: lane of tensor memory = token of the tile; a warp reaches the 32 lanes of its index modulo 4
+    // ---- epilogue: this CTA's 128 tokens of the tile
     const int quad = warp & 3;
     const uint32_t lane_bits = (uint32_t)(quad * 32) << 16;
     pdl_wait();  // the output may alias memory that the kernel before this one still reads
     int local = 0;
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
-      const int m = tile % p.m_tiles, n = tile / p.m_tiles;
+    for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+      const int m = tile % m_pairs, n = tile / m_pairs;
       const int buf = local & 1;
       bool ok = mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1, p.wait_limit, failed);
       if (!ok && !*failed) { *failed = 4; atomicExch(p.error_flag, 4); }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      epilogue_row(p, tmem + buf * BN + lane_bits, m * BM + quad * 32 + lane, n);
+      epilogue_row(p, tmem + buf * BN + lane_bits, m * 2 * BM + (int)rank * BM + quad * 32 + lane, n);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(acc_empty0 + 8 * buf);
+      mbar_arrive_at(acc_empty0 + 8 * buf, 0);
     }
   }
 
-  // ---- teardown: nobody touches tensor memory after this barrier; the warp that allocated it frees it
+  // ---- teardown: neither CTA leaves while the other may still send to its barriers or read its shared memory
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  cluster_sync_all();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
 }
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -388,6 +425,31 @@ int* error_flag_host = nullptr;
 
 }  // namespace
 
+// launch_pdl with the cluster along x
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl_x(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  attr[n].id = cudaLaunchAttributeClusterDimension;
+  attr[n].val.clusterDim.x = cluster_x;
+  attr[n].val.clusterDim.y = 1;
+  attr[n].val.clusterDim.z = 1;
+  ++n;
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 static int launch_dense(DenseParams p, const void* x, const void* w, int tokens, int features, int K, cudaStream_t stream) {
   if (tokens < 1 || features < 8 || features % 8 || K < 8 || K % 8) return DLI_ERR_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)p.out) & 15) return DLI_ERR_UNSUPPORTED;
@@ -397,7 +459,7 @@ static int launch_dense(DenseParams p, const void* x, const void* w, int tokens,
     if (cudaHostGetDevicePointer((void**)&error_flag_device, error_flag_host, 0) != cudaSuccess) return (int)cudaGetLastError();
   }
   CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, x, tokens, K, BM) || !make_map(&map_w, w, features, K, BN)) return DLI_ERR_UNSUPPORTED;
+  if (!make_map(&map_x, x, tokens, K, BM) || !make_map(&map_w, w, features, K, BN / 2)) return DLI_ERR_UNSUPPORTED;  // W in boxes of half a tile's rows
   p.tokens = tokens; p.features = features;
   p.k_tiles = (K + BK - 1) / BK;
   p.m_tiles = (tokens + BM - 1) / BM;
@@ -406,13 +468,14 @@ static int launch_dense(DenseParams p, const void* x, const void* w, int tokens,
   p.wait_limit = WAIT_LIMIT;
   static OncePerDevice configured;
   if (!configured.here()) {
-    cudaError_t e = cudaFuncSetAttribute(dense_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(dense_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured.here() = true;
   }
-  const long long tiles = (long long)p.m_tiles * p.n_tiles;
-  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  cudaError_t e = launch_pdl(dense_gemm_kernel, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, stream, 1, map_x, map_w, p);
+  const long long tiles = (long long)((p.m_tiles + 1) / 2) * p.n_tiles;
+  const long long pairs = sm_count() / 2;
+  const int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
+  cudaError_t e = launch_pdl_x(dense_gemm_pair_kernel, dim3(grid), dim3(THREADS), (size_t)PAIR_SMEM_BYTES, stream, 2, map_x, map_w, p);
   return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 

@@ -44,13 +44,13 @@ def fused_epilogue(x: torch.Tensor) -> bool:
 # From this many tokens two of a layer's bfloat16 products go to the engine's tcgen05 product for many tokens, which
 # does the elementwise step behind the product in its epilogue.  Measured on B200 at Llama-3.2-1B sizes (us, this
 # product against the library's product plus the kernel it saves; 512 / 2,048 / 8,192 tokens): gate|up with SiLU * up
-# 39/42, 107/115, 397/424: always.  q|k|v with rotary and cache write 26/37, 41/38, 93/97: when its tiles fill their
-# waves (2,048 tokens are 192 tiles on 148 SMs).  The o and down products stay with the library: with the residual
-# addition and the norm's sums in the epilogue they took 31/34 and 68/58 us at 2,048 tokens and 98/81, 259/209 at
-# 8,192 (the epilogue reads and writes the float32 residual a row per thread, and at K = 8,192 the plain product is
-# 0.87 of the library's), so that epilogue was taken out again.
+# 39/38, 102/116, 383/427: always.  q|k|v with rotary and cache write 26/37, 39/37, 87/98: when its tiles fill their
+# waves (2,048 tokens are 96 tiles on 74 pairs of SMs).  The plain product takes 1.00 of the library's time for gate|up
+# at 2,048 tokens, 0.96-1.07 for o and down, which stay with the library: with the residual addition and the norm's
+# sums in the epilogue they were slower than the library's product and the norm kernel (the epilogue read and wrote
+# the float32 residual a row per thread), so that epilogue was taken out again.
 DENSE_MIN_TOKENS = 512
-DENSE_TILE = (128, 256)  # tokens x features of the product's tiles
+DENSE_TILE = (256, 256)  # tokens x features of a tile, which a pair of SMs computes
 WAVE_FILL_MIN = 0.8
 
 
@@ -71,11 +71,11 @@ def dense_product(x, features: int, epilogue: str) -> bool:
 
     if not _dense_candidate(x, features):
         return False
-    tiles, sms = _dense_tiles(x.shape[0], features), sm_count()
+    tiles, pairs = _dense_tiles(x.shape[0], features), max(1, sm_count() // 2)
     if epilogue == "swiglu":
         return True
     if epilogue == "rotary":
-        return tiles <= sms or tiles / (-(-tiles // sms) * sms) >= WAVE_FILL_MIN
+        return tiles <= pairs or tiles / (-(-tiles // pairs) * pairs) >= WAVE_FILL_MIN
     raise ValueError(f"unknown epilogue {epilogue!r}")
 
 

@@ -702,7 +702,8 @@ def _dense_sizes(x: torch.Tensor, weight: torch.Tensor, name: str):
 
 def dense_gemm(x, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """x [tokens, K] times weight [features, K] transposed, bfloat16 in and out, float32 sums, on tcgen05 tensor
-    cores fed by TMA: persistent CTAs over tiles of 128 tokens x 256 features, two accumulators in tensor memory."""
+    cores fed by TMA: persistent pairs of CTAs (cta_group::2) over tiles of 256 tokens x 256 features, two
+    accumulators in each CTA's tensor memory."""
     tokens, features, K = _dense_sizes(x, weight, "dense_gemm")
     if out is None:
         out = torch.empty((tokens, features), dtype=torch.bfloat16, device=x.device)
