@@ -109,6 +109,7 @@ struct DenseParams {
   __nv_bfloat16* k_pool;
   __nv_bfloat16* v_pool;
   int nh, nkv, d, rot, page_size, write_kv;
+  int skip_tile;  // -1 in every launch of the engine: the k step whose copies a test leaves out (dli_dense_gemm_wait_test)
 };
 
 // 32 consecutive columns of this thread's row of the accumulator.  `rounded`: as bfloat16 would hold them.  The
@@ -325,9 +326,10 @@ __global__ void __launch_bounds__(THREADS, 1) dense_gemm_pair_kernel(const __gri
         for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
           const int s = it % PAIR_STAGES;
           if (it >= PAIR_STAGES && !mbar_wait(empty0 + 8 * s, ((it / PAIR_STAGES) - 1) & 1, p.wait_limit, failed)) {
-            if (!*failed) { *failed = 1; atomicExch(p.error_flag, 1); }
+            if (!*failed) { *failed = 1; atomicCAS(p.error_flag, 0, 1); }
             break;
           }
+          if (kt == p.skip_tile) continue;
           const uint32_t a = smem_u32(smem + (size_t)s * PAIR_STAGE_BYTES);
           if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
           tma_load_2d_pair(a, &map_x, kt * BK, m * 2 * BM + (int)rank * BM, full0 + 8 * s);
@@ -344,7 +346,7 @@ __global__ void __launch_bounds__(THREADS, 1) dense_gemm_pair_kernel(const __gri
       for (int tile = pair; tile < tiles && !*failed; tile += pairs, ++local) {
         const int buf = local & 1;
         if (local >= 2 && !mbar_wait(acc_empty0 + 8 * buf, ((local >> 1) - 1) & 1, p.wait_limit, failed)) {
-          if (!*failed) { *failed = 2; atomicExch(p.error_flag, 2); }
+          if (!*failed) { *failed = 2; atomicCAS(p.error_flag, 0, 2); }
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -352,7 +354,7 @@ __global__ void __launch_bounds__(THREADS, 1) dense_gemm_pair_kernel(const __gri
         for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
           const int s = it % PAIR_STAGES;
           if (!mbar_wait(full0 + 8 * s, (it / PAIR_STAGES) & 1, p.wait_limit, failed)) {
-            if (!*failed) { *failed = 3; atomicExch(p.error_flag, 3); }
+            if (!*failed) { *failed = 3; atomicCAS(p.error_flag, 0, 3); }
             ok = false;
             break;
           }
@@ -378,7 +380,7 @@ __global__ void __launch_bounds__(THREADS, 1) dense_gemm_pair_kernel(const __gri
       const int m = tile % m_pairs, n = tile / m_pairs;
       const int buf = local & 1;
       bool ok = mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1, p.wait_limit, failed);
-      if (!ok && !*failed) { *failed = 4; atomicExch(p.error_flag, 4); }
+      if (!ok && !*failed) { *failed = 4; atomicCAS(p.error_flag, 0, 4); }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -465,7 +467,10 @@ static int launch_dense(DenseParams p, const void* x, const void* w, int tokens,
   p.m_tiles = (tokens + BM - 1) / BM;
   p.n_tiles = (features + BN - 1) / BN;
   p.error_flag = error_flag_device;
-  p.wait_limit = WAIT_LIMIT;
+  if (p.wait_limit == 0) {
+    p.wait_limit = WAIT_LIMIT;
+    p.skip_tile = -1;
+  }
   static OncePerDevice configured;
   if (!configured.here()) {
     cudaError_t e = cudaFuncSetAttribute(dense_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
@@ -511,6 +516,23 @@ DLI_EXPORT int dli_dense_gemm_rotary(void* q_out, const void* x, const void* w, 
   p.trig = trig; p.slots = slots; p.k_pool = (__nv_bfloat16*)k_pool; p.v_pool = (__nv_bfloat16*)v_pool;
   p.nh = nh; p.nkv = nkv; p.d = d; p.rot = rot; p.page_size = page_size; p.write_kv = write_kv;
   return launch_dense(p, x, w, tokens, (nh + 2 * nkv) * d, K, stream);
+}
+
+// For the test of the bounded waits only.  The plain product of ONE tile (tokens <= 256, features <= 256) whose k
+// steps all have a stage of their own (K <= 384), but neither CTA issues the copies of the last k step and every wait
+// gives up after `wait_limit` polls: the waits for those operands, and for the accumulator that depends on them, run
+// out; the kernel records the first one's code, both CTAs reach the end together, free their tensor memory and
+// return.  No copy is in flight then: every copy that was issued has been waited for.  The engine never calls this.
+DLI_EXPORT int dli_dense_gemm_wait_test(void* out, const void* x, const void* w, int tokens, int features, int K, unsigned wait_limit,
+                                        cudaStream_t stream) {
+  const int k_tiles = (K + BK - 1) / BK;
+  if (wait_limit < 1 || wait_limit > WAIT_LIMIT || tokens > 2 * BM || features > BN || k_tiles > PAIR_STAGES || k_tiles < 1) return DLI_ERR_UNSUPPORTED;
+  DenseParams p = {};
+  p.out = (__nv_bfloat16*)out;
+  p.mode = EP_STORE;
+  p.wait_limit = wait_limit;
+  p.skip_tile = k_tiles - 1;
+  return launch_dense(p, x, w, tokens, features, K, stream);
 }
 
 // 0, or the code of the first wait that ran out (1 copies, 2 and 3 products, 4 epilogue)

@@ -754,6 +754,19 @@ def dense_gemm_rotary(x, wqkv, table, slots, k_pool, v_pool, num_heads: int, num
     return q
 
 
+def dense_gemm_wait_test(x: torch.Tensor, weight: torch.Tensor, wait_limit: int) -> torch.Tensor:
+    """For the test of the kernel's bounded waits: the product of one tile (tokens <= 256, features <= 256, K <= 384)
+    in which neither CTA of the pair issues the copies of the last k step and every wait gives up after
+    ``wait_limit`` polls.  The kernel records a code (``dense_gemm_error``: 3, the wait for operands, or 4, the wait
+    for the accumulator that depends on them), both CTAs end together and free their tensor memory; nothing hangs or
+    faults.  Not used by the engine."""
+    tokens, features, K = _dense_sizes(x, weight, "dense_gemm_wait_test")
+    out = torch.zeros((tokens, features), dtype=torch.bfloat16, device=x.device)
+    f = _fn("dense_gemm.cu", "dli_dense_gemm_wait_test", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, ctypes.c_uint, c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(weight), tokens, features, K, int(wait_limit), _stream()), "dense_gemm_wait_test")
+    return out
+
+
 def dense_gemm_error() -> int:
     """0, or which bounded wait of the many-token product ran out (1 copies, 2 and 3 products, 4 epilogue)."""
     return _fn("dense_gemm.cu", "dli_dense_gemm_error", [])()

@@ -724,6 +724,26 @@ def test_dense_gemm_with_rotary_epilogue(nh, nkv, d, rot, page, tokens):
     assert ops.dense_gemm_error() == 0
 
 
+def test_a_wait_inside_the_many_token_product_runs_out_and_both_ctas_give_up_in_order():
+    """Neither CTA of the pair issues the copies of the last k step (a test-only entry; a flag that nothing sets) and
+    the waits are limited to a few thousand polls: the waits for those operands and for the accumulator run out, the
+    first one's code is recorded, both CTAs reach the end together and free their tensor memory.  The host reads the
+    code, nothing hangs, and the next ordinary product of the same shapes is right."""
+    tokens, features, K = 200, 256, 320  # one tile, five k steps, each in a stage of its own
+    x, w = rnd(tokens, K, dtype=torch.bfloat16, seed=1), rnd(features, K, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = (x.float() @ w.float().T).cpu().numpy()
+    assert ops.device_wait_errors() == {}
+    ops.dense_gemm_wait_test(x, w, wait_limit=4000)
+    torch.cuda.synchronize()  # returns: the kernel ended by itself
+    assert ops.dense_gemm_error() in (3, 4)
+    found = ops.device_wait_errors()
+    assert found.get("dense_gemm.cu") in (3, 4) and ops.device_wait_errors() == {}  # read once, then forgotten
+    for _ in range(3):
+        got = ops.dense_gemm(x, w)
+        np.testing.assert_allclose(got.float().cpu().numpy(), want, atol=2e-2)
+    assert ops.dense_gemm_error() == 0
+
+
 def test_a_wait_inside_the_decode_product_runs_out_and_the_kernel_gives_up_in_order():
     """The copies of one k tile are never issued (a test-only entry; a flag that nothing sets) and the waits are
     limited to a few thousand polls: the kernel gives the wait up, records which one it was, completes its cluster
