@@ -65,8 +65,8 @@ def _dense_candidate(x, features: int) -> bool:
 
 
 def dense_product(x, features: int, epilogue: str) -> bool:
-    """Whether the product of these activations with a [features, K] weight, followed by ``epilogue`` ("swiglu",
-    "rotary" or "residual"), goes to the engine's product for many tokens."""
+    """Whether the product of these activations with a [features, K] weight, followed by ``epilogue`` ("swiglu" or
+    "rotary"), goes to the engine's product for many tokens."""
     from .attention import sm_count
 
     if not _dense_candidate(x, features):
