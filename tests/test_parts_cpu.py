@@ -1,7 +1,7 @@
 """The tests of tests/test_parts_gpu.py once more, on the CPU with torch stand-ins for the
 kernels (tests/cpu_ops.py): each part alone, a block against the plain layer, and the generality of the
 assembly (a layer run twice, a shared cache, a windowed group that gives pages back, other position
-encodings, the toy mixer with state, the toy routed feed-forward).  What they check here is the Python
+encodings, the toy mixer with state, the toy routed feed-forward, the toy position encoding).  What they check here is the Python
 above the kernels; the kernels themselves are checked on the GPU."""
 
 import functools
@@ -67,6 +67,11 @@ def toy_architecture():
 def test_toy_parts(toy_architecture):
     g.test_toy_mixer_with_state_is_registered_built_and_stepped(toy_architecture)
     g.test_toy_routed_feed_forward_is_registered_and_stepped()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["float32", "bfloat16"])
+def test_toy_position_encoding(dtype):
+    g.test_toy_position_encoding_with_a_table_is_registered_and_stepped(dtype)
 
 
 def test_toy_layer_with_pages_and_state_and_toy_mixer_with_a_launch_key():

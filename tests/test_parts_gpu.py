@@ -14,6 +14,7 @@ from dli_b200.cache import StateNeed
 from dli_b200.config import Architecture, LlamaConfig, llama_model_spec, register_architecture, unregister_architecture
 from dli_b200.config.spec import LayerSpec, ModelSpec, PartSpec, RunStep
 from dli_b200.engine import ModelRunner, StepEntry, random_model
+from dli_b200.kernels import ops
 from dli_b200.parts import BuildEnv, DecoderModel, Part, build_part, register_part, unregister_part
 from dli_b200.parts.base import ResidualStream
 from dli_b200.weights import TensorDecl, random_tensors
@@ -638,3 +639,80 @@ def test_toy_routed_feed_forward_is_registered_and_stepped():
         np.testing.assert_allclose(cut, want, atol=1e-4)
     finally:
         unregister_part("feed_forward", "toy_routed")
+
+
+# ------------------------------------------------------------------ a toy position encoding with a table of its own
+
+
+class LearnedOffsets(Part):
+    """Adds a learned row offsets[position] to every q and k head before the scores are taken
+    (absolute positions, no rotation); defined here only.  It has a tensor of its own, and it
+    offers ``rotate_and_store`` alone, so the mixer makes the q | k | v product itself."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.head_dim, self.max_positions = int(spec.params["head_dim"]), int(spec.params["max_positions"])
+
+    def declare(self):
+        return {self.spec.prefix + "offsets.weight": TensorDecl((self.max_positions, self.head_dim))}
+
+    def load(self, tensors):
+        self.offsets = tensors[self.spec.prefix + "offsets.weight"]
+
+    def rotate_and_store(self, qkv, batch, cache, num_heads, num_kv_heads, write_kv):
+        n, d = qkv.shape[0], self.head_dim
+        rows = self.offsets[batch.positions.long()].float()  # [n, d]
+        heads = qkv[:, : (num_heads + num_kv_heads) * d].view(n, num_heads + num_kv_heads, d)
+        heads.copy_((heads.float() + rows[:, None, :]).to(qkv.dtype))
+        slots = batch.group(cache.group).slots
+        ops.rotary_store(qkv, batch.positions, None, slots if write_kv else None, cache.k if write_kv else None,
+                         cache.v if write_kv else None, num_heads, num_kv_heads, d, 0, cache.page_size, write_kv)
+        return qkv
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_position_encoding_with_a_table_is_registered_and_stepped(dtype):
+    """Layer 0 keeps its rotary encoding, layer 1 takes the toy one: its table is declared, loaded by
+    name and indexed by the positions of the step, whole and in portions down to single tokens."""
+    register_part("position", "toy_learned_offsets")(LearnedOffsets)
+    try:
+        base = llama_model_spec(LlamaConfig.from_hf_dict(TINY_A))
+        c = plain.read_config(TINY_A)
+        layers = list(base.layers)
+        mixer = layers[1].parts["mixer"]
+        toy = PartSpec("toy_learned_offsets", {"head_dim": c["head_dim"], "max_positions": 64}, "model.layers.1.self_attn.position.")
+        layers[1] = LayerSpec(layers[1].arrangement, {**layers[1].parts, "mixer": dataclasses.replace(mixer, params={**mixer.params, "position": toy})})
+        spec = dataclasses.replace(base, layers=tuple(layers))
+        model = DecoderModel(spec, dtype, DEV)
+        tensors = random_tensors(model.declared_tensors(), 21, dtype=dtype, device=DEV)
+        table = "model.layers.1.self_attn.position.offsets.weight"
+        tensors[table] = tensors[table] * 32  # a power of two, exact in bfloat16 too: the offsets move the scores visibly
+        model.load(tensors)
+        w = weights_as_plain(tensors, dtype)
+        tokens = np.random.default_rng(9).integers(0, 256, 43).tolist()
+
+        x = w["model.embed_tokens.weight"][np.asarray(tokens)]
+        cos, sin = plain.rope_cos_sin(plain.inverse_frequencies(c), np.arange(len(tokens)))
+        x, _ = plain_layer(x, w, 0, c, cos, sin)
+        p = "model.layers.1."
+        n, d = len(tokens), c["head_dim"]
+        y = plain.rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
+        rows = w[p + "self_attn.position.offsets.weight"][:n]
+        q = (y @ w[p + "self_attn.q_proj.weight"].T).reshape(n, c["heads"], d) + rows[:, None, :]
+        k = (y @ w[p + "self_attn.k_proj.weight"].T).reshape(n, c["kv_heads"], d) + rows[:, None, :]
+        v = (y @ w[p + "self_attn.v_proj.weight"].T).reshape(n, c["kv_heads"], d)
+        o = plain.causal_attention(q.transpose(1, 0, 2), k.transpose(1, 0, 2), v.transpose(1, 0, 2)).transpose(1, 0, 2).reshape(n, -1)
+        x = x + o @ w[p + "self_attn.o_proj.weight"].T
+        x = x + plain.swiglu_mlp(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"]), w, p + "mlp.")
+        want = plain.rms_norm(x, w["model.norm.weight"], c["eps"]) @ w["model.embed_tokens.weight"].T
+
+        # the table matters: it moves the scores by far more than the tolerance
+        with_rows = np.einsum("nhd,mhd->hnm", q, k[:, : 1].repeat(c["heads"], 1))
+        without = np.einsum("nhd,mhd->hnm", q - rows[:, None, :], (k - rows[:, None, :])[:, : 1].repeat(c["heads"], 1))
+        assert np.abs(with_rows - without).max() > 1.0, "the offsets are too small to show a fault"
+
+        whole, cut = run_whole_and_cut(model, tokens, 4, [9, 1, 1, 2, 28, 1, 1])
+        np.testing.assert_allclose(whole, want, atol=TOL[dtype])
+        np.testing.assert_allclose(cut, want, atol=TOL[dtype])
+    finally:
+        unregister_part("position", "toy_learned_offsets")
