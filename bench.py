@@ -155,8 +155,9 @@ def make_engine(model, batch, prompt_len=PROMPT_LEN, context=CONTEXT):
 
 
 def decode_device_timed(model, batch, steps, warmup, sampler_clock=None, graphs=True, prompt_len=PROMPT_LEN, context=CONTEXT,
-                        portion=2048, blocks=None):
-    """Blocks of K decode steps timed on the device: step function plus greedy sampling.  Each step runs
+                        portion=2048, blocks=None, sampling=None):
+    """Blocks of K decode steps timed on the device: step function plus sampling (greedy, or with ``sampling``:
+    SamplingParams that every request gets, bound to its state slot as the engine binds them).  Each step runs
     on the ids the step before sampled, taken on the device; the host reads every step's ids, one
     step late (the engine's own way of stepping).  Prompts are prefilled in portions of ``portion``."""
     import torch
@@ -168,10 +169,18 @@ def decode_device_timed(model, batch, steps, warmup, sampler_clock=None, graphs=
 
     runner = ModelRunner(model, num_pages=batch * (context // PAGE) + 8, page_size=PAGE, max_requests=batch,
                          enable_prefix_caching=False, watermark=0.0, cuda_graphs=graphs)
-    sampler = Sampler(model.device)
+    sampler = Sampler(model.device, max_requests=batch if sampling else 0)
     g = torch.Generator().manual_seed(1)
     vocab = model.spec.vocab_size
     params = [SamplingParams()] * batch
+    for b in range(batch if sampling else 0):
+        sampler.bind(b, sampling, (sampling.seed or 0) + b, 0)
+
+    def sample_rows(logits):
+        if sampling:
+            return sampler.sample_slots_async(logits, list(range(batch)), all_greedy=False)
+        return sampler.sample_async(logits, params, [0] * batch, [0] * batch)
+
     tokens = []
     for b in range(batch):
         prompt = torch.randint(1000, vocab, (prompt_len,), generator=g).tolist()
@@ -188,14 +197,12 @@ def decode_device_timed(model, batch, steps, warmup, sampler_clock=None, graphs=
         for b in range(batch):
             runner.manager.append_slots(b, [UNKNOWN_TOKEN])  # no prefix index in this run: the id is never needed
             entries.append(StepEntry(b, [0], [0], token_src=b))
-        logits = runner.step(entries, borrow=True, token_source=prev.device_ids)
-        return sampler.sample_async(logits, params, [0] * batch, [0] * batch)
+        return sample_rows(runner.step(entries, borrow=True, token_source=prev.device_ids))
 
     # the first step runs on ids the host knows
     for b in range(batch):
         runner.manager.append_slots(b, [tokens[b]])
-    flight = sampler.sample_async(runner.step([StepEntry(b, [tokens[b]], [0]) for b in range(batch)], borrow=True),
-                                  params, [0] * batch, [0] * batch)
+    flight = sample_rows(runner.step([StepEntry(b, [tokens[b]], [0]) for b in range(batch)], borrow=True))
 
     def one_step(flight):
         ahead = launch(flight)
@@ -294,6 +301,51 @@ def prefill_timed(model, cfg, layers, peak_tflops, reps=5, warmup=3, tokens=PROM
             "flops": flops, "unit": "tokens/s"}
 
 
+def sampling_timed(vocab, reps=5, per_graph=8):
+    """Microseconds of the sampling kernel alone, by what the rows ask for, at 1, 8 and 64 rows of ``vocab`` logits:
+    a graph of ``per_graph`` launches, replayed ``reps`` times between two events."""
+    import torch
+
+    from dli_b200.kernels import ops
+
+    dev = "cuda:0"
+    modes = {"greedy": None, "temperature": (0.8, -1, 1.0), "top_k_50": (0.8, 50, 1.0), "top_p_0.9": (0.8, -1, 0.9), "top_k_50_top_p_0.9": (0.8, 50, 0.9)}
+    out = {}
+    for rows in (1, 8, 64):
+        g = torch.Generator().manual_seed(rows)
+        logits = (torch.randn(rows, vocab, generator=g) * 3).to(dev)
+        ids = torch.empty(rows, dtype=torch.int32, device=dev)
+        seed, draw = torch.arange(rows, dtype=torch.int64, device=dev), torch.zeros(rows, dtype=torch.int64, device=dev)
+        for name, mode in modes.items():
+            if mode is None:
+                fn = lambda: ops.sample(ids, logits)
+            else:
+                t, k, p = (torch.full((rows,), mode[0], device=dev), torch.full((rows,), mode[1], dtype=torch.int32, device=dev),
+                           torch.full((rows,), mode[2], device=dev))
+                fn = lambda t=t, k=k, p=p: ops.sample(ids, logits, t, k, p, seed, draw)
+            fn()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(per_graph):
+                    fn()
+            graph.replay()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(reps):
+                graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            out[f"rows{rows}_{name}"] = round(start.elapsed_time(end) * 1000.0 / reps / per_graph, 1)
+    return out
+
+
 def decode_point(model, batch, steps, warmup, hbm_gbs, **kw):
     """A decode measurement as a record: tokens a second, ms a step, the bytes a step has to read
     (every weight once and the live cache at the block's mean context) and their share of the HBM peak."""
@@ -311,8 +363,13 @@ def more_points(model_1b, steps, warmup, pk):
 
     import dli_b200
 
+    from dli_b200.sampling import SamplingParams
+
     steps = min(steps, 32)
     out = {}
+    # the headline step with every request sampling at temperature 0.8 among the 50 likeliest tokens and 0.9 of their mass
+    out["decode_b8_sampled"] = decode_point(model_1b, 8, steps, warmup, pk["hbm_gbs"], blocks=1,
+                                            sampling=SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=1))
     for name, batch, ctx in (("decode_b8_ctx16k", 8, 16384), ("decode_b1_ctx32k", 1, 32768), ("decode_b8_ctx32k", 8, 32768)):
         out[name] = decode_point(model_1b, batch, steps, warmup, pk["hbm_gbs"], prompt_len=ctx, context=ctx + 512, blocks=1)
     cfg = LLAMA_3_2_3B
@@ -523,8 +580,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the main batch size (for profiling runs)")
     ap.add_argument("--skip-more", action="store_true", help="leave out the other shapes and contexts (the \"more\" key)")
-    ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
-                    help="profiling runs: only the device-timed decode steps, or only the prefill step (prints a short line)")
+    ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "sample"],
+                    help="profiling runs: only the device-timed decode steps, only the prefill step, or only the sampling kernel (prints a short line)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling runs: launch the decode step's kernels one by one")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="profiling runs of --phase decode: the context at which decoding starts")
     args = ap.parse_args()
@@ -543,6 +600,9 @@ def main() -> int:
 
     cfg = dict(LLAMA_3_2_1B, num_hidden_layers=args.layers)
     pk = peaks()
+    if args.phase == "sample":
+        print(json.dumps({"phase": "sample", "vocab": cfg["vocab_size"], "unit": "us", **sampling_timed(cfg["vocab_size"])}))
+        return 0
     model = dli_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     clocks = ClockSampler(device_id_for_smi())
     if args.phase == "decode":

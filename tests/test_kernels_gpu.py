@@ -466,8 +466,10 @@ def sample_rows(logits, temps, ks, ps, seeds, draws):
     return out.tolist()
 
 
-@pytest.mark.parametrize("V", [517, 5000])
+@pytest.mark.parametrize("V", [517, 5000, 10000, 20001, 128256])
 def test_sampling_equals_the_plain_sampler(V):
+    """Vocabularies that one CTA holds and ones that a cluster of 2, 4 and 8 shares (20,001: rows that do not
+    start on a 16-byte boundary, and a last CTA with a shorter part)."""
     g = torch.Generator().manual_seed(V)
     logits = (torch.randn(24, V, generator=g) * 2.5).to(DEV)
     temps = [0.8, 1.0, 0.3, 2.0, 0.0, 1.3] * 4
@@ -501,6 +503,33 @@ def test_sampled_frequencies_follow_the_distribution():
     assert freq[2:].sum() == 0 and abs(freq[0] - 2 / 3) < 0.03
     toks = sample_rows(logits[:50].contiguous(), [1.0] * 50, [-1] * 50, [0.01] * 50, [9] * 50, list(range(50)))
     assert set(toks) == {0}
+    # ties at the k-th value are all kept: top_k = 2 of (0.4, 0.2, 0.2, 0.2) leaves the distribution as it is
+    probs = np.array([0.4, 0.2, 0.2, 0.2])
+    logits = torch.tensor(np.log(probs), dtype=torch.float32, device=DEV).repeat(4000, 1)
+    toks = sample_rows(logits, [1.0] * 4000, [2] * 4000, [1.0] * 4000, [5] * 4000, list(range(4000)))
+    assert np.abs(np.bincount(toks, minlength=4) / 4000 - probs).max() < 0.03
+
+
+def test_sampling_in_a_large_vocabulary_finds_far_tokens_and_cuts_at_the_right_one():
+    """128,256 logits shared by eight CTAs: the kept tokens lie in different CTAs' parts, so the cut, the totals and
+    the draw all cross the cluster.  Five tokens hold nearly all the mass (0.4, 0.3, 0.15, 0.1, 0.05 of it)."""
+    V, n = 128256, 3000
+    ids = [128255, 7, 64000, 16032, 99999]
+    probs = np.array([0.4, 0.3, 0.15, 0.1, 0.05])
+    row = torch.full((V,), -30.0)
+    row[ids] = torch.tensor(np.log(probs), dtype=torch.float32)
+    logits = row.to(DEV).repeat(n, 1)
+    def freq(k, p):
+        toks = sample_rows(logits, [1.0] * n, [k] * n, [p] * n, [3] * n, list(range(n)))
+        assert set(toks) <= set(ids)
+        return np.array([toks.count(i) for i in ids]) / n
+    assert np.abs(freq(-1, 1.0) - probs).max() < 0.035
+    f = freq(3, 1.0)  # the three best, renormalised
+    assert f[3:].sum() == 0 and np.abs(f[:3] - probs[:3] / probs[:3].sum()).max() < 0.035
+    f = freq(-1, 0.75)  # 0.4 + 0.3 < 0.75 <= 0.4 + 0.3 + 0.15: the third is the last one kept
+    assert f[3:].sum() == 0 and np.abs(f[:3] - probs[:3] / probs[:3].sum()).max() < 0.035
+    f = freq(4, 0.5)  # top-k keeps four, top-p of their mass (0.95): 0.4 < 0.475 <= 0.7: two
+    assert f[2:].sum() == 0 and np.abs(f[:2] - probs[:2] / probs[:2].sum()).max() < 0.035
 
 
 def test_sampling_by_state_slot_reads_the_table_and_advances_the_draws():
