@@ -75,6 +75,12 @@ def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_s
     if tma and splits > 8:  # a cluster merges its splits on the chip: 16 of them for one or two sequences' head groups, else 8
         pairs = num_seqs * ctas_per_seq
         splits = CLUSTER_SPLITS_MAX if splits >= CLUSTER_SPLITS_MAX and pairs <= CLUSTER_16_MAX_CTAS_PER_SPLIT else 8
+    elif tma:
+        # The splits of a sequence are a cluster, and clusters of 3 or 6 CTAs run slower than the power of two below
+        # them.  Measured in replayed graphs (us a launch, splits 2 / 3 / 4): 24 sequences at head size 64 and 2 K keys
+        # 21.8 / 31.4 / 28.7, at 16 K keys 139 / 161 / 136; 12 sequences at head size 128 and 2 K keys 21.9 / 34.5 /
+        # 29.5; 12 sequences at head size 64 with 4 / 6 splits 13.5 / 20.1.
+        splits = 1 << (splits.bit_length() - 1)
     return splits
 
 

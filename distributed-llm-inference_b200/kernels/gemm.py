@@ -10,6 +10,9 @@ from __future__ import annotations
 
 import torch
 
+from . import ops
+from .attention import sm_count
+
 torch.backends.cuda.matmul.allow_tf32 = False
 torch.backends.cudnn.allow_tf32 = False
 torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
@@ -26,8 +29,6 @@ SKINNY_MAX_TOKENS_HEAD = 64
 
 def decode_product(x: torch.Tensor, max_tokens: int = SKINNY_MAX_TOKENS) -> bool:
     """Whether a product with these activations goes to the engine's own decode kernel."""
-    from . import ops
-
     return x.dtype == torch.bfloat16 and x.shape[0] <= max_tokens and ops.skinny_gemm_supported(x.shape[0], x.shape[1])
 
 
@@ -59,16 +60,12 @@ def _dense_tiles(tokens: int, features: int) -> int:
 
 
 def _dense_candidate(x, features: int) -> bool:
-    from . import ops
-
     return x.dtype == torch.bfloat16 and x.shape[0] >= DENSE_MIN_TOKENS and ops.dense_gemm_supported(x.shape[1], features)
 
 
 def dense_product(x, features: int, epilogue: str) -> bool:
     """Whether the product of these activations with a [features, K] weight, followed by ``epilogue`` ("swiglu" or
     "rotary"), goes to the engine's product for many tokens."""
-    from .attention import sm_count
-
     if not _dense_candidate(x, features):
         return False
     tiles, pairs = _dense_tiles(x.shape[0], features), max(1, sm_count() // 2)
@@ -83,8 +80,6 @@ def project(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, max_t
     """y = x W^T for a step's tokens, in x's dtype or in ``out_dtype`` (float32 for logits).  x may be
     ops.ScaledRows (rows that still lack their norm's factor): those only exist for token counts that
     the decode kernel serves, which applies the factor."""
-    from . import ops
-
     if isinstance(x, ops.ScaledRows) or decode_product(x, max_tokens):
         return ops.skinny_gemm(x, weight, out_dtype or x.dtype)
     y = linear(x, weight)

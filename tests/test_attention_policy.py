@@ -25,3 +25,15 @@ def test_long_sequences_stay_with_a_cluster():
     assert splits(1, 49152) == CLUSTER_SPLITS_MAX and splits(1, 131072) == CLUSTER_SPLITS_MAX
     assert splits(2, 65536) == CLUSTER_SPLITS_MAX and splits(4, 131072) == 8
     assert splits(1, 65536, heads=24, d=128) == CLUSTER_SPLITS_MAX
+
+
+def test_a_cluster_of_splits_is_a_power_of_two():
+    """One wave of CTAs would allow 3 splits at 24 sequences and 6 at 12; clusters of those sizes are slower than
+    the power of two below."""
+    assert splits(24, 2048) == 2 and splits(20, 8192) == 2
+    assert splits(12, 2048) == 4 and splits(10, 8192) == 4
+    assert splits(12, 8192, heads=24, d=128) == 2
+    for seqs in range(1, 80):
+        for ctx in (256, 2048, 16384):
+            s = splits(seqs, ctx)
+            assert s & (s - 1) == 0
