@@ -370,6 +370,10 @@ def more_points(model_1b, steps, warmup, pk):
     # the headline step with every request sampling at temperature 0.8 among the 50 likeliest tokens and 0.9 of their mass
     out["decode_b8_sampled"] = decode_point(model_1b, 8, steps, warmup, pk["hbm_gbs"], blocks=1,
                                             sampling=SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=1))
+    # a short prompt in one step: launched kernel by kernel the host needs 2.3 ms for it; once the shape has come
+    # often enough the step is replayed from a graph (engine/graphs.py, MixedGraph)
+    short = prefill_timed(model_1b, LLAMA_3_2_1B, LLAMA_3_2_1B["num_hidden_layers"], pk["bf16_tflops"], reps=5, warmup=40, tokens=256)
+    out["prefill_256"] = {"tok_s": round(short["value"], 1), "ms": round(short["ms"], 4), "frac": round(short["frac"], 4)}
     for name, batch, ctx in (("decode_b8_ctx16k", 8, 16384), ("decode_b1_ctx32k", 1, 32768), ("decode_b8_ctx32k", 8, 32768)):
         out[name] = decode_point(model_1b, batch, steps, warmup, pk["hbm_gbs"], prompt_len=ctx, context=ctx + 512, blocks=1)
     cfg = LLAMA_3_2_3B

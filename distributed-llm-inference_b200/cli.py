@@ -105,7 +105,7 @@ def cmd_bench(args) -> int:
         "batch": args.batch, "input_len": args.input_len, "steps": args.steps, "step_ms": step_ms, "tokens_per_s": args.batch / step_ms * 1e3,
         "schedule_ms_mean": statistics.mean(s.schedule_s for s in st) * 1e3, "forward_ms_mean": statistics.mean(s.forward_s for s in st) * 1e3,
         "postprocess_ms_mean": statistics.mean(s.postprocess_s for s in st) * 1e3, "steps_launched_ahead": eng.steps_ahead,
-        "graph_steps": eng.runner.graph_steps, "weight_bytes": weights, "kv_bytes_read_per_step": kv,
+        "graph_steps": eng.runner.graph_steps, "mixed_graph_steps": eng.runner.mixed_graph_steps, "weight_bytes": weights, "kv_bytes_read_per_step": kv,
         "bandwidth_floor_ms": (weights + kv) / (args.bandwidth_gbs * 1e9) * 1e3, "bandwidth_gbs": args.bandwidth_gbs,
         "max_memory_allocated_mib": torch.cuda.max_memory_allocated() >> 20,
     }))
@@ -193,7 +193,9 @@ def cmd_workload(args) -> int:
         "first_token_s_median": percentile(ttft, 0.5), "first_token_s_p99": percentile(ttft, 0.99), "first_token_s_max": ttft[-1] if ttft else None,
         "per_output_token_s_median": percentile(tpot, 0.5), "per_output_token_s_p99": percentile(tpot, 0.99),
         "schedule_ms_mean": statistics.mean(s.schedule_s for s in st) * 1e3, "forward_ms_mean": statistics.mean(s.forward_s for s in st) * 1e3,
-        "steps_launched_ahead": eng.steps_ahead, "graph_steps": eng.runner.graph_steps,
+        "steps_launched_ahead": eng.steps_ahead, "graph_steps": eng.runner.graph_steps, "mixed_graph_steps": eng.runner.mixed_graph_steps,
+        "mixed_graph_captures": getattr(getattr(eng.runner, "graphs", None), "mixed_captures", 0),
+        "mixed_graph_capture_s": round(getattr(getattr(eng.runner, "graphs", None), "mixed_capture_seconds", 0.0), 3),
         "pages": eng.manager.groups[0].num_pages, "max_memory_allocated_mib": torch.cuda.max_memory_allocated() >> 20,
     }))
     _note_env(args)

@@ -230,14 +230,16 @@ def gather_single_tokens(entries: Sequence[StepEntry], manager, vocab_size: int)
                 slots=slots, tables=tables, S=S, width=width, token_src=src if (src >= 0).any() else None)
 
 
-def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int, uploader: Uploader | None = None) -> tuple[StepBatch, list[int]]:
+def build_batch(entries: Sequence[StepEntry], manager, device, vocab_size: int, uploader: Uploader | None = None,
+                gathered: dict | None = None) -> tuple[StepBatch, list[int]]:
     """Flatten ``entries`` against the cache manager's tables.
 
     Each request's tokens must already have slots (allocate / append_slots); its first token
     sits at the position the manager has computed up to.  Returns the batch and, for each
-    entry in the caller's order, its index in the batch's sequence order.
+    entry in the caller's order, its index in the batch's sequence order.  ``gathered``: what
+    gather_host made of these entries, if the caller has it already.
     """
-    h = gather_host(entries, manager, vocab_size)
+    h = gathered if gathered is not None else gather_host(entries, manager, vocab_size)
     n, S, width = h["n"], h["S"], h["width"]
     pieces = [h["token_ids"], h["positions"], h["seq_of_token"], h["q_start"], h["kv_len"], h["state_slot"], h["logit_rows"]]
     for g in range(len(manager.pools)):

@@ -1,4 +1,4 @@
-"""CUDA graphs of the pure-decode step.
+"""CUDA graphs of the pure-decode step, and of small steps that mix prompt portions with decoded tokens.
 
 A step in which every sequence brings one token has the same kernels whatever the tokens
 are, so its launches are captured once per shape and replayed: shapes are buckets of
@@ -7,9 +7,17 @@ device buffer before the replay; rows beyond the real sequences are padding that
 writes a scratch page no request owns.  (The reference replays its decode forward the same
 way, src/dli/engine/cuda_graph.py:83-237, to hide the launch cost of its eager kernels; here
 it removes the Python time between this engine's launches.)
+
+A step with prompt portions launches some 130 kernels, which the host issues in about 2.3 ms whatever their size;
+the GPU needs less than that for up to about a thousand tokens.  Such steps are captured too (``MixedGraph``),
+by (single-token sequences, longer portions, the portions' tokens together, width), each rounded up to a bucket: the
+attention kernels take each sequence's first row and length from device arrays and size their grids for the longest
+portion the bucket allows, so a shorter step runs in the same launches and the surplus CTAs return at once.
 """
 
 from __future__ import annotations
+
+import time
 
 import numpy as np
 import torch
@@ -19,6 +27,12 @@ from .batch import GroupView, StepBatch
 
 SEQ_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 WIDTH_STEP = 64  # block-table widths are rounded up to a multiple of this many pages
+# Buckets of a mixed step: a capture costs what some twenty steps launched one by one cost (47 ms at Llama-3.2-1B
+# sizes), so there are few shapes.  Padding is cheap: an empty portion's CTAs return at once, a padding single-token
+# row reads one key, and below a few hundred tokens a step's time is the weights'.
+PORTION_BUCKETS = (4,)  # sequences of a mixed step that bring more than one token
+TOKEN_BUCKETS = (32, 128, 256, 512, 1024)  # their tokens together
+MIXED_SINGLE_BUCKETS = (0, 8, 16, 32, 64, 128, 256)
 
 
 def bucket_seqs(n: int) -> int | None:
@@ -107,6 +121,128 @@ class DecodeGraph:
         return self.logits
 
 
+def _bucket(n: int, buckets) -> int | None:
+    return next((b for b in buckets if b >= n), None)
+
+
+class MixedGraph:
+    """One captured shape of a step with prompt portions: ``singles`` single-token sequences, then ``portions`` longer
+    ones with ``tokens`` tokens together, then one empty sequence in the scratch page, which the token rows that no
+    request fills name as theirs (a kernel that walks tokens, not sequences, finds one key for them).  Token rows:
+    the singles' first, then the portions' back to back, then padding."""
+
+    def __init__(self, model, caches, num_groups: int, scratch_pages: list[int], page_size: int, singles: int, portions: int,
+                 tokens: int, width: int, launch_keys: dict, pool=None) -> None:
+        self.set_layout(singles, portions, tokens, width, num_groups)
+        dev = model.device
+        self._pad = self.padding(scratch_pages, page_size)
+        self.ints = torch.zeros(self.size, dtype=torch.int32, device=dev)
+        self.ints.copy_(torch.from_numpy(self._pad))
+        n, S, o = self.n, self.S, self.offsets
+        views = []
+        for g in range(num_groups):
+            base = o["groups"] + g * self.per_group
+            views.append(GroupView(self.ints[base + n : base + self.per_group].view(S, width), self.ints[base : base + n]))
+        self.batch = StepBatch(
+            n=n, num_seqs=S, num_single=singles, token_ids=self.ints[0:n], positions=self.ints[o["positions"] : o["positions"] + n],
+            seq_of_token=self.ints[o["seq_of_token"] : o["seq_of_token"] + n], q_start=self.ints[o["q_start"] : o["q_start"] + S + 1],
+            kv_len=self.ints[o["kv_len"] : o["kv_len"] + S], state_slot=self.ints[o["state_slot"] : o["state_slot"] + S],
+            logit_rows=self.ints[o["logit_rows"] : o["logit_rows"] + S - 1], groups=views, q_lens=[1] * singles + [0] * (portions + 1),
+            starts=[0] * S, state_slots=[0] * S, max_q_len=tokens, max_kv_len=width * page_size, max_kv_len_single=width * page_size,
+            launch_keys=launch_keys, logits_all_rows=False,
+        )
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                model.forward(self.batch, caches)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        before = ops.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=pool):
+            self.logits = model.forward(self.batch, caches)
+        self.kernels = ops.launch_count - before
+
+    def set_layout(self, singles: int, portions: int, tokens: int, width: int, num_groups: int) -> None:
+        self.singles, self.portions, self.tokens, self.width, self.num_groups = singles, portions, tokens, width, num_groups
+        n, S = singles + tokens, singles + portions + 1
+        self.n, self.S = n, S
+        self.per_group = n + S * width
+        o, at = {}, 0
+        for name, count in (("token_ids", n), ("positions", n), ("seq_of_token", n), ("q_start", S + 1), ("kv_len", S), ("state_slot", S),
+                            ("logit_rows", S - 1), ("groups", num_groups * self.per_group), ("token_src", n)):
+            o[name] = at
+            at += count
+        self.offsets, self.size = o, at
+
+    def padding(self, scratch_pages: list[int], page_size: int) -> np.ndarray:
+        """Integers of a step whose every row is padding: the singles are one-token sequences in the scratch page, the
+        portions are empty, every token row beyond the singles names the empty last sequence."""
+        n, S, o, singles = self.n, self.S, self.offsets, self.singles
+        flat = np.zeros(self.size, dtype=np.int32)
+        flat[o["seq_of_token"] : o["seq_of_token"] + singles] = np.arange(singles)
+        flat[o["seq_of_token"] + singles : o["seq_of_token"] + n] = S - 1
+        flat[o["q_start"] : o["q_start"] + singles + 1] = np.arange(singles + 1)
+        flat[o["q_start"] + singles + 1 : o["q_start"] + S + 1] = singles
+        flat[o["kv_len"] : o["kv_len"] + S] = 1
+        for g, page in enumerate(scratch_pages):
+            base = o["groups"] + g * self.per_group
+            flat[base : base + n] = page * page_size
+            flat[base + n : base + self.per_group] = page
+        flat[o["token_src"] : o["token_src"] + n] = -1
+        return flat
+
+    def fill(self, h: dict) -> np.ndarray:
+        """The static buffer's contents for a gathered step (engine.batch.gather_host) that fits this shape: its S1
+        single-token sequences come first in ``h``, then its longer portions."""
+        n, S, o, singles, width = self.n, self.S, self.offsets, self.singles, self.width
+        q_lens = h["q_lens"]
+        S1 = int((q_lens == 1).sum())
+        S2, Q = h["S"] - S1, h["n"] - S1
+        flat = self._pad.copy()
+
+        def rows(name: str, values) -> None:  # per token: the singles' rows, then the portions' behind the padding singles
+            at = o[name]
+            flat[at : at + S1] = values[:S1]
+            flat[at + singles : at + singles + Q] = values[S1:]
+
+        rows("token_ids", h["token_ids"])
+        rows("positions", h["positions"])
+        flat[o["seq_of_token"] + singles : o["seq_of_token"] + singles + Q] = h["seq_of_token"][S1:] - S1 + singles
+        ends = singles + np.cumsum(q_lens[S1:])
+        flat[o["q_start"] + singles + 1 : o["q_start"] + singles + 1 + S2] = ends
+        flat[o["q_start"] + singles + 1 + S2 : o["q_start"] + S + 1] = singles + Q
+        for name in ("kv_len", "state_slot"):
+            at = o[name]
+            flat[at : at + S1] = h[name][:S1]
+            flat[at + singles : at + singles + S2] = h[name][S1:]
+        wanted = h["logit_rows"]  # token rows in the gathered step's numbering, caller's order: logits[:len(wanted)] answers the step
+        flat[o["logit_rows"] : o["logit_rows"] + wanted.size] = np.where(wanted < S1, wanted, wanted - S1 + singles)
+        for g in range(self.num_groups):
+            base = o["groups"] + g * self.per_group
+            flat[base : base + S1] = h["slots"][g][:S1]
+            flat[base + singles : base + singles + Q] = h["slots"][g][S1:]
+            tables = flat[base + n : base + self.per_group].reshape(S, width)
+            tables[:S1, : h["width"]] = h["tables"][g][:S1]
+            tables[singles : singles + S2, : h["width"]] = h["tables"][g][S1:]
+        if h.get("token_src") is not None:
+            rows("token_src", h["token_src"])
+        return flat
+
+    @property
+    def max_logit_rows(self) -> int:
+        return self.S - 1
+
+    def replay(self, token_source: torch.Tensor | None = None) -> torch.Tensor:
+        if token_source is not None:
+            o = self.offsets
+            ops.patch_tokens(self.ints[0 : self.n], token_source, self.ints[o["token_src"] : o["token_src"] + self.n])
+        self.graph.replay()
+        ops.launch_count += self.kernels
+        return self.logits
+
+
 class DecodeGraphs:
     """Graphs by shape, captured at first use."""
 
@@ -116,6 +252,17 @@ class DecodeGraphs:
         self.max_graphs = 32  # at the cap the graph that was used least recently makes room
         self.failure: str | None = None
         self._asked: dict[tuple[int, int], dict] = {}  # (sequences, width) -> the parts' answers (they depend on nothing else)
+        self.mixed: dict[tuple, MixedGraph] = {}  # (singles, portions, tokens, width, launch keys) -> graph, oldest use first
+        self.max_mixed = 32
+        # a capture pays for itself after some fifty replays (and the first one of a process, which also loads the
+        # library's kernels for the new row count, takes up to half a second), so a shape is captured only when it
+        # keeps coming
+        self.mixed_after = 32
+        self.mixed_failure: str | None = None
+        self._sightings: dict[tuple, int] = {}
+        self._needed: dict[tuple, int] = {}  # sightings a shape needs: doubled each time its graph had to make room
+        self._pool = None  # the mixed graphs share one memory pool: they never run at the same time
+        self.mixed_captures, self.mixed_capture_seconds = 0, 0.0
 
     def launch_keys(self, seqs: int, max_kv_len: int) -> dict:
         """id(part) -> the part's answer, for every part of the model that has one (``Part.decode_launch_key``)."""
@@ -152,4 +299,48 @@ class DecodeGraphs:
                 self.failure = str(exc)
                 torch.cuda.synchronize(self.model.device)
                 return None
+        return graph
+
+    def lookup_mixed(self, singles: int, portions: int, tokens: int, width: int, logit_rows: int) -> MixedGraph | None:
+        """The graph for a step of ``singles`` single-token sequences and ``portions`` longer ones of ``tokens`` tokens
+        together; None if the shape is outside the buckets, wants more logits than a graph returns, or has not
+        come often enough to be captured."""
+        sb, pb, tb = _bucket(singles, MIXED_SINGLE_BUCKETS), _bucket(portions, PORTION_BUCKETS), _bucket(tokens, TOKEN_BUCKETS)
+        if sb is None or pb is None or tb is None or logit_rows > sb + pb or self.max_graphs == 0 or self.max_mixed == 0:
+            return None
+        wb = WIDTH_STEP
+        while wb < width:  # widths double: few shapes
+            wb *= 2
+        launch = {}
+        if sb:
+            launch = self._asked.get((sb, wb))
+            if launch is None:
+                launch = self._asked[(sb, wb)] = self.launch_keys(sb, wb * self.page_size)
+        key = (sb, pb, tb, wb, tuple(launch.values()))
+        graph = self.mixed.pop(key, None)
+        if graph is not None:
+            self.mixed[key] = graph
+            return graph
+        seen = self._sightings[key] = self._sightings.get(key, 0) + 1
+        if seen < self._needed.get(key, self.mixed_after):
+            return None
+        while len(self.mixed) >= self.max_mixed:
+            stale = next(iter(self.mixed))
+            del self.mixed[stale]
+            # a shape that keeps coming back after it made room has to come twice as often before it is captured again
+            self._needed[stale], self._sightings[stale] = 2 * self._needed.get(stale, self.mixed_after), 0
+        if self._pool is None:
+            self._pool = torch.cuda.graph_pool_handle()
+        began = time.perf_counter()
+        try:
+            graph = self.mixed[key] = MixedGraph(self.model, self.pools.layer_caches, len(self.pools.group_needs), self.pools.scratch_pages,
+                                                 self.page_size, sb, pb, tb, wb, launch, self._pool)
+            self.mixed_captures += 1
+            self.mixed_capture_seconds += time.perf_counter() - began
+        except RuntimeError as exc:  # no memory for it, or a part that cannot be captured with longer portions: these steps stay uncaptured
+            self.max_mixed = 0
+            self.mixed_failure = str(exc)
+            self.mixed.clear()
+            torch.cuda.synchronize(self.model.device)
+            return None
         return graph

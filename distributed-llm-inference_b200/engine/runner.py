@@ -20,8 +20,8 @@ from ..config.registry import load_config, resolve_architecture
 from ..kernels import ops
 from ..parts import DecoderModel
 from ..weights import load_tensors, random_tensors
-from .batch import StepEntry, Uploader, build_batch, gather_single_tokens
-from .graphs import DecodeGraphs
+from .batch import StepEntry, Uploader, build_batch, gather_host, gather_single_tokens
+from .graphs import PORTION_BUCKETS, SEQ_BUCKETS, TOKEN_BUCKETS, DecodeGraphs
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -91,7 +91,8 @@ class ModelRunner:
         # graphs replay padding rows through every mixer: not with per-request state, which they would touch
         capturable = all(getattr(part, "graph_capturable", False) for part in model.parts())
         self.graphs = DecodeGraphs(model, self.pools, page_size) if cuda_graphs and capturable and not self.pools.has_state else None
-        self.graph_steps = 0
+        self.graph_steps = 0  # pure-decode steps replayed from a graph
+        self.mixed_graph_steps = 0  # small steps with prompt portions replayed from a graph
 
     @staticmethod
     def pages_for_budget(model: DecoderModel, budget_bytes: float, page_size: int) -> int:
@@ -126,8 +127,14 @@ class ModelRunner:
             logits = self._replay_decode(entries, token_source)
             if logits is not None and not borrow:
                 logits = logits.clone()
+        gathered = None
+        if logits is None and self.graphs is not None and self._small_mixed_step(entries):
+            gathered = gather_host(entries, self.manager, self.model.spec.vocab_size)
+            logits = self._replay_mixed(gathered, token_source)
+            if logits is not None and not borrow:
+                logits = logits.clone()
         if logits is None:
-            batch, _ = build_batch(entries, self.manager, self.model.device, self.model.spec.vocab_size, self.uploader)
+            batch, _ = build_batch(entries, self.manager, self.model.device, self.model.spec.vocab_size, self.uploader, gathered)
             if batch.token_src is not None:
                 ops.patch_tokens(batch.token_ids, token_source, batch.token_src)
             logits = self.model.forward(batch, self.pools.layer_caches)
@@ -149,6 +156,28 @@ class ModelRunner:
         if rows.size == h["S"] and (rows == np.arange(h["S"])).all():
             return logits[: h["S"]]
         return logits[torch.from_numpy(rows).to(logits.device)]
+
+    @staticmethod
+    def _small_mixed_step(entries: Sequence[StepEntry]) -> bool:
+        """Whether a step with longer portions is small enough that launching it kernel by kernel would take the host
+        longer than the GPU needs for it (the buckets of engine.graphs end there)."""
+        portions = tokens = 0
+        for e in entries:
+            if len(e.token_ids) > 1:
+                portions += 1
+                tokens += len(e.token_ids)
+        return 0 < portions <= PORTION_BUCKETS[-1] and tokens <= TOKEN_BUCKETS[-1] and len(entries) - portions <= SEQ_BUCKETS[-1]
+
+    def _replay_mixed(self, h: dict, token_source: torch.Tensor | None = None) -> torch.Tensor | None:
+        """A small step with prompt portions through a captured graph; None if no graph takes its shape (yet)."""
+        singles = int((h["q_lens"] == 1).sum())
+        graph = self.graphs.lookup_mixed(singles, h["S"] - singles, h["n"] - singles, h["width"], h["logit_rows"].size)
+        if graph is None:
+            return None
+        self.uploader.upload(graph.fill(h), out=graph.ints)
+        logits = graph.replay(token_source if h["token_src"] is not None else None)
+        self.mixed_graph_steps += 1
+        return logits[: h["logit_rows"].size]
 
     def check_device_errors(self) -> None:
         """Raise if a bounded wait inside one of the kernels gave up since this was last asked: what

@@ -281,9 +281,9 @@ def patched():
     with the decode products' fused epilogues)."""
     saved = {name: getattr(ops, name) for name in OPS}
     saved_linear, saved_model_linear, saved_require = gemm.linear, model_mod.linear, runner_mod._require_cuda
-    saved_lookup = graphs_mod.DecodeGraphs.lookup
+    saved_lookup, saved_mixed = graphs_mod.DecodeGraphs.lookup, graphs_mod.DecodeGraphs.lookup_mixed
     try:
-        graphs_mod.DecodeGraphs.lookup = lambda self, *a, **k: None  # no captured steps without a device
+        graphs_mod.DecodeGraphs.lookup = graphs_mod.DecodeGraphs.lookup_mixed = lambda self, *a, **k: None  # no captured steps without a device
         calls.clear()
         for name, fn in OPS.items():
             setattr(ops, name, _counted(name, fn))
@@ -294,5 +294,5 @@ def patched():
         for name, fn in saved.items():
             setattr(ops, name, fn)
         gemm.linear, model_mod.linear, runner_mod._require_cuda = saved_linear, saved_model_linear, saved_require
-        graphs_mod.DecodeGraphs.lookup = saved_lookup
+        graphs_mod.DecodeGraphs.lookup, graphs_mod.DecodeGraphs.lookup_mixed = saved_lookup, saved_mixed
 

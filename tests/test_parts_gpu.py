@@ -55,6 +55,7 @@ def build(spec, dtype, seed, sharpen=6.0):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_norm_part(dtype):
+    torch.manual_seed(11)  # the inputs below come from the global generator: the same ones in every order of tests
     part = build_part("norm", PartSpec("rmsnorm", {"size": 72, "eps": 2e-5}, "n."), env(dtype))
     assert part.declare() == {"n.weight": TensorDecl((72,), "vector32")}
     w = torch.rand(72, device=DEV) + 0.5
@@ -76,6 +77,7 @@ def test_rotary_part_frequencies(cfg):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_feed_forward_part(dtype):
+    torch.manual_seed(12)
     part = build_part("feed_forward", PartSpec("swiglu", {"hidden_size": 40, "intermediate_size": 72}, "m."), env(dtype))
     t = random_tensors(part.declare(), 3, dtype=dtype, device=DEV)
     t = {k: (v.float() * 10).to(dtype) for k, v in t.items()}
@@ -88,6 +90,7 @@ def test_feed_forward_part(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tied", [True, False])
 def test_embedding_and_head_parts(dtype, tied):
+    torch.manual_seed(13)
     e = build_part("embedding", PartSpec("token_embedding", {"vocab_size": 130, "hidden_size": 24}, "emb."), env(dtype))
     hd = build_part("head", PartSpec("lm_head", {"vocab_size": 130, "hidden_size": 24, "tied_to": "emb.weight" if tied else None}, "head."), env(dtype))
     decl = {**e.declare(), **hd.declare()}

@@ -63,7 +63,7 @@ def test_workload_command_with_a_fake_engine(monkeypatch, capsys, tmp_path):
 
     def for_model(model, *, num_blocks, block_size, config, **kw):
         eng, runner = fake_engine(num_pages=num_blocks, page_size=block_size, max_num_seqs=config.max_num_seqs, budget=config.max_num_batched_tokens)
-        runner.graph_steps = 0
+        runner.graph_steps = runner.mixed_graph_steps = 0
         made["engine"], made["blocks"] = eng, num_blocks
         return eng
 
@@ -87,7 +87,7 @@ def _fake_factory(made):
     def make(*args, num_blocks=None, block_size=16, config=None, **kw):
         eng, runner = fake_engine(num_pages=num_blocks or 64, page_size=block_size, max_num_seqs=config.max_num_seqs,
                                   budget=config.max_num_batched_tokens, watermark=kw.get("watermark", 0.01))
-        runner.graph_steps = 0
+        runner.graph_steps = runner.mixed_graph_steps = 0
         runner.pools = types.SimpleNamespace(bytes_per_page=lambda *a: [64])
         made["engine"] = eng
         return eng
