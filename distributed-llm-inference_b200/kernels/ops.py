@@ -401,6 +401,10 @@ def device_wait_errors(clear: bool = True) -> dict[str, int]:
 # ------------------------------------------------------------------ sampling
 
 
+# A stochastic row's logits are kept in the shared memory of a cluster of 8 CTAs, 47 K floats each
+SAMPLE_MAX_VOCAB_STOCHASTIC = 8 * 47 * 1024
+
+
 def sample(
     out: torch.Tensor,
     logits: torch.Tensor,
@@ -422,6 +426,9 @@ def sample(
     if temperature is not None:
         if top_k is None or top_p is None or seed is None or draw is None:
             raise KernelError("sample: stochastic rows need top_k, top_p, seed and draw")
+        if V > SAMPLE_MAX_VOCAB_STOCHASTIC:
+            raise KernelError(f"sample: temperature sampling takes vocabularies of up to {SAMPLE_MAX_VOCAB_STOCHASTIC} tokens, not {V} "
+                              "(greedy rows alone, passed without parameters, take any)")
         _need(temperature, "temperature", torch.float32), _need(top_k, "top_k", torch.int32), _need(top_p, "top_p", torch.float32)
         _need(seed, "seed", torch.int64), _need(draw, "draw", torch.int64)
         entries = rows if slots is None else temperature.numel()

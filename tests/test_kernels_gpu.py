@@ -510,6 +510,20 @@ def test_sampled_frequencies_follow_the_distribution():
     assert np.abs(np.bincount(toks, minlength=4) / 4000 - probs).max() < 0.03
 
 
+def test_a_vocabulary_too_large_for_temperature_sampling_is_refused_and_greedy_still_works():
+    V = ops.SAMPLE_MAX_VOCAB_STOCHASTIC + 1
+    logits = torch.zeros(2, V, device=DEV)
+    logits[0, V - 1] = logits[1, 12345] = 3.0
+    out = torch.empty(2, dtype=torch.int32, device=DEV)
+    ops.sample(out, logits)
+    assert out.tolist() == [V - 1, 12345]
+    with pytest.raises(ops.KernelError, match="temperature sampling takes vocabularies of up to"):
+        sample_rows(logits, [1.0, 1.0], [-1, -1], [1.0, 1.0], [1, 2], [0, 0])
+    edge = logits[:, : ops.SAMPLE_MAX_VOCAB_STOCHASTIC].contiguous()  # the largest one that is taken: 47 K floats a CTA
+    edge[0, 77] = 40.0
+    assert sample_rows(edge, [1.0, 0.0], [-1, -1], [1.0, 1.0], [1, 2], [0, 0]) == [77, 12345]
+
+
 def test_sampling_in_a_large_vocabulary_finds_far_tokens_and_cuts_at_the_right_one():
     """128,256 logits shared by eight CTAs: the kept tokens lie in different CTAs' parts, so the cut, the totals and
     the draw all cross the cluster.  Five tokens hold nearly all the mass (0.4, 0.3, 0.15, 0.1, 0.05 of it)."""
