@@ -957,11 +957,27 @@ struct DecodeParams {
 
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-// store into the same shared-memory offset of another CTA of the cluster
-__device__ __forceinline__ void st_peer_shared(uint32_t local_addr, uint32_t cta_rank, float v) {
-  uint32_t remote;
+// as wait_or_fail, for a barrier whose bytes other CTAs of the cluster send (st.async)
+__device__ __forceinline__ bool wait_cluster_or_fail(uint32_t bar, uint32_t parity, volatile int* failed, int code, int* error_flag) {
+  for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  *failed = code;
+  atomicExch(error_flag, code);
+  return false;
+}
+// store into the same shared-memory offset of another CTA of the cluster; the four bytes are counted on that CTA's
+// mbarrier at `local_bar` when they have landed
+__device__ __forceinline__ void st_async_peer(uint32_t local_addr, uint32_t local_bar, uint32_t cta_rank, float v) {
+  uint32_t remote, remote_bar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(local_bar), "r"(cta_rank));
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(remote), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
 }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -1017,7 +1033,14 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
   const int t_begin = first_tile + split * tiles_per_split;
   const int t_end = min(first_tile + tiles_total, t_begin + tiles_per_split);
 
-  if (tid == 0) *failed = 0;
+  // rows r = split, split + splits, .. of the head group are merged by this CTA
+  const int mine = split < nheads ? (nheads - split + p.splits - 1) / p.splits : 0;
+  const uint32_t merged = smem_u32(bars + DWARPS * DSTAGES + 1);  // completes when every split's partial results of those rows have landed
+  if (tid == 0) {
+    *failed = 0;
+    mbar_init(merged, 1);
+    if (p.cluster_merge && mine > 0) mbar_expect_tx(merged, (uint32_t)(p.splits * mine * RECV_ROW * 4));
+  }
   if (lane == 0) {
     for (int st = 0; st < DSTAGES; ++st) mbar_init(smem_u32(bars + warp * DSTAGES + st), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1223,10 +1246,10 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
     } else if (p.cluster_merge) {
       const uint32_t dst = smem_u32(recv + (split * owned_max + r / p.splits) * RECV_ROW);
       const int owner = r % p.splits;
-      st_peer_shared(dst + dcol * 4, owner, acc);
+      st_async_peer(dst + dcol * 4, merged, owner, acc);
       if (dcol == 0) {
-        st_peer_shared(dst + D * 4, owner, mx);
-        st_peer_shared(dst + (D + 1) * 4, owner, L);
+        st_async_peer(dst + D * 4, merged, owner, mx);
+        st_async_peer(dst + (D + 1) * 4, merged, owner, L);
       }
     } else {
       p.part_acc[(row * p.splits + split) * D + dcol] = acc;
@@ -1236,12 +1259,11 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
       }
     }
   }
-  if (!p.cluster_merge) return;
-  __syncwarp();
-  cluster_arrive();
-  cluster_wait();  // every split's partial result of my rows has arrived; nobody touches a peer's memory from here on
-  if (bad) return;
-  const int mine = split < nheads ? (nheads - split + p.splits - 1) / p.splits : 0;
+  if (!p.cluster_merge || mine == 0) return;
+  // every split's partial result of my rows has arrived (each store counted its bytes on this CTA's barrier: no
+  // cluster barrier, which would also hold the CTAs that merge nothing); nobody reads a peer's memory, and a CTA
+  // leaves only after what was sent to it has landed
+  if (!wait_cluster_or_fail(merged, 0, failed, 22, p.error_flag) || bad) return;
   for (int idx = tid; idx < mine * D; idx += DWARPS * 32) {
     const int ri = idx / D, dcol = idx - ri * D;
     const int r = split + ri * p.splits;

@@ -20,12 +20,14 @@
 // feature tiles.  The CTAs of one tile's slices form a thread-block cluster (up to 16, the largest this
 // GPU takes; more than 8 is the kernel's opt-in): each
 // pushes its partial sums of a token into the shared memory of the CTA that owns the token
-// (distributed shared memory), and after one cluster barrier the owner adds them, slice 0
-// first, so the order is fixed, and writes the output.  No partial sum ever leaves the chip,
+// (distributed shared memory; st.async, which counts the bytes on the owner's mbarrier), and when
+// its bytes are complete the owner adds them, slice 0 first, so the order is fixed, and writes the
+// output.  No partial sum ever leaves the chip,
 // and no scratch memory is needed.
 //
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel records an error
-// code in *error_flag, stops issuing work, frees its tensor memory and returns.
+// code in *error_flag (1 copies, 2 products, 3 accumulator, 5 the slices' partial sums), stops
+// issuing work, frees its tensor memory and returns.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -188,16 +190,31 @@ __device__ __forceinline__ void fused_epilogue(const Epilogue& ep, void* out, co
   else ep.v_pool[(((size_t)page * ep.nkv + (kvh - ep.nkv)) * ep.page_size + off) * ep.d + i] = b;
 }
 
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+// (relaxed: the barrier only tells that every CTA of the cluster runs and has set up its mbarriers, which
+// fence.mbarrier_init.release.cluster has made visible; no data is handed over through it)
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// store into the same shared-memory offset of another CTA of the cluster
-__device__ __forceinline__ void st_peer_shared(uint32_t local_addr, uint32_t cta_rank, float v) {
-  uint32_t remote;
+// Store into the same shared-memory offset of another CTA of the cluster, and count the four bytes on that CTA's
+// mbarrier at `local_bar` when they have landed: the receiver waits for its bytes and nobody for a cluster barrier.
+__device__ __forceinline__ void st_async_peer(uint32_t local_addr, uint32_t local_bar, uint32_t cta_rank, float v) {
+  uint32_t remote, remote_bar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(local_bar), "r"(cta_rank));
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(remote), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
+}
+// as mbar_wait, for a barrier that other CTAs of the cluster complete
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, unsigned limit) {
+  for (unsigned i = 0; i < limit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
 }
 
 __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -210,14 +227,17 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int b_bytes = npad * BK * 2;
   const int stage_bytes = A_BYTES + b_bytes;
-  uint64_t* bars = (uint64_t*)(smem + (size_t)stages * stage_bytes);  // full[stages], empty[stages], accum
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * stages + 1);
+  uint64_t* bars = (uint64_t*)(smem + (size_t)stages * stage_bytes);  // full[stages], empty[stages], accum, reduced
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * stages + 2);
   volatile int* failed = (volatile int*)(tmem_slot + 1);
   float* wsum = (float*)((unsigned char*)bars + WSUM_OFFSET);
   float* rstd = (float*)((unsigned char*)bars + RSTD_OFFSET);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + stages), accum = smem_u32(bars + 2 * stages);
+  const uint32_t reduced = accum + 8;  // completes when every slice's partial sums of this CTA's tokens have landed
+  // tokens t = rank, rank + slices, .. of the cluster belong to this CTA
+  const int owned = (int)blockIdx.y < tokens ? (tokens - (int)blockIdx.y + (int)gridDim.y - 1) / (int)gridDim.y : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -225,6 +245,8 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
       mbar_init(empty0 + 8 * s, 1);
     }
     mbar_init(accum, 1);
+    mbar_init(reduced, 1);
+    if (gridDim.y > 1 && owned > 0) mbar_expect_tx(reduced, (uint32_t)(gridDim.y * owned * BM * 4));
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -333,9 +355,11 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   const float h_pre = have_h ? ep.h[(size_t)slice * features + f] : 0.f;
   const bool fused = ep.mode != EP_STORE;
   // With several slices, token t belongs to CTA (t mod slices) of the cluster.  Every CTA pushes its
-  // partial sums of a token straight into the owner's shared memory (remote stores need no answer),
-  // one cluster barrier makes them visible, and the owner adds them from its own memory, slice 0
-  // first.  Nobody reads a peer's memory after the barrier, so CTAs may leave as they finish.
+  // partial sums of a token straight into the owner's shared memory (remote stores need no answer); each
+  // store counts its bytes on the owner's mbarrier, the owner waits until all of them have landed (0.3 us
+  // less than a cluster barrier, which also holds back the CTAs that own nothing) and adds them from its
+  // own memory, slice 0 first.  Nobody reads a peer's memory, and a CTA leaves only after what was sent
+  // to it has arrived, so CTAs may leave as they finish.
   //   recv[slice][owned token][feature of the tile], a region of its own behind the barriers: a peer
   // may push while this CTA's pipeline stages are still in use
   float* recv = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes + BARRIER_BYTES);
@@ -361,7 +385,7 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
       if (t >= tokens) continue;
       if (slices > 1) {
         const int owner = t % slices, ti = t / slices;
-        st_peer_shared(recv_addr + (uint32_t)(((slice * owned_max + ti) * BM + fl) * 4), owner, __uint_as_float(r[j]));
+        st_async_peer(recv_addr + (uint32_t)(((slice * owned_max + ti) * BM + fl) * 4), reduced, owner, __uint_as_float(r[j]));
       } else if (fused) {
         recv[t * BM + fl] = __uint_as_float(r[j]) * (scaled ? rstd[t] : 1.f);
       } else if (f < features) {
@@ -372,8 +396,11 @@ __global__ void __launch_bounds__(128) skinny_gemm_kernel(const __grid_constant_
   // finished sums of the owned tokens for the fused epilogues (they combine features of a tile)
   float* fin = slices > 1 ? recv + slices * owned_max * BM : recv;
   if (slices > 1) {
-    cluster_sync();  // every slice's partial sums of my tokens have arrived
-    for (int t = slice, ti = 0; t < tokens; t += slices, ++ti) {
+    if (owned > 0 && !mbar_wait_cluster(reduced, 0, wait_limit)) {  // every slice's partial sums of my tokens have arrived
+      atomicExch(error_flag, 5);
+      ok = false;
+    }
+    for (int t = slice, ti = 0; t < tokens && ok; t += slices, ++ti) {
       float acc = 0.f;
 #pragma unroll 8
       for (int s2 = 0; s2 < slices; ++s2) acc += recv[(s2 * owned_max + ti) * BM + fl];  // slice 0 first
