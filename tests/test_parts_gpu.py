@@ -120,7 +120,11 @@ def one_layer_model(cfg_json, dtype, seed=5, **mixer_overrides):
 
 
 def run_whole_and_cut(model, tokens, page, cuts):
-    """Logits of one request run whole, and run in the given portions; [n, vocab] each."""
+    """Logits of one request run whole, and run in the given portions; [n, vocab] each.  Both want every
+    position, so their steps are launched kernel by kernel.  Where the model's parts can be recorded, the
+    portions run a third time wanting only each portion's last position: those steps replay graphs captured at
+    their first coming (engine.graphs.MixedGraph: padded shapes, an empty sequence for the rows nobody fills),
+    and their logits must be the whole run's at those positions."""
     out = []
     for portions in ([len(tokens)], cuts):
         r = ModelRunner(model, num_pages=64, page_size=page, max_requests=4, enable_prefix_caching=False, watermark=0.0)
@@ -132,6 +136,18 @@ def run_whole_and_cut(model, tokens, page, cuts):
             pos += n
         assert pos == len(tokens)
         out.append(np32(torch.cat(parts)))
+        r.manager.free("x")
+        r.manager.check_invariants()
+    r = ModelRunner(model, num_pages=64, page_size=page, max_requests=4, enable_prefix_caching=False, watermark=0.0)
+    if r.graphs is not None and DEV.type == "cuda":
+        r.graphs.mixed_after = 1
+        r.manager.allocate("x", tokens)
+        pos = 0
+        for n in cuts:
+            got = np32(r.step([StepEntry("x", tokens[pos : pos + n], [n - 1])]))[0]
+            pos += n
+            np.testing.assert_allclose(got, out[0][pos - 1], atol=TOL[model.dtype], err_msg=f"from a graph: position {pos - 1}")
+        assert r.mixed_graph_steps == sum(n > 1 for n in cuts), r.graphs.mixed_failure
         r.manager.free("x")
         r.manager.check_invariants()
     return out
