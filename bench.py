@@ -273,12 +273,13 @@ def decode_end_to_end(model, batch, steps, warmup):
     return {"value": batch * steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt / steps * 1e3}
 
 
-def prefill_timed(model, cfg, layers, peak_tflops, reps=5, warmup=3, tokens=PROMPT_LEN):
+def prefill_timed(model, cfg, layers, peak_tflops, reps=5, warmup=3, tokens=PROMPT_LEN, graphs=True):
     import torch
 
     from dli_b200.engine import ModelRunner, StepEntry
 
-    runner = ModelRunner(model, num_pages=tokens // PAGE + 8, page_size=PAGE, max_requests=2, enable_prefix_caching=False, watermark=0.0)
+    runner = ModelRunner(model, num_pages=tokens // PAGE + 8, page_size=PAGE, max_requests=2, enable_prefix_caching=False, watermark=0.0,
+                         cuda_graphs=graphs)
     g = torch.Generator().manual_seed(3)
     times = []
     for i in range(warmup + reps):
@@ -586,8 +587,9 @@ def main() -> int:
     ap.add_argument("--skip-more", action="store_true", help="leave out the other shapes and contexts (the \"more\" key)")
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "sample"],
                     help="profiling runs: only the device-timed decode steps, only the prefill step, or only the sampling kernel (prints a short line)")
-    ap.add_argument("--no-graphs", action="store_true", help="profiling runs: launch the decode step's kernels one by one")
-    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="profiling runs of --phase decode: the context at which decoding starts")
+    ap.add_argument("--no-graphs", action="store_true", help="profiling runs: launch the step's kernels one by one")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
+                    help="profiling runs: the context at which decoding starts (--phase decode), the prompt's length (--phase prefill)")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -615,7 +617,9 @@ def main() -> int:
         print(json.dumps({"phase": "decode", "batch": args.batch, "layers": args.layers, "prompt_len": args.prompt_len, **run}))
         return 0
     if args.phase == "prefill":
-        print(json.dumps({"phase": "prefill", "layers": args.layers, **prefill_timed(model, cfg, args.layers, pk["bf16_tflops"], reps=args.steps)}))
+        print(json.dumps({"phase": "prefill", "layers": args.layers, "graphs": not args.no_graphs,
+                          **prefill_timed(model, cfg, args.layers, pk["bf16_tflops"], reps=args.steps, warmup=args.warmup, tokens=args.prompt_len,
+                                          graphs=not args.no_graphs)}))
         return 0
     main_run = decode_device_timed(model, args.batch, args.steps, args.warmup, clocks)
     clocks.start()  # the end-to-end steps are timed too: keep sampling
