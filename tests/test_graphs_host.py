@@ -190,3 +190,16 @@ def test_mixed_shapes_are_captured_when_they_keep_coming_and_thrashing_shapes_wa
     first = (8, 4, 128, 64, ())
     assert graphs._needed[first] == 4  # the shape that made room must now come four times
     assert [graphs.lookup_mixed(4, 1, 128, 60, 5) for _ in range(3)] == [None] * 3 and graphs.lookup_mixed(4, 1, 128, 60, 5) is not None
+
+
+def test_which_steps_are_small_enough_to_be_replayed():
+    from dli_b200.engine.runner import ModelRunner
+
+    small = ModelRunner._small_mixed_step
+    one = lambda i: StepEntry(i, [5], [0])
+    portion = lambda i, n: StepEntry(i, list(range(n)), [n - 1])
+    assert not small([one(0), one(1)])  # single tokens only: the decode graphs' business
+    assert small([portion(0, 2)]) and small([one(0), portion(1, 1024)]) and small([portion(i, 256) for i in range(4)])
+    assert not small([portion(0, 1025)]) and not small([portion(i, 300) for i in range(4)])  # more tokens than the largest bucket
+    assert not small([portion(i, 3) for i in range(5)])  # more portions than a graph has places for
+    assert small([one(i) for i in range(256)] + [portion(300, 16)]) and not small([one(i) for i in range(257)] + [portion(300, 16)])
